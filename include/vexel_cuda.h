@@ -1,0 +1,220 @@
+/*
+ * vexel_cuda.h -- C ABI of the B200 (sm_100a) CUDA backend for the Vexel inference engine.
+ *
+ * This is the boundary a cgo wrapper binds.  Every entry point is extern "C", takes plain
+ * pointers / integers / floats, and returns an int status (VX_OK == 0).  Device buffers are
+ * raw device addresses carried as uint64_t: the Go side passes DevicePtr.addr + DevicePtr.offset
+ * (the reference keeps GPU offsets separate from the base, inference/tensor/device.go:36-80).
+ *
+ * Two layers:
+ *   1. Interface-level kernels, 1:1 with the reference's backend interfaces
+ *      (inference/backend/backend.go).  Each declaration cites the method it implements.
+ *   2. The batched decode fast path: model + device block pool + one call per scheduler step,
+ *      replacing the per-sequence loop of inference/runtime/decode.go:612-654.
+ *
+ * Threading: a vx_ctx serialises its entry points with a mutex and makes its device current on
+ * every call (goroutines migrate between OS threads).  All work runs on one stream per context.
+ * There is no CPU fallback: without a CUDA device vx_init fails with VX_E_CUDA.
+ */
+#ifndef VEXEL_CUDA_H
+#define VEXEL_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct vx_ctx vx_ctx;
+typedef struct vx_model vx_model;
+typedef uint64_t vx_dptr; /* device address (base + offset already applied) */
+
+enum {
+    VX_OK = 0,
+    VX_E_BAD_ARG = 1,     /* programmer error: the Go wrapper panics (void interface methods) */
+    VX_E_CUDA = 2,        /* CUDA runtime error, text in vx_last_error */
+    VX_E_OOM = 3,         /* device allocation failed: Alloc returns a nil DevicePtr (backend.go:315-317) */
+    VX_E_OOM_BLOCKS = 4,  /* block pool exhausted (runtime/gpu_block_pool.go:200-204) */
+    VX_E_NO_SEQ = 5,      /* unknown sequence id (runtime/gpu_block_pool.go:229-232) */
+    VX_E_TIMEOUT = 6,     /* a bounded device-side wait gave up */
+    VX_E_UNSUPPORTED = 7
+};
+
+/* GGUF tensor type ids (inference/pkg/gguf/gguf.go:40-75) accepted for weights. */
+enum { VX_T_F32 = 0, VX_T_F16 = 1, VX_T_Q4_0 = 2, VX_T_Q4_K = 12, VX_T_Q6_K = 14 };
+
+/* ------------------------------------------------------------------ lifecycle
+ * replaces inference/backend/cuda/backend.go:15-37 (NewBackend stub). */
+int vx_init(int device, vx_ctx **out);
+int vx_destroy(vx_ctx *ctx);
+const char *vx_last_error(vx_ctx *ctx);          /* never NULL */
+int vx_device_index(vx_ctx *ctx);                /* Backend.Device(), backend.go:311 */
+
+/* ------------------------------------------------------------------ memory
+ * Backend.Alloc/Free/ToDevice/ToHost/Sync (backend.go:317-331); AllocPermanent and ResetPool
+ * (runtime/gpu_block_pool.go:69-81, runtime/decode.go:366; inference/backend/backend.go:8-10);
+ * BufferCopier.CopyBuffer (backend.go:38-43).  vx_alloc buffers are recycled wholesale by
+ * vx_reset_pool; vx_alloc_permanent buffers live until vx_free / vx_destroy. */
+int vx_alloc(vx_ctx *ctx, size_t bytes, vx_dptr *out);
+int vx_alloc_permanent(vx_ctx *ctx, size_t bytes, vx_dptr *out);
+int vx_free(vx_ctx *ctx, vx_dptr p);
+int vx_reset_pool(vx_ctx *ctx);
+int vx_h2d(vx_ctx *ctx, vx_dptr dst, const void *src, size_t bytes);
+int vx_d2h(vx_ctx *ctx, void *dst, vx_dptr src, size_t bytes);
+int vx_d2d(vx_ctx *ctx, vx_dptr dst, vx_dptr src, size_t bytes);
+int vx_memset(vx_ctx *ctx, vx_dptr dst, int byte, size_t bytes);
+int vx_sync(vx_ctx *ctx);
+
+/* ------------------------------------------------------------------ Backend kernels (backend.go:333-390)
+ * All operands are float32 on the device unless stated. */
+int vx_matmul_f32(vx_ctx *, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k);    /* MatMul :338 */
+int vx_matmul_f32_t(vx_ctx *, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k);  /* MatMulTransposed :341 */
+int vx_rmsnorm(vx_ctx *, vx_dptr x, vx_dptr w, vx_dptr out, int rows, int cols, float eps);              /* RMSNorm :345 */
+int vx_rope(vx_ctx *, vx_dptr q, vx_dptr k /*0 = nil*/, int head_dim, int n_heads, int n_kv_heads,
+            int seq_len, int start_pos, int rope_dim, float theta, int neox);                            /* RoPE :352 */
+int vx_silu(vx_ctx *, vx_dptr x, vx_dptr out, int n);                                                    /* SiLU :356 */
+int vx_silu_mul(vx_ctx *, vx_dptr gate, vx_dptr up, vx_dptr out, int n);                                 /* SiLUMul :360 */
+int vx_softmax(vx_ctx *, vx_dptr x, vx_dptr out, int rows, int cols);                                    /* Softmax :364 */
+int vx_add(vx_ctx *, vx_dptr a, vx_dptr b, vx_dptr out, int n);                                          /* Add :367 */
+int vx_mul(vx_ctx *, vx_dptr a, vx_dptr b, vx_dptr out, int n);                                          /* Mul :370 */
+int vx_embedding(vx_ctx *, vx_dptr ids_i32, int n_tokens, vx_dptr table, vx_dptr out, int vocab, int dim); /* Embedding :374 */
+int vx_sdpa(vx_ctx *, vx_dptr q, vx_dptr k, vx_dptr v, vx_dptr out, int kv_len, int n_q_heads,
+            int n_kv_heads, int head_dim, float scale, int kv_head_stride);                              /* SDPA :382 */
+int vx_sdpa_prefill(vx_ctx *, vx_dptr q, vx_dptr k, vx_dptr v, vx_dptr out, int seq_len, int n_q_heads,
+                    int n_kv_heads, int head_dim, float scale);                                          /* SDPAPrefill :389 */
+
+/* Optional capability interfaces */
+int vx_matmul_q4_0(vx_ctx *, vx_dptr a, vx_dptr b_raw, vx_dptr out, int m, int n, int k); /* QuantizedMatMul.MatMulQ4_0 backend.go:50 */
+int vx_matmul_q4_k(vx_ctx *, vx_dptr a, vx_dptr b_raw, vx_dptr out, int m, int n, int k); /* MatMulQ4_K :55 */
+int vx_matmul_q6_k(vx_ctx *, vx_dptr a, vx_dptr b_raw, vx_dptr out, int m, int n, int k); /* MatMulQ6_K :60 */
+int vx_argmax(vx_ctx *, vx_dptr x, int n, int *out_index);                /* ArgmaxOps.Argmax :202 (synchronous, first max wins) */
+int vx_argmax_rows(vx_ctx *, vx_dptr x, int rows, int cols, vx_dptr out_i32); /* batched form, asynchronous */
+int vx_gelu(vx_ctx *, vx_dptr x, vx_dptr out, int n);                     /* GELUOps.GELU :220 */
+int vx_gelu_mul(vx_ctx *, vx_dptr gate, vx_dptr up, vx_dptr out, int n);  /* GELUOps.GELUMul :224 */
+int vx_scale(vx_ctx *, vx_dptr buf, float scale, int n);                  /* ScaleOps.ScaleBuffer :262 */
+int vx_sdpa_softcap(vx_ctx *, vx_dptr q, vx_dptr k, vx_dptr v, vx_dptr out, int kv_len, int n_q_heads,
+                    int n_kv_heads, int head_dim, float scale, float softcap, int kv_head_stride);       /* SoftCapAttentionOps.SDPASoftCap :234 */
+int vx_sdpa_prefill_softcap(vx_ctx *, vx_dptr q, vx_dptr k, vx_dptr v, vx_dptr out, int seq_len,
+                            int n_q_heads, int n_kv_heads, int head_dim, float scale, float softcap);    /* SDPAPrefillSoftCap :238 */
+int vx_rope_freqs(vx_ctx *, vx_dptr q, vx_dptr k, vx_dptr freqs, int head_dim, int n_heads,
+                  int n_kv_heads, int seq_len, int start_pos, int neox);                                 /* ScaledRoPEOps :246 */
+/* bit-exact dequantisation of GGUF blocks to float32 (inference/pkg/gguf/dequant.go:16-56, 272-331, 342-396) */
+int vx_dequantize(vx_ctx *, int type, vx_dptr raw, vx_dptr out_f32, int64_t n_elements);
+
+/* PagedKVOps (backend.go:415-466).  Pool layout per layer:
+ * element((blk*2 + isV)*bs*Hkv*D + off*Hkv*D + h*D + d). */
+int vx_reshape_paged_kv(vx_ctx *, vx_dptr src, vx_dptr pool, vx_dptr page_table_i32, vx_dptr block_offsets_i32,
+                        int n_tokens, int n_kv_heads, int head_dim, int block_size, int is_value);       /* ReshapePagedKV :424 */
+int vx_reshape_paged_kv_f16(vx_ctx *, vx_dptr src, vx_dptr pool, vx_dptr page_table_i32, vx_dptr block_offsets_i32,
+                            int n_tokens, int n_kv_heads, int head_dim, int block_size, int is_value);   /* ReshapePagedKVF16 :457 */
+int vx_sdpa_paged_decode(vx_ctx *, vx_dptr q, vx_dptr pool, vx_dptr block_table_i32, vx_dptr out,
+                         int n_blocks, int block_size, int n_q_heads, int n_kv_heads, int head_dim,
+                         float scale, int tokens_in_last_block);                                         /* SDPAPagedDecode :432 */
+int vx_sdpa_paged_decode_f16(vx_ctx *, vx_dptr q, vx_dptr pool, vx_dptr block_table_i32, vx_dptr out,
+                             int n_blocks, int block_size, int n_q_heads, int n_kv_heads, int head_dim,
+                             float scale, int tokens_in_last_block);                                     /* SDPAPagedDecodeF16 :436 */
+/* block_tables: host array of batch device addresses; seq_lens: host array (as the Go slices are) */
+int vx_sdpa_paged_decode_batched(vx_ctx *, vx_dptr q, vx_dptr pool, const vx_dptr *block_tables, vx_dptr out,
+                                 int batch, int max_blocks, int block_size, int n_q_heads, int n_kv_heads,
+                                 int head_dim, float scale, const int *seq_lens, int pool_is_f16);       /* SDPAPagedDecodeBatched :447 */
+int vx_sdpa_paged_decode_multiquery(vx_ctx *, vx_dptr q, vx_dptr pool, vx_dptr block_table_i32, vx_dptr out,
+                                    vx_dptr kv_lens_i32, int n_blocks, int block_size, int n_q_heads,
+                                    int n_kv_heads, int head_dim, float scale, int query_len,
+                                    int pool_is_f16);                                                    /* SDPAPagedDecodeMultiquery :463 */
+/* the same paged kernel with the Gemma-2 variants the CPU branch applies
+ * (runtime/block.go:925-953): softcap > 0 and/or kv_start (first attended position) per query */
+int vx_sdpa_paged_decode_ex(vx_ctx *, vx_dptr q, vx_dptr pool, vx_dptr block_table_i32, vx_dptr out,
+                            int kv_start, int kv_len, int block_size, int n_q_heads, int n_kv_heads,
+                            int head_dim, float scale, float softcap, int pool_is_f16);
+
+/* ------------------------------------------------------------------ batched decode fast path */
+typedef struct {
+    int n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab;   /* runtime/config.go:98-109 */
+    float rms_eps, rope_theta;
+    int rope_neox;            /* config.go:119 */
+    int geglu;                /* MLPGeGLU, config.go:437-452 */
+    int post_norms;           /* config.go:129 */
+    float embed_scale;        /* config.go:133, 0 = off */
+    float attn_softcap;       /* config.go:127 */
+    float final_softcap;      /* config.go:128 (monotone: applied to returned logits only) */
+    int sliding_window;       /* config.go:121, 0 = off */
+    int window_alternating;   /* odd layers slide, runtime/block.go:464-476 */
+    int max_blocks;           /* physical 16-token blocks per layer (runtime/model.go:305-327) */
+    int max_seqs;             /* concurrent sequences tracked by the pool */
+    int max_batch_tokens;     /* upper bound on packed query rows per step */
+    int max_blocks_per_seq;   /* block-table width = ceil(context limit / 16) */
+} vx_model_config;
+
+/* per-layer tensor slots, named after inference/runtime/block.go:256-266 */
+enum {
+    VX_W_ATTN_NORM, VX_W_WQ, VX_W_WK, VX_W_WV, VX_W_WO, VX_W_POST_ATTN_NORM,
+    VX_W_FFN_NORM, VX_W_W1, VX_W_W3, VX_W_W2, VX_W_POST_FFN_NORM, VX_W_PER_LAYER
+};
+enum { VX_G_EMBED = 0, VX_G_FINAL_NORM = 1, VX_G_OUTPUT = 2 };
+
+/* replaces NewModelRuntime + CopyWeightsToDevice + CreateGPUBlockPool
+ * (runtime/model.go:56-96, runtime/loader.go:507-708, runtime/model.go:305-327) */
+int vx_model_create(vx_ctx *ctx, const vx_model_config *cfg, vx_model **out);
+int vx_model_destroy(vx_model *m);
+/* raw GGUF tensor bytes, row-major [n_out][k] in GGUF block format; data_on_device != 0 means `data`
+ * is a device address.  layer < 0 selects the global slots (VX_G_*). */
+int vx_model_set_tensor(vx_model *m, int layer, int slot, int ggml_type, const void *data,
+                        size_t bytes, int data_on_device);
+int vx_model_finalize(vx_model *m);    /* repack for the MMA kernels, fuse QKV and gate|up */
+
+/* GPUBlockPool sequence bookkeeping, device-resident (runtime/gpu_block_pool.go:129-190, 572-635) */
+int vx_seq_create(vx_model *m, int64_t seq_id);
+int vx_seq_delete(vx_model *m, int64_t seq_id);
+int vx_seq_truncate(vx_model *m, int64_t seq_id, int new_len);
+int vx_seq_share(vx_model *m, int64_t src_seq, int64_t dst_seq, int n_tokens);
+int vx_seq_len(vx_model *m, int64_t seq_id, int *out_len);
+int vx_seq_block_table(vx_model *m, int64_t seq_id, int32_t *out, int cap, int *out_n); /* device -> host copy */
+int vx_pool_stats(vx_model *m, int *total_blocks, int *free_blocks, int *shared_blocks);  /* BlockStats :610-625 */
+int vx_pool_layer_ptr(vx_model *m, int layer, vx_dptr *out, size_t *bytes);
+/* test/bench helper: give a sequence `len` tokens of KV filled with deterministic f16 noise (no forward pass) */
+int vx_seq_fill_synthetic(vx_model *m, int64_t seq_id, int len, uint32_t seed);
+
+/* One scheduler step over a ragged batch: replaces Scheduler.runDecodeStep's per-sequence calls
+ * (scheduler/scheduler.go:290-303 -> runtime/decode.go:612-654).  Row i of the batch is sequence
+ * seq_ids[i] fed q_lens[i] tokens (NULL = 1 each; >1 = speculative verify, decode.go:1446-1569)
+ * starting at positions[i], which must equal the sequence's current length.  tokens holds
+ * sum(q_lens) ids.  out_tokens receives the greedy (first-max) token of every packed row.
+ * logits (optional, host) receives [sum(q_lens), vocab] float32. */
+int vx_decode_step(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t *tokens,
+                   const int32_t *positions, const int32_t *q_lens, int32_t *out_tokens,
+                   float *logits);
+/* Prompt processing for one sequence (runtime/decode.go:961-1096): start_pos == 0 attends causally
+ * over the fresh float32 K/V (SDPAPrefill), start_pos > 0 goes through the paged multi-query
+ * kernel.  out_token / logits refer to the last prompt token. */
+int vx_prefill(vx_model *m, int64_t seq_id, const int32_t *tokens, int n_tokens, int start_pos,
+               int32_t *out_token, float *logits);
+
+/* parity instrumentation: capture the residual stream after the embedding and after each layer of
+ * the next forward ([n_layers+1, rows, hidden] float32), the idea of inference/debug's capture hooks. */
+int vx_model_set_capture(vx_model *m, int enable);
+int vx_model_get_capture(vx_model *m, float *host_out, size_t n_floats);
+/* slot mapping / positions / cu_seqlens produced by the packing kernel for the last step */
+int vx_model_get_packing(vx_model *m, int32_t *cu_seqlens, int32_t *slot_mapping, int32_t *row_kv_len,
+                         int n_seqs, int n_rows);
+/* counters: kernels launched and steps run since creation */
+int vx_model_counters(vx_model *m, uint64_t *kernel_launches, uint64_t *steps);
+/* timing of the dominant kernel class inside vx_decode_step (CUDA events on the context's stream):
+ * which: 0 = paged attention, 1 = quantised projections.  Returns accumulated ms and launch count. */
+int vx_model_kernel_time(vx_model *m, int which, int enable, float *ms, uint64_t *launches);
+/* deterministic synthetic Q4_0 weights generated on the device: ~N(0, sigma) quantised with
+ * d = signed-absmax / -8, q = clamp(round(x/d) + 8, 0, 15); writes GGUF Q4_0 blocks */
+int vx_synth_q4_0(vx_ctx *ctx, vx_dptr dst_raw, int64_t n_elements, uint64_t seed, float sigma);
+/* bench helper: permute the pool's free list so that consecutive logical blocks land on scattered
+ * physical blocks; only valid while no sequence holds blocks */
+int vx_pool_shuffle_free_list(vx_model *m, uint32_t seed);
+/* GGUF bytes of all weights read once per step (projections, output head, norm vectors) */
+int vx_model_weight_bytes(vx_model *m, uint64_t *bytes);
+/* activation terms fed to the tensor cores by the projections: 2 = fp16 hi+lo split (float32-faithful,
+ * default), 1 = single fp16 (half the MMA work, ~2e-4 relative rounding per projection) */
+int vx_set_gemm_terms(int terms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

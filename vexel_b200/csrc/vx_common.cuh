@@ -1,0 +1,148 @@
+// Shared declarations of the CUDA backend: context, status handling, small device helpers.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "vexel_cuda.h"
+
+struct vx_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    std::recursive_mutex mu;
+    std::string err;
+    // Alloc/ResetPool semantics of the reference's pooled backend (backend/metal/backend.go:490-566):
+    // pooled buffers are handed out again after ResetPool, permanent ones never are.
+    struct Buf { void *p; size_t bytes; bool in_use; };
+    std::vector<Buf> pooled;
+    std::unordered_map<void *, size_t> permanent;
+    // scratch owned by the interface-level entry points
+    void *scratch = nullptr; size_t scratch_bytes = 0;
+    int *d_int_result = nullptr;      // device int for the synchronous Argmax
+    int *h_int_result = nullptr;      // pinned
+    int sm_count = 148;
+    uint64_t launches = 0;
+};
+
+struct VxGuard {
+    vx_ctx *c;
+    explicit VxGuard(vx_ctx *ctx) : c(ctx) { c->mu.lock(); cudaSetDevice(c->device); }
+    ~VxGuard() { c->mu.unlock(); }
+};
+
+int vx_fail(vx_ctx *c, int code, const char *fmt, ...);
+int vx_cuda_fail(vx_ctx *c, cudaError_t e, const char *what);
+int vx_scratch(vx_ctx *c, size_t bytes, void **out);   // grows the interface-level scratch buffer
+
+#define VX_CUDA(ctx, call)                                                        \
+    do {                                                                          \
+        cudaError_t e__ = (call);                                                 \
+        if (e__ != cudaSuccess) return vx_cuda_fail((ctx), e__, #call);           \
+    } while (0)
+#define VX_LAUNCH_CHECK(ctx)                                                      \
+    do {                                                                          \
+        (ctx)->launches++;                                                        \
+        cudaError_t e__ = cudaGetLastError();                                     \
+        if (e__ != cudaSuccess) return vx_cuda_fail((ctx), e__, "kernel launch"); \
+    } while (0)
+#define VX_REQUIRE(ctx, cond, msg)                                                \
+    do {                                                                          \
+        if (!(cond)) return vx_fail((ctx), VX_E_BAD_ARG, "%s: %s", __func__, msg); \
+    } while (0)
+#define VX_TRY(expr)                                                              \
+    do {                                                                          \
+        int rc__ = (expr);                                                        \
+        if (rc__ != VX_OK) return rc__;                                           \
+    } while (0)
+
+template <typename T> static inline T *dp(vx_dptr p) { return reinterpret_cast<T *>(static_cast<uintptr_t>(p)); }
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- device helpers -------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// block-wide reductions; `red` is >= 32 floats of shared memory; every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float *red) {
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    float r = lane < nw ? red[lane] : 0.f;
+    r = warp_sum(r);
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float *red) {
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    float r = lane < nw ? red[lane] : -INFINITY;
+    r = warp_max(r);
+    return r;
+}
+
+// ---- shared between translation units ---------------------------------------------------------
+// Activation rows prepared for the tensor-core projections: x = s * (hi + lo) with hi, lo fp16 and
+// s a power of two per row; element k is stored at position perm4(k) so that one 8-byte load gives
+// a thread its two B-fragment registers (see vx_quant.cu).
+struct VxSplit {
+    __half *hi; __half *lo; float *scale; float *bsum;   // bsum: per-32-block sums of x/s (K-quant minima)
+    int k_pad;                                           // row stride in elements (multiple of 128)
+};
+__host__ __device__ __forceinline__ int vx_perm4(int k) {   // within each group of 4: order 0,2,1,3
+    int r = k & 3;
+    return (k & ~3) | ((r == 1) ? 2 : (r == 2) ? 1 : r);
+}
+
+// Repacked weight matrix for the MMA kernels (built by vx_model_finalize / the interface entry points).
+struct VxWeight {
+    int type = -1;          // VX_T_*
+    int n = 0, k = 0, k_pad = 0;
+    void *qs = nullptr;     // Q4_0: [n][k_pad/128][4 lanes][4 words]; F32: raw
+    void *sc = nullptr;     // Q4_0: half [n][k_pad/32]
+    void *aux = nullptr;
+    size_t bytes = 0;       // GGUF byte size (roofline accounting)
+};
+
+// launchers implemented in vx_quant.cu
+int vxq_repack(vx_ctx *c, int type, const void *raw_dev, int n, int k, VxWeight *w, void *qs_dst, void *sc_dst);
+size_t vxq_repack_bytes(int type, int n, int k, size_t *qs_bytes, size_t *sc_bytes);
+int vxq_gemm(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out,
+             float *parts, size_t parts_cap_floats);
+int vxq_split_rows(vx_ctx *c, const float *x, int rows, int cols, int ld, const VxSplit &s);
+int vxq_reduce_parts(vx_ctx *c, const float *parts, int n_parts, int m, int n, float *out, int ld_out);
+size_t vxq_split_bytes(int rows, int k, size_t *hi_off, size_t *lo_off, size_t *scale_off, size_t *bsum_off, int *k_pad);
+
+// launchers implemented in vx_paged.cu
+struct VxAttnArgs {
+    const float *q; int q_row_stride;        // [rows][Hq*D] float32
+    const void *pool; int pool_is_f16;
+    const int32_t *const *tables;             // per sequence-slot block table base pointers (device array)
+    const int32_t *row_slot;                  // [rows] -> index into tables
+    const int32_t *row_kv_start;              // [rows] first attended position (nullptr = 0)
+    const int32_t *row_kv_len;                // [rows]
+    const int4 *work; const int32_t *n_work_dev; int n_work;   // (row, first_page, n_pages, chunk_index)
+    const int32_t *row_work_start;            // [rows+1]
+    float *partials;                          // [n_work][Hq][D+2]
+    float *out; int out_row_stride;           // [rows][Hq*D]
+    int rows, n_q_heads, n_kv_heads, head_dim, block_size;
+    float scale, softcap;
+};
+int vxp_attention(vx_ctx *c, const VxAttnArgs &a);

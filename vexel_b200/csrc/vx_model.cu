@@ -1,0 +1,1109 @@
+// The batched decode fast path: model weights, the device-resident block pool, and one call per
+// scheduler step.  Replaces the per-sequence loop of inference/runtime/decode.go:612-654 and the host
+// bookkeeping of inference/runtime/gpu_block_pool.go with device kernels:
+//   pack_kernel        cu_seqlens / slot mapping / block tables / split-K work lists by prefix scans
+//   add_norm_split     residual add (+ Gemma post-norm) + RMSNorm + fp16 hi/lo split for the projections
+//   rope_append        RoPE on q,k and the f32->f16 append of k,v into the paged pool
+//   vxp_attention      paged FlashDecoding (vx_paged.cu)       vxq_gemm  dequant-fused projections (vx_quant.cu)
+// Layer order and arithmetic follow inference/runtime/block.go:763-1081.
+#include <math.h>
+#include <string.h>
+
+#include <algorithm>
+
+#include "vx_paged.cuh"
+
+namespace {
+
+constexpr int BS = 16;   // tokens per KV block (runtime/decode.go:351)
+constexpr int MAX_PARTS = 8;
+constexpr int MAX_WORK = 32768;
+
+struct LayerW {
+    VxWeight wqkv, wo, w13, w2;
+    float *attn_norm = nullptr, *ffn_norm = nullptr, *post_attn_norm = nullptr, *post_ffn_norm = nullptr;
+};
+struct RawTensor { int type = -1; void *dev = nullptr; size_t bytes = 0; };
+
+}  // namespace
+
+struct vx_model {
+    vx_ctx *c = nullptr;
+    vx_model_config cfg{};
+    bool finalized = false;
+    std::vector<RawTensor> raw;           // [layer][VX_W_PER_LAYER] + 3 globals, until finalize
+    std::vector<LayerW> layers;
+    std::vector<void *> owned;            // device allocations freed at destroy
+    RawTensor embed;                      // kept in GGUF form; rows are dequantised on lookup
+    float *final_norm = nullptr;
+    VxWeight w_out;
+    size_t weight_bytes = 0;
+    // ---- pool
+    __half *pool = nullptr; size_t layer_stride = 0;      // elements per layer
+    int32_t *d_tables = nullptr; const int32_t **d_table_ptrs = nullptr;
+    int32_t *d_seq_len = nullptr, *d_n_blocks = nullptr, *d_free_list = nullptr, *d_free_top = nullptr, *d_refcnt = nullptr;
+    int32_t *d_status = nullptr;
+    std::unordered_map<int64_t, int> seq_slot;
+    std::vector<int> free_slots, h_seq_len, h_n_blocks;
+    int h_free = 0;
+    // ---- per-step buffers
+    int32_t *d_step_in = nullptr, *h_step_in = nullptr;   // pinned staging + device copy
+    int32_t *d_cu = nullptr, *d_row_slot = nullptr, *d_row_pos = nullptr, *d_slot_map = nullptr, *d_row_kv_len = nullptr,
+            *d_row_kv_start = nullptr;
+    int4 *d_work[2] = {nullptr, nullptr}; int32_t *d_rws[2] = {nullptr, nullptr}; int32_t *d_n_work[2] = {nullptr, nullptr};
+    float *d_partials = nullptr;
+    float *d_cos = nullptr, *d_sin = nullptr, *d_freq = nullptr;
+    float *x = nullptr, *qkv = nullptr, *attn = nullptr, *h13 = nullptr, *act = nullptr, *parts = nullptr, *logits = nullptr;
+    size_t parts_cap = 0;
+    VxSplit sp_h{}, sp_q{}, sp_f{};
+    int32_t *d_out_tok = nullptr, *h_out_tok = nullptr;
+    float *capture = nullptr; bool capture_on = false; int capture_rows = 0;
+    int last_rows = 0, last_seqs = 0;
+    uint64_t steps = 0;
+    // kernel timing
+    bool time_on[2] = {false, false}; float time_ms[2] = {0, 0}; uint64_t time_n[2] = {0, 0};
+    std::vector<cudaEvent_t> ev_pool; std::vector<std::pair<int, int>> ev_used;   // (which, index of start event)
+    size_t ev_next = 0;
+};
+
+namespace {
+
+int model_alloc(vx_model *m, size_t bytes, void **out) {
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes ? bytes : 16);
+    if (e != cudaSuccess) { cudaGetLastError(); return vx_fail(m->c, VX_E_OOM, "cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e)); }
+    m->owned.push_back(p);
+    *out = p;
+    return VX_OK;
+}
+template <typename T> int model_alloc_t(vx_model *m, size_t n, T **out) { return model_alloc(m, n * sizeof(T), (void **)out); }
+
+void slot_dims(const vx_model_config &c, int slot, int *n, int *k) {
+    int qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim;
+    switch (slot) {
+    case VX_W_WQ: *n = qd; *k = c.hidden; break;
+    case VX_W_WK: case VX_W_WV: *n = kvd; *k = c.hidden; break;
+    case VX_W_WO: *n = c.hidden; *k = qd; break;
+    case VX_W_W1: case VX_W_W3: *n = c.ffn; *k = c.hidden; break;
+    case VX_W_W2: *n = c.hidden; *k = c.ffn; break;
+    default: *n = 1; *k = c.hidden; break;
+    }
+}
+size_t type_row_bytes(int type, int k) {
+    switch (type) {
+    case VX_T_F32: return (size_t)k * 4;
+    case VX_T_F16: return (size_t)k * 2;
+    case VX_T_Q4_0: return (size_t)(k / 32) * 18;
+    case VX_T_Q4_K: return (size_t)(k / 256) * 144;
+    case VX_T_Q6_K: return (size_t)(k / 256) * 210;
+    default: return 0;
+    }
+}
+
+// ------------------------------------------------------------------ sequence bookkeeping kernels
+// runtime/gpu_block_pool.go:210-219 (releaseBlock) applied to table entries [keep, n_blocks), in table order
+__global__ void seq_release_kernel(int32_t *tables, int width, int32_t *n_blocks, int32_t *seq_len, int32_t *free_list,
+                                   int32_t *free_top, int32_t *refcnt, int slot, int keep, int new_len) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int nb = n_blocks[slot], top = *free_top;
+    for (int i = keep; i < nb; i++) {
+        int b = tables[(size_t)slot * width + i];
+        int rc = refcnt[b];
+        if (rc <= 1) { refcnt[b] = 0; free_list[top++] = b; }
+        else refcnt[b] = rc - 1;
+    }
+    *free_top = top;
+    if (keep < nb) n_blocks[slot] = keep;
+    seq_len[slot] = new_len;
+}
+// runtime/gpu_block_pool.go:572-607
+__global__ void seq_share_kernel(int32_t *tables, int width, int32_t *n_blocks, int32_t *seq_len, int32_t *refcnt, int src, int dst,
+                                 int nb, int n_tokens) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int dn = n_blocks[dst];
+    for (int i = 0; i < nb; i++) {
+        int b = tables[(size_t)src * width + i];
+        tables[(size_t)dst * width + dn + i] = b;
+        refcnt[b]++;
+    }
+    n_blocks[dst] = dn + nb;
+    if (n_tokens > seq_len[dst]) seq_len[dst] = n_tokens;
+}
+// grows one sequence to new_len tokens (allocBlock order of runtime/gpu_block_pool.go:200-208: pop from the end)
+__global__ void seq_grow_kernel(int32_t *tables, int width, int32_t *n_blocks, int32_t *seq_len, int32_t *free_list,
+                                int32_t *free_top, int32_t *refcnt, int slot, int new_len, int32_t *status) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int need = (new_len + BS - 1) / BS, nb = n_blocks[slot], top = *free_top;
+    if (need - nb > top || need > width) { *status = VX_E_OOM_BLOCKS; return; }
+    for (; nb < need; nb++) { int b = free_list[--top]; refcnt[b] = 1; tables[(size_t)slot * width + nb] = b; }
+    n_blocks[slot] = nb; *free_top = top;
+    if (new_len > seq_len[slot]) seq_len[slot] = new_len;
+}
+__global__ void init_free_list_kernel(int32_t *free_list, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) free_list[i] = i;   // ascending, so the first pop is n-1 (runtime/gpu_block_pool.go:114-116)
+}
+__global__ void init_table_ptrs_kernel(const int32_t **ptrs, const int32_t *tables, int width, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) ptrs[i] = tables + (size_t)i * width;
+}
+__device__ __forceinline__ uint32_t hash32(uint32_t x) {
+    x ^= x >> 16; x *= 0x7feb352dU; x ^= x >> 15; x *= 0x846ca68bU; x ^= x >> 16; return x;
+}
+// fills the KV of positions [0,len) of one sequence in every layer with fp16 noise in [-0.25, 0.25)
+__global__ void fill_noise_kernel(__half *pool, size_t layer_stride, int n_layers, const int32_t *table, int len, int hs, uint32_t seed) {
+    size_t per_layer = (size_t)len * hs * 2;   // K and V
+    size_t total = per_layer * n_layers;
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        int layer = (int)(idx / per_layer); size_t r = idx % per_layer;
+        int is_v = (int)(r / ((size_t)len * hs)); size_t r2 = r % ((size_t)len * hs);
+        int pos = (int)(r2 / hs), e = (int)(r2 % hs);
+        size_t part = (size_t)BS * hs;
+        size_t dst = (size_t)layer * layer_stride + (size_t)table[pos / BS] * 2 * part + (is_v ? part : 0) + (size_t)(pos % BS) * hs + e;
+        uint32_t h = hash32((uint32_t)idx * 2654435761u + seed);
+        pool[dst] = __float2half_rn(((int)(h & 0xFFFF) - 32768) * (0.25f / 32768.f));
+    }
+}
+// random permutation of the free list by sorting on hashed keys (single block, bitonic-free: rank by counting)
+__global__ void shuffle_free_list_kernel(int32_t *free_list, int32_t *tmp, int n, uint32_t seed) {
+    // rank of element i = number of elements with a smaller (hash, index) key
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        uint32_t ki = hash32((uint32_t)i ^ seed);
+        int rank = 0;
+        for (int j = 0; j < n; j++) { uint32_t kj = hash32((uint32_t)j ^ seed); rank += (kj < ki) || (kj == ki && j < i); }
+        tmp[rank] = free_list[i];
+    }
+}
+
+// ------------------------------------------------------------------ the packing kernel (one CTA)
+// step_in = [n_seqs slots][n_seqs q_lens][n_seqs positions][n_rows tokens]
+struct PackArgs {
+    const int32_t *step_in; int n_seqs, n_rows;
+    int32_t *tables; int width; int32_t *seq_len, *n_blocks, *free_list, *free_top, *refcnt, *status;
+    int32_t *cu, *row_slot, *row_pos, *slot_map, *row_kv_len, *row_kv_start;
+    int window;                          // 0 = no sliding layers
+    int4 *work0, *work1; int32_t *rws0, *rws1, *n_work0, *n_work1; int chunk0, chunk1, max_work;
+};
+__global__ void __launch_bounds__(1024) pack_kernel(PackArgs a) {
+    __shared__ int tmp[33];
+    __shared__ int s_err, s_ovf;
+    const int32_t *slots = a.step_in, *qlens = a.step_in + a.n_seqs, *positions = a.step_in + 2 * a.n_seqs;
+    if (threadIdx.x == 0) { s_err = 0; s_ovf = 0; }
+    __syncthreads();
+    // pass A: validate, prefix sums of q_len (rows) and of newly needed blocks; nothing is modified yet
+    int row_base = 0, need_base = 0;
+    for (int i0 = 0; i0 < a.n_seqs; i0 += blockDim.x) {
+        int i = i0 + threadIdx.x, ql = 0, need = 0;
+        if (i < a.n_seqs) {
+            int s = slots[i]; ql = qlens[i];
+            int start = a.seq_len[s];
+            if (positions[i] != start || ql <= 0) atomicExch(&s_err, VX_E_BAD_ARG);
+            int nb_new = (start + ql + BS - 1) / BS;
+            if (nb_new > a.width) atomicExch(&s_err, VX_E_OOM_BLOCKS);
+            need = max(0, nb_new - a.n_blocks[s]);
+        }
+        int tq, tn;
+        int oq = vx_block_excl_scan(ql, tmp, &tq);
+        int on = vx_block_excl_scan(need, tmp, &tn);
+        if (i < a.n_seqs) { a.cu[i] = row_base + oq; a.row_kv_start[i] = need_base + on; /* scratch: block offset */ }
+        row_base += tq; need_base += tn;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        a.cu[a.n_seqs] = row_base;
+        if (row_base != a.n_rows) s_err = VX_E_BAD_ARG;
+        if (need_base > *a.free_top) s_err = VX_E_OOM_BLOCKS;
+    }
+    __syncthreads();
+    if (s_err) { if (threadIdx.x == 0) *a.status = s_err; return; }
+    // pass B: pop blocks in batch order (sequence i takes the pops numbered [off_i, off_i + need_i) from the end of the stack)
+    const int top = *a.free_top;
+    __syncthreads();
+    for (int i = threadIdx.x; i < a.n_seqs; i += blockDim.x) {
+        int s = slots[i], ql = qlens[i], start = a.seq_len[s];
+        int nb = a.n_blocks[s], nb_new = (start + ql + BS - 1) / BS, off = a.row_kv_start[i];
+        for (int j = 0; nb + j < nb_new; j++) {
+            int b = a.free_list[top - 1 - (off + j)];
+            a.refcnt[b] = 1;
+            a.tables[(size_t)s * a.width + nb + j] = b;
+        }
+        if (nb_new > nb) a.n_blocks[s] = nb_new;
+        a.seq_len[s] = start + ql;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *a.free_top = top - need_base;
+    // per-row arrays
+    for (int t = threadIdx.x; t < a.n_rows; t += blockDim.x) {
+        int lo = 0, hi = a.n_seqs;                       // last i with cu[i] <= t
+        while (hi - lo > 1) { int mid = (lo + hi) >> 1; if (a.cu[mid] <= t) lo = mid; else hi = mid; }
+        int s = slots[lo], pos = positions[lo] + (t - a.cu[lo]);
+        a.row_slot[t] = s; a.row_pos[t] = pos;
+        a.slot_map[t] = a.tables[(size_t)s * a.width + pos / BS] * BS + pos % BS;
+        a.row_kv_len[t] = pos + 1;
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < a.n_rows; t += blockDim.x)
+        a.row_kv_start[t] = a.window > 0 ? max(0, a.row_pos[t] + 1 - a.window) : 0;   // runtime/block.go:925-929
+    __syncthreads();
+    int n0 = vx_build_work(a.n_rows, nullptr, a.row_kv_len, BS, a.chunk0, a.work0, a.rws0, a.max_work, &s_ovf, tmp);
+    if (threadIdx.x == 0) *a.n_work0 = n0;
+    if (a.window > 0) {
+        int n1 = vx_build_work(a.n_rows, a.row_kv_start, a.row_kv_len, BS, a.chunk1, a.work1, a.rws1, a.max_work, &s_ovf, tmp);
+        if (threadIdx.x == 0) *a.n_work1 = n1;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && s_ovf) *a.status = VX_E_BAD_ARG;
+}
+
+// cos/sin of angle = float32(pos) * freq[j], evaluated in float64 and rounded once (backend/cpu/cpu.go:256-260)
+__global__ void rope_table_kernel(const int32_t *row_pos, const float *freq, float *cs, float *sn, int n_rows, int half) {
+    int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_rows * half) return;
+    int t = idx / half, j = idx % half;
+    float angle = __fmul_rn((float)row_pos[t], freq[j]);
+    cs[idx] = (float)cos((double)angle); sn[idx] = (float)sin((double)angle);
+}
+
+// ------------------------------------------------------------------ embedding (GGUF rows dequantised on lookup)
+__global__ void embed_kernel(const int32_t *tokens, const void *table, int type, float *x, int hidden, int vocab, float scale) {
+    int t = blockIdx.x, id = tokens[t];
+    float *o = x + (size_t)t * hidden;
+    if (id < 0 || id >= vocab) { for (int j = threadIdx.x; j < hidden; j += blockDim.x) o[j] = 0.f; return; }
+    if (type == VX_T_Q4_0) {
+        const uint8_t *row = (const uint8_t *)table + (size_t)id * (hidden / 32) * 18;
+        for (int j = threadIdx.x; j < hidden / 2; j += blockDim.x) {     // one packed byte per iteration
+            int b = j >> 4, i = j & 15;
+            const uint8_t *blk = row + b * 18;
+            float d = __half2float(__ushort_as_half((unsigned short)(blk[0] | (blk[1] << 8))));
+            uint8_t bv = blk[2 + i];
+            float lo = __fmul_rn(d, (float)((int)(bv & 0xF) - 8)), hi = __fmul_rn(d, (float)((int)(bv >> 4) - 8));
+            if (scale != 0.f) { lo = __fmul_rn(lo, scale); hi = __fmul_rn(hi, scale); }
+            o[b * 32 + i] = lo; o[b * 32 + i + 16] = hi;
+        }
+    } else {
+        const float *row = (const float *)table + (size_t)id * hidden;
+        for (int j = threadIdx.x; j < hidden; j += blockDim.x) o[j] = scale != 0.f ? __fmul_rn(row[j], scale) : row[j];
+    }
+}
+
+// ------------------------------------------------------------------ residual add + RMSNorm + split
+// x[row] += (post_w ? rmsnorm(sum parts)*post_w : sum parts);  y = rmsnorm(x)*w;  y -> fp16 hi/lo (+ per-block sums).
+// n_parts == 0 skips the add; w == nullptr skips the norm/split.  One CTA per row, row staged in shared memory.
+__global__ void __launch_bounds__(256)
+add_norm_split_kernel(float *x, const float *parts, int n_parts, size_t part_stride, int part_ld, const float *post_w, const float *w,
+                      float eps, int hidden, VxSplit s, float *capture) {
+    extern __shared__ float row[];
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    float *xr = x + (size_t)r * hidden;
+    if (n_parts > 0) {
+        float ss = 0.f;
+        for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+            float v = 0.f;
+            for (int p = 0; p < n_parts; p++) v += parts[p * part_stride + (size_t)r * part_ld + j];
+            row[j] = v; ss = fmaf(v, v, ss);
+        }
+        if (post_w) {   // Gemma 2 post-norm, runtime/block.go:985-987 / 1067-1070
+            ss = block_sum(ss, red);
+            float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps));
+            for (int j = threadIdx.x; j < hidden; j += blockDim.x) row[j] = __fmul_rn(__fdiv_rn(row[j], rms), post_w[j]);
+        }
+        for (int j = threadIdx.x; j < hidden; j += blockDim.x) { float v = __fadd_rn(xr[j], row[j]); xr[j] = v; row[j] = v; }
+    } else {
+        for (int j = threadIdx.x; j < hidden; j += blockDim.x) row[j] = xr[j];
+    }
+    if (capture) for (int j = threadIdx.x; j < hidden; j += blockDim.x) capture[(size_t)r * hidden + j] = row[j];
+    if (!w) return;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) ss = fmaf(row[j], row[j], ss);
+    ss = block_sum(ss, red);
+    float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps));   // backend/cpu/cpu.go:213-218
+    float amax = 0.f;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) { float y = __fmul_rn(__fdiv_rn(row[j], rms), w[j]); row[j] = y; amax = fmaxf(amax, fabsf(y)); }
+    amax = block_max(amax, red);
+    float sc = 1.0f, inv = 1.0f;
+    if (amax > 0.f && amax < INFINITY) { int e; frexpf(amax, &e); e = max(-100, min(100, e - 11)); sc = ldexpf(1.0f, e); inv = ldexpf(1.0f, -e); }
+    if (threadIdx.x == 0) s.scale[r] = sc;
+    __syncthreads();
+    __half *hi = s.hi + (size_t)r * s.k_pad, *lo = s.lo + (size_t)r * s.k_pad;
+    float *bs = s.bsum + (size_t)r * (s.k_pad / 32);
+    for (int k0 = threadIdx.x * 4; k0 < s.k_pad; k0 += blockDim.x * 4) {
+        float v[4], sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) { int kk = k0 + i; v[i] = kk < hidden ? row[kk] * inv : 0.f; sum += v[i]; }
+        __half h[4], l[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) { h[i] = __float2half_rn(v[i]); l[i] = __float2half_rn(v[i] - __half2float(h[i])); }
+        *reinterpret_cast<uint2 *>(hi + k0) = make_uint2((uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[2]) << 16),
+                                                         (uint32_t)__half_as_ushort(h[1]) | ((uint32_t)__half_as_ushort(h[3]) << 16));
+        *reinterpret_cast<uint2 *>(lo + k0) = make_uint2((uint32_t)__half_as_ushort(l[0]) | ((uint32_t)__half_as_ushort(l[2]) << 16),
+                                                         (uint32_t)__half_as_ushort(l[1]) | ((uint32_t)__half_as_ushort(l[3]) << 16));
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        if ((threadIdx.x & 7) == 0) bs[k0 / 32] = sum;
+    }
+}
+
+// ------------------------------------------------------------------ RoPE + KV append
+// qkv row = [q (Hq*D) | k (Hkv*D) | v (Hkv*D)] float32.  q and k are rotated in place (backend/cpu/cpu.go:226-303);
+// k and v are rounded to fp16 (round-to-nearest-even, as reshape_paged_kv_f16) and written to the row's pool slot.
+__global__ void rope_append_kernel(float *qkv, int ld, const float *cs, const float *sn, const int32_t *slot_map, __half *pool_layer,
+                                   int n_heads, int n_kv_heads, int D, int neox) {
+    const int t = blockIdx.x, half = D / 2;
+    float *rowp = qkv + (size_t)t * ld;
+    const float *c = cs + (size_t)t * half, *s = sn + (size_t)t * half;
+    const int slot = slot_map[t];
+    const size_t hs = (size_t)n_kv_heads * D, part = (size_t)BS * hs;
+    __half *kdst = pool_layer + (size_t)(slot / BS) * 2 * part + (size_t)(slot % BS) * hs;
+    __half *vdst = kdst + part;
+    const int qk_pairs = (n_heads + n_kv_heads) * half;
+    for (int idx = threadIdx.x; idx < qk_pairs; idx += blockDim.x) {
+        int hd = idx / half, j = idx % half;
+        float *v = rowp + (size_t)hd * D;            // q heads then k heads are contiguous in the row
+        int i0 = neox ? j : 2 * j, i1 = neox ? j + half : 2 * j + 1;
+        float a = v[i0], b = v[i1];
+        float r0 = __fsub_rn(__fmul_rn(a, c[j]), __fmul_rn(b, s[j]));
+        float r1 = __fadd_rn(__fmul_rn(a, s[j]), __fmul_rn(b, c[j]));
+        v[i0] = r0; v[i1] = r1;
+        if (hd >= n_heads) {
+            int kh = hd - n_heads;
+            kdst[(size_t)kh * D + i0] = __float2half_rn(r0);
+            kdst[(size_t)kh * D + i1] = __float2half_rn(r1);
+        }
+    }
+    const float *vsrc = rowp + (size_t)(n_heads + n_kv_heads) * D;
+    for (int e = threadIdx.x; e < (int)hs; e += blockDim.x) vdst[e] = __float2half_rn(vsrc[e]);
+}
+
+// ------------------------------------------------------------------ gated activation (SwiGLU / GeGLU)
+__global__ void gate_act_kernel(const float *h13, int ffn, float *act, int geglu, long total) {
+    long idx = blockIdx.x * (long)blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    long r = idx / ffn; int j = (int)(idx % ffn);
+    float g = h13[r * 2 * ffn + j], u = h13[r * 2 * ffn + ffn + j];
+    float a;
+    if (geglu) {   // backend/cpu/cpu.go:457-473
+        const float s2pi = 0.7978845608f, coeff = 0.044715f;
+        float x3 = __fmul_rn(__fmul_rn(g, g), g);
+        float ta = __fmul_rn(s2pi, __fadd_rn(g, __fmul_rn(coeff, x3)));
+        float th = (float)tanh((double)ta);
+        a = __fmul_rn(__fmul_rn(0.5f, g), __fadd_rn(1.0f, th));
+    } else {       // backend/cpu/cpu.go:390-400
+        float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, (float)exp((double)(-g))));
+        a = __fmul_rn(g, sg);
+    }
+    act[idx] = __fmul_rn(a, u);
+}
+
+__global__ void final_softcap_kernel(float *logits, long n, float cap) {   // runtime/model.go:340-349
+    long i = blockIdx.x * (long)blockDim.x + threadIdx.x;
+    if (i < n) logits[i] = (float)((double)cap * tanh((double)logits[i] * (1.0 / (double)cap)));
+}
+
+}  // namespace
+
+// launchers living in other translation units
+int vxe_argmax_rows(vx_ctx *c, const float *x, int rows, int cols, int32_t *out);
+int vxe_sdpa_strided(vx_ctx *c, const float *q, int q_ld, const float *k, const float *v, float *out, int out_ld, int rows, int kv_len,
+                     int causal, int hq, int hkv, int d, long pos_stride, long head_stride, float scale, float softcap);
+
+namespace {
+
+// ---- timing helpers
+void time_begin(vx_model *m, int which) {
+    if (!m->time_on[which]) return;
+    if (m->ev_next + 2 > m->ev_pool.size()) {
+        for (int i = 0; i < 64; i++) { cudaEvent_t e; cudaEventCreate(&e); m->ev_pool.push_back(e); }
+    }
+    m->ev_used.push_back({which, (int)m->ev_next});
+    cudaEventRecord(m->ev_pool[m->ev_next], m->c->stream);
+}
+void time_end(vx_model *m, int which) {
+    if (!m->time_on[which]) return;
+    cudaEventRecord(m->ev_pool[m->ev_next + 1], m->c->stream);
+    m->ev_next += 2;
+}
+void time_collect(vx_model *m) {   // call after the stream has been synchronised
+    for (auto &u : m->ev_used) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, m->ev_pool[u.second], m->ev_pool[u.second + 1]) == cudaSuccess) { m->time_ms[u.first] += ms; m->time_n[u.first]++; }
+    }
+    m->ev_used.clear(); m->ev_next = 0;
+}
+
+int gemm(vx_model *m, const VxWeight &w, const VxSplit &x, int rows, float *out, int ld_out, int *n_parts) {
+    time_begin(m, 1);
+    int rc = vxq_gemm(m->c, w, x, rows, out, ld_out, n_parts, m->parts, m->parts_cap);
+    time_end(m, 1);
+    return rc;
+}
+// projection whose consumer wants a plain [rows][n] result
+int gemm_full(vx_model *m, const VxWeight &w, const VxSplit &x, int rows, float *out, int ld_out) {
+    int np = 1;
+    VX_TRY(gemm(m, w, x, rows, out, ld_out, &np));
+    if (np > 1) VX_TRY(vxq_reduce_parts(m->c, m->parts, np, rows, w.n, out, ld_out));
+    return VX_OK;
+}
+
+int add_norm_split(vx_model *m, int rows, const float *parts, int n_parts, size_t part_stride, int part_ld, const float *post_w,
+                   const float *w, const VxSplit &s, float *capture) {
+    size_t smem = (size_t)m->cfg.hidden * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(add_norm_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    add_norm_split_kernel<<<rows, 256, smem, m->c->stream>>>(m->x, parts, n_parts, part_stride, part_ld, post_w, w, m->cfg.rms_eps,
+                                                             m->cfg.hidden, s, capture);
+    VX_LAUNCH_CHECK(m->c);
+    return VX_OK;
+}
+
+bool layer_slides(const vx_model_config &c, int layer) {   // runtime/block.go:464-476
+    if (c.sliding_window <= 0) return false;
+    return c.window_alternating ? (layer % 2 == 1) : true;
+}
+
+// The transformer stack over `rows` packed query rows whose packing arrays are already on the device.
+// mode 0: paged attention for every row (decode / verify / chunked prefill)
+// mode 1: causal attention over the fresh float32 K/V of this call (prefill from position 0, block.go:891-895)
+// logit_rows: how many trailing rows get logits (all rows, or 1 for prefill)
+int forward(vx_model *m, int rows, int mode, int n_work_host[2], int logit_rows) {
+    vx_ctx *c = m->c; const vx_model_config &cf = m->cfg;
+    const int H = cf.hidden, Hq = cf.n_heads, Hkv = cf.n_kv_heads, D = cf.head_dim, F = cf.ffn;
+    const int qd = Hq * D, kvd = Hkv * D, nqkv = qd + 2 * kvd;
+    const float scale = (float)(1.0 / sqrt((double)D));   // block.go:862
+    const int32_t *tokens = m->d_step_in + 3 * m->last_seqs;
+    embed_kernel<<<rows, 256, 0, c->stream>>>(tokens, m->embed.dev, m->embed.type, m->x, H, cf.vocab, cf.embed_scale);
+    VX_LAUNCH_CHECK(c);
+    {
+        int n = rows * (D / 2);
+        rope_table_kernel<<<ceil_div(n, 256), 256, 0, c->stream>>>(m->d_row_pos, m->d_freq, m->d_cos, m->d_sin, rows, D / 2);
+        VX_LAUNCH_CHECK(c);
+    }
+    const size_t cap_stride = (size_t)rows * H;
+    int np_prev = 0;                 // partial count of the previous W2 projection, consumed by the next add
+    const float *post_prev = nullptr;
+    for (int l = 0; l < cf.n_layers; l++) {
+        const LayerW &L = m->layers[l];
+        // x += W2 output of the previous layer; normOut = RMSNorm(x) (block.go:836)
+        VX_TRY(add_norm_split(m, rows, m->parts, np_prev, (size_t)rows * H, H, post_prev, L.attn_norm, m->sp_h,
+                              m->capture_on ? m->capture + (size_t)l * cap_stride : nullptr));
+        VX_TRY(gemm_full(m, L.wqkv, m->sp_h, rows, m->qkv, nqkv));                     // block.go:841-854
+        rope_append_kernel<<<rows, 256, 0, c->stream>>>(m->qkv, nqkv, m->d_cos, m->d_sin, m->d_slot_map,
+                                                        m->pool + (size_t)l * m->layer_stride, Hq, Hkv, D, cf.rope_neox);   // block.go:858-868
+        VX_LAUNCH_CHECK(c);
+        time_begin(m, 0);
+        if (mode == 1) {
+            VX_TRY(vxe_sdpa_strided(c, m->qkv, nqkv, m->qkv + qd, m->qkv + qd + kvd, m->attn, qd, rows, 0, 1, Hq, Hkv, D, nqkv, D, scale,
+                                    cf.attn_softcap));
+        } else {
+            const int wl = layer_slides(cf, l) ? 1 : 0;
+            VxAttnArgs a{};
+            a.q = m->qkv; a.q_row_stride = nqkv; a.pool = m->pool + (size_t)l * m->layer_stride; a.pool_is_f16 = 1;
+            a.tables = m->d_table_ptrs; a.row_slot = m->d_row_slot;
+            a.row_kv_start = wl ? m->d_row_kv_start : nullptr; a.row_kv_len = m->d_row_kv_len;
+            a.work = m->d_work[wl]; a.n_work_dev = m->d_n_work[wl]; a.n_work = n_work_host[wl]; a.row_work_start = m->d_rws[wl];
+            a.partials = m->d_partials; a.out = m->attn; a.out_row_stride = qd;
+            a.rows = rows; a.n_q_heads = Hq; a.n_kv_heads = Hkv; a.head_dim = D; a.block_size = BS;
+            a.scale = scale; a.softcap = cf.attn_softcap;
+            VX_TRY(vxp_attention(c, a));                                                // block.go:872 / 881-890
+        }
+        time_end(m, 0);
+        VX_TRY(vxq_split_rows(c, m->attn, rows, qd, qd, m->sp_q));
+        int np_o = 1;
+        VX_TRY(gemm(m, L.wo, m->sp_q, rows, m->parts, H, &np_o));                       // block.go:983
+        // x += Wo output (post-attn norm first for Gemma 2); normOut = RMSNorm(x, ffn_norm) (block.go:985-997)
+        VX_TRY(add_norm_split(m, rows, m->parts, np_o, (size_t)rows * H, H, cf.post_norms ? L.post_attn_norm : nullptr, L.ffn_norm,
+                              m->sp_h, nullptr));
+        VX_TRY(gemm_full(m, L.w13, m->sp_h, rows, m->h13, 2 * F));                      // block.go:1045-1049
+        {
+            long total = (long)rows * F;
+            gate_act_kernel<<<(unsigned)((total + 255) / 256), 256, 0, c->stream>>>(m->h13, F, m->act, cf.geglu, total);   // block.go:1051-1057
+            VX_LAUNCH_CHECK(c);
+        }
+        VX_TRY(vxq_split_rows(c, m->act, rows, F, F, m->sp_f));
+        VX_TRY(gemm(m, L.w2, m->sp_f, rows, m->parts, H, &np_prev));                    // block.go:1060
+        post_prev = cf.post_norms ? L.post_ffn_norm : nullptr;
+    }
+    // last residual add, then the final norm on the rows that need logits (decode.go:442, 1057-1086)
+    const int r0 = rows - logit_rows;
+    VX_TRY(add_norm_split(m, rows, m->parts, np_prev, (size_t)rows * H, H, post_prev, nullptr, m->sp_h,
+                          m->capture_on ? m->capture + (size_t)cf.n_layers * cap_stride : nullptr));
+    {
+        // norm + split only the logit rows, written to split rows [0, logit_rows)
+        float *xs = m->x + (size_t)r0 * H;
+        size_t smem = (size_t)H * sizeof(float);
+        add_norm_split_kernel<<<logit_rows, 256, smem, c->stream>>>(xs, nullptr, 0, 0, 0, nullptr, m->final_norm, cf.rms_eps, H, m->sp_h, nullptr);
+        VX_LAUNCH_CHECK(c);
+    }
+    VX_TRY(gemm_full(m, m->w_out, m->sp_h, logit_rows, m->logits, cf.vocab));           // model.go:352-422
+    VX_TRY(vxe_argmax_rows(c, m->logits, logit_rows, cf.vocab, m->d_out_tok));          // sampler.go:79-90
+    return VX_OK;
+}
+
+int check_status(vx_model *m) {
+    int32_t st = 0;
+    VX_CUDA(m->c, cudaMemcpyAsync(m->h_out_tok + m->cfg.max_batch_tokens, m->d_status, 4, cudaMemcpyDeviceToHost, m->c->stream));
+    VX_CUDA(m->c, cudaStreamSynchronize(m->c->stream));
+    st = m->h_out_tok[m->cfg.max_batch_tokens];
+    if (st != 0) {
+        cudaMemsetAsync(m->d_status, 0, 4, m->c->stream);
+        return vx_fail(m->c, st, "device bookkeeping reported status %d (%s)", st,
+                       st == VX_E_OOM_BLOCKS ? "block pool exhausted" : "inconsistent step arguments");
+    }
+    return VX_OK;
+}
+
+int refresh_free(vx_model *m) {
+    VX_CUDA(m->c, cudaMemcpyAsync(m->h_out_tok + m->cfg.max_batch_tokens + 1, m->d_free_top, 4, cudaMemcpyDeviceToHost, m->c->stream));
+    VX_CUDA(m->c, cudaStreamSynchronize(m->c->stream));
+    m->h_free = m->h_out_tok[m->cfg.max_batch_tokens + 1];
+    return VX_OK;
+}
+
+// chooses the split-K chunk (in pages) for a step and returns the exact work-item count
+int plan_chunks(vx_model *m, const std::vector<int> &kv_start, const std::vector<int> &kv_len, int *chunk_out) {
+    long pages = 0;
+    for (size_t i = 0; i < kv_len.size(); i++) pages += (kv_len[i] - 1) / BS - kv_start[i] / BS + 1;
+    long target = 6L * m->c->sm_count;
+    int chunk = (int)std::min<long>(16, std::max<long>(4, (pages * m->cfg.n_kv_heads + target - 1) / target));
+    for (;;) {
+        long n = 0;
+        for (size_t i = 0; i < kv_len.size(); i++) { int np = (kv_len[i] - 1) / BS - kv_start[i] / BS + 1; n += (np + chunk - 1) / chunk; }
+        if (n <= MAX_WORK) { *chunk_out = chunk; return (int)n; }
+        chunk *= 2;
+    }
+}
+
+int run_step(vx_model *m, int n_seqs, const int *slots, const int32_t *tokens, const int32_t *positions, const int32_t *q_lens,
+             int mode, int logit_rows_req, int32_t *out_tokens, float *logits) {
+    vx_ctx *c = m->c; const vx_model_config &cf = m->cfg;
+    int rows = 0;
+    for (int i = 0; i < n_seqs; i++) rows += q_lens ? q_lens[i] : 1;
+    if (rows <= 0 || rows > cf.max_batch_tokens) return vx_fail(c, VX_E_BAD_ARG, "step has %d rows (limit %d)", rows, cf.max_batch_tokens);
+    // host-side admission control against the mirror (no device state is touched on failure)
+    long need = 0;
+    std::vector<int> kv_len, kv_start0, kv_start1;
+    std::vector<char> seen(cf.max_seqs, 0);
+    kv_len.reserve(rows);
+    for (int i = 0; i < n_seqs; i++) {
+        int s = slots[i], ql = q_lens ? q_lens[i] : 1;
+        if (ql <= 0) return vx_fail(c, VX_E_BAD_ARG, "q_len[%d] = %d", i, ql);
+        if (seen[s]) return vx_fail(c, VX_E_BAD_ARG, "sequence appears twice in one step");
+        seen[s] = 1;
+        if (positions[i] != m->h_seq_len[s])
+            return vx_fail(c, VX_E_BAD_ARG, "position %d of batch entry %d != sequence length %d", positions[i], i, m->h_seq_len[s]);
+        int nb_new = (positions[i] + ql + BS - 1) / BS;
+        if (nb_new > cf.max_blocks_per_seq) return vx_fail(c, VX_E_OOM_BLOCKS, "sequence would need %d blocks (table width %d)", nb_new, cf.max_blocks_per_seq);
+        need += std::max(0, nb_new - m->h_n_blocks[s]);
+        for (int j = 0; j < ql; j++) kv_len.push_back(positions[i] + j + 1);
+    }
+    if (need > m->h_free) return vx_fail(c, VX_E_OOM_BLOCKS, "no free blocks: need %ld, have %d (max=%d)", need, m->h_free, cf.max_blocks);
+    kv_start0.assign(rows, 0); kv_start1.assign(rows, 0);
+    if (cf.sliding_window > 0) for (int t = 0; t < rows; t++) kv_start1[t] = std::max(0, kv_len[t] - cf.sliding_window);
+    int chunk[2] = {4, 4}, n_work[2] = {0, 0};
+    n_work[0] = plan_chunks(m, kv_start0, kv_len, &chunk[0]);
+    if (cf.sliding_window > 0) n_work[1] = plan_chunks(m, kv_start1, kv_len, &chunk[1]);
+
+    int32_t *h = m->h_step_in;
+    for (int i = 0; i < n_seqs; i++) { h[i] = slots[i]; h[n_seqs + i] = q_lens ? q_lens[i] : 1; h[2 * n_seqs + i] = positions[i]; }
+    memcpy(h + 3 * n_seqs, tokens, sizeof(int32_t) * rows);
+    VX_CUDA(c, cudaMemcpyAsync(m->d_step_in, h, sizeof(int32_t) * (3 * n_seqs + rows), cudaMemcpyHostToDevice, c->stream));
+    m->last_rows = rows; m->last_seqs = n_seqs;
+    PackArgs pa{};
+    pa.step_in = m->d_step_in; pa.n_seqs = n_seqs; pa.n_rows = rows;
+    pa.tables = m->d_tables; pa.width = cf.max_blocks_per_seq; pa.seq_len = m->d_seq_len; pa.n_blocks = m->d_n_blocks;
+    pa.free_list = m->d_free_list; pa.free_top = m->d_free_top; pa.refcnt = m->d_refcnt; pa.status = m->d_status;
+    pa.cu = m->d_cu; pa.row_slot = m->d_row_slot; pa.row_pos = m->d_row_pos; pa.slot_map = m->d_slot_map;
+    pa.row_kv_len = m->d_row_kv_len; pa.row_kv_start = m->d_row_kv_start; pa.window = cf.sliding_window;
+    pa.work0 = m->d_work[0]; pa.work1 = m->d_work[1]; pa.rws0 = m->d_rws[0]; pa.rws1 = m->d_rws[1];
+    pa.n_work0 = m->d_n_work[0]; pa.n_work1 = m->d_n_work[1]; pa.chunk0 = chunk[0]; pa.chunk1 = chunk[1]; pa.max_work = MAX_WORK;
+    pack_kernel<<<1, 1024, 0, c->stream>>>(pa);
+    VX_LAUNCH_CHECK(c);
+    // mirror the bookkeeping on the host
+    for (int i = 0; i < n_seqs; i++) {
+        int s = slots[i], ql = q_lens ? q_lens[i] : 1;
+        int nb_new = (positions[i] + ql + BS - 1) / BS;
+        if (nb_new > m->h_n_blocks[s]) { m->h_free -= nb_new - m->h_n_blocks[s]; m->h_n_blocks[s] = nb_new; }
+        m->h_seq_len[s] = positions[i] + ql;
+    }
+    if (m->capture_on) m->capture_rows = rows;
+    int logit_rows = logit_rows_req > 0 ? logit_rows_req : rows;
+    VX_TRY(forward(m, rows, mode, n_work, logit_rows));
+    if (logits && cf.final_softcap > 0.f) {
+        long n = (long)logit_rows * cf.vocab;
+        final_softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(m->logits, n, cf.final_softcap);
+        VX_LAUNCH_CHECK(c);
+    }
+    VX_CUDA(c, cudaMemcpyAsync(m->h_out_tok, m->d_out_tok, sizeof(int32_t) * logit_rows, cudaMemcpyDeviceToHost, c->stream));
+    if (logits) VX_CUDA(c, cudaMemcpyAsync(logits, m->logits, sizeof(float) * (size_t)logit_rows * cf.vocab, cudaMemcpyDeviceToHost, c->stream));
+    VX_TRY(check_status(m));   // synchronises the stream
+    time_collect(m);
+    if (out_tokens) memcpy(out_tokens, m->h_out_tok, sizeof(int32_t) * logit_rows);
+    m->steps++;
+    return VX_OK;
+}
+
+int get_slot(vx_model *m, int64_t id, bool create, int *slot) {
+    auto it = m->seq_slot.find(id);
+    if (it != m->seq_slot.end()) { *slot = it->second; return VX_OK; }
+    if (!create) return vx_fail(m->c, VX_E_NO_SEQ, "sequence %lld not found", (long long)id);
+    if (m->free_slots.empty()) return vx_fail(m->c, VX_E_OOM, "all %d sequence slots are in use", m->cfg.max_seqs);
+    int s = m->free_slots.back(); m->free_slots.pop_back();
+    m->seq_slot[id] = s; m->h_seq_len[s] = 0; m->h_n_blocks[s] = 0;
+    // device state of a free slot is already zero (reset by delete / creation)
+    *slot = s;
+    return VX_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int vx_model_create(vx_ctx *c, const vx_model_config *cfg, vx_model **out) {
+    if (!c || !cfg || !out) return VX_E_BAD_ARG;
+    VxGuard g(c);
+    *out = nullptr;
+    VX_REQUIRE(c, cfg->n_layers > 0 && cfg->hidden > 0 && cfg->n_heads > 0 && cfg->n_kv_heads > 0 && cfg->head_dim > 0 && cfg->ffn > 0 && cfg->vocab > 0, "non-positive dimension");
+    VX_REQUIRE(c, cfg->n_heads % cfg->n_kv_heads == 0, "n_heads must be a multiple of n_kv_heads");
+    VX_REQUIRE(c, cfg->head_dim % 8 == 0 && cfg->head_dim <= 256, "head_dim must be a multiple of 8, at most 256");
+    VX_REQUIRE(c, cfg->hidden % 32 == 0 && cfg->ffn % 32 == 0, "hidden and ffn must be multiples of 32");
+    VX_REQUIRE(c, cfg->max_blocks > 0 && cfg->max_seqs > 0 && cfg->max_batch_tokens > 0 && cfg->max_blocks_per_seq > 0, "non-positive pool limits");
+    vx_model *m = new vx_model();
+    m->c = c; m->cfg = *cfg;
+    m->raw.resize((size_t)cfg->n_layers * VX_W_PER_LAYER + 3);
+    m->layers.resize(cfg->n_layers);
+    auto fail = [&](int rc) { vx_model_destroy(m); return rc; };
+    const int T = cfg->max_batch_tokens, H = cfg->hidden, D = cfg->head_dim, F = cfg->ffn;
+    const int qd = cfg->n_heads * D, kvd = cfg->n_kv_heads * D, nqkv = qd + 2 * kvd;
+    int rc;
+#define MA(expr) if ((rc = (expr)) != VX_OK) return fail(rc)
+    // ---- pool: [layer][block][K|V][16][Hkv][D] fp16, zero-filled so every byte is a finite fp16
+    m->layer_stride = (size_t)cfg->max_blocks * 2 * BS * kvd;
+    MA(model_alloc_t(m, m->layer_stride * cfg->n_layers, &m->pool));
+    if (cudaMemsetAsync(m->pool, 0, m->layer_stride * cfg->n_layers * sizeof(__half), c->stream) != cudaSuccess) return fail(VX_E_CUDA);
+    MA(model_alloc_t(m, (size_t)cfg->max_seqs * cfg->max_blocks_per_seq, &m->d_tables));
+    MA(model_alloc_t(m, (size_t)cfg->max_seqs, &m->d_table_ptrs));
+    MA(model_alloc_t(m, (size_t)cfg->max_seqs, &m->d_seq_len));
+    MA(model_alloc_t(m, (size_t)cfg->max_seqs, &m->d_n_blocks));
+    MA(model_alloc_t(m, (size_t)cfg->max_blocks, &m->d_free_list));
+    MA(model_alloc_t(m, (size_t)cfg->max_blocks, &m->d_refcnt));
+    MA(model_alloc_t(m, 4, &m->d_free_top));
+    MA(model_alloc_t(m, 4, &m->d_status));
+    cudaMemsetAsync(m->d_tables, 0, sizeof(int32_t) * (size_t)cfg->max_seqs * cfg->max_blocks_per_seq, c->stream);
+    cudaMemsetAsync(m->d_seq_len, 0, sizeof(int32_t) * cfg->max_seqs, c->stream);
+    cudaMemsetAsync(m->d_n_blocks, 0, sizeof(int32_t) * cfg->max_seqs, c->stream);
+    cudaMemsetAsync(m->d_refcnt, 0, sizeof(int32_t) * cfg->max_blocks, c->stream);
+    cudaMemsetAsync(m->d_status, 0, 16, c->stream);
+    init_free_list_kernel<<<ceil_div(cfg->max_blocks, 256), 256, 0, c->stream>>>(m->d_free_list, cfg->max_blocks);
+    init_table_ptrs_kernel<<<ceil_div(cfg->max_seqs, 256), 256, 0, c->stream>>>(m->d_table_ptrs, m->d_tables, cfg->max_blocks_per_seq, cfg->max_seqs);
+    cudaMemcpyAsync(m->d_free_top, &cfg->max_blocks, 4, cudaMemcpyHostToDevice, c->stream);
+    m->h_free = cfg->max_blocks;
+    m->h_seq_len.assign(cfg->max_seqs, 0); m->h_n_blocks.assign(cfg->max_seqs, 0);
+    for (int s = cfg->max_seqs - 1; s >= 0; s--) m->free_slots.push_back(s);
+    // ---- step buffers
+    const size_t step_ints = (size_t)3 * cfg->max_seqs + T;
+    MA(model_alloc_t(m, step_ints, &m->d_step_in));
+    if (cudaMallocHost(&m->h_step_in, step_ints * 4) != cudaSuccess || cudaMallocHost(&m->h_out_tok, (size_t)(T + 8) * 4) != cudaSuccess) return fail(VX_E_OOM);
+    MA(model_alloc_t(m, (size_t)cfg->max_seqs + 1, &m->d_cu));
+    MA(model_alloc_t(m, (size_t)T, &m->d_row_slot)); MA(model_alloc_t(m, (size_t)T, &m->d_row_pos));
+    MA(model_alloc_t(m, (size_t)T, &m->d_slot_map)); MA(model_alloc_t(m, (size_t)T, &m->d_row_kv_len));
+    MA(model_alloc_t(m, (size_t)std::max(T, cfg->max_seqs), &m->d_row_kv_start));
+    for (int i = 0; i < 2; i++) {
+        MA(model_alloc_t(m, (size_t)MAX_WORK, &m->d_work[i]));
+        MA(model_alloc_t(m, (size_t)T + 1, &m->d_rws[i]));
+        MA(model_alloc_t(m, 4, &m->d_n_work[i]));
+    }
+    // partials: rows cut into >1 chunk only exist when contexts are long; size for the planner's worst case
+    {
+        size_t max_items = std::min<size_t>(MAX_WORK, (size_t)T * ((size_t)ceil_div(cfg->max_blocks_per_seq, 4) + 1));
+        MA(model_alloc_t(m, max_items * cfg->n_heads * (D + 2), &m->d_partials));
+    }
+    MA(model_alloc_t(m, (size_t)T * (D / 2), &m->d_cos)); MA(model_alloc_t(m, (size_t)T * (D / 2), &m->d_sin));
+    MA(model_alloc_t(m, (size_t)(D / 2), &m->d_freq));
+    {
+        std::vector<float> fr(D / 2);   // backend/cpu/cpu.go:253-254
+        for (int j = 0; j < D / 2; j++) fr[j] = (float)(1.0 / pow((double)cfg->rope_theta, (double)(2 * j) / (double)D));
+        cudaMemcpyAsync(m->d_freq, fr.data(), sizeof(float) * fr.size(), cudaMemcpyHostToDevice, c->stream);
+        cudaStreamSynchronize(c->stream);
+    }
+    MA(model_alloc_t(m, (size_t)T * H, &m->x)); MA(model_alloc_t(m, (size_t)T * nqkv, &m->qkv));
+    MA(model_alloc_t(m, (size_t)T * qd, &m->attn)); MA(model_alloc_t(m, (size_t)T * 2 * F, &m->h13));
+    MA(model_alloc_t(m, (size_t)T * F, &m->act)); MA(model_alloc_t(m, (size_t)T * cfg->vocab, &m->logits));
+    m->parts_cap = (size_t)MAX_PARTS * T * std::max(std::max(H, nqkv), 2 * F);
+    MA(model_alloc_t(m, m->parts_cap, &m->parts));
+    MA(model_alloc_t(m, (size_t)T, &m->d_out_tok));
+    auto mk_split = [&](int k, VxSplit *s) {
+        size_t hi, lo, so, bo; int kp;
+        size_t bytes = vxq_split_bytes(T, k, &hi, &lo, &so, &bo, &kp);
+        void *p; int r = model_alloc(m, bytes, &p); if (r != VX_OK) return r;
+        cudaMemsetAsync(p, 0, bytes, c->stream);
+        char *b = (char *)p;
+        *s = VxSplit{(__half *)(b + hi), (__half *)(b + lo), (float *)(b + so), (float *)(b + bo), kp};
+        return (int)VX_OK;
+    };
+    MA(mk_split(H, &m->sp_h)); MA(mk_split(qd, &m->sp_q)); MA(mk_split(F, &m->sp_f));
+#undef MA
+    if (cudaStreamSynchronize(c->stream) != cudaSuccess) return fail(VX_E_CUDA);
+    *out = m;
+    return VX_OK;
+}
+
+int vx_model_destroy(vx_model *m) {
+    if (!m) return VX_E_BAD_ARG;
+    VxGuard g(m->c);
+    cudaStreamSynchronize(m->c->stream);
+    for (void *p : m->owned) cudaFree(p);
+    for (auto &r : m->raw) if (r.dev) cudaFree(r.dev);
+    if (m->h_step_in) cudaFreeHost(m->h_step_in);
+    if (m->h_out_tok) cudaFreeHost(m->h_out_tok);
+    for (auto e : m->ev_pool) cudaEventDestroy(e);
+    delete m;
+    return VX_OK;
+}
+
+int vx_model_set_tensor(vx_model *m, int layer, int slot, int type, const void *data, size_t bytes, int on_device) {
+    if (!m) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    VX_REQUIRE(c, !m->finalized, "model already finalized");
+    VX_REQUIRE(c, data != nullptr, "nil tensor data");
+    int n, k; size_t idx;
+    if (layer < 0) {
+        VX_REQUIRE(c, slot >= 0 && slot < 3, "bad global slot");
+        n = slot == VX_G_FINAL_NORM ? 1 : m->cfg.vocab; k = m->cfg.hidden;
+        idx = (size_t)m->cfg.n_layers * VX_W_PER_LAYER + slot;
+    } else {
+        VX_REQUIRE(c, layer < m->cfg.n_layers && slot >= 0 && slot < VX_W_PER_LAYER, "bad layer/slot");
+        slot_dims(m->cfg, slot, &n, &k);
+        idx = (size_t)layer * VX_W_PER_LAYER + slot;
+    }
+    size_t want = type_row_bytes(type, k) * (size_t)n;
+    if (want == 0) return vx_fail(c, VX_E_UNSUPPORTED, "unsupported GGUF tensor type %d", type);
+    if (bytes != want) return vx_fail(c, VX_E_BAD_ARG, "tensor (layer %d slot %d type %d) has %zu bytes, expected %zu", layer, slot, type, bytes, want);
+    RawTensor &r = m->raw[idx];
+    if (r.dev) { cudaFree(r.dev); r.dev = nullptr; }
+    cudaError_t e = cudaMalloc(&r.dev, bytes);
+    if (e != cudaSuccess) { cudaGetLastError(); return vx_fail(c, VX_E_OOM, "cudaMalloc(%zu) for weights failed", bytes); }
+    VX_CUDA(c, cudaMemcpyAsync(r.dev, data, bytes, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, c->stream));
+    VX_CUDA(c, cudaStreamSynchronize(c->stream));
+    r.type = type; r.bytes = bytes;
+    return VX_OK;
+}
+
+// Repacks the projection matrices for the MMA kernel, concatenating Wq|Wk|Wv and W1|W3 row-wise
+// (rows are independent in the GGUF row-major block layout), and releases the raw copies.
+int vx_model_finalize(vx_model *m) {
+    if (!m) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    VX_REQUIRE(c, !m->finalized, "model already finalized");
+    const vx_model_config &cf = m->cfg;
+    auto raw_at = [&](int layer, int slot) -> RawTensor & { return m->raw[(size_t)layer * VX_W_PER_LAYER + slot]; };
+    auto norm_f32 = [&](RawTensor &r, float **dst) -> int {
+        if (!r.dev) { *dst = nullptr; return VX_OK; }
+        if (r.type != VX_T_F32) return vx_fail(c, VX_E_UNSUPPORTED, "norm weights must be F32 (got type %d)", r.type);
+        *dst = (float *)r.dev; m->owned.push_back(r.dev); r.dev = nullptr;   // ownership moves to the model
+        return VX_OK;
+    };
+    // concatenated repack of up to three row groups sharing k
+    auto build = [&](std::initializer_list<RawTensor *> srcs, std::initializer_list<int> ns, int k, VxWeight *w) -> int {
+        int n_total = 0;
+        for (int n : ns) n_total += n;
+        for (RawTensor *r : srcs) {
+            if (!r->dev) return vx_fail(c, VX_E_BAD_ARG, "a projection tensor was never set");
+            if (r->type != VX_T_Q4_0) return vx_fail(c, VX_E_UNSUPPORTED, "projection type %d: only Q4_0 has a device kernel", r->type);
+        }
+        size_t qsb, scb;
+        size_t bytes = vxq_repack_bytes(VX_T_Q4_0, n_total, k, &qsb, &scb);
+        void *p; VX_TRY(model_alloc(m, bytes, &p));
+        char *qs = (char *)p, *sc = (char *)p + qsb;
+        int k_groups = ceil_div(k, 128), row = 0; size_t gg = 0;
+        auto it_n = ns.begin();
+        for (RawTensor *r : srcs) {
+            VxWeight tmp;
+            VX_TRY(vxq_repack(c, VX_T_Q4_0, r->dev, *it_n, k, &tmp, qs + (size_t)row * k_groups * 64, sc + (size_t)row * k_groups * 4 * sizeof(__half)));
+            gg += tmp.bytes; row += *it_n; ++it_n;
+        }
+        w->type = VX_T_Q4_0; w->n = n_total; w->k = k; w->k_pad = k_groups * 128; w->qs = qs; w->sc = sc; w->bytes = gg;
+        m->weight_bytes += gg;
+        VX_CUDA(c, cudaStreamSynchronize(c->stream));
+        for (RawTensor *r : srcs) { cudaFree(r->dev); r->dev = nullptr; }
+        return VX_OK;
+    };
+    const int qd = cf.n_heads * cf.head_dim, kvd = cf.n_kv_heads * cf.head_dim;
+    for (int l = 0; l < cf.n_layers; l++) {
+        LayerW &L = m->layers[l];
+        VX_TRY(norm_f32(raw_at(l, VX_W_ATTN_NORM), &L.attn_norm));
+        VX_TRY(norm_f32(raw_at(l, VX_W_FFN_NORM), &L.ffn_norm));
+        VX_TRY(norm_f32(raw_at(l, VX_W_POST_ATTN_NORM), &L.post_attn_norm));
+        VX_TRY(norm_f32(raw_at(l, VX_W_POST_FFN_NORM), &L.post_ffn_norm));
+        VX_REQUIRE(c, L.attn_norm && L.ffn_norm, "attn_norm / ffn_norm missing");
+        if (cf.post_norms) VX_REQUIRE(c, L.post_attn_norm && L.post_ffn_norm, "post norms missing");
+        VX_TRY(build({&raw_at(l, VX_W_WQ), &raw_at(l, VX_W_WK), &raw_at(l, VX_W_WV)}, {qd, kvd, kvd}, cf.hidden, &L.wqkv));
+        VX_TRY(build({&raw_at(l, VX_W_WO)}, {cf.hidden}, qd, &L.wo));
+        VX_TRY(build({&raw_at(l, VX_W_W1), &raw_at(l, VX_W_W3)}, {cf.ffn, cf.ffn}, cf.hidden, &L.w13));
+        VX_TRY(build({&raw_at(l, VX_W_W2)}, {cf.hidden}, cf.ffn, &L.w2));
+        m->weight_bytes += (size_t)cf.hidden * 4 * (cf.post_norms ? 4 : 2);
+    }
+    size_t gi = (size_t)cf.n_layers * VX_W_PER_LAYER;
+    RawTensor &emb = m->raw[gi + VX_G_EMBED], &fn = m->raw[gi + VX_G_FINAL_NORM], &outw = m->raw[gi + VX_G_OUTPUT];
+    VX_REQUIRE(c, emb.dev && fn.dev, "token embedding / final norm missing");
+    VX_REQUIRE(c, emb.type == VX_T_Q4_0 || emb.type == VX_T_F32, "token embedding must be Q4_0 or F32");
+    VX_TRY(norm_f32(fn, &m->final_norm));
+    m->weight_bytes += (size_t)cf.hidden * 4;
+    if (outw.dev) {
+        VX_TRY(build({&outw}, {cf.vocab}, cf.hidden, &m->w_out));
+    } else {   // tied output head (runtime/loader.go:596-600)
+        VX_REQUIRE(c, emb.type == VX_T_Q4_0, "tied output head needs a Q4_0 embedding");
+        RawTensor copy = emb;
+        void *dup; VX_CUDA(c, cudaMalloc(&dup, emb.bytes));
+        VX_CUDA(c, cudaMemcpyAsync(dup, emb.dev, emb.bytes, cudaMemcpyDeviceToDevice, c->stream));
+        copy.dev = dup;
+        VX_TRY(build({&copy}, {cf.vocab}, cf.hidden, &m->w_out));
+    }
+    m->embed = emb; m->owned.push_back(emb.dev); emb.dev = nullptr;
+    m->finalized = true;
+    return VX_OK;
+}
+
+int vx_seq_create(vx_model *m, int64_t id) {
+    if (!m) return VX_E_BAD_ARG;
+    VxGuard g(m->c);
+    if (m->seq_slot.count(id)) {   // re-creating an id starts it from empty; its blocks go back to the pool
+        VX_TRY(vx_seq_truncate(m, id, 0));
+        return VX_OK;
+    }
+    int s;
+    return get_slot(m, id, true, &s);
+}
+
+int vx_seq_delete(vx_model *m, int64_t id) {
+    if (!m) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    auto it = m->seq_slot.find(id);
+    if (it == m->seq_slot.end()) return VX_OK;   // unknown ids are ignored (runtime/gpu_block_pool.go:144-147)
+    int s = it->second;
+    seq_release_kernel<<<1, 1, 0, c->stream>>>(m->d_tables, m->cfg.max_blocks_per_seq, m->d_n_blocks, m->d_seq_len, m->d_free_list,
+                                               m->d_free_top, m->d_refcnt, s, 0, 0);
+    VX_LAUNCH_CHECK(c);
+    m->seq_slot.erase(it); m->free_slots.push_back(s);
+    m->h_seq_len[s] = 0; m->h_n_blocks[s] = 0;
+    return refresh_free(m);
+}
+
+int vx_seq_truncate(vx_model *m, int64_t id, int new_len) {
+    if (!m) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    auto it = m->seq_slot.find(id);
+    if (it == m->seq_slot.end()) return VX_OK;                          // runtime/gpu_block_pool.go:169-172
+    int s = it->second;
+    if (new_len < 0 || new_len >= m->h_seq_len[s]) return VX_OK;
+    int keep = new_len > 0 ? (new_len - 1) / BS + 1 : 0;
+    seq_release_kernel<<<1, 1, 0, c->stream>>>(m->d_tables, m->cfg.max_blocks_per_seq, m->d_n_blocks, m->d_seq_len, m->d_free_list,
+                                               m->d_free_top, m->d_refcnt, s, keep, new_len);
+    VX_LAUNCH_CHECK(c);
+    m->h_seq_len[s] = new_len; m->h_n_blocks[s] = std::min(m->h_n_blocks[s], keep);
+    return refresh_free(m);
+}
+
+int vx_seq_share(vx_model *m, int64_t src, int64_t dst, int n_tokens) {
+    if (!m) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    int a, b;
+    VX_TRY(get_slot(m, src, false, &a));
+    VX_TRY(get_slot(m, dst, false, &b));
+    int nb = (n_tokens + BS - 1) / BS;
+    if (nb > m->h_n_blocks[a]) return vx_fail(c, VX_E_BAD_ARG, "source seq has %d blocks, need %d", m->h_n_blocks[a], nb);
+    if (m->h_n_blocks[b] + nb > m->cfg.max_blocks_per_seq) return vx_fail(c, VX_E_OOM_BLOCKS, "destination block table is full");
+    seq_share_kernel<<<1, 1, 0, c->stream>>>(m->d_tables, m->cfg.max_blocks_per_seq, m->d_n_blocks, m->d_seq_len, m->d_refcnt, a, b, nb, n_tokens);
+    VX_LAUNCH_CHECK(c);
+    m->h_n_blocks[b] += nb;
+    if (n_tokens > m->h_seq_len[b]) m->h_seq_len[b] = n_tokens;
+    return VX_OK;
+}
+
+int vx_seq_len(vx_model *m, int64_t id, int *out_len) {
+    if (!m || !out_len) return VX_E_BAD_ARG;
+    VxGuard g(m->c);
+    int s;
+    VX_TRY(get_slot(m, id, false, &s));
+    *out_len = m->h_seq_len[s];
+    return VX_OK;
+}
+
+int vx_seq_block_table(vx_model *m, int64_t id, int32_t *out, int cap, int *out_n) {
+    if (!m || !out_n) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    int s;
+    VX_TRY(get_slot(m, id, false, &s));
+    int32_t nb = 0;
+    VX_CUDA(c, cudaMemcpyAsync(&nb, m->d_n_blocks + s, 4, cudaMemcpyDeviceToHost, c->stream));
+    VX_CUDA(c, cudaStreamSynchronize(c->stream));
+    *out_n = nb;
+    int n = std::min(nb, cap);
+    if (out && n > 0) {
+        VX_CUDA(c, cudaMemcpyAsync(out, m->d_tables + (size_t)s * m->cfg.max_blocks_per_seq, 4 * (size_t)n, cudaMemcpyDeviceToHost, c->stream));
+        VX_CUDA(c, cudaStreamSynchronize(c->stream));
+    }
+    return VX_OK;
+}
+
+int vx_pool_stats(vx_model *m, int *total, int *free_blocks, int *shared) {
+    if (!m) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    VX_TRY(refresh_free(m));
+    // every layer's pool evolves identically, so totals are per-layer counts times n_layers (gpu_block_pool.go:610-625)
+    if (total) *total = m->cfg.max_blocks * m->cfg.n_layers;
+    if (free_blocks) *free_blocks = m->h_free * m->cfg.n_layers;
+    if (shared) {
+        std::vector<int32_t> rc(m->cfg.max_blocks);
+        VX_CUDA(c, cudaMemcpy(rc.data(), m->d_refcnt, 4 * rc.size(), cudaMemcpyDeviceToHost));
+        int n = 0;
+        for (int v : rc) n += v > 1;
+        *shared = n * m->cfg.n_layers;
+    }
+    return VX_OK;
+}
+
+int vx_pool_layer_ptr(vx_model *m, int layer, vx_dptr *out, size_t *bytes) {
+    if (!m || !out || layer < 0 || layer >= m->cfg.n_layers) return VX_E_BAD_ARG;
+    *out = (vx_dptr)(uintptr_t)(m->pool + (size_t)layer * m->layer_stride);
+    if (bytes) *bytes = m->layer_stride * sizeof(__half);
+    return VX_OK;
+}
+
+int vx_pool_shuffle_free_list(vx_model *m, uint32_t seed) {
+    if (!m) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    VX_REQUIRE(c, m->seq_slot.empty() && m->h_free == m->cfg.max_blocks, "the free list can only be shuffled while no sequence holds blocks");
+    int32_t *tmp;
+    VX_CUDA(c, cudaMalloc(&tmp, sizeof(int32_t) * m->cfg.max_blocks));
+    shuffle_free_list_kernel<<<std::min(1024, ceil_div(m->cfg.max_blocks, 128)), 128, 0, c->stream>>>(m->d_free_list, tmp, m->cfg.max_blocks, seed);
+    cudaMemcpyAsync(m->d_free_list, tmp, sizeof(int32_t) * m->cfg.max_blocks, cudaMemcpyDeviceToDevice, c->stream);
+    cudaError_t e = cudaStreamSynchronize(c->stream);
+    cudaFree(tmp);
+    if (e != cudaSuccess) return vx_cuda_fail(c, e, "shuffle free list");
+    return VX_OK;
+}
+
+int vx_seq_fill_synthetic(vx_model *m, int64_t id, int len, uint32_t seed) {
+    if (!m) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    int s;
+    VX_TRY(get_slot(m, id, true, &s));
+    VX_REQUIRE(c, len > 0 && len >= m->h_seq_len[s], "length must grow");
+    int nb = (len + BS - 1) / BS;
+    if (nb > m->cfg.max_blocks_per_seq || nb - m->h_n_blocks[s] > m->h_free) return vx_fail(c, VX_E_OOM_BLOCKS, "not enough free blocks for %d tokens", len);
+    seq_grow_kernel<<<1, 1, 0, c->stream>>>(m->d_tables, m->cfg.max_blocks_per_seq, m->d_n_blocks, m->d_seq_len, m->d_free_list, m->d_free_top,
+                                            m->d_refcnt, s, len, m->d_status);
+    VX_LAUNCH_CHECK(c);
+    m->h_free -= nb - m->h_n_blocks[s]; m->h_n_blocks[s] = nb; m->h_seq_len[s] = len;
+    int hs = m->cfg.n_kv_heads * m->cfg.head_dim;
+    fill_noise_kernel<<<c->sm_count * 8, 256, 0, c->stream>>>(m->pool, m->layer_stride, m->cfg.n_layers,
+                                                              m->d_tables + (size_t)s * m->cfg.max_blocks_per_seq, len, hs, seed);
+    VX_LAUNCH_CHECK(c);
+    return check_status(m);
+}
+
+int vx_decode_step(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t *tokens, const int32_t *positions,
+                   const int32_t *q_lens, int32_t *out_tokens, float *logits) {
+    if (!m) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    VX_REQUIRE(c, m->finalized, "model not finalized");
+    VX_REQUIRE(c, n_seqs > 0 && n_seqs <= m->cfg.max_seqs && seq_ids && tokens && positions, "bad arguments");
+    std::vector<int> slots(n_seqs);
+    for (int i = 0; i < n_seqs; i++) VX_TRY(get_slot(m, seq_ids[i], true, &slots[i]));   // created on first use (runtime/decode.go:362-364)
+    return run_step(m, n_seqs, slots.data(), tokens, positions, q_lens, 0, 0, out_tokens, logits);
+}
+
+int vx_prefill(vx_model *m, int64_t id, const int32_t *tokens, int n_tokens, int start_pos, int32_t *out_token, float *logits) {
+    if (!m) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    VX_REQUIRE(c, m->finalized, "model not finalized");
+    VX_REQUIRE(c, tokens && n_tokens > 0 && start_pos >= 0, "bad arguments");
+    int slot;
+    VX_TRY(get_slot(m, id, true, &slot));
+    const int T = m->cfg.max_batch_tokens;
+    int done = 0;
+    while (done < n_tokens) {
+        int n = std::min(T, n_tokens - done);
+        int pos = start_pos + done, ql = n;
+        bool last = done + n == n_tokens;
+        // the first chunk of a prompt that starts at 0 attends over its own float32 K/V (SDPAPrefill);
+        // later chunks read the paged fp16 cache like the multi-query verify path
+        int mode = (pos == 0) ? 1 : 0;
+        VX_TRY(run_step(m, 1, &slot, tokens + done, &pos, &ql, mode, 1, last ? out_token : nullptr, last ? logits : nullptr));
+        done += n;
+    }
+    return VX_OK;
+}
+
+int vx_model_set_capture(vx_model *m, int enable) {
+    if (!m) return VX_E_BAD_ARG;
+    VxGuard g(m->c);
+    if (enable && !m->capture) {
+        size_t n = (size_t)(m->cfg.n_layers + 1) * m->cfg.max_batch_tokens * m->cfg.hidden;
+        VX_TRY(model_alloc_t(m, n, &m->capture));
+    }
+    m->capture_on = enable != 0;
+    return VX_OK;
+}
+
+int vx_model_get_capture(vx_model *m, float *host_out, size_t n_floats) {
+    if (!m || !host_out) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    VX_REQUIRE(c, m->capture != nullptr, "capture was never enabled");
+    size_t have = (size_t)(m->cfg.n_layers + 1) * m->capture_rows * m->cfg.hidden;
+    VX_REQUIRE(c, n_floats >= have, "capture buffer too small");
+    VX_CUDA(c, cudaMemcpyAsync(host_out, m->capture, have * 4, cudaMemcpyDeviceToHost, c->stream));
+    VX_CUDA(c, cudaStreamSynchronize(c->stream));
+    return VX_OK;
+}
+
+int vx_model_get_packing(vx_model *m, int32_t *cu, int32_t *slot_map, int32_t *row_kv_len, int n_seqs, int n_rows) {
+    if (!m) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    VX_REQUIRE(c, n_seqs == m->last_seqs && n_rows == m->last_rows, "shape does not match the last step");
+    if (cu) VX_CUDA(c, cudaMemcpyAsync(cu, m->d_cu, 4 * (size_t)(n_seqs + 1), cudaMemcpyDeviceToHost, c->stream));
+    if (slot_map) VX_CUDA(c, cudaMemcpyAsync(slot_map, m->d_slot_map, 4 * (size_t)n_rows, cudaMemcpyDeviceToHost, c->stream));
+    if (row_kv_len) VX_CUDA(c, cudaMemcpyAsync(row_kv_len, m->d_row_kv_len, 4 * (size_t)n_rows, cudaMemcpyDeviceToHost, c->stream));
+    VX_CUDA(c, cudaStreamSynchronize(c->stream));
+    return VX_OK;
+}
+
+int vx_model_counters(vx_model *m, uint64_t *launches, uint64_t *steps) {
+    if (!m) return VX_E_BAD_ARG;
+    if (launches) *launches = m->c->launches;
+    if (steps) *steps = m->steps;
+    return VX_OK;
+}
+
+int vx_model_kernel_time(vx_model *m, int which, int enable, float *ms, uint64_t *launches) {
+    if (!m || which < 0 || which > 1) return VX_E_BAD_ARG;
+    VxGuard g(m->c);
+    if (ms) *ms = m->time_ms[which];
+    if (launches) *launches = m->time_n[which];
+    if (enable >= 0) {
+        if ((enable != 0) != m->time_on[which]) { m->time_ms[which] = 0; m->time_n[which] = 0; }
+        m->time_on[which] = enable != 0;
+    }
+    return VX_OK;
+}
+
+int vx_model_weight_bytes(vx_model *m, uint64_t *bytes) {
+    if (!m || !bytes) return VX_E_BAD_ARG;
+    *bytes = m->weight_bytes;
+    return VX_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,409 @@
+// PagedKVOps (inference/backend/backend.go:415-466): scatter into the block pool and paged decode
+// attention.  Semantics follow the reference's Metal shaders (backend/metal/metal_bridge_darwin.m:
+// 8539-8755, 11074-11311): score = (q.k)*scale, max-subtracted softmax, out = sum w*v, GQA
+// kvHead = qHead / (Hq/Hkv); plus the soft-cap and sliding-window variants the CPU branch applies
+// (runtime/block.go:925-953, backend/cpu/cpu.go:705-767).
+//
+// The decode kernel is a ragged, split-K FlashDecoding pass: a work item is (query row, chunk of pages);
+// a CTA of four warps handles one work item for one KV head, each warp streaming whole 16-token pages
+// with 128-bit loads (a token's head slice is D*2 contiguous bytes), online softmax with warp shuffles,
+// then a four-way merge in shared memory.  Rows cut into several chunks are finished by a merge kernel.
+#include "vx_paged.cuh"
+
+// ------------------------------------------------------------------ scatter (ReshapePagedKV[F16])
+template <typename T>
+__global__ void reshape_paged_kernel(const float *__restrict__ src, T *__restrict__ pool, const int32_t *__restrict__ blk,
+                                     const int32_t *__restrict__ off, int n_tokens, int hs, int block_size, int is_v) {
+    long idx = blockIdx.x * (long)blockDim.x + threadIdx.x;
+    if (idx >= (long)n_tokens * hs) return;
+    int t = (int)(idx / hs), e = (int)(idx % hs);
+    size_t part = (size_t)block_size * hs;
+    size_t dst = (size_t)blk[t] * 2 * part + (is_v ? part : 0) + (size_t)off[t] * hs + e;
+    if (sizeof(T) == 2) reinterpret_cast<__half *>(pool)[dst] = __float2half_rn(src[idx]);   // (half)x, round-to-nearest-even
+    else reinterpret_cast<float *>(pool)[dst] = src[idx];
+}
+
+// ------------------------------------------------------------------ generic paged attention
+// Any block size / head dim <= 256 / pool type.  One CTA (256 threads) per (row, q head).
+__global__ void paged_generic_kernel(VxAttnArgs a) {
+    extern __shared__ float sm[];
+    float *qs = sm, *ps = sm + a.head_dim;
+    __shared__ float red[32];
+    int h = blockIdx.x, row = blockIdx.y, D = a.head_dim;
+    int kvh = h / (a.n_q_heads / a.n_kv_heads);
+    int kv_start = a.row_kv_start ? a.row_kv_start[row] : 0, kv_len = a.row_kv_len[row];
+    const int32_t *table = a.tables[a.row_slot[row]];
+    size_t hs = (size_t)a.n_kv_heads * D, part = (size_t)a.block_size * hs;
+    const float *qh = a.q + (size_t)row * a.q_row_stride + (size_t)h * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = qh[d];
+    __syncthreads();
+    const __half *ph = (const __half *)a.pool; const float *pf = (const float *)a.pool;
+    float m_run = -INFINITY, l_run = 0.f, acc = 0.f;
+    for (int t0 = kv_start; t0 < kv_len; t0 += 256) {
+        int pos = t0 + threadIdx.x;
+        float s = -INFINITY;
+        if (pos < kv_len) {
+            size_t base = (size_t)table[pos / a.block_size] * 2 * part + (size_t)(pos % a.block_size) * hs + (size_t)kvh * D;
+            float dot = 0.f;
+            for (int d = 0; d < D; d++) dot = fmaf(qs[d], a.pool_is_f16 ? __half2float(ph[base + d]) : pf[base + d], dot);
+            s = dot * a.scale;
+            if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+        }
+        float m_new = fmaxf(m_run, block_max(s, red));
+        float p = pos < kv_len ? __expf(s - m_new) : 0.f;
+        float corr = __expf(m_run - m_new);
+        float psum = block_sum(p, red);
+        ps[threadIdx.x] = p;
+        __syncthreads();
+        l_run = l_run * corr + psum;
+        acc *= corr;
+        if (threadIdx.x < D) {
+            int cnt = min(256, kv_len - t0);
+            for (int i = 0; i < cnt; i++) {
+                int pp = t0 + i;
+                size_t base = (size_t)table[pp / a.block_size] * 2 * part + part + (size_t)(pp % a.block_size) * hs + (size_t)kvh * D + threadIdx.x;
+                acc = fmaf(ps[i], a.pool_is_f16 ? __half2float(ph[base]) : pf[base], acc);
+            }
+        }
+        m_run = m_new;
+        __syncthreads();
+    }
+    if (threadIdx.x < D) a.out[(size_t)row * a.out_row_stride + (size_t)h * D + threadIdx.x] = l_run > 0.f ? acc / l_run : 0.f;
+}
+
+// ------------------------------------------------------------------ split-K FlashDecoding kernel (f16 pool, 16-token pages)
+constexpr int ATT_WARPS = 4;
+constexpr int ATT_BS = 16;
+
+__device__ __forceinline__ void unpack8(const uint4 &u, float (&f)[8]) {
+    const __half2 *h = reinterpret_cast<const __half2 *>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; i++) { float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+
+template <int D, int G>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+paged_flash_kernel(VxAttnArgs a) {
+    constexpr int LPT = D / 8;            // lanes per token
+    constexpr int TPW = 32 / LPT;         // tokens per warp-wide load
+    constexpr int NI = ATT_BS / TPW;      // loads per page
+    __shared__ float sm_m[ATT_WARPS][G], sm_l[ATT_WARPS][G];
+    __shared__ __align__(16) float sm_acc[ATT_WARPS][G][D];
+
+    const int wi = blockIdx.x;
+    if (wi >= *a.n_work_dev) return;
+    const int4 item = a.work[wi];
+    const int row = item.x, first_page = item.y, n_pages = item.z;
+    const int kvh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tg = lane / LPT, dl = lane % LPT;
+    const int kv_start = a.row_kv_start ? a.row_kv_start[row] : 0, kv_len = a.row_kv_len[row];
+    const int32_t *table = a.tables[a.row_slot[row]];
+    const size_t hs = (size_t)a.n_kv_heads * D;
+    const __half *pool = (const __half *)a.pool;
+
+    float qf[G][8];
+#pragma unroll
+    for (int gi = 0; gi < G; gi++) {
+        const float *qp = a.q + (size_t)row * a.q_row_stride + (size_t)(kvh * G + gi) * D + dl * 8;
+        float4 q0 = *reinterpret_cast<const float4 *>(qp), q1 = *reinterpret_cast<const float4 *>(qp + 4);
+        qf[gi][0] = q0.x; qf[gi][1] = q0.y; qf[gi][2] = q0.z; qf[gi][3] = q0.w;
+        qf[gi][4] = q1.x; qf[gi][5] = q1.y; qf[gi][6] = q1.z; qf[gi][7] = q1.w;
+    }
+    float m_run[G], l_run[G], acc[G][8];
+#pragma unroll
+    for (int gi = 0; gi < G; gi++) {
+        m_run[gi] = -INFINITY; l_run[gi] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[gi][e] = 0.f;
+    }
+
+    int page = first_page + warp;
+    int blk_next = page < first_page + n_pages ? table[page] : 0;
+    for (; page < first_page + n_pages; page += ATT_WARPS) {
+        const int blk = blk_next;
+        if (page + ATT_WARPS < first_page + n_pages) blk_next = table[page + ATT_WARPS];
+        const __half *kbase = pool + (size_t)blk * 2 * ATT_BS * hs + (size_t)kvh * D + dl * 8;
+        uint4 kr[NI], vr[NI];
+#pragma unroll
+        for (int i = 0; i < NI; i++) {
+            const __half *kp = kbase + (size_t)(i * TPW + tg) * hs;
+            kr[i] = *reinterpret_cast<const uint4 *>(kp);
+            vr[i] = *reinterpret_cast<const uint4 *>(kp + ATT_BS * hs);
+        }
+        float s[NI][G];
+        float pmax[G];
+#pragma unroll
+        for (int gi = 0; gi < G; gi++) pmax[gi] = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < NI; i++) {
+            float kf[8];
+            unpack8(kr[i], kf);
+            const int pos = page * ATT_BS + i * TPW + tg;
+            const bool valid = pos >= kv_start && pos < kv_len;
+#pragma unroll
+            for (int gi = 0; gi < G; gi++) {
+                float d = 0.f;
+#pragma unroll
+                for (int e = 0; e < 8; e++) d = fmaf(qf[gi][e], kf[e], d);
+#pragma unroll
+                for (int o = 1; o < LPT; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                d *= a.scale;
+                if (a.softcap > 0.f) d = a.softcap * tanhf(d / a.softcap);
+                s[i][gi] = valid ? d : -INFINITY;
+                pmax[gi] = fmaxf(pmax[gi], s[i][gi]);
+            }
+        }
+#pragma unroll
+        for (int gi = 0; gi < G; gi++) {
+#pragma unroll
+            for (int o = LPT; o < 32; o <<= 1) pmax[gi] = fmaxf(pmax[gi], __shfl_xor_sync(0xffffffffu, pmax[gi], o));
+            const float m_new = fmaxf(m_run[gi], pmax[gi]);
+            if (m_new == -INFINITY) continue;      // page entirely outside the window (uniform across the warp)
+            const float corr = __expf(m_run[gi] - m_new);
+            l_run[gi] *= corr;
+#pragma unroll
+            for (int e = 0; e < 8; e++) acc[gi][e] *= corr;
+            m_run[gi] = m_new;
+        }
+#pragma unroll
+        for (int i = 0; i < NI; i++) {
+            float vf[8];
+            unpack8(vr[i], vf);
+#pragma unroll
+            for (int gi = 0; gi < G; gi++) {
+                // masked positions have s = -inf -> p = 0; the pool holds only finite fp16 values
+                const float p = (s[i][gi] == -INFINITY) ? 0.f : __expf(s[i][gi] - m_run[gi]);
+                l_run[gi] += p;
+#pragma unroll
+                for (int e = 0; e < 8; e++) acc[gi][e] = fmaf(p, vf[e], acc[gi][e]);
+            }
+        }
+    }
+
+    // combine the token groups of the warp, then the warps of the CTA
+#pragma unroll
+    for (int gi = 0; gi < G; gi++) {
+#pragma unroll
+        for (int o = LPT; o < 32; o <<= 1) {
+            l_run[gi] += __shfl_xor_sync(0xffffffffu, l_run[gi], o);
+#pragma unroll
+            for (int e = 0; e < 8; e++) acc[gi][e] += __shfl_xor_sync(0xffffffffu, acc[gi][e], o);
+        }
+        if (tg == 0) {
+            if (dl == 0) { sm_m[warp][gi] = m_run[gi]; sm_l[warp][gi] = l_run[gi]; }
+            float4 *dst = reinterpret_cast<float4 *>(&sm_acc[warp][gi][dl * 8]);
+            dst[0] = make_float4(acc[gi][0], acc[gi][1], acc[gi][2], acc[gi][3]);
+            dst[1] = make_float4(acc[gi][4], acc[gi][5], acc[gi][6], acc[gi][7]);
+        }
+    }
+    __syncthreads();
+    const bool single = (a.row_work_start[row + 1] - a.row_work_start[row]) == 1;
+    for (int idx = threadIdx.x; idx < G * D; idx += ATT_WARPS * 32) {
+        const int gi = idx / D, d = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++) M = fmaxf(M, sm_m[w][gi]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++) {
+            const float f = sm_m[w][gi] == -INFINITY ? 0.f : __expf(sm_m[w][gi] - M);
+            L = fmaf(sm_l[w][gi], f, L); O = fmaf(sm_acc[w][gi][d], f, O);
+        }
+        const int h = kvh * G + gi;
+        if (single) {
+            a.out[(size_t)row * a.out_row_stride + (size_t)h * D + d] = L > 0.f ? O / L : 0.f;
+        } else {
+            float *part = a.partials + ((size_t)wi * a.n_q_heads + h) * (D + 2);
+            part[d] = O;
+            if (d == 0) { part[D] = M; part[D + 1] = L; }
+        }
+    }
+}
+
+// rows cut into more than one chunk: out = sum_c O_c e^{m_c-M} / sum_c l_c e^{m_c-M}
+__global__ void paged_merge_kernel(VxAttnArgs a) {
+    const int row = blockIdx.y, h = blockIdx.x, D = a.head_dim;
+    const int w0 = a.row_work_start[row], n = a.row_work_start[row + 1] - w0;
+    if (n <= 1) return;
+    float M = -INFINITY;
+    for (int c = 0; c < n; c++) M = fmaxf(M, a.partials[((size_t)(w0 + c) * a.n_q_heads + h) * (D + 2) + D]);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float L = 0.f, O = 0.f;
+        for (int c = 0; c < n; c++) {
+            const float *part = a.partials + ((size_t)(w0 + c) * a.n_q_heads + h) * (D + 2);
+            const float f = part[D] == -INFINITY ? 0.f : __expf(part[D] - M);
+            L = fmaf(part[D + 1], f, L); O = fmaf(part[d], f, O);
+        }
+        a.out[(size_t)row * a.out_row_stride + (size_t)h * D + d] = L > 0.f ? O / L : 0.f;
+    }
+}
+
+template <int D>
+static int flash_launch_g(vx_ctx *c, const VxAttnArgs &a, int G) {
+    dim3 grid(a.n_work, a.n_kv_heads);
+    switch (G) {
+    case 1: paged_flash_kernel<D, 1><<<grid, ATT_WARPS * 32, 0, c->stream>>>(a); break;
+    case 2: paged_flash_kernel<D, 2><<<grid, ATT_WARPS * 32, 0, c->stream>>>(a); break;
+    case 4: paged_flash_kernel<D, 4><<<grid, ATT_WARPS * 32, 0, c->stream>>>(a); break;
+    case 8: paged_flash_kernel<D, 8><<<grid, ATT_WARPS * 32, 0, c->stream>>>(a); break;
+    default: return -1;
+    }
+    return 0;
+}
+
+int vxp_attention(vx_ctx *c, const VxAttnArgs &a) {
+    if (a.rows <= 0) return VX_OK;
+    if (a.n_q_heads <= 0 || a.n_kv_heads <= 0 || a.n_q_heads % a.n_kv_heads != 0)
+        return vx_fail(c, VX_E_BAD_ARG, "paged attention: %d q heads over %d kv heads", a.n_q_heads, a.n_kv_heads);
+    if (a.head_dim <= 0 || a.head_dim > 256) return vx_fail(c, VX_E_BAD_ARG, "paged attention: head_dim %d (max 256)", a.head_dim);
+    const int G = a.n_q_heads / a.n_kv_heads, D = a.head_dim;
+    bool fast = a.pool_is_f16 && a.block_size == ATT_BS && (D == 64 || D == 128 || D == 256) &&
+                (G == 1 || G == 2 || G == 4 || G == 8) && a.work != nullptr && a.n_work > 0 && (a.q_row_stride % 4 == 0);
+    if (fast) {
+        int rc = D == 64 ? flash_launch_g<64>(c, a, G) : D == 128 ? flash_launch_g<128>(c, a, G) : flash_launch_g<256>(c, a, G);
+        if (rc == 0) {
+            VX_LAUNCH_CHECK(c);
+            dim3 mg(a.n_q_heads, a.rows);
+            paged_merge_kernel<<<mg, min(D, 256), 0, c->stream>>>(a);
+            VX_LAUNCH_CHECK(c);
+            return VX_OK;
+        }
+    }
+    dim3 grid(a.n_q_heads, a.rows);
+    size_t smem = (size_t)(D + 256) * sizeof(float);
+    paged_generic_kernel<<<grid, 256, smem, c->stream>>>(a);
+    VX_LAUNCH_CHECK(c);
+    return VX_OK;
+}
+
+// ------------------------------------------------------------------ interface-level entry points
+__global__ void iface_build_work_kernel(int rows, const int32_t *kv_start, const int32_t *kv_len, int block_size, int chunk_pages,
+                                        int4 *work, int32_t *row_work_start, int32_t *n_work, int max_work) {
+    __shared__ int tmp[33];
+    __shared__ int ovf;
+    if (threadIdx.x == 0) ovf = 0;
+    __syncthreads();
+    int n = vx_build_work(rows, kv_start, kv_len, block_size, chunk_pages, work, row_work_start, max_work, &ovf, tmp);
+    if (threadIdx.x == 0) *n_work = n;
+}
+
+// Lays out in the context scratch: tables[], row_slot[], kv_start[], kv_len[], row_work_start[], n_work, work[], partials.
+// kv_len_dev != 0: per-row lengths already on the device (multi-query verify); else kv_len_host is uploaded.
+static int paged_iface(vx_ctx *c, vx_dptr q, vx_dptr pool, int pool_is_f16, const vx_dptr *tables, const int *row_slot,
+                       const int *kv_start_host, const int *kv_len_host, vx_dptr kv_len_dev, int max_kv_len, vx_dptr out,
+                       int rows, int n_tables, int block_size, int hq, int hkv, int d, float scale, float softcap) {
+    VX_REQUIRE(c, q && pool && out, "nil device pointer");
+    VX_REQUIRE(c, rows > 0 && block_size > 0 && hq > 0 && hkv > 0 && d > 0 && d <= 256 && hq % hkv == 0, "bad dimensions");
+    int max_pages = ceil_div(max_kv_len, block_size);
+    int chunk_pages = max(4, ceil_div(max_pages * rows * hkv, 4 * c->sm_count));
+    int max_work = rows * ceil_div(max_pages, chunk_pages) + rows;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off += (bytes + 255) & ~(size_t)255; return o; };
+    size_t o_tab = take(sizeof(void *) * n_tables), o_slot = take(4 * rows), o_ks = take(4 * rows), o_kl = take(4 * rows),
+           o_rws = take(4 * (rows + 1)), o_nw = take(4), o_work = take(sizeof(int4) * max_work),
+           o_part = take((size_t)max_work * hq * (d + 2) * 4);
+    void *base;
+    VX_TRY(vx_scratch(c, off, &base));
+    char *p = (char *)base;
+    std::vector<int32_t> ks(rows, 0);
+    if (kv_start_host) for (int i = 0; i < rows; i++) ks[i] = kv_start_host[i];
+    VX_CUDA(c, cudaMemcpyAsync(p + o_tab, tables, sizeof(vx_dptr) * n_tables, cudaMemcpyHostToDevice, c->stream));
+    VX_CUDA(c, cudaMemcpyAsync(p + o_slot, row_slot, 4 * rows, cudaMemcpyHostToDevice, c->stream));
+    VX_CUDA(c, cudaMemcpyAsync(p + o_ks, ks.data(), 4 * rows, cudaMemcpyHostToDevice, c->stream));
+    const int32_t *kl_dev;
+    if (kv_len_dev) kl_dev = dp<int32_t>(kv_len_dev);
+    else { VX_CUDA(c, cudaMemcpyAsync(p + o_kl, kv_len_host, 4 * rows, cudaMemcpyHostToDevice, c->stream)); kl_dev = (const int32_t *)(p + o_kl); }
+    VX_CUDA(c, cudaStreamSynchronize(c->stream));   // host staging arrays go out of scope
+    iface_build_work_kernel<<<1, 256, 0, c->stream>>>(rows, (const int32_t *)(p + o_ks), kl_dev, block_size, chunk_pages,
+                                                      (int4 *)(p + o_work), (int32_t *)(p + o_rws), (int32_t *)(p + o_nw), max_work);
+    VX_LAUNCH_CHECK(c);
+    VxAttnArgs a{};
+    a.q = dp<float>(q); a.q_row_stride = hq * d; a.pool = dp<void>(pool); a.pool_is_f16 = pool_is_f16;
+    a.tables = (const int32_t *const *)(p + o_tab); a.row_slot = (const int32_t *)(p + o_slot);
+    a.row_kv_start = (const int32_t *)(p + o_ks); a.row_kv_len = kl_dev;
+    a.work = (const int4 *)(p + o_work); a.n_work_dev = (const int32_t *)(p + o_nw); a.n_work = max_work;
+    a.row_work_start = (const int32_t *)(p + o_rws); a.partials = (float *)(p + o_part);
+    a.out = dp<float>(out); a.out_row_stride = hq * d;
+    a.rows = rows; a.n_q_heads = hq; a.n_kv_heads = hkv; a.head_dim = d; a.block_size = block_size;
+    a.scale = scale; a.softcap = softcap;
+    return vxp_attention(c, a);
+}
+
+template <typename T>
+static int reshape_launch(vx_ctx *c, vx_dptr src, vx_dptr pool, vx_dptr pt, vx_dptr bo, int n_tokens, int hkv, int d, int bs, int is_v) {
+    if (!c) return VX_E_BAD_ARG;
+    VxGuard g(c);
+    if (n_tokens <= 0) return VX_OK;
+    VX_REQUIRE(c, src && pool && pt && bo && hkv > 0 && d > 0 && bs > 0, "bad arguments");
+    long total = (long)n_tokens * hkv * d;
+    reshape_paged_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, c->stream>>>(dp<float>(src), dp<T>(pool), dp<int32_t>(pt),
+                                                                                   dp<int32_t>(bo), n_tokens, hkv * d, bs, is_v);
+    VX_LAUNCH_CHECK(c);
+    return VX_OK;
+}
+
+extern "C" {
+
+int vx_reshape_paged_kv(vx_ctx *c, vx_dptr src, vx_dptr pool, vx_dptr pt, vx_dptr bo, int n_tokens, int hkv, int d, int bs, int is_v) {
+    return reshape_launch<float>(c, src, pool, pt, bo, n_tokens, hkv, d, bs, is_v);
+}
+int vx_reshape_paged_kv_f16(vx_ctx *c, vx_dptr src, vx_dptr pool, vx_dptr pt, vx_dptr bo, int n_tokens, int hkv, int d, int bs, int is_v) {
+    return reshape_launch<__half>(c, src, pool, pt, bo, n_tokens, hkv, d, bs, is_v);
+}
+
+// kvLen = (numBlocks-1)*blockSize + tokensInLastBlock (backend/metal/metal_bridge_darwin.m:11092-11100)
+static int decode_one(vx_ctx *c, vx_dptr q, vx_dptr pool, int f16, vx_dptr table, vx_dptr out, int n_blocks, int bs, int hq,
+                      int hkv, int d, float scale, int til) {
+    if (!c) return VX_E_BAD_ARG;
+    VxGuard g(c);
+    VX_REQUIRE(c, n_blocks > 0 && til > 0 && til <= bs && table, "bad block table arguments");
+    int kv_len = (n_blocks - 1) * bs + til, slot = 0;
+    return paged_iface(c, q, pool, f16, &table, &slot, nullptr, &kv_len, 0, kv_len, out, 1, 1, bs, hq, hkv, d, scale, 0.f);
+}
+int vx_sdpa_paged_decode(vx_ctx *c, vx_dptr q, vx_dptr pool, vx_dptr table, vx_dptr out, int n_blocks, int bs, int hq, int hkv,
+                         int d, float scale, int til) {
+    return decode_one(c, q, pool, 0, table, out, n_blocks, bs, hq, hkv, d, scale, til);
+}
+int vx_sdpa_paged_decode_f16(vx_ctx *c, vx_dptr q, vx_dptr pool, vx_dptr table, vx_dptr out, int n_blocks, int bs, int hq, int hkv,
+                             int d, float scale, int til) {
+    return decode_one(c, q, pool, 1, table, out, n_blocks, bs, hq, hkv, d, scale, til);
+}
+
+int vx_sdpa_paged_decode_ex(vx_ctx *c, vx_dptr q, vx_dptr pool, vx_dptr table, vx_dptr out, int kv_start, int kv_len, int bs,
+                            int hq, int hkv, int d, float scale, float softcap, int f16) {
+    if (!c) return VX_E_BAD_ARG;
+    VxGuard g(c);
+    VX_REQUIRE(c, table && kv_start >= 0 && kv_len > kv_start, "empty attention range");
+    int slot = 0;
+    return paged_iface(c, q, pool, f16, &table, &slot, &kv_start, &kv_len, 0, kv_len, out, 1, 1, bs, hq, hkv, d, scale, softcap);
+}
+
+// every sequence has its own table pointer and length; queries and outputs are packed [batch][Hq*D]
+int vx_sdpa_paged_decode_batched(vx_ctx *c, vx_dptr q, vx_dptr pool, const vx_dptr *tables, vx_dptr out, int batch,
+                                 int max_blocks, int bs, int hq, int hkv, int d, float scale, const int *seq_lens, int f16) {
+    if (!c) return VX_E_BAD_ARG;
+    VxGuard g(c);
+    VX_REQUIRE(c, batch > 0 && tables && seq_lens && max_blocks > 0, "bad arguments");
+    std::vector<int> slot(batch);
+    int mx = 0;
+    for (int i = 0; i < batch; i++) {
+        slot[i] = i;
+        VX_REQUIRE(c, tables[i] != 0 && seq_lens[i] > 0 && seq_lens[i] <= max_blocks * bs, "sequence length outside its block table");
+        mx = max(mx, seq_lens[i]);
+    }
+    return paged_iface(c, q, pool, f16, tables, slot.data(), nullptr, seq_lens, 0, mx, out, batch, batch, bs, hq, hkv, d, scale, 0.f);
+}
+
+// query i attends positions [0, kvLens[i]) (backend/metal/metal_bridge_darwin.m:11205-11311); kvLens is a device buffer
+int vx_sdpa_paged_decode_multiquery(vx_ctx *c, vx_dptr q, vx_dptr pool, vx_dptr table, vx_dptr out, vx_dptr kv_lens,
+                                    int n_blocks, int bs, int hq, int hkv, int d, float scale, int query_len, int f16) {
+    if (!c) return VX_E_BAD_ARG;
+    VxGuard g(c);
+    VX_REQUIRE(c, table && kv_lens && n_blocks > 0 && query_len > 0, "bad arguments");
+    std::vector<int> slot(query_len, 0);
+    return paged_iface(c, q, pool, f16, &table, slot.data(), nullptr, nullptr, kv_lens, n_blocks * bs, out, query_len, 1, bs, hq, hkv, d,
+                       scale, 0.f);
+}
+
+}  // extern "C"

@@ -1,0 +1,498 @@
+// GGUF block formats on the device: bit-exact dequantisation (inference/pkg/gguf/dequant.go), the
+// repacked weight layout, activation splitting and the dequant-fused tensor-core projection kernel
+// behind QuantizedMatMul (inference/backend/backend.go:47-81).
+//
+// Projection arithmetic.  The reference computes sum_k x[k] * (d_b * float32(q_k - 8)) in float32
+// (inference/backend/cpu/cpu.go:842-911).  Here, per 32-weight block b,
+//     y += d_b * ( sum_{k in b} (q_k - 8) * x_hi[k]  +  sum_{k in b} (q_k - 8) * x_lo[k] )
+// where x = s * (x_hi + x_lo) is an exact-to-2^-22 split of the float32 activation into two fp16
+// numbers (s a per-row power of two).  (q-8) is exact in fp16, the products are exact in the
+// tensor core's float32 accumulator, and d_b is applied in float32 outside the MMA, so the only
+// rounding is float32 accumulation, as in the reference.
+#include "vx_common.cuh"
+
+// ------------------------------------------------------------------ dequantisation (bit-exact)
+__global__ void dequant_q4_0_kernel(const uint8_t *__restrict__ raw, float *__restrict__ out, int64_t n) {
+    int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;   // one thread per packed byte
+    int64_t nb = (n + 31) / 32;
+    if (idx >= nb * 16) return;
+    int64_t b = idx >> 4; int i = (int)(idx & 15);
+    const uint8_t *blk = raw + b * 18;
+    float scale = __half2float(__ushort_as_half((unsigned short)(blk[0] | (blk[1] << 8))));
+    uint8_t bv = blk[2 + i];
+    int64_t e0 = b * 32 + i, e1 = e0 + 16;
+    if (e0 < n) out[e0] = __fmul_rn(scale, (float)((int)(bv & 0x0F) - 8));       // dequant.go:43
+    if (e1 < n) out[e1] = __fmul_rn(scale, (float)((int)(bv >> 4) - 8));         // dequant.go:50
+}
+
+__device__ __forceinline__ void scale_min_k4(int j, const uint8_t *q, uint8_t &sc, uint8_t &mn) {   // dequant.go:400-409
+    if (j < 4) { sc = q[j] & 63; mn = q[j + 4] & 63; }
+    else { sc = (q[j + 4] & 0x0F) | ((q[j - 4] >> 6) << 4); mn = (q[j + 4] >> 4) | ((q[j] >> 6) << 4); }
+}
+
+__global__ void dequant_q4_k_kernel(const uint8_t *__restrict__ raw, float *__restrict__ out, int64_t n) {
+    int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;   // one thread per qs byte (128 per block)
+    int64_t nb = (n + 255) / 256;
+    if (idx >= nb * 128) return;
+    int64_t b = idx >> 7; int t = (int)(idx & 127);
+    int grp = t >> 5, l = t & 31;                                   // 64-element group, byte within it
+    const uint8_t *blk = raw + b * 144;
+    float d = __half2float(__ushort_as_half((unsigned short)(blk[0] | (blk[1] << 8))));
+    float dmin = __half2float(__ushort_as_half((unsigned short)(blk[2] | (blk[3] << 8))));
+    uint8_t s1, m1, s2, m2;
+    scale_min_k4(2 * grp, blk + 4, s1, m1);
+    scale_min_k4(2 * grp + 1, blk + 4, s2, m2);
+    float d1 = __fmul_rn(d, (float)s1), dm1 = __fmul_rn(dmin, (float)m1);
+    float d2 = __fmul_rn(d, (float)s2), dm2 = __fmul_rn(dmin, (float)m2);
+    uint8_t q = blk[16 + grp * 32 + l];
+    int64_t i1 = b * 256 + grp * 64 + l, i2 = i1 + 32;
+    if (i1 < n) out[i1] = __fsub_rn(__fmul_rn(d1, (float)(q & 0x0F)), dm1);      // dequant.go:383
+    if (i2 < n) out[i2] = __fsub_rn(__fmul_rn(d2, (float)(q >> 4)), dm2);        // dequant.go:386
+}
+
+__global__ void dequant_q6_k_kernel(const uint8_t *__restrict__ raw, float *__restrict__ out, int64_t n) {
+    int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;   // one thread per (half, l): 64 per block
+    int64_t nb = (n + 255) / 256;
+    if (idx >= nb * 64) return;
+    int64_t b = idx >> 6; int t = (int)(idx & 63);
+    int hf = t >> 5, l = t & 31, is = l / 16;
+    const uint8_t *ql = raw + b * 210 + hf * 64, *qh = raw + b * 210 + 128 + hf * 32;
+    const int8_t *sc = (const int8_t *)(raw + b * 210 + 192) + hf * 8;
+    const uint8_t *dp2 = raw + b * 210 + 208;
+    float d = __half2float(__ushort_as_half((unsigned short)(dp2[0] | (dp2[1] << 8))));
+    int q1 = (int)(int8_t)((ql[l] & 0xF) | (((qh[l] >> 0) & 3) << 4)) - 32;
+    int q2 = (int)(int8_t)((ql[l + 32] & 0xF) | (((qh[l] >> 2) & 3) << 4)) - 32;
+    int q3 = (int)(int8_t)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32;
+    int q4 = (int)(int8_t)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32;
+    int64_t y = b * 256 + hf * 128 + l;
+    if (y < n)      out[y]      = __fmul_rn(__fmul_rn(d, (float)sc[is + 0]), (float)q1);   // dequant.go:313
+    if (y + 32 < n) out[y + 32] = __fmul_rn(__fmul_rn(d, (float)sc[is + 2]), (float)q2);
+    if (y + 64 < n) out[y + 64] = __fmul_rn(__fmul_rn(d, (float)sc[is + 4]), (float)q3);
+    if (y + 96 < n) out[y + 96] = __fmul_rn(__fmul_rn(d, (float)sc[is + 6]), (float)q4);
+}
+
+__global__ void f16_to_f32_kernel(const __half *__restrict__ in, float *__restrict__ out, int64_t n) {
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __half2float(in[i]);
+}
+
+static int dequant_launch(vx_ctx *c, int type, const void *raw, float *out, int64_t n) {
+    if (n <= 0) return VX_OK;
+    switch (type) {
+    case VX_T_F32: VX_CUDA(c, cudaMemcpyAsync(out, raw, (size_t)n * 4, cudaMemcpyDeviceToDevice, c->stream)); return VX_OK;
+    case VX_T_F16: f16_to_f32_kernel<<<(unsigned)ceil_div64(n, 256), 256, 0, c->stream>>>((const __half *)raw, out, n); break;
+    case VX_T_Q4_0: dequant_q4_0_kernel<<<(unsigned)ceil_div64(ceil_div64(n, 32) * 16, 256), 256, 0, c->stream>>>((const uint8_t *)raw, out, n); break;
+    case VX_T_Q4_K: dequant_q4_k_kernel<<<(unsigned)ceil_div64(ceil_div64(n, 256) * 128, 256), 256, 0, c->stream>>>((const uint8_t *)raw, out, n); break;
+    case VX_T_Q6_K: dequant_q6_k_kernel<<<(unsigned)ceil_div64(ceil_div64(n, 256) * 64, 256), 256, 0, c->stream>>>((const uint8_t *)raw, out, n); break;
+    default: return vx_fail(c, VX_E_UNSUPPORTED, "dequantize: unsupported GGUF type %d", type);
+    }
+    VX_LAUNCH_CHECK(c);
+    return VX_OK;
+}
+
+// ------------------------------------------------------------------ repacked Q4_0 layout
+// For row r and group j of four 32-weight blocks (128 weights), 64 bytes are stored as
+//   uint4 slot[c], c = 0..3, slot[c] = { word c of block 4j, word c of 4j+1, word c of 4j+2, word c of 4j+3 }
+// where word c of a block is its raw nibble bytes [4c, 4c+4) as a little-endian u32.  A fixed byte
+// permutation of the GGUF data: dequantising from it gives the same bits.  Scales go to a separate
+// half array [n][k_pad/32]; blocks that pad k to a multiple of 128 have scale 0.
+__global__ void repack_q4_0_kernel(const uint8_t *__restrict__ raw, uint4 *__restrict__ qs, __half *__restrict__ sc,
+                                   int n, int k_blocks, int k_groups) {
+    long idx = blockIdx.x * (long)blockDim.x + threadIdx.x;   // (row, group, c)
+    long total = (long)n * k_groups * 4;
+    if (idx >= total) return;
+    int c = (int)(idx & 3); long rg = idx >> 2;
+    int j = (int)(rg % k_groups); long r = rg / k_groups;
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int blk = 4 * j + i;
+        if (blk < k_blocks) {
+            const uint8_t *p = raw + ((size_t)r * k_blocks + blk) * 18;
+            w[i] = (uint32_t)p[2 + 4 * c] | ((uint32_t)p[3 + 4 * c] << 8) | ((uint32_t)p[4 + 4 * c] << 16) | ((uint32_t)p[5 + 4 * c] << 24);
+            if (c == 0) sc[(size_t)r * k_groups * 4 + blk] = __ushort_as_half((unsigned short)(p[0] | (p[1] << 8)));
+        } else {
+            w[i] = 0x88888888u;
+            if (c == 0) sc[(size_t)r * k_groups * 4 + blk] = __ushort_as_half((unsigned short)0);
+        }
+    }
+    qs[idx] = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+size_t vxq_repack_bytes(int type, int n, int k, size_t *qs_bytes, size_t *sc_bytes) {
+    if (type != VX_T_Q4_0) { *qs_bytes = *sc_bytes = 0; return 0; }
+    int k_groups = ceil_div(k, 128);
+    *qs_bytes = (size_t)n * k_groups * 64;
+    *sc_bytes = ((size_t)n * k_groups * 4 * sizeof(__half) + 255) & ~(size_t)255;
+    return *qs_bytes + *sc_bytes;
+}
+
+int vxq_repack(vx_ctx *c, int type, const void *raw_dev, int n, int k, VxWeight *w, void *qs_dst, void *sc_dst) {
+    if (type != VX_T_Q4_0) return vx_fail(c, VX_E_UNSUPPORTED, "repack: only Q4_0 has an MMA layout (type %d)", type);
+    if (k % 32 != 0) return vx_fail(c, VX_E_BAD_ARG, "repack: k=%d is not a multiple of the 32-weight block", k);
+    int k_groups = ceil_div(k, 128);
+    long total = (long)n * k_groups * 4;
+    repack_q4_0_kernel<<<(unsigned)((total + 255) / 256), 256, 0, c->stream>>>((const uint8_t *)raw_dev, (uint4 *)qs_dst, (__half *)sc_dst,
+                                                                              n, k / 32, k_groups);
+    VX_LAUNCH_CHECK(c);
+    w->type = type; w->n = n; w->k = k; w->k_pad = k_groups * 128; w->qs = qs_dst; w->sc = sc_dst;
+    w->bytes = (size_t)n * (k / 32) * 18;
+    return VX_OK;
+}
+
+// ------------------------------------------------------------------ activation split
+size_t vxq_split_bytes(int rows, int k, size_t *hi_off, size_t *lo_off, size_t *scale_off, size_t *bsum_off, int *k_pad) {
+    int kp = ceil_div(k, 128) * 128;
+    size_t rp = (size_t)((rows + 63) / 64) * 64;
+    size_t off = 0;
+    *hi_off = off; off += rp * kp * sizeof(__half);
+    *lo_off = off; off += rp * kp * sizeof(__half);
+    *scale_off = off; off += ((rp * sizeof(float)) + 255) & ~(size_t)255;
+    *bsum_off = off; off += ((rp * (kp / 32) * sizeof(float)) + 255) & ~(size_t)255;
+    *k_pad = kp;
+    return off;
+}
+
+// One CTA per row.  s = 2^(e-11) with max|x| = f * 2^e, f in [0.5, 1), so max|x/s| lies in [1024, 2048).
+__global__ void split_rows_kernel(const float *__restrict__ x, int cols, int ld, VxSplit s) {
+    __shared__ float red[32];
+    int row = blockIdx.x;
+    const float *xr = x + (size_t)row * ld;
+    float amax = 0.f;
+    for (int j = threadIdx.x; j < cols; j += blockDim.x) amax = fmaxf(amax, fabsf(xr[j]));
+    amax = block_max(amax, red);
+    float sc = 1.0f, inv = 1.0f;
+    if (amax > 0.f && amax < INFINITY) {
+        int e; frexpf(amax, &e);
+        e = max(-100, min(100, e - 11));
+        sc = ldexpf(1.0f, e); inv = ldexpf(1.0f, -e);
+    }
+    if (threadIdx.x == 0) s.scale[row] = sc;
+    __half *hi = s.hi + (size_t)row * s.k_pad, *lo = s.lo + (size_t)row * s.k_pad;
+    float *bs = s.bsum + (size_t)row * (s.k_pad / 32);
+    // each thread owns 4 consecutive k (one perm4 group); 8 threads cover a 32-block
+    for (int k0 = threadIdx.x * 4; k0 < s.k_pad; k0 += blockDim.x * 4) {
+        float v[4]; float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) { int kk = k0 + i; v[i] = kk < cols ? xr[kk] * inv : 0.f; sum += v[i]; }
+        __half h[4], l[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) { h[i] = __float2half_rn(v[i]); l[i] = __float2half_rn(v[i] - __half2float(h[i])); }
+        // stored order 0,2,1,3
+        *reinterpret_cast<uint2 *>(hi + k0) = make_uint2((uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[2]) << 16),
+                                                         (uint32_t)__half_as_ushort(h[1]) | ((uint32_t)__half_as_ushort(h[3]) << 16));
+        *reinterpret_cast<uint2 *>(lo + k0) = make_uint2((uint32_t)__half_as_ushort(l[0]) | ((uint32_t)__half_as_ushort(l[2]) << 16),
+                                                         (uint32_t)__half_as_ushort(l[1]) | ((uint32_t)__half_as_ushort(l[3]) << 16));
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        if ((threadIdx.x & 7) == 0) bs[k0 / 32] = sum;
+    }
+}
+
+int vxq_split_rows(vx_ctx *c, const float *x, int rows, int cols, int ld, const VxSplit &s) {
+    if (rows <= 0) return VX_OK;
+    split_rows_kernel<<<rows, 256, 0, c->stream>>>(x, cols, ld, s);
+    VX_LAUNCH_CHECK(c);
+    return VX_OK;
+}
+
+// ------------------------------------------------------------------ the projection kernel
+__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
+    uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// two packed nibbles (bits 0-3 and 16-19 of v) -> half2 {q0 - 8, q1 - 8}, exact
+__device__ __forceinline__ uint32_t nib2_to_half2(uint32_t v) {
+    uint32_t h = (v & 0x000F000Fu) | 0x64006400u;          // 1024 + q in each half
+    __half2 r = __hsub2(*reinterpret_cast<__half2 *>(&h), __floats2half2_rn(1032.f, 1032.f));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+
+constexpr int GEMM_ROWS = 128;      // weight rows per CTA (8 warps x 16)
+constexpr int GEMM_XLD = 144;       // smem row stride in halfs: 128 + 16 keeps 8-byte fragment loads conflict-free
+constexpr int GEMM_STAGES = 3;
+
+// grid: (ceil(N/128), split_k, ceil(M / (8*NT))).  out layout: [split][M][ld_out]
+template <int NT, int TERMS>
+__global__ void __launch_bounds__(256)
+gemm_q4_0_kernel(const uint4 *__restrict__ qs, const __half *__restrict__ sc, const __half *__restrict__ xh,
+                 const __half *__restrict__ xl, const float *__restrict__ xscale, float *__restrict__ out,
+                 int M, int N, int k_groups, int groups_per_split, int x_ld, int ld_out, size_t part_stride) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int MT = 8 * NT;
+    constexpr int STAGE_HALFS = TERMS * MT * GEMM_XLD;
+    __half *xs = reinterpret_cast<__half *>(smem_raw);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+    const int m0 = blockIdx.z * MT;
+    const int g_begin = blockIdx.y * groups_per_split;
+    const int g_end = min(k_groups, g_begin + groups_per_split);
+    const int n_iter = g_end - g_begin;
+    const int r0 = blockIdx.x * GEMM_ROWS + warp * 16;
+    const int rowA = min(r0 + g, N - 1), rowB = min(r0 + g + 8, N - 1);
+    const uint4 *qA = qs + ((size_t)rowA * k_groups) * 4 + c;
+    const uint4 *qB = qs + ((size_t)rowB * k_groups) * 4 + c;
+    const uint2 *sA = reinterpret_cast<const uint2 *>(sc + (size_t)rowA * k_groups * 4);
+    const uint2 *sB = reinterpret_cast<const uint2 *>(sc + (size_t)rowB * k_groups * 4);
+
+    auto load_x = [&](int stage, int grp) {
+        // TERMS * MT rows of 256 bytes = 16 chunks of 16 bytes each
+        constexpr int CHUNKS = TERMS * MT * 16;
+        for (int i = threadIdx.x; i < CHUNKS; i += 256) {
+            int term = i / (MT * 16), rem = i % (MT * 16), r = rem >> 4, ch = rem & 15;
+            int m = min(m0 + r, M - 1);
+            const __half *src = (term == 0 ? xh : xl) + (size_t)m * x_ld + (size_t)grp * 128 + ch * 8;
+            cp_async16(xs + stage * STAGE_HALFS + (term * MT + r) * GEMM_XLD + ch * 8, src);
+        }
+    };
+
+    float acc[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; t++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[t][i] = 0.f;
+
+    // prologue: x stages and the first weight registers
+#pragma unroll
+    for (int s = 0; s < GEMM_STAGES - 1; s++) {
+        if (s < n_iter) load_x(s, g_begin + s);
+        cp_async_commit();
+    }
+    uint4 wA = make_uint4(0, 0, 0, 0), wB = wA; uint2 dA = make_uint2(0, 0), dB = dA;
+    if (n_iter > 0) { wA = __ldg(qA + (size_t)g_begin * 4); wB = __ldg(qB + (size_t)g_begin * 4); dA = __ldg(sA + g_begin); dB = __ldg(sB + g_begin); }
+
+    for (int it = 0; it < n_iter; it++) {
+        const int grp = g_begin + it;
+        // prefetch the next group's weights into registers
+        uint4 nA = wA, nB = wB; uint2 ndA = dA, ndB = dB;
+        if (it + 1 < n_iter) { nA = __ldg(qA + (size_t)(grp + 1) * 4); nB = __ldg(qB + (size_t)(grp + 1) * 4); ndA = __ldg(sA + grp + 1); ndB = __ldg(sB + grp + 1); }
+        cp_async_wait<GEMM_STAGES - 2>();
+        __syncthreads();
+        // refill the stage freed by the previous iteration
+        if (it + GEMM_STAGES - 1 < n_iter) load_x((it + GEMM_STAGES - 1) % GEMM_STAGES, grp + GEMM_STAGES - 1);
+        cp_async_commit();
+
+        const __half *xst = xs + (it % GEMM_STAGES) * STAGE_HALFS;
+        const uint32_t wa[4] = {wA.x, wA.y, wA.z, wA.w}, wb[4] = {wB.x, wB.y, wB.z, wB.w};
+        const uint32_t da[2] = {dA.x, dA.y}, db[2] = {dB.x, dB.y};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float blk[NT][4];
+#pragma unroll
+            for (int t = 0; t < NT; t++) { blk[t][0] = blk[t][1] = blk[t][2] = blk[t][3] = 0.f; }
+#pragma unroll
+            for (int nib = 0; nib < 2; nib++) {
+                uint32_t va = wa[i] >> (4 * nib), vb = wb[i] >> (4 * nib);
+                uint32_t a[4];
+                a[0] = nib2_to_half2(va); a[2] = nib2_to_half2(va >> 8);
+                a[1] = nib2_to_half2(vb); a[3] = nib2_to_half2(vb >> 8);
+#pragma unroll
+                for (int t = 0; t < NT; t++) {
+                    const __half *p = xst + (8 * t + g) * GEMM_XLD + 32 * i + 16 * nib + 4 * c;
+                    uint2 b = *reinterpret_cast<const uint2 *>(p);
+                    mma_f16(blk[t], a, b.x, b.y);
+                    if (TERMS == 2) {
+                        uint2 bl = *reinterpret_cast<const uint2 *>(p + MT * GEMM_XLD);
+                        mma_f16(blk[t], a, bl.x, bl.y);
+                    }
+                }
+            }
+            uint32_t dpa = da[i >> 1], dpb = db[i >> 1];
+            float fa = __half2float(__ushort_as_half((unsigned short)((i & 1) ? (dpa >> 16) : (dpa & 0xFFFF))));
+            float fb = __half2float(__ushort_as_half((unsigned short)((i & 1) ? (dpb >> 16) : (dpb & 0xFFFF))));
+#pragma unroll
+            for (int t = 0; t < NT; t++) {
+                acc[t][0] = fmaf(fa, blk[t][0], acc[t][0]); acc[t][1] = fmaf(fa, blk[t][1], acc[t][1]);
+                acc[t][2] = fmaf(fb, blk[t][2], acc[t][2]); acc[t][3] = fmaf(fb, blk[t][3], acc[t][3]);
+            }
+        }
+        wA = nA; wB = nB; dA = ndA; dB = ndB;
+    }
+    cp_async_wait<0>();
+
+    float *o = out + (size_t)blockIdx.y * part_stride;
+    const int nA = r0 + g, nB = r0 + g + 8;
+#pragma unroll
+    for (int t = 0; t < NT; t++) {
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            int m = m0 + 8 * t + 2 * c + e;
+            if (m < M) {
+                float s = xscale[m];
+                if (nA < N) o[(size_t)m * ld_out + nA] = acc[t][e] * s;
+                if (nB < N) o[(size_t)m * ld_out + nB] = acc[t][2 + e] * s;
+            }
+        }
+    }
+}
+
+template <int NT, int TERMS>
+static int gemm_launch_nt(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int split,
+                          int gps, size_t part_stride) {
+    constexpr int MT = 8 * NT;
+    size_t smem = (size_t)GEMM_STAGES * TERMS * MT * GEMM_XLD * sizeof(__half);
+    auto kern = gemm_q4_0_kernel<NT, TERMS>;
+    if (smem > 48 * 1024) VX_CUDA(c, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid(ceil_div(w.n, GEMM_ROWS), split, ceil_div(m, MT));
+    kern<<<grid, 256, smem, c->stream>>>((const uint4 *)w.qs, (const __half *)w.sc, x.hi, x.lo, x.scale, out, m, w.n,
+                                         w.k_pad / 128, gps, x.k_pad, ld_out, part_stride);
+    VX_LAUNCH_CHECK(c);
+    return VX_OK;
+}
+
+static int g_gemm_terms = 2;   // 2: x = hi + lo (float32-faithful); 1: fp16 activations only
+
+// out receives [m][ld_out] when *n_parts_out == 1, otherwise `parts` holds [n_parts][m][w.n]
+int vxq_gemm(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out,
+             float *parts, size_t parts_cap_floats) {
+    if (w.type != VX_T_Q4_0) return vx_fail(c, VX_E_UNSUPPORTED, "projection: weight type %d has no MMA kernel", w.type);
+    if (x.k_pad != w.k_pad) return vx_fail(c, VX_E_BAD_ARG, "projection: activation row stride %d != weight k_pad %d", x.k_pad, w.k_pad);
+    int k_groups = w.k_pad / 128;
+    int nt = m <= 8 ? 1 : m <= 16 ? 2 : m <= 32 ? 4 : 8;
+    int ctas = ceil_div(w.n, GEMM_ROWS) * ceil_div(m, 8 * nt);
+    int split = 1;
+    if (parts && ctas < 2 * c->sm_count) {
+        split = min(min(ceil_div(2 * c->sm_count, ctas), max(1, k_groups / 4)), 8);
+        while (split > 1 && (size_t)split * m * w.n > parts_cap_floats) split--;
+    }
+    int gps = ceil_div(k_groups, split);
+    split = ceil_div(k_groups, gps);
+    float *dst = split > 1 ? parts : out;
+    int ld = split > 1 ? w.n : ld_out;
+    size_t pstride = (size_t)m * w.n;
+    *n_parts_out = split;
+    int terms = g_gemm_terms;
+#define VX_GEMM_CASE(NTV)                                                                                   \
+    case NTV:                                                                                               \
+        return terms == 2 ? gemm_launch_nt<NTV, 2>(c, w, x, m, dst, ld, split, gps, pstride)                \
+                          : gemm_launch_nt<NTV, 1>(c, w, x, m, dst, ld, split, gps, pstride);
+    switch (nt) {
+        VX_GEMM_CASE(1) VX_GEMM_CASE(2) VX_GEMM_CASE(4) VX_GEMM_CASE(8)
+    }
+#undef VX_GEMM_CASE
+    return VX_E_BAD_ARG;
+}
+
+__global__ void reduce_parts_kernel(const float *__restrict__ parts, int n_parts, int m, int n, float *__restrict__ out, int ld_out) {
+    long idx = blockIdx.x * (long)blockDim.x + threadIdx.x;
+    if (idx >= (long)m * n) return;
+    float s = 0.f;
+    for (int p = 0; p < n_parts; p++) s += parts[(size_t)p * m * n + idx];
+    out[(size_t)(idx / n) * ld_out + idx % n] = s;
+}
+
+int vxq_reduce_parts(vx_ctx *c, const float *parts, int n_parts, int m, int n, float *out, int ld_out) {
+    long total = (long)m * n;
+    reduce_parts_kernel<<<(unsigned)((total + 255) / 256), 256, 0, c->stream>>>(parts, n_parts, m, n, out, ld_out);
+    VX_LAUNCH_CHECK(c);
+    return VX_OK;
+}
+
+// ------------------------------------------------------------------ synthetic Q4_0 weights
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull; z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull; z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+// one thread per 32-weight block: draw ~N(0, sigma) with a counter hash + Box-Muller, then quantise with
+// d = signed-absmax / -8 (stored as fp16), q = clamp(round(x/d) + 8, 0, 15)
+__global__ void synth_q4_0_kernel(uint8_t *__restrict__ dst, int64_t n_blocks, uint64_t seed, float sigma) {
+    int64_t b = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    float x[32]; float amax = 0.f, vmax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+        uint64_t r = mix64(seed ^ mix64((uint64_t)b * 16 + i / 2));
+        float u1 = ((uint32_t)(r >> 40) + 1.0f) * (1.0f / 16777217.0f), u2 = (uint32_t)(r & 0xFFFFFF) * (1.0f / 16777216.0f);
+        float rad = sqrtf(-2.0f * __logf(u1)) * sigma;
+        float sn, cs; __sincosf(6.283185307f * u2, &sn, &cs);
+        x[i] = rad * cs; x[i + 1] = rad * sn;
+    }
+#pragma unroll
+    for (int i = 0; i < 32; i++) if (fabsf(x[i]) > amax) { amax = fabsf(x[i]); vmax = x[i]; }
+    float d = vmax / -8.0f;
+    float id = d != 0.f ? 1.0f / d : 0.f;
+    uint8_t *p = dst + b * 18;
+    unsigned short dh = __half_as_ushort(__float2half_rn(d));
+    p[0] = (uint8_t)(dh & 0xFF); p[1] = (uint8_t)(dh >> 8);
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        int q0 = min(15, max(0, (int)floorf(x[i] * id + 8.5f)));
+        int q1 = min(15, max(0, (int)floorf(x[i + 16] * id + 8.5f)));
+        p[2 + i] = (uint8_t)(q0 | (q1 << 4));
+    }
+}
+
+extern "C" {
+
+int vx_dequantize(vx_ctx *c, int type, vx_dptr raw, vx_dptr out, int64_t n) {
+    if (!c) return VX_E_BAD_ARG;
+    VxGuard g(c);
+    VX_REQUIRE(c, raw && out && n >= 0, "bad arguments");
+    return dequant_launch(c, type, dp<void>(raw), dp<float>(out), n);
+}
+
+int vx_synth_q4_0(vx_ctx *c, vx_dptr dst, int64_t n, uint64_t seed, float sigma) {
+    if (!c) return VX_E_BAD_ARG;
+    VxGuard g(c);
+    VX_REQUIRE(c, dst && n > 0 && n % 32 == 0, "element count must be a positive multiple of 32");
+    int64_t nb = n / 32;
+    synth_q4_0_kernel<<<(unsigned)ceil_div64(nb, 128), 128, 0, c->stream>>>(dp<uint8_t>(dst), nb, seed, sigma);
+    VX_LAUNCH_CHECK(c);
+    return VX_OK;
+}
+
+// QuantizedMatMul.MatMulQ4_0 on raw GGUF bytes: repack + split into scratch, then the MMA kernel.
+int vx_matmul_q4_0(vx_ctx *c, vx_dptr a, vx_dptr b_raw, vx_dptr out, int m, int n, int k) {
+    if (!c) return VX_E_BAD_ARG;
+    VxGuard g(c);
+    if (m <= 0 || n <= 0) return VX_OK;
+    VX_REQUIRE(c, a && b_raw && out, "nil device pointer");
+    VX_REQUIRE(c, k > 0 && k % 32 == 0, "k must be a positive multiple of 32");
+    size_t qsb, scb, hi, lo, so, bo; int kp;
+    size_t wbytes = vxq_repack_bytes(VX_T_Q4_0, n, k, &qsb, &scb);
+    size_t sbytes = vxq_split_bytes(m, k, &hi, &lo, &so, &bo, &kp);
+    size_t parts_floats = (size_t)8 * m * n;
+    void *base;
+    VX_TRY(vx_scratch(c, wbytes + sbytes + parts_floats * 4 + 1024, &base));
+    char *p = (char *)base;
+    VxWeight w;
+    VX_TRY(vxq_repack(c, VX_T_Q4_0, dp<void>(b_raw), n, k, &w, p, p + qsb));
+    char *sp = p + wbytes;
+    VxSplit s{(__half *)(sp + hi), (__half *)(sp + lo), (float *)(sp + so), (float *)(sp + bo), kp};
+    VX_TRY(vxq_split_rows(c, dp<float>(a), m, k, k, s));
+    float *parts = (float *)(sp + sbytes);
+    int np = 1;
+    VX_TRY(vxq_gemm(c, w, s, m, dp<float>(out), n, &np, parts, parts_floats));
+    if (np > 1) VX_TRY(vxq_reduce_parts(c, parts, np, m, n, dp<float>(out), n));
+    return VX_OK;
+}
+
+// K-quant projections at the interface level: bit-exact dequantisation to float32 followed by the
+// float32 transposed matmul -- the reference's own CPU route for K-quants (runtime/loader.go:214-271).
+static int matmul_kquant(vx_ctx *c, int type, vx_dptr a, vx_dptr b_raw, vx_dptr out, int m, int n, int k) {
+    if (!c) return VX_E_BAD_ARG;
+    VxGuard g(c);
+    if (m <= 0 || n <= 0) return VX_OK;
+    VX_REQUIRE(c, a && b_raw && out, "nil device pointer");
+    VX_REQUIRE(c, k > 0 && k % 256 == 0, "k must be a positive multiple of 256");
+    void *base;
+    VX_TRY(vx_scratch(c, (size_t)n * k * 4, &base));
+    VX_TRY(dequant_launch(c, type, dp<void>(b_raw), (float *)base, (int64_t)n * k));
+    return vx_matmul_f32_t(c, a, (vx_dptr)(uintptr_t)base, out, m, n, k);
+}
+int vx_matmul_q4_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k) { return matmul_kquant(c, VX_T_Q4_K, a, b, out, m, n, k); }
+int vx_matmul_q6_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k) { return matmul_kquant(c, VX_T_Q6_K, a, b, out, m, n, k); }
+
+int vx_set_gemm_terms(int terms) { if (terms == 1 || terms == 2) { g_gemm_terms = terms; return VX_OK; } return VX_E_BAD_ARG; }
+
+}  // extern "C"
