@@ -184,6 +184,12 @@ int vx_seq_fill_synthetic(vx_model *m, int64_t seq_id, int len, uint32_t seed);
 int vx_decode_step(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t *tokens,
                    const int32_t *positions, const int32_t *q_lens, int32_t *out_tokens,
                    float *logits);
+/* Greedy generation of n_steps tokens for a fixed batch with the token feedback kept on the device (no host
+ * round trip between steps).  tokens/positions describe the first step as in vx_decode_step (one token per
+ * sequence).  out_tokens (optional, host) receives [n_steps, n_seqs]; device_ms (optional) the CUDA-event time of
+ * the steps on the context's stream. */
+int vx_decode_run(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t *tokens, const int32_t *positions,
+                  int n_steps, int32_t *out_tokens, float *device_ms);
 /* Prompt processing for one sequence (runtime/decode.go:961-1096): start_pos == 0 attends causally
  * over the fresh float32 K/V (SDPAPrefill), start_pos > 0 goes through the paged multi-query
  * kernel.  out_token / logits refer to the last prompt token. */

@@ -75,6 +75,7 @@ SIGNATURES = {
     "vx_seq_fill_synthetic": [_vp, _i64, _i, C.c_uint32],
     "vx_decode_step": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp],
     "vx_prefill": [_vp, _i64, _vp, _i, _i, _vp, _vp],
+    "vx_decode_run": [_vp, _i, _vp, _vp, _vp, _i, _vp, C.POINTER(_f)],
     "vx_model_set_capture": [_vp, _i], "vx_model_get_capture": [_vp, _vp, _sz],
     "vx_model_get_packing": [_vp, _vp, _vp, _vp, _i, _i],
     "vx_model_counters": [_vp, C.POINTER(_u64), C.POINTER(_u64)],
@@ -287,6 +288,15 @@ class Model:
         self._ck(self.lib.vx_decode_step(self.h, seq_ids.size, _np_ptr(seq_ids), _np_ptr(tokens), _np_ptr(positions),
                                         _np_ptr(ql), _np_ptr(out), _np_ptr(logits)))
         return (out, logits) if want_logits else out
+
+    def decode_run(self, seq_ids, tokens, positions, n_steps):
+        """n_steps greedy steps with on-device token feedback; returns (tokens [n_steps, n_seqs], device ms)."""
+        seq_ids = np.ascontiguousarray(seq_ids, np.int64); tokens = np.ascontiguousarray(tokens, np.int32)
+        positions = np.ascontiguousarray(positions, np.int32)
+        out = np.empty((n_steps, seq_ids.size), np.int32); ms = C.c_float()
+        self._ck(self.lib.vx_decode_run(self.h, seq_ids.size, _np_ptr(seq_ids), _np_ptr(tokens), _np_ptr(positions), n_steps,
+                                       _np_ptr(out), C.byref(ms)))
+        return out, ms.value
 
     def prefill(self, seq, tokens, start_pos=0, want_logits=False):
         tokens = np.ascontiguousarray(tokens, np.int32)

@@ -60,6 +60,7 @@ struct vx_model {
     float *capture = nullptr; bool capture_on = false; int capture_rows = 0;
     int last_rows = 0, last_seqs = 0;
     uint64_t steps = 0;
+    int32_t *d_run_out = nullptr; size_t run_out_cap = 0;
     // kernel timing
     bool time_on[2] = {false, false}; float time_ms[2] = {0, 0}; uint64_t time_n[2] = {0, 0};
     std::vector<cudaEvent_t> ev_pool; std::vector<std::pair<int, int>> ev_used;   // (which, index of start event)
@@ -573,13 +574,22 @@ int plan_chunks(vx_model *m, const std::vector<int> &kv_start, const std::vector
     }
 }
 
-int run_step(vx_model *m, int n_seqs, const int *slots, const int32_t *tokens, const int32_t *positions, const int32_t *q_lens,
-             int mode, int logit_rows_req, int32_t *out_tokens, float *logits) {
+// advances a resident batch by one position: every sequence is fed the token the previous step produced
+__global__ void advance_step_kernel(int32_t *step_in, int n_seqs, const int32_t *prev_tokens) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_seqs) return;
+    step_in[2 * n_seqs + i] += 1;
+    step_in[3 * n_seqs + i] = prev_tokens[i];
+}
+
+// Host half of a step: validation and admission control against the host mirror, split-K planning, then the
+// mirror update.  No device state is touched; on failure nothing has changed.
+struct StepPlan { int n_seqs, rows, chunk[2], n_work[2]; };
+int plan_step(vx_model *m, int n_seqs, const int *slots, const int32_t *positions, const int32_t *q_lens, StepPlan *p) {
     vx_ctx *c = m->c; const vx_model_config &cf = m->cfg;
     int rows = 0;
     for (int i = 0; i < n_seqs; i++) rows += q_lens ? q_lens[i] : 1;
     if (rows <= 0 || rows > cf.max_batch_tokens) return vx_fail(c, VX_E_BAD_ARG, "step has %d rows (limit %d)", rows, cf.max_batch_tokens);
-    // host-side admission control against the mirror (no device state is touched on failure)
     long need = 0;
     std::vector<int> kv_len, kv_start0, kv_start1;
     std::vector<char> seen(cf.max_seqs, 0);
@@ -599,35 +609,50 @@ int run_step(vx_model *m, int n_seqs, const int *slots, const int32_t *tokens, c
     if (need > m->h_free) return vx_fail(c, VX_E_OOM_BLOCKS, "no free blocks: need %ld, have %d (max=%d)", need, m->h_free, cf.max_blocks);
     kv_start0.assign(rows, 0); kv_start1.assign(rows, 0);
     if (cf.sliding_window > 0) for (int t = 0; t < rows; t++) kv_start1[t] = std::max(0, kv_len[t] - cf.sliding_window);
-    int chunk[2] = {4, 4}, n_work[2] = {0, 0};
-    n_work[0] = plan_chunks(m, kv_start0, kv_len, &chunk[0]);
-    if (cf.sliding_window > 0) n_work[1] = plan_chunks(m, kv_start1, kv_len, &chunk[1]);
-
-    int32_t *h = m->h_step_in;
-    for (int i = 0; i < n_seqs; i++) { h[i] = slots[i]; h[n_seqs + i] = q_lens ? q_lens[i] : 1; h[2 * n_seqs + i] = positions[i]; }
-    memcpy(h + 3 * n_seqs, tokens, sizeof(int32_t) * rows);
-    VX_CUDA(c, cudaMemcpyAsync(m->d_step_in, h, sizeof(int32_t) * (3 * n_seqs + rows), cudaMemcpyHostToDevice, c->stream));
-    m->last_rows = rows; m->last_seqs = n_seqs;
-    PackArgs pa{};
-    pa.step_in = m->d_step_in; pa.n_seqs = n_seqs; pa.n_rows = rows;
-    pa.tables = m->d_tables; pa.width = cf.max_blocks_per_seq; pa.seq_len = m->d_seq_len; pa.n_blocks = m->d_n_blocks;
-    pa.free_list = m->d_free_list; pa.free_top = m->d_free_top; pa.refcnt = m->d_refcnt; pa.status = m->d_status;
-    pa.cu = m->d_cu; pa.row_slot = m->d_row_slot; pa.row_pos = m->d_row_pos; pa.slot_map = m->d_slot_map;
-    pa.row_kv_len = m->d_row_kv_len; pa.row_kv_start = m->d_row_kv_start; pa.window = cf.sliding_window;
-    pa.work0 = m->d_work[0]; pa.work1 = m->d_work[1]; pa.rws0 = m->d_rws[0]; pa.rws1 = m->d_rws[1];
-    pa.n_work0 = m->d_n_work[0]; pa.n_work1 = m->d_n_work[1]; pa.chunk0 = chunk[0]; pa.chunk1 = chunk[1]; pa.max_work = MAX_WORK;
-    pack_kernel<<<1, 1024, 0, c->stream>>>(pa);
-    VX_LAUNCH_CHECK(c);
-    // mirror the bookkeeping on the host
+    p->n_seqs = n_seqs; p->rows = rows; p->chunk[0] = p->chunk[1] = 4; p->n_work[0] = p->n_work[1] = 0;
+    p->n_work[0] = plan_chunks(m, kv_start0, kv_len, &p->chunk[0]);
+    if (cf.sliding_window > 0) p->n_work[1] = plan_chunks(m, kv_start1, kv_len, &p->chunk[1]);
     for (int i = 0; i < n_seqs; i++) {
         int s = slots[i], ql = q_lens ? q_lens[i] : 1;
         int nb_new = (positions[i] + ql + BS - 1) / BS;
         if (nb_new > m->h_n_blocks[s]) { m->h_free -= nb_new - m->h_n_blocks[s]; m->h_n_blocks[s] = nb_new; }
         m->h_seq_len[s] = positions[i] + ql;
     }
-    if (m->capture_on) m->capture_rows = rows;
-    int logit_rows = logit_rows_req > 0 ? logit_rows_req : rows;
-    VX_TRY(forward(m, rows, mode, n_work, logit_rows));
+    return VX_OK;
+}
+
+// Device half: packing kernel + the transformer stack, reading the step description already in d_step_in.
+int enqueue_step(vx_model *m, const StepPlan &p, int mode, int logit_rows) {
+    vx_ctx *c = m->c; const vx_model_config &cf = m->cfg;
+    m->last_rows = p.rows; m->last_seqs = p.n_seqs;
+    PackArgs pa{};
+    pa.step_in = m->d_step_in; pa.n_seqs = p.n_seqs; pa.n_rows = p.rows;
+    pa.tables = m->d_tables; pa.width = cf.max_blocks_per_seq; pa.seq_len = m->d_seq_len; pa.n_blocks = m->d_n_blocks;
+    pa.free_list = m->d_free_list; pa.free_top = m->d_free_top; pa.refcnt = m->d_refcnt; pa.status = m->d_status;
+    pa.cu = m->d_cu; pa.row_slot = m->d_row_slot; pa.row_pos = m->d_row_pos; pa.slot_map = m->d_slot_map;
+    pa.row_kv_len = m->d_row_kv_len; pa.row_kv_start = m->d_row_kv_start; pa.window = cf.sliding_window;
+    pa.work0 = m->d_work[0]; pa.work1 = m->d_work[1]; pa.rws0 = m->d_rws[0]; pa.rws1 = m->d_rws[1];
+    pa.n_work0 = m->d_n_work[0]; pa.n_work1 = m->d_n_work[1]; pa.chunk0 = p.chunk[0]; pa.chunk1 = p.chunk[1]; pa.max_work = MAX_WORK;
+    pack_kernel<<<1, 1024, 0, c->stream>>>(pa);
+    VX_LAUNCH_CHECK(c);
+    if (m->capture_on) m->capture_rows = p.rows;
+    int n_work[2] = {p.n_work[0], p.n_work[1]};
+    VX_TRY(forward(m, p.rows, mode, n_work, logit_rows));
+    m->steps++;
+    return VX_OK;
+}
+
+int run_step(vx_model *m, int n_seqs, const int *slots, const int32_t *tokens, const int32_t *positions, const int32_t *q_lens,
+             int mode, int logit_rows_req, int32_t *out_tokens, float *logits) {
+    vx_ctx *c = m->c; const vx_model_config &cf = m->cfg;
+    StepPlan p;
+    VX_TRY(plan_step(m, n_seqs, slots, positions, q_lens, &p));
+    int32_t *h = m->h_step_in;
+    for (int i = 0; i < n_seqs; i++) { h[i] = slots[i]; h[n_seqs + i] = q_lens ? q_lens[i] : 1; h[2 * n_seqs + i] = positions[i]; }
+    memcpy(h + 3 * n_seqs, tokens, sizeof(int32_t) * p.rows);
+    VX_CUDA(c, cudaMemcpyAsync(m->d_step_in, h, sizeof(int32_t) * (3 * n_seqs + p.rows), cudaMemcpyHostToDevice, c->stream));
+    int logit_rows = logit_rows_req > 0 ? logit_rows_req : p.rows;
+    VX_TRY(enqueue_step(m, p, mode, logit_rows));
     if (logits && cf.final_softcap > 0.f) {
         long n = (long)logit_rows * cf.vocab;
         final_softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(m->logits, n, cf.final_softcap);
@@ -638,7 +663,6 @@ int run_step(vx_model *m, int n_seqs, const int *slots, const int32_t *tokens, c
     VX_TRY(check_status(m));   // synchronises the stream
     time_collect(m);
     if (out_tokens) memcpy(out_tokens, m->h_out_tok, sizeof(int32_t) * logit_rows);
-    m->steps++;
     return VX_OK;
 }
 
@@ -755,6 +779,7 @@ int vx_model_destroy(vx_model *m) {
     for (auto &r : m->raw) if (r.dev) cudaFree(r.dev);
     if (m->h_step_in) cudaFreeHost(m->h_step_in);
     if (m->h_out_tok) cudaFreeHost(m->h_out_tok);
+    if (m->d_run_out) cudaFree(m->d_run_out);
     for (auto e : m->ev_pool) cudaEventDestroy(e);
     delete m;
     return VX_OK;
@@ -1021,6 +1046,67 @@ int vx_decode_step(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_
     std::vector<int> slots(n_seqs);
     for (int i = 0; i < n_seqs; i++) VX_TRY(get_slot(m, seq_ids[i], true, &slots[i]));   // created on first use (runtime/decode.go:362-364)
     return run_step(m, n_seqs, slots.data(), tokens, positions, q_lens, 0, 0, out_tokens, logits);
+}
+
+// Greedy generation for a fixed batch with the token feedback kept on the device: step s+1 is fed the
+// argmax of step s without a host round trip.  Only the first step's inputs cross PCIe; all produced
+// tokens come back in one copy at the end.  device_ms (optional) is the CUDA-event time of the n_steps
+// steps on the context's stream, measured after the first step's inputs are resident.
+int vx_decode_run(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t *tokens, const int32_t *positions,
+                  int n_steps, int32_t *out_tokens, float *device_ms) {
+    if (!m) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    VX_REQUIRE(c, m->finalized, "model not finalized");
+    VX_REQUIRE(c, n_seqs > 0 && n_seqs <= m->cfg.max_seqs && n_seqs <= m->cfg.max_batch_tokens && seq_ids && tokens && positions && n_steps > 0, "bad arguments");
+    std::vector<int> slots(n_seqs);
+    for (int i = 0; i < n_seqs; i++) VX_TRY(get_slot(m, seq_ids[i], true, &slots[i]));
+    // admission for the whole run up front: blocks needed after n_steps tokens
+    long need = 0;
+    for (int i = 0; i < n_seqs; i++) {
+        if (positions[i] != m->h_seq_len[slots[i]]) return vx_fail(c, VX_E_BAD_ARG, "position %d of batch entry %d != sequence length %d", positions[i], i, m->h_seq_len[slots[i]]);
+        int nb = (positions[i] + n_steps + BS - 1) / BS;
+        if (nb > m->cfg.max_blocks_per_seq) return vx_fail(c, VX_E_OOM_BLOCKS, "sequence would need %d blocks (table width %d)", nb, m->cfg.max_blocks_per_seq);
+        need += std::max(0, nb - m->h_n_blocks[slots[i]]);
+    }
+    if (need > m->h_free) return vx_fail(c, VX_E_OOM_BLOCKS, "no free blocks: need %ld, have %d (max=%d)", need, m->h_free, m->cfg.max_blocks);
+    if (m->run_out_cap < (size_t)n_steps * n_seqs) {
+        if (m->d_run_out) { cudaStreamSynchronize(c->stream); cudaFree(m->d_run_out); m->d_run_out = nullptr; }
+        VX_CUDA(c, cudaMalloc(&m->d_run_out, sizeof(int32_t) * (size_t)n_steps * n_seqs));
+        m->run_out_cap = (size_t)n_steps * n_seqs;
+    }
+    int32_t *h = m->h_step_in;
+    for (int i = 0; i < n_seqs; i++) { h[i] = slots[i]; h[n_seqs + i] = 1; h[2 * n_seqs + i] = positions[i]; h[3 * n_seqs + i] = tokens[i]; }
+    VX_CUDA(c, cudaMemcpyAsync(m->d_step_in, h, sizeof(int32_t) * 4 * n_seqs, cudaMemcpyHostToDevice, c->stream));
+    cudaEvent_t e0, e1;
+    VX_CUDA(c, cudaEventCreate(&e0)); VX_CUDA(c, cudaEventCreate(&e1));
+    cudaEventRecord(e0, c->stream);
+    std::vector<int32_t> pos(positions, positions + n_seqs);
+    int rc = VX_OK;
+    for (int st = 0; st < n_steps && rc == VX_OK; st++) {
+        StepPlan p;
+        rc = plan_step(m, n_seqs, slots.data(), pos.data(), nullptr, &p);
+        if (rc != VX_OK) break;
+        if (st > 0) {
+            advance_step_kernel<<<ceil_div(n_seqs, 256), 256, 0, c->stream>>>(m->d_step_in, n_seqs, m->d_out_tok);
+            c->launches++;
+        }
+        rc = enqueue_step(m, p, 0, n_seqs);
+        if (rc != VX_OK) break;
+        cudaMemcpyAsync(m->d_run_out + (size_t)st * n_seqs, m->d_out_tok, sizeof(int32_t) * n_seqs, cudaMemcpyDeviceToDevice, c->stream);
+        for (int i = 0; i < n_seqs; i++) pos[i]++;
+    }
+    cudaEventRecord(e1, c->stream);
+    int rc2 = check_status(m);
+    time_collect(m);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    if (device_ms) *device_ms = ms;
+    if (rc != VX_OK) return rc;
+    if (rc2 != VX_OK) return rc2;
+    if (out_tokens) VX_CUDA(c, cudaMemcpy(out_tokens, m->d_run_out, sizeof(int32_t) * (size_t)n_steps * n_seqs, cudaMemcpyDeviceToHost));
+    return VX_OK;
 }
 
 int vx_prefill(vx_model *m, int64_t id, const int32_t *tokens, int n_tokens, int start_pos, int32_t *out_token, float *logits) {
