@@ -24,7 +24,7 @@ struct vx_ctx {
     std::unordered_map<void *, size_t> permanent;
     // scratch owned by the interface-level entry points
     void *scratch = nullptr; size_t scratch_bytes = 0;
-    int *d_int_result = nullptr;      // device int for the synchronous Argmax
+    int *d_int_result = nullptr;      // device ints: [0] synchronous Argmax result, [8] sticky kernel error word
     int *h_int_result = nullptr;      // pinned
     int sm_count = 148;
     uint64_t launches = 0;
@@ -111,6 +111,33 @@ __host__ __device__ __forceinline__ int vx_perm4(int k) {   // within each group
     return (k & ~3) | ((r == 1) ? 2 : (r == 2) ? 1 : r);
 }
 
+// power-of-two row scale: max|x| = f * 2^e with f in [0.5, 1)  ->  s = 2^(e-11), so max|x/s| lies in [1024, 2048)
+__device__ __forceinline__ void vx_row_scale(float amax, float &sc, float &inv) {
+    sc = 1.0f; inv = 1.0f;
+    if (amax > 0.f && amax < INFINITY) {
+        int e; frexpf(amax, &e);
+        e = max(-100, min(100, e - 11));
+        sc = ldexpf(1.0f, e); inv = ldexpf(1.0f, -e);
+    }
+}
+// splits four consecutive, already scaled activations starting at column k0 (a multiple of 4) into fp16 hi/lo, stores them
+// in the 0,2,1,3 order and accumulates the 32-column block sum.  Must be reached by all 8 lanes that share a 32-block.
+__device__ __forceinline__ void vx_split_store4(const float (&v)[4], __half *hi, __half *lo, float *bs, int k0) {
+    __half h[4], l[4];
+    float sum = (v[0] + v[1]) + (v[2] + v[3]);
+#pragma unroll
+    for (int i = 0; i < 4; i++) { h[i] = __float2half_rn(v[i]); l[i] = __float2half_rn(v[i] - __half2float(h[i])); }
+    *reinterpret_cast<uint2 *>(hi + k0) = make_uint2((uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[2]) << 16),
+                                                     (uint32_t)__half_as_ushort(h[1]) | ((uint32_t)__half_as_ushort(h[3]) << 16));
+    *reinterpret_cast<uint2 *>(lo + k0) = make_uint2((uint32_t)__half_as_ushort(l[0]) | ((uint32_t)__half_as_ushort(l[2]) << 16),
+                                                     (uint32_t)__half_as_ushort(l[1]) | ((uint32_t)__half_as_ushort(l[3]) << 16));
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    if ((threadIdx.x & 7) == 0) bs[k0 >> 5] = sum;
+}
+constexpr int VX_ROW_THREADS = 1024;   // row kernels: one CTA per row, thread t owns columns (c*1024 + t)*4 .. +3 of chunk c
+
 // Repacked weight matrix for the MMA kernels (built by vx_model_finalize / the interface entry points).
 struct VxWeight {
     int type = -1;          // VX_T_*
@@ -126,6 +153,9 @@ int vxq_repack(vx_ctx *c, int type, const void *raw_dev, int n, int k, VxWeight 
 size_t vxq_repack_bytes(int type, int n, int k, size_t *qs_bytes, size_t *sc_bytes);
 int vxq_gemm(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out,
              float *parts, size_t parts_cap_floats);
+int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out, float *parts,
+                size_t parts_cap_floats);
+int vx_check_device_error(vx_ctx *c);   // after a stream synchronisation: reports and clears the sticky kernel error word
 int vxq_split_rows(vx_ctx *c, const float *x, int rows, int cols, int ld, const VxSplit &s);
 int vxq_reduce_parts(vx_ctx *c, const float *parts, int n_parts, int m, int n, float *out, int ld_out);
 size_t vxq_split_bytes(int rows, int k, size_t *hi_off, size_t *lo_off, size_t *scale_off, size_t *bsum_off, int *k_pad);

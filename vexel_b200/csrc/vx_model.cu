@@ -289,60 +289,93 @@ __global__ void embed_kernel(const int32_t *tokens, const void *table, int type,
 
 // ------------------------------------------------------------------ residual add + RMSNorm + split
 // x[row] += (post_w ? rmsnorm(sum parts)*post_w : sum parts);  y = rmsnorm(x)*w;  y -> fp16 hi/lo (+ per-block sums).
-// n_parts == 0 skips the add; w == nullptr skips the norm/split.  One CTA per row, row staged in shared memory.
-__global__ void __launch_bounds__(256)
+// n_parts == 0 skips the add; w == nullptr skips the norm/split.  One CTA of 1024 threads per row, row in registers.
+template <int NC>
+__global__ void __launch_bounds__(VX_ROW_THREADS)
 add_norm_split_kernel(float *x, const float *parts, int n_parts, size_t part_stride, int part_ld, const float *post_w, const float *w,
                       float eps, int hidden, VxSplit s, float *capture) {
-    extern __shared__ float row[];
     __shared__ float red[32];
     const int r = blockIdx.x;
     float *xr = x + (size_t)r * hidden;
+    float4 v[NC];
+    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int c = 0; c < NC; c++) {
+        int k0 = (c * VX_ROW_THREADS + threadIdx.x) * 4;
+        v[c] = k0 < hidden ? *reinterpret_cast<const float4 *>(xr + k0) : z4;
+    }
     if (n_parts > 0) {
+        float4 a[NC];
         float ss = 0.f;
-        for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
-            float v = 0.f;
-            for (int p = 0; p < n_parts; p++) v += parts[p * part_stride + (size_t)r * part_ld + j];
-            row[j] = v; ss = fmaf(v, v, ss);
+#pragma unroll
+        for (int c = 0; c < NC; c++) {
+            int k0 = (c * VX_ROW_THREADS + threadIdx.x) * 4;
+            a[c] = z4;
+            if (k0 < hidden)
+                for (int p = 0; p < n_parts; p++) {
+                    float4 t = *reinterpret_cast<const float4 *>(parts + p * part_stride + (size_t)r * part_ld + k0);
+                    a[c].x += t.x; a[c].y += t.y; a[c].z += t.z; a[c].w += t.w;
+                }
+            ss = fmaf(a[c].x, a[c].x, fmaf(a[c].y, a[c].y, fmaf(a[c].z, a[c].z, fmaf(a[c].w, a[c].w, ss))));
         }
         if (post_w) {   // Gemma 2 post-norm, runtime/block.go:985-987 / 1067-1070
             ss = block_sum(ss, red);
             float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps));
-            for (int j = threadIdx.x; j < hidden; j += blockDim.x) row[j] = __fmul_rn(__fdiv_rn(row[j], rms), post_w[j]);
+#pragma unroll
+            for (int c = 0; c < NC; c++) {
+                int k0 = (c * VX_ROW_THREADS + threadIdx.x) * 4;
+                if (k0 < hidden) {
+                    float4 pw = *reinterpret_cast<const float4 *>(post_w + k0);
+                    a[c].x = __fmul_rn(__fdiv_rn(a[c].x, rms), pw.x); a[c].y = __fmul_rn(__fdiv_rn(a[c].y, rms), pw.y);
+                    a[c].z = __fmul_rn(__fdiv_rn(a[c].z, rms), pw.z); a[c].w = __fmul_rn(__fdiv_rn(a[c].w, rms), pw.w);
+                }
+            }
         }
-        for (int j = threadIdx.x; j < hidden; j += blockDim.x) { float v = __fadd_rn(xr[j], row[j]); xr[j] = v; row[j] = v; }
-    } else {
-        for (int j = threadIdx.x; j < hidden; j += blockDim.x) row[j] = xr[j];
+#pragma unroll
+        for (int c = 0; c < NC; c++) {
+            int k0 = (c * VX_ROW_THREADS + threadIdx.x) * 4;
+            v[c].x = __fadd_rn(v[c].x, a[c].x); v[c].y = __fadd_rn(v[c].y, a[c].y);
+            v[c].z = __fadd_rn(v[c].z, a[c].z); v[c].w = __fadd_rn(v[c].w, a[c].w);
+            if (k0 < hidden) *reinterpret_cast<float4 *>(xr + k0) = v[c];
+        }
     }
-    if (capture) for (int j = threadIdx.x; j < hidden; j += blockDim.x) capture[(size_t)r * hidden + j] = row[j];
+    if (capture) {
+#pragma unroll
+        for (int c = 0; c < NC; c++) {
+            int k0 = (c * VX_ROW_THREADS + threadIdx.x) * 4;
+            if (k0 < hidden) *reinterpret_cast<float4 *>(capture + (size_t)r * hidden + k0) = v[c];
+        }
+    }
     if (!w) return;
     float ss = 0.f;
-    for (int j = threadIdx.x; j < hidden; j += blockDim.x) ss = fmaf(row[j], row[j], ss);
+#pragma unroll
+    for (int c = 0; c < NC; c++) ss = fmaf(v[c].x, v[c].x, fmaf(v[c].y, v[c].y, fmaf(v[c].z, v[c].z, fmaf(v[c].w, v[c].w, ss))));
     ss = block_sum(ss, red);
-    float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps));   // backend/cpu/cpu.go:213-218
+    const float rms = __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)hidden), eps));   // backend/cpu/cpu.go:213-218
     float amax = 0.f;
-    for (int j = threadIdx.x; j < hidden; j += blockDim.x) { float y = __fmul_rn(__fdiv_rn(row[j], rms), w[j]); row[j] = y; amax = fmaxf(amax, fabsf(y)); }
+#pragma unroll
+    for (int c = 0; c < NC; c++) {
+        int k0 = (c * VX_ROW_THREADS + threadIdx.x) * 4;
+        if (k0 < hidden) {
+            float4 ww = *reinterpret_cast<const float4 *>(w + k0);
+            v[c].x = __fmul_rn(__fdiv_rn(v[c].x, rms), ww.x); v[c].y = __fmul_rn(__fdiv_rn(v[c].y, rms), ww.y);
+            v[c].z = __fmul_rn(__fdiv_rn(v[c].z, rms), ww.z); v[c].w = __fmul_rn(__fdiv_rn(v[c].w, rms), ww.w);
+        }
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[c].x), fabsf(v[c].y)), fmaxf(fabsf(v[c].z), fabsf(v[c].w))));
+    }
     amax = block_max(amax, red);
-    float sc = 1.0f, inv = 1.0f;
-    if (amax > 0.f && amax < INFINITY) { int e; frexpf(amax, &e); e = max(-100, min(100, e - 11)); sc = ldexpf(1.0f, e); inv = ldexpf(1.0f, -e); }
+    float sc, inv;
+    vx_row_scale(amax, sc, inv);
     if (threadIdx.x == 0) s.scale[r] = sc;
-    __syncthreads();
     __half *hi = s.hi + (size_t)r * s.k_pad, *lo = s.lo + (size_t)r * s.k_pad;
     float *bs = s.bsum + (size_t)r * (s.k_pad / 32);
-    for (int k0 = threadIdx.x * 4; k0 < s.k_pad; k0 += blockDim.x * 4) {
-        float v[4], sum = 0.f;
 #pragma unroll
-        for (int i = 0; i < 4; i++) { int kk = k0 + i; v[i] = kk < hidden ? row[kk] * inv : 0.f; sum += v[i]; }
-        __half h[4], l[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) { h[i] = __float2half_rn(v[i]); l[i] = __float2half_rn(v[i] - __half2float(h[i])); }
-        *reinterpret_cast<uint2 *>(hi + k0) = make_uint2((uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[2]) << 16),
-                                                         (uint32_t)__half_as_ushort(h[1]) | ((uint32_t)__half_as_ushort(h[3]) << 16));
-        *reinterpret_cast<uint2 *>(lo + k0) = make_uint2((uint32_t)__half_as_ushort(l[0]) | ((uint32_t)__half_as_ushort(l[2]) << 16),
-                                                         (uint32_t)__half_as_ushort(l[1]) | ((uint32_t)__half_as_ushort(l[3]) << 16));
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-        if ((threadIdx.x & 7) == 0) bs[k0 / 32] = sum;
+    for (int c = 0; c < NC; c++) {
+        int k0 = (c * VX_ROW_THREADS + threadIdx.x) * 4;
+        if (k0 < s.k_pad) {
+            const float t[4] = {v[c].x * inv, v[c].y * inv, v[c].z * inv, v[c].w * inv};
+            vx_split_store4(t, hi, lo, bs, k0);
+        }
     }
 }
 
@@ -377,12 +410,8 @@ __global__ void rope_append_kernel(float *qkv, int ld, const float *cs, const fl
     for (int e = threadIdx.x; e < (int)hs; e += blockDim.x) vdst[e] = __float2half_rn(vsrc[e]);
 }
 
-// ------------------------------------------------------------------ gated activation (SwiGLU / GeGLU)
-__global__ void gate_act_kernel(const float *h13, int ffn, float *act, int geglu, long total) {
-    long idx = blockIdx.x * (long)blockDim.x + threadIdx.x;
-    if (idx >= total) return;
-    long r = idx / ffn; int j = (int)(idx % ffn);
-    float g = h13[r * 2 * ffn + j], u = h13[r * 2 * ffn + ffn + j];
+// ------------------------------------------------------------------ gated activation (SwiGLU / GeGLU) + split
+__device__ __forceinline__ float gate_act(float g, float u, int geglu) {
     float a;
     if (geglu) {   // backend/cpu/cpu.go:457-473
         const float s2pi = 0.7978845608f, coeff = 0.044715f;
@@ -394,7 +423,40 @@ __global__ void gate_act_kernel(const float *h13, int ffn, float *act, int geglu
         float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, (float)exp((double)(-g))));
         a = __fmul_rn(g, sg);
     }
-    act[idx] = __fmul_rn(a, u);
+    return __fmul_rn(a, u);
+}
+// h13 row = [gate (F) | up (F)]; act = activation(gate)*up is split for the W2 projection without touching memory in between
+template <int NC>
+__global__ void __launch_bounds__(VX_ROW_THREADS) act_split_kernel(const float *__restrict__ h13, int ffn, int geglu, VxSplit s) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const float *gr = h13 + (size_t)r * 2 * ffn, *ur = gr + ffn;
+    float4 v[NC];
+    float amax = 0.f;
+#pragma unroll
+    for (int c = 0; c < NC; c++) {
+        int k0 = (c * VX_ROW_THREADS + threadIdx.x) * 4;
+        v[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k0 < ffn) {
+            float4 g = *reinterpret_cast<const float4 *>(gr + k0), u = *reinterpret_cast<const float4 *>(ur + k0);
+            v[c] = make_float4(gate_act(g.x, u.x, geglu), gate_act(g.y, u.y, geglu), gate_act(g.z, u.z, geglu), gate_act(g.w, u.w, geglu));
+        }
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[c].x), fabsf(v[c].y)), fmaxf(fabsf(v[c].z), fabsf(v[c].w))));
+    }
+    amax = block_max(amax, red);
+    float sc, inv;
+    vx_row_scale(amax, sc, inv);
+    if (threadIdx.x == 0) s.scale[r] = sc;
+    __half *hi = s.hi + (size_t)r * s.k_pad, *lo = s.lo + (size_t)r * s.k_pad;
+    float *bs = s.bsum + (size_t)r * (s.k_pad / 32);
+#pragma unroll
+    for (int c = 0; c < NC; c++) {
+        int k0 = (c * VX_ROW_THREADS + threadIdx.x) * 4;
+        if (k0 < s.k_pad) {
+            const float t[4] = {v[c].x * inv, v[c].y * inv, v[c].z * inv, v[c].w * inv};
+            vx_split_store4(t, hi, lo, bs, k0);
+        }
+    }
 }
 
 __global__ void final_softcap_kernel(float *logits, long n, float cap) {   // runtime/model.go:340-349
@@ -447,12 +509,28 @@ int gemm_full(vx_model *m, const VxWeight &w, const VxSplit &x, int rows, float 
     return VX_OK;
 }
 
+int add_norm_split_rows(vx_model *m, float *x, int rows, const float *parts, int n_parts, size_t part_stride, int part_ld,
+                        const float *post_w, const float *w, const VxSplit &s, float *capture) {
+    const int H = m->cfg.hidden;
+    if (H > 8192) return vx_fail(m->c, VX_E_UNSUPPORTED, "hidden size %d > 8192", H);
+    if (H > 4096) add_norm_split_kernel<2><<<rows, VX_ROW_THREADS, 0, m->c->stream>>>(x, parts, n_parts, part_stride, part_ld, post_w, w, m->cfg.rms_eps, H, s, capture);
+    else add_norm_split_kernel<1><<<rows, VX_ROW_THREADS, 0, m->c->stream>>>(x, parts, n_parts, part_stride, part_ld, post_w, w, m->cfg.rms_eps, H, s, capture);
+    VX_LAUNCH_CHECK(m->c);
+    return VX_OK;
+}
 int add_norm_split(vx_model *m, int rows, const float *parts, int n_parts, size_t part_stride, int part_ld, const float *post_w,
                    const float *w, const VxSplit &s, float *capture) {
-    size_t smem = (size_t)m->cfg.hidden * sizeof(float);
-    if (smem > 48 * 1024) cudaFuncSetAttribute(add_norm_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_norm_split_kernel<<<rows, 256, smem, m->c->stream>>>(m->x, parts, n_parts, part_stride, part_ld, post_w, w, m->cfg.rms_eps,
-                                                             m->cfg.hidden, s, capture);
+    return add_norm_split_rows(m, m->x, rows, parts, n_parts, part_stride, part_ld, post_w, w, s, capture);
+}
+int act_split(vx_model *m, int rows) {
+    const int F = m->cfg.ffn;
+    int nc = ceil_div(m->sp_f.k_pad, VX_ROW_THREADS * 4);
+    switch (nc) {
+#define VX_ACT_CASE(N) case N: act_split_kernel<N><<<rows, VX_ROW_THREADS, 0, m->c->stream>>>(m->h13, F, m->cfg.geglu, m->sp_f); break;
+        VX_ACT_CASE(1) VX_ACT_CASE(2) VX_ACT_CASE(3) VX_ACT_CASE(4) VX_ACT_CASE(5) VX_ACT_CASE(6) VX_ACT_CASE(7) VX_ACT_CASE(8)
+#undef VX_ACT_CASE
+    default: return vx_fail(m->c, VX_E_UNSUPPORTED, "ffn size %d is not supported (max 32768)", F);
+    }
     VX_LAUNCH_CHECK(m->c);
     return VX_OK;
 }
@@ -515,12 +593,7 @@ int forward(vx_model *m, int rows, int mode, int n_work_host[2], int logit_rows)
         VX_TRY(add_norm_split(m, rows, m->parts, np_o, (size_t)rows * H, H, cf.post_norms ? L.post_attn_norm : nullptr, L.ffn_norm,
                               m->sp_h, nullptr));
         VX_TRY(gemm_full(m, L.w13, m->sp_h, rows, m->h13, 2 * F));                      // block.go:1045-1049
-        {
-            long total = (long)rows * F;
-            gate_act_kernel<<<(unsigned)((total + 255) / 256), 256, 0, c->stream>>>(m->h13, F, m->act, cf.geglu, total);   // block.go:1051-1057
-            VX_LAUNCH_CHECK(c);
-        }
-        VX_TRY(vxq_split_rows(c, m->act, rows, F, F, m->sp_f));
+        VX_TRY(act_split(m, rows));                                                     // block.go:1051-1057
         VX_TRY(gemm(m, L.w2, m->sp_f, rows, m->parts, H, &np_prev));                    // block.go:1060
         post_prev = cf.post_norms ? L.post_ffn_norm : nullptr;
     }
@@ -528,13 +601,8 @@ int forward(vx_model *m, int rows, int mode, int n_work_host[2], int logit_rows)
     const int r0 = rows - logit_rows;
     VX_TRY(add_norm_split(m, rows, m->parts, np_prev, (size_t)rows * H, H, post_prev, nullptr, m->sp_h,
                           m->capture_on ? m->capture + (size_t)cf.n_layers * cap_stride : nullptr));
-    {
-        // norm + split only the logit rows, written to split rows [0, logit_rows)
-        float *xs = m->x + (size_t)r0 * H;
-        size_t smem = (size_t)H * sizeof(float);
-        add_norm_split_kernel<<<logit_rows, 256, smem, c->stream>>>(xs, nullptr, 0, 0, 0, nullptr, m->final_norm, cf.rms_eps, H, m->sp_h, nullptr);
-        VX_LAUNCH_CHECK(c);
-    }
+    // norm + split only the logit rows, written to split rows [0, logit_rows)
+    VX_TRY(add_norm_split_rows(m, m->x + (size_t)r0 * H, logit_rows, nullptr, 0, 0, 0, nullptr, m->final_norm, m->sp_h, nullptr));
     VX_TRY(gemm_full(m, m->w_out, m->sp_h, logit_rows, m->logits, cf.vocab));           // model.go:352-422
     VX_TRY(vxe_argmax_rows(c, m->logits, logit_rows, cf.vocab, m->d_out_tok));          // sampler.go:79-90
     return VX_OK;
@@ -545,6 +613,7 @@ int check_status(vx_model *m) {
     VX_CUDA(m->c, cudaMemcpyAsync(m->h_out_tok + m->cfg.max_batch_tokens, m->d_status, 4, cudaMemcpyDeviceToHost, m->c->stream));
     VX_CUDA(m->c, cudaStreamSynchronize(m->c->stream));
     st = m->h_out_tok[m->cfg.max_batch_tokens];
+    VX_TRY(vx_check_device_error(m->c));
     if (st != 0) {
         cudaMemsetAsync(m->d_status, 0, 4, m->c->stream);
         return vx_fail(m->c, st, "device bookkeeping reported status %d (%s)", st,
@@ -690,6 +759,7 @@ int vx_model_create(vx_ctx *c, const vx_model_config *cfg, vx_model **out) {
     VX_REQUIRE(c, cfg->n_heads % cfg->n_kv_heads == 0, "n_heads must be a multiple of n_kv_heads");
     VX_REQUIRE(c, cfg->head_dim % 8 == 0 && cfg->head_dim <= 256, "head_dim must be a multiple of 8, at most 256");
     VX_REQUIRE(c, cfg->hidden % 32 == 0 && cfg->ffn % 32 == 0, "hidden and ffn must be multiples of 32");
+    VX_REQUIRE(c, cfg->hidden <= 8192 && cfg->ffn <= 32768, "hidden <= 8192 and ffn <= 32768");
     VX_REQUIRE(c, cfg->max_blocks > 0 && cfg->max_seqs > 0 && cfg->max_batch_tokens > 0 && cfg->max_blocks_per_seq > 0, "non-positive pool limits");
     vx_model *m = new vx_model();
     m->c = c; m->cfg = *cfg;

@@ -153,46 +153,46 @@ size_t vxq_split_bytes(int rows, int k, size_t *hi_off, size_t *lo_off, size_t *
     return off;
 }
 
-// One CTA per row.  s = 2^(e-11) with max|x| = f * 2^e, f in [0.5, 1), so max|x/s| lies in [1024, 2048).
-__global__ void split_rows_kernel(const float *__restrict__ x, int cols, int ld, VxSplit s) {
+// One CTA of 1024 threads per row; the row lives in registers (NC chunks of 4096 columns).
+template <int NC>
+__global__ void __launch_bounds__(VX_ROW_THREADS) split_rows_kernel(const float *__restrict__ x, int cols, int ld, VxSplit s) {
     __shared__ float red[32];
-    int row = blockIdx.x;
+    const int row = blockIdx.x;
     const float *xr = x + (size_t)row * ld;
+    float4 v[NC];
     float amax = 0.f;
-    for (int j = threadIdx.x; j < cols; j += blockDim.x) amax = fmaxf(amax, fabsf(xr[j]));
-    amax = block_max(amax, red);
-    float sc = 1.0f, inv = 1.0f;
-    if (amax > 0.f && amax < INFINITY) {
-        int e; frexpf(amax, &e);
-        e = max(-100, min(100, e - 11));
-        sc = ldexpf(1.0f, e); inv = ldexpf(1.0f, -e);
+#pragma unroll
+    for (int c = 0; c < NC; c++) {
+        int k0 = (c * VX_ROW_THREADS + threadIdx.x) * 4;
+        v[c] = k0 < cols ? *reinterpret_cast<const float4 *>(xr + k0) : make_float4(0.f, 0.f, 0.f, 0.f);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[c].x), fabsf(v[c].y)), fmaxf(fabsf(v[c].z), fabsf(v[c].w))));
     }
+    amax = block_max(amax, red);
+    float sc, inv;
+    vx_row_scale(amax, sc, inv);
     if (threadIdx.x == 0) s.scale[row] = sc;
     __half *hi = s.hi + (size_t)row * s.k_pad, *lo = s.lo + (size_t)row * s.k_pad;
     float *bs = s.bsum + (size_t)row * (s.k_pad / 32);
-    // each thread owns 4 consecutive k (one perm4 group); 8 threads cover a 32-block
-    for (int k0 = threadIdx.x * 4; k0 < s.k_pad; k0 += blockDim.x * 4) {
-        float v[4]; float sum = 0.f;
 #pragma unroll
-        for (int i = 0; i < 4; i++) { int kk = k0 + i; v[i] = kk < cols ? xr[kk] * inv : 0.f; sum += v[i]; }
-        __half h[4], l[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) { h[i] = __float2half_rn(v[i]); l[i] = __float2half_rn(v[i] - __half2float(h[i])); }
-        // stored order 0,2,1,3
-        *reinterpret_cast<uint2 *>(hi + k0) = make_uint2((uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[2]) << 16),
-                                                         (uint32_t)__half_as_ushort(h[1]) | ((uint32_t)__half_as_ushort(h[3]) << 16));
-        *reinterpret_cast<uint2 *>(lo + k0) = make_uint2((uint32_t)__half_as_ushort(l[0]) | ((uint32_t)__half_as_ushort(l[2]) << 16),
-                                                         (uint32_t)__half_as_ushort(l[1]) | ((uint32_t)__half_as_ushort(l[3]) << 16));
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-        if ((threadIdx.x & 7) == 0) bs[k0 / 32] = sum;
+    for (int c = 0; c < NC; c++) {
+        int k0 = (c * VX_ROW_THREADS + threadIdx.x) * 4;
+        if (k0 < s.k_pad) {
+            const float t[4] = {v[c].x * inv, v[c].y * inv, v[c].z * inv, v[c].w * inv};
+            vx_split_store4(t, hi, lo, bs, k0);
+        }
     }
 }
 
 int vxq_split_rows(vx_ctx *c, const float *x, int rows, int cols, int ld, const VxSplit &s) {
     if (rows <= 0) return VX_OK;
-    split_rows_kernel<<<rows, 256, 0, c->stream>>>(x, cols, ld, s);
+    if (cols % 4 != 0 || ld % 4 != 0) return vx_fail(c, VX_E_BAD_ARG, "activation rows must be multiples of 4 columns");
+    int nc = ceil_div(s.k_pad, VX_ROW_THREADS * 4);
+    switch (nc) {
+#define VX_SPLIT_CASE(N) case N: split_rows_kernel<N><<<rows, VX_ROW_THREADS, 0, c->stream>>>(x, cols, ld, s); break;
+        VX_SPLIT_CASE(1) VX_SPLIT_CASE(2) VX_SPLIT_CASE(3) VX_SPLIT_CASE(4) VX_SPLIT_CASE(5) VX_SPLIT_CASE(6) VX_SPLIT_CASE(7) VX_SPLIT_CASE(8)
+#undef VX_SPLIT_CASE
+    default: return vx_fail(c, VX_E_UNSUPPORTED, "activation rows of %d columns are not supported (max 32768)", cols);
+    }
     VX_LAUNCH_CHECK(c);
     return VX_OK;
 }
@@ -224,7 +224,7 @@ constexpr int GEMM_STAGES = 3;
 
 // grid: (ceil(N/128), split_k, ceil(M / (8*NT))).  out layout: [split][M][ld_out]
 template <int NT, int TERMS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 gemm_q4_0_kernel(const uint4 *__restrict__ qs, const __half *__restrict__ sc, const __half *__restrict__ xh,
                  const __half *__restrict__ xl, const float *__restrict__ xscale, float *__restrict__ out,
                  int M, int N, int k_groups, int groups_per_split, int x_ld, int ld_out, size_t part_stride) {
@@ -351,19 +351,31 @@ static int gemm_launch_nt(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m,
 }
 
 static int g_gemm_terms = 2;   // 2: x = hi + lo (float32-faithful); 1: fp16 activations only
+static int g_tc_min_rows = 17;  // batches of at least this many rows use the tcgen05 kernel (0 = never)
 
 // out receives [m][ld_out] when *n_parts_out == 1, otherwise `parts` holds [n_parts][m][w.n]
 int vxq_gemm(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out,
              float *parts, size_t parts_cap_floats) {
     if (w.type != VX_T_Q4_0) return vx_fail(c, VX_E_UNSUPPORTED, "projection: weight type %d has no MMA kernel", w.type);
     if (x.k_pad != w.k_pad) return vx_fail(c, VX_E_BAD_ARG, "projection: activation row stride %d != weight k_pad %d", x.k_pad, w.k_pad);
+    if (g_tc_min_rows > 0 && m >= g_tc_min_rows && g_gemm_terms == 2)
+        return vxq_gemm_tc(c, w, x, m, out, ld_out, n_parts_out, parts, parts_cap_floats);
     int k_groups = w.k_pad / 128;
     int nt = m <= 8 ? 1 : m <= 16 ? 2 : m <= 32 ? 4 : 8;
     int ctas = ceil_div(w.n, GEMM_ROWS) * ceil_div(m, 8 * nt);
+    // split-K so that the CTAs fill whole waves of the GPU (two resident CTAs per SM): pick the split with the best
+    // wave efficiency, preferring fewer partials on ties
     int split = 1;
-    if (parts && ctas < 2 * c->sm_count) {
-        split = min(min(ceil_div(2 * c->sm_count, ctas), max(1, k_groups / 4)), 8);
-        while (split > 1 && (size_t)split * m * w.n > parts_cap_floats) split--;
+    if (parts) {
+        const int slots = 2 * c->sm_count;
+        double best = 0.0;
+        for (int s = 1; s <= 8 && s <= max(1, k_groups / 4); s++) {
+            if ((size_t)s * m * w.n > parts_cap_floats) break;
+            int gps_s = ceil_div(k_groups, s), s_eff = ceil_div(k_groups, gps_s);
+            long n_cta = (long)ctas * s_eff;
+            double eff = (double)n_cta / (double)(ceil_div64(n_cta, slots) * slots) * ((double)k_groups / (double)(gps_s * s_eff));
+            if (eff > best + 0.03) { best = eff; split = s; }
+        }
     }
     int gps = ceil_div(k_groups, split);
     split = ceil_div(k_groups, gps);
@@ -493,6 +505,7 @@ static int matmul_kquant(vx_ctx *c, int type, vx_dptr a, vx_dptr b_raw, vx_dptr 
 int vx_matmul_q4_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k) { return matmul_kquant(c, VX_T_Q4_K, a, b, out, m, n, k); }
 int vx_matmul_q6_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k) { return matmul_kquant(c, VX_T_Q6_K, a, b, out, m, n, k); }
 
+int vx_set_tc_min_rows(int rows) { g_tc_min_rows = rows; return VX_OK; }
 int vx_set_gemm_terms(int terms) { if (terms == 1 || terms == 2) { g_gemm_terms = terms; return VX_OK; } return VX_E_BAD_ARG; }
 
 }  // extern "C"

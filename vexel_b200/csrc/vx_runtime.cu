@@ -31,6 +31,17 @@ int vx_scratch(vx_ctx *c, size_t bytes, void **out) {
     return VX_OK;
 }
 
+int vx_check_device_error(vx_ctx *c) {
+    VX_CUDA(c, cudaMemcpyAsync(c->h_int_result + 8, c->d_int_result + 8, 4, cudaMemcpyDeviceToHost, c->stream));
+    VX_CUDA(c, cudaStreamSynchronize(c->stream));
+    int e = c->h_int_result[8];
+    if (e != 0) {
+        cudaMemsetAsync(c->d_int_result + 8, 0, 4, c->stream);
+        return vx_fail(c, e, "a kernel reported status %d (%s)", e, e == VX_E_TIMEOUT ? "a bounded device-side wait gave up" : "device error");
+    }
+    return VX_OK;
+}
+
 extern "C" {
 
 int vx_init(int device, vx_ctx **out) {
@@ -44,7 +55,8 @@ int vx_init(int device, vx_ctx **out) {
     c->device = device;
     if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return VX_E_CUDA; }
     cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, device);
-    if (cudaMalloc(&c->d_int_result, 64) != cudaSuccess || cudaMallocHost(&c->h_int_result, 64) != cudaSuccess) {
+    if (cudaMalloc(&c->d_int_result, 64) != cudaSuccess || cudaMallocHost(&c->h_int_result, 64) != cudaSuccess ||
+        cudaMemset(c->d_int_result, 0, 64) != cudaSuccess) {
         cudaStreamDestroy(c->stream); delete c; return VX_E_CUDA;
     }
     *out = c;
@@ -168,7 +180,7 @@ int vx_sync(vx_ctx *c) {
     if (!c) return VX_E_BAD_ARG;
     VxGuard g(c);
     VX_CUDA(c, cudaStreamSynchronize(c->stream));
-    return VX_OK;
+    return vx_check_device_error(c);
 }
 
 }  // extern "C"
