@@ -1,16 +1,19 @@
-// Q4_0 projection on the 5th-generation tensor cores (tcgen05 + TMEM) for batches of 17..64 rows per tile.
+// Q4_0 projection on the 5th-generation tensor cores (tcgen05 + TMEM) for batches of 17 or more rows.
 //
 // Shape ("swap-AB"): D[128 weight rows x 64 batch rows] += A[128 x 64k] * B[64 x 64k]^T per pipeline stage, accumulator in
-// TMEM (128 lanes x 64 fp32 columns), one CTA per 128-row weight tile and split-K slice.
-//   * A is produced on the fly: 8 producer warps copy the packed nibbles of the stage into shared memory (cp.async),
-//     expand them to fp16 and write two K-major, 128-byte-swizzled operand tiles A_hi and A_lo with
-//         w = d*(q-8) = A_hi + A_lo exactly      (A_hi = fp16 product, A_lo = fp16 FMA residual).
-//   * B is the activation split x = s*(x_hi + x_lo) (vx_common.cuh), copied by cp.async into the same swizzled layout.
-//   * One elected thread issues tcgen05.mma for A_hi*x_hi + A_lo*x_hi + A_hi*x_lo (the dropped A_lo*x_lo is 2^-22 relative),
-//     and tcgen05.commit hands the stage back to the producers.
-//   * Warps 0-3 read the accumulator with tcgen05.ld, scale by the row's power of two and store.
-// Every wait on an mbarrier is bounded: on timeout the kernel raises an error flag, skips to the end, frees its TMEM and
-// returns, so a protocol bug cannot hang the GPU.
+// TMEM (128 lanes x 64 fp32 columns), one CTA per (128-row weight tile, split-K slice, 64-row batch tile).
+//   warp 9   TMA producer: per stage the activation tiles x_hi / x_lo (64 rows x 128 B, SWIZZLE_128B) and, every second
+//            stage, the packed nibbles of a 128-weight group (128 rows x 64 B, SWIZZLE_64B).
+//   warps 0-7 dequantisers: read their row's nibbles from shared memory, expand to fp16 and write the two K-major,
+//            128-byte-swizzled operand tiles A_hi and A_lo with  w = d*(q-8) = A_hi + A_lo  exactly
+//            (A_hi = fp16 product, A_lo = fp16 FMA residual).
+//   warp 8   one elected thread issues tcgen05.mma for A_hi*x_hi + A_lo*x_hi + A_hi*x_lo (the dropped A_lo*x_lo is 2^-22
+//            relative); tcgen05.commit hands the stage back.
+//   warps 0-3 epilogue: tcgen05.ld of the accumulator, scale by the row's power of two, store.
+// No TMA load uses cluster multicast.  Every mbarrier wait is bounded: on timeout the kernel raises an error word, skips
+// to the end, frees its TMEM and returns, so a protocol bug cannot hang the GPU.
+#include <cuda.h>
+
 #include "vx_common.cuh"
 
 namespace {
@@ -19,15 +22,14 @@ constexpr int TC_ROWS = 128;          // weight rows per CTA (MMA M)
 constexpr int TC_MT = 64;             // batch rows per CTA (MMA N)
 constexpr int TC_BK = 64;             // k per stage = one 128-byte swizzle row of fp16
 constexpr int TC_STAGES = 4;
-constexpr int TC_RAW_STAGES = 4;        // > PREFETCH + 1: a slot is rewritten only after a producer barrier follows its last read
-constexpr int TC_PREFETCH = 2;        // stages of cp.async in flight
-constexpr int TC_PRODUCERS = 256;
-constexpr int TC_THREADS = TC_PRODUCERS + 32;
+constexpr int TC_RAW = 3;             // ring of 128-weight nibble groups (each feeds two stages)
+constexpr int TC_DEQ = 256;           // dequantiser threads
+constexpr int TC_THREADS = TC_DEQ + 64;
 constexpr int A_TILE = TC_ROWS * 128;         // bytes of one fp16 operand tile (128 rows x 128 B)
 constexpr int X_TILE = TC_MT * 128;
 constexpr int STAGE_BYTES = 2 * A_TILE + 2 * X_TILE;       // A_hi, A_lo, X_hi, X_lo
-constexpr int RAW_BYTES = TC_ROWS * 32;                    // packed nibbles of one stage
-constexpr int SMEM_BYTES = TC_STAGES * STAGE_BYTES + TC_RAW_STAGES * RAW_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr int RAW_BYTES = TC_ROWS * 64;                    // packed nibbles of one 128-weight group
+constexpr int SMEM_BYTES = TC_STAGES * STAGE_BYTES + TC_RAW * RAW_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 constexpr long long WAIT_CLOCKS = 400000000LL;             // ~0.2 s at 2 GHz
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -37,6 +39,9 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -54,14 +59,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (clock64() - t0 > WAIT_CLOCKS) { *abort_flag = 1; return false; }
     }
 }
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void *src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src));
+// 2-D tiled TMA load (no multicast) completing on an mbarrier of this CTA
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
-}
-__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
@@ -91,31 +93,34 @@ __device__ __forceinline__ __half2 nib2(uint32_t v) {
 }
 __device__ __forceinline__ uint32_t h2u(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
 
-// grid: (ceil(N/128), split_k, ceil(M/64)); out layout [split][M][ld_out]
+// grid: (ceil(N/128), split_k, ceil(M/64)); out layout [split][M][ld_out]; kb_per_split is even
 __global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_q4_0_tc_kernel(const uint4 *__restrict__ qs, const __half *__restrict__ sc, const __half *__restrict__ xh,
-                    const __half *__restrict__ xl, const float *__restrict__ xscale, float *__restrict__ out, int M, int N,
-                    int k_groups, int kb_per_split, int x_ld, int ld_out, size_t part_stride, int *__restrict__ err_flag) {
+gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_xh,
+                    const __grid_constant__ CUtensorMap map_xl, const __half *__restrict__ sc, const float *__restrict__ xscale,
+                    float *__restrict__ out, int M, int N, int k_groups, int kb_per_split, int ld_out, size_t part_stride,
+                    int *__restrict__ err_flag) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;            // operand tiles need 1024-byte alignment
     const uint32_t raw_base = base + TC_STAGES * STAGE_BYTES;
-    const uint32_t bar_base = raw_base + TC_RAW_STAGES * RAW_BYTES;         // full[S], empty[S], accum
+    const uint32_t bar_base = raw_base + TC_RAW * RAW_BYTES;
     unsigned char *gen_base = smem_raw + (base - smem_u32(smem_raw));
-    auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (TC_STAGES + s); };
-    const uint32_t accum_bar = bar_base + 8u * (2 * TC_STAGES);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };                              // dequantisers + x bytes -> MMA
+    auto empty_bar = [&](int s) { return bar_base + 8u * (TC_STAGES + s); };               // MMA done -> stage reusable
+    auto rawf_bar = [&](int s) { return bar_base + 8u * (2 * TC_STAGES + s); };            // nibbles landed
+    auto rawe_bar = [&](int s) { return bar_base + 8u * (2 * TC_STAGES + TC_RAW + s); };   // nibbles consumed
+    const uint32_t accum_bar = bar_base + 8u * (2 * TC_STAGES + 2 * TC_RAW);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r0 = blockIdx.x * TC_ROWS, m0 = blockIdx.z * TC_MT;
-    const int n_kb_total = k_groups * 2;
     const int kb_begin = blockIdx.y * kb_per_split;
-    const int n_kb = min(n_kb_total, kb_begin + kb_per_split) - kb_begin;
+    const int n_kb = min(k_groups * 2, kb_begin + kb_per_split) - kb_begin;
 
     if (tid == 0) {
         s_abort = 0;
-        for (int s = 0; s < TC_STAGES; s++) { mbar_init(full_bar(s), TC_PRODUCERS); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < TC_STAGES; s++) { mbar_init(full_bar(s), TC_DEQ + 1); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < TC_RAW; s++) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), TC_DEQ); }
         mbar_init(accum_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -130,68 +135,33 @@ gemm_q4_0_tc_kernel(const uint4 *__restrict__ qs, const __half *__restrict__ sc,
     volatile int *abort_flag = &s_abort;
 
     if (warp < 8) {
-        // ------------------------------------------------------------------ producers
+        // ------------------------------------------------------------------ dequantisers
         const int row = tid & 127, h = tid >> 7;                 // operand row and which word pair {2h, 2h+1}
         const int grow = min(r0 + row, N - 1);
-        const __half2 *scp = reinterpret_cast<const __half2 *>(sc + (size_t)grow * k_groups * 4);
-
-        auto issue_loads = [&](int kb) {      // packed nibbles -> raw ring, activations -> stage
-            const int gkb = kb_begin + kb, j = gkb >> 1, sub = gkb & 1, st = kb % TC_STAGES, rs = kb % TC_RAW_STAGES;
-#pragma unroll
-            for (int u = 0; u < 2; u++) {
-                int i = tid + TC_PRODUCERS * u, rr = i >> 2, c = i & 3;
-                int gr = min(r0 + rr, N - 1);
-                const unsigned char *src = reinterpret_cast<const unsigned char *>(qs + ((size_t)gr * k_groups + j) * 4 + c) + sub * 8;
-                cp_async8(raw_base + rs * RAW_BYTES + rr * 32 + c * 8, src);
+        const __half2 *scp = reinterpret_cast<const __half2 *>(sc + (size_t)grow * k_groups * 4) + kb_begin;
+        // nibble tile rows are 64 bytes with SWIZZLE_64B: 16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3)
+        const int rsw = (row >> 1) & 3;
+        const int raw_off0 = row * 64 + (((2 * h) ^ rsw) << 4), raw_off1 = row * 64 + (((2 * h + 1) ^ rsw) << 4);
+        unsigned char *a_row = gen_base + (row >> 3) * 1024 + (row & 7) * 128;
+        __half2 d0 = n_kb > 0 ? scp[0] : __floats2half2_rn(0.f, 0.f);
+        __half2 d1 = n_kb > 1 ? scp[1] : d0;
+        uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
+        for (int kb = 0; kb < n_kb; kb++) {
+            const int st = kb % TC_STAGES, g = kb >> 1, slot = g % TC_RAW;
+            const __half2 d2n = (kb + 2 < n_kb) ? scp[kb + 2] : d1;      // scales two stages ahead
+            if ((kb & 1) == 0) {
+                if (!mbar_wait(rawf_bar(slot), (g / TC_RAW) & 1, abort_flag)) break;
+                const unsigned char *rp = gen_base + TC_STAGES * STAGE_BYTES + slot * RAW_BYTES;
+                w0 = *reinterpret_cast<const uint4 *>(rp + raw_off0);    // word 2h   of blocks 0..3 of the group
+                w1 = *reinterpret_cast<const uint4 *>(rp + raw_off1);    // word 2h+1 of blocks 0..3
+                mbar_arrive(rawe_bar(slot));
             }
-            const uint32_t xs = base + st * STAGE_BYTES + 2 * A_TILE;
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                int i = tid + TC_PRODUCERS * u;                  // 0..1023: term, row, chunk
-                int term = i >> 9, rr = (i >> 3) & 63, ch = i & 7;
-                int m = min(m0 + rr, M - 1);
-                const __half *src = (term ? xl : xh) + (size_t)m * x_ld + (size_t)gkb * TC_BK + ch * 8;
-                cp_async16(xs + term * X_TILE + (rr >> 3) * 1024 + (rr & 7) * 128 + ((ch ^ (rr & 7)) << 4), src);
-            }
-        };
-
-        bool ok = true;
-        // prologue: loads for the first TC_PREFETCH stages (their buffers are fresh)
-#pragma unroll
-        for (int p = 0; p < TC_PREFETCH; p++) {
-            if (p < n_kb) issue_loads(p);
-            cp_commit();
-        }
-        __half2 d_cur = n_kb > 0 ? scp[kb_begin] : __floats2half2_rn(0.f, 0.f);
-        for (int kb = 0; kb < n_kb && ok; kb++) {
-            const int st = kb % TC_STAGES, rs = kb % TC_RAW_STAGES;
-            // issue the loads of stage kb+PREFETCH once the tensor core has released its buffer
-            const int nk = kb + TC_PREFETCH;
-            if (nk < n_kb) {
-                if (nk >= TC_STAGES) ok = mbar_wait(empty_bar(nk % TC_STAGES), ((nk / TC_STAGES) - 1) & 1, abort_flag);
-                if (ok) issue_loads(nk);
-            }
-            cp_commit();
-            const __half2 d_next = (kb + 1 < n_kb) ? scp[kb_begin + kb + 1] : d_cur;
-            // the buffer of stage kb was released before its loads were issued (PREFETCH iterations ago)
-            cp_wait<TC_PREFETCH>();          // this thread's copies for stage kb have landed
-            // raw nibbles are read by other threads than the ones that copied them; the barrier also makes the decision to
-            // give up uniform across the producers (a thread leaving alone would strand the others at the next barrier)
-            {
-                uint32_t give_up = (!ok || *abort_flag) ? 1u : 0u, any;
-                asm volatile("{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.or.pred p, 1, %2, q;\nselp.u32 %0, 1, 0, p;\n}"
-                             : "=r"(any) : "r"(give_up), "n"(TC_PRODUCERS) : "memory");
-                if (any) { ok = false; break; }
-            }
-            const uint4 w = *reinterpret_cast<const uint4 *>(gen_base + TC_STAGES * STAGE_BYTES + rs * RAW_BYTES + row * 32 + h * 16);
-            // w = { word 2h of block 0, word 2h of block 1, word 2h+1 of block 0, word 2h+1 of block 1 }
-            const uint32_t wb[2][2] = {{w.x, w.z}, {w.y, w.w}};   // [block][word of the pair]
-            unsigned char *a_hi = gen_base + st * STAGE_BYTES + (row >> 3) * 1024 + (row & 7) * 128;
-            unsigned char *a_lo = a_hi + A_TILE;
+            if (kb >= TC_STAGES && !mbar_wait(empty_bar(st), ((kb / TC_STAGES) - 1) & 1, abort_flag)) break;
+            const uint32_t wb[2][2] = {{(kb & 1) ? w0.z : w0.x, (kb & 1) ? w1.z : w1.x}, {(kb & 1) ? w0.w : w0.y, (kb & 1) ? w1.w : w1.y}};
+            unsigned char *a_hi = a_row + st * STAGE_BYTES, *a_lo = a_hi + A_TILE;
 #pragma unroll
             for (int b = 0; b < 2; b++) {
-                const __half dd = b == 0 ? __low2half(d_cur) : __high2half(d_cur);
-                const __half2 d2 = __half2half2(dd);
+                const __half2 dd = __half2half2(b == 0 ? __low2half(d0) : __high2half(d0));
 #pragma unroll
                 for (int nib = 0; nib < 2; nib++) {
                     __half2 q[4];
@@ -200,23 +170,39 @@ gemm_q4_0_tc_kernel(const uint4 *__restrict__ qs, const __half *__restrict__ sc,
                     uint32_t hi[4], lo[4];
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
-                        __half2 ph = __hmul2(q[e], d2);
-                        __half2 pl = __hfma2(q[e], d2, __hneg2(ph));
+                        const __half2 ph = __hmul2(q[e], dd);
+                        const __half2 pl = __hfma2(q[e], dd, __hneg2(ph));
                         hi[e] = h2u(ph); lo[e] = h2u(pl);
                     }
-                    const int chunk = 4 * b + 2 * nib + h;          // 16-byte chunk of the 128-byte row
-                    const int off = (chunk ^ (row & 7)) << 4;
+                    const int off = ((4 * b + 2 * nib + h) ^ (row & 7)) << 4;   // 16-byte chunk of the 128-byte row, swizzled
                     *reinterpret_cast<uint4 *>(a_hi + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                     *reinterpret_cast<uint4 *>(a_lo + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                 }
             }
-            d_cur = d_next;
+            d0 = d1; d1 = d2n;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
             mbar_arrive(full_bar(st));
         }
-        cp_wait<0>();
+    } else if (warp == 9) {
+        // ------------------------------------------------------------------ TMA producer (one thread)
+        if (lane == 0) {
+            for (int kb = 0; kb < n_kb; kb++) {
+                const int gkb = kb_begin + kb, st = kb % TC_STAGES;
+                if ((kb & 1) == 0) {
+                    const int g = kb >> 1, slot = g % TC_RAW;
+                    if (g >= TC_RAW && !mbar_wait(rawe_bar(slot), ((g / TC_RAW) - 1) & 1, abort_flag)) break;
+                    mbar_arrive_expect_tx(rawf_bar(slot), RAW_BYTES);
+                    tma_load_2d(raw_base + slot * RAW_BYTES, &map_w, (gkb >> 1) * 64, r0, rawf_bar(slot));
+                }
+                if (kb >= TC_STAGES && !mbar_wait(empty_bar(st), ((kb / TC_STAGES) - 1) & 1, abort_flag)) break;
+                mbar_arrive_expect_tx(full_bar(st), 2 * X_TILE);
+                const uint32_t xs = base + st * STAGE_BYTES + 2 * A_TILE;
+                tma_load_2d(xs, &map_xh, gkb * TC_BK, m0, full_bar(st));
+                tma_load_2d(xs + X_TILE, &map_xl, gkb * TC_BK, m0, full_bar(st));
+            }
+        }
     } else if (lane == 0) {
-        // ------------------------------------------------------------------ MMA issue (one thread)
+        // ------------------------------------------------------------------ MMA issue (one thread of warp 8)
         bool ok = true;
         for (int kb = 0; kb < n_kb && ok; kb++) {
             const int st = kb % TC_STAGES;
@@ -277,6 +263,36 @@ gemm_q4_0_tc_kernel(const uint4 *__restrict__ qs, const __half *__restrict__ sc,
     if (tid == 0 && s_abort) atomicExch(err_flag, VX_E_TIMEOUT);
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+// row-major 2-D tensor [rows][row_bytes] of `elem`-byte elements, box = box_cols x box_rows
+int make_map(vx_ctx *c, CUtensorMap *map, CUtensorMapDataType dt, int elem, const void *base, uint64_t cols, uint64_t rows,
+             uint64_t row_stride_bytes, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle sw) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return vx_fail(c, VX_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    if (((uintptr_t)base & 15) != 0 || (row_stride_bytes & 15) != 0) return vx_fail(c, VX_E_BAD_ARG, "tensor map: base and row stride must be 16-byte aligned");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    (void)elem;
+    if (r != CUDA_SUCCESS) return vx_fail(c, VX_E_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return VX_OK;
+}
+
 }  // namespace
 
 // same contract as vxq_gemm (vx_quant.cu); the context's device error word receives VX_E_TIMEOUT if a bounded wait gave up
@@ -290,29 +306,38 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
         VX_CUDA(c, cudaFuncSetAttribute(gemm_q4_0_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         attr_set = true;
     }
-    const int k_groups = w.k_pad / 128, n_kb = k_groups * 2;
+    const int k_groups = w.k_pad / 128;
     const int tiles = ceil_div(w.n, TC_ROWS) * ceil_div(m, TC_MT);
-    // split-K for whole waves of one CTA per SM
+    // split-K (in whole 128-weight groups) for whole waves of one CTA per SM
     int split = 1;
     if (parts) {
         const int slots = c->sm_count;
         double best = 0.0;
-        for (int s = 1; s <= 8 && s <= max(1, n_kb / 8); s++) {
+        for (int s = 1; s <= 8 && s <= max(1, k_groups / 4); s++) {
             if ((size_t)s * m * w.n > parts_cap_floats) break;
-            int per = ceil_div(n_kb, s), s_eff = ceil_div(n_kb, per);
+            int per = ceil_div(k_groups, s), s_eff = ceil_div(k_groups, per);
             long n_cta = (long)tiles * s_eff;
-            double eff = (double)n_cta / (double)(ceil_div64(n_cta, slots) * slots) * ((double)n_kb / (double)(per * s_eff));
+            double eff = (double)n_cta / (double)(ceil_div64(n_cta, slots) * slots) * ((double)k_groups / (double)(per * s_eff));
             if (eff > best + 0.03) { best = eff; split = s; }
         }
     }
-    int per = ceil_div(n_kb, split);
-    split = ceil_div(n_kb, per);
+    int per = ceil_div(k_groups, split);
+    split = ceil_div(k_groups, per);
     float *dst = split > 1 ? parts : out;
     int ld = split > 1 ? w.n : ld_out;
     *n_parts_out = split;
+    // tensor maps: packed nibbles as bytes [n][k_groups*64], activations as fp16 [rows][k_pad]
+    CUtensorMap map_w, map_xh, map_xl;
+    const uint64_t x_rows = (uint64_t)((m + 63) / 64) * 64;     // the split buffers are allocated in multiples of 64 rows
+    VX_TRY(make_map(c, &map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w.qs, (uint64_t)k_groups * 64, (uint64_t)w.n, (uint64_t)k_groups * 64, 64,
+                    TC_ROWS, CU_TENSOR_MAP_SWIZZLE_64B));
+    VX_TRY(make_map(c, &map_xh, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x.hi, (uint64_t)x.k_pad, x_rows, (uint64_t)x.k_pad * 2, TC_BK, TC_MT,
+                    CU_TENSOR_MAP_SWIZZLE_128B));
+    VX_TRY(make_map(c, &map_xl, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x.lo, (uint64_t)x.k_pad, x_rows, (uint64_t)x.k_pad * 2, TC_BK, TC_MT,
+                    CU_TENSOR_MAP_SWIZZLE_128B));
     dim3 grid(ceil_div(w.n, TC_ROWS), split, ceil_div(m, TC_MT));
-    gemm_q4_0_tc_kernel<<<grid, TC_THREADS, SMEM_BYTES, c->stream>>>((const uint4 *)w.qs, (const __half *)w.sc, x.hi, x.lo, x.scale, dst,
-                                                                    m, w.n, k_groups, per, x.k_pad, ld, (size_t)m * w.n, err_flag);
+    gemm_q4_0_tc_kernel<<<grid, TC_THREADS, SMEM_BYTES, c->stream>>>(map_w, map_xh, map_xl, (const __half *)w.sc, x.scale, dst, m, w.n, k_groups,
+                                                                    per * 2, ld, (size_t)m * w.n, err_flag);
     VX_LAUNCH_CHECK(c);
     return VX_OK;
 }
