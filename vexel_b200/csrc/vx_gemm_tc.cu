@@ -1,17 +1,20 @@
 // Q4_0 projection on the 5th-generation tensor cores (tcgen05 + TMEM) for batches of 17 or more rows.
 //
-// Shape ("swap-AB"): D[128 weight rows x 64 batch rows] += A[128 x 64k] * B[64 x 64k]^T per pipeline stage, accumulator in
-// TMEM (128 lanes x 64 fp32 columns), one CTA per (128-row weight tile, split-K slice, 64-row batch tile).
-//   warp 9   TMA producer: per stage the activation tiles x_hi / x_lo (64 rows x 128 B, SWIZZLE_128B) and, every second
-//            stage, the packed nibbles of a 128-weight group (128 rows x 64 B, SWIZZLE_64B).
-//   warps 0-7 dequantisers: read their row's nibbles from shared memory, expand to fp16 and write the two K-major,
-//            128-byte-swizzled operand tiles A_hi and A_lo with  w = d*(q-8) = A_hi + A_lo  exactly
-//            (A_hi = fp16 product, A_lo = fp16 FMA residual).
-//   warp 8   one elected thread issues tcgen05.mma for A_hi*x_hi + A_lo*x_hi + A_hi*x_lo (the dropped A_lo*x_lo is 2^-22
-//            relative); tcgen05.commit hands the stage back.
-//   warps 0-3 epilogue: tcgen05.ld of the accumulator, scale by the row's power of two, store.
+// Shape ("swap-AB"): D[128 weight rows x batch] += A[128 x 64k] * B[batch x 64k]^T per pipeline stage, accumulator in tensor
+// memory, one CTA per (128-row weight tile, split-K slice, 64-row batch tile).
+//   warp 17    TMA producer: per stage the activation tiles x_hi and x_lo (64 rows x 128 B each, SWIZZLE_128B, stacked into
+//              one 128-row operand) and, every second stage, the packed nibbles of a 128-weight group (128 rows x 64 B,
+//              SWIZZLE_64B).
+//   warps 0-15 dequantisers: read their row's nibbles from shared memory, expand to fp16 and store the A operand straight
+//              into TENSOR MEMORY (tcgen05.st; lane = weight row, two fp16 per 32-bit column) as two terms with
+//              w = d*(q-8) = A_hi + A_lo exactly (A_hi = fp16 product, A_lo = fp16 FMA residual).  With A in shared
+//              memory every MMA re-read 4 KB of it and the kernel was bound by shared-memory traffic.
+//   warp 16    one elected thread issues, per K=16 step, A_hi x [x_hi; x_lo] (N=128) and A_lo x x_hi (N=64); the dropped
+//              A_lo*x_lo term is 2^-22 relative.  Two instructions instead of three: a single thread issues an MMA only
+//              every ~45 cycles, which bounds small-N shapes.  tcgen05.commit hands the stage buffers back.
+//   warps 0-15 epilogue: tcgen05.ld of the accumulator halves, add, scale by the row's power of two, store.
 // No TMA load uses cluster multicast.  Every mbarrier wait is bounded: on timeout the kernel raises an error word, skips
-// to the end, frees its TMEM and returns, so a protocol bug cannot hang the GPU.
+// to the end, frees its tensor memory and returns, so a protocol bug cannot hang the GPU.
 #include <cuda.h>
 
 #include "vx_common.cuh"
@@ -19,17 +22,21 @@
 namespace {
 
 constexpr int TC_ROWS = 128;          // weight rows per CTA (MMA M)
-constexpr int TC_MT = 64;             // batch rows per CTA (MMA N)
+constexpr int TC_MT = 64;             // batch rows per CTA
 constexpr int TC_BK = 64;             // k per stage = one 128-byte swizzle row of fp16
-constexpr int TC_STAGES = 4;
-constexpr int TC_RAW = 3;             // ring of 128-weight nibble groups (each feeds two stages)
-constexpr int TC_DEQ = 256;           // dequantiser threads
+constexpr int TC_XS = 8;              // activation-tile ring (shared memory)
+constexpr int TC_AS = 4;              // weight-operand ring (tensor memory)
+constexpr int TC_RAW = 4;             // ring of 128-weight nibble groups (each feeds two stages)
+constexpr int TC_DEQ = 512;           // dequantiser threads: (row, block of the stage, word pair)
 constexpr int TC_THREADS = TC_DEQ + 64;
-constexpr int A_TILE = TC_ROWS * 128;         // bytes of one fp16 operand tile (128 rows x 128 B)
-constexpr int X_TILE = TC_MT * 128;
-constexpr int STAGE_BYTES = 2 * A_TILE + 2 * X_TILE;       // A_hi, A_lo, X_hi, X_lo
-constexpr int RAW_BYTES = TC_ROWS * 64;                    // packed nibbles of one 128-weight group
-constexpr int SMEM_BYTES = TC_STAGES * STAGE_BYTES + TC_RAW * RAW_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr int X_TILE = TC_MT * 128;           // bytes of one fp16 activation tile (64 rows x 128 B)
+constexpr int STAGE_BYTES = 2 * X_TILE;       // x_hi rows 0-63 followed by x_lo rows 64-127: one 128-row K-major operand
+constexpr int RAW_BYTES = TC_ROWS * 64;       // packed nibbles of one 128-weight group
+constexpr int SMEM_BYTES = TC_XS * STAGE_BYTES + TC_RAW * RAW_BYTES + 1024 /*alignment*/ + 512 /*barriers*/ + 256 /*row scales*/;
+// tensor memory columns: accumulator [0,128): cols 0-63 = A_hi*x_hi + A_lo*x_hi, cols 64-127 = A_hi*x_lo;
+// weight stage s: A_hi at 128 + 64*s, A_lo 32 columns further (two fp16 per 32-bit column)
+constexpr int TMEM_A = 2 * TC_MT;
+constexpr int TMEM_COLS = 512;                // 128 + 4 * 64 = 384, rounded to the next power of two
 constexpr long long WAIT_CLOCKS = 400000000LL;             // ~0.2 s at 2 GHz
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -45,7 +52,7 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 }
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+    asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
@@ -75,16 +82,26 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
     d |= (uint64_t)2 << 61;                           // SWIZZLE_128B
     return d;
 }
-// instruction descriptor: D=f32, A=B=f16, both K-major, N=64, M=128
-constexpr uint32_t UMMA_IDESC = (1u << 4) | ((uint32_t)(TC_MT >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
+// instruction descriptors: D=f32, A=B=f16, both K-major, M=128, N = 128 (x_hi and x_lo stacked) or 64 (x_hi only)
+constexpr uint32_t UMMA_IDESC_N128 = (1u << 4) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
+constexpr uint32_t UMMA_IDESC_N64 = (1u << 4) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
 
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(UMMA_IDESC), "r"(accumulate) : "memory");
+// D[tmem_d] (+)= A[tmem_a] * B[smem desc]^T, the A operand read from tensor memory (8 columns of fp16 pairs per K=16)
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+#define VX_TMEM_LD16(v, taddr)                                                                                                    \
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"      \
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),    \
+                   "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])                       \
+                 : "r"(taddr))
 
 // (v & 0x000F000F) holds two nibbles -> half2 {q0-8, q1-8}
 __device__ __forceinline__ __half2 nib2(uint32_t v) {
@@ -103,14 +120,17 @@ gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;            // operand tiles need 1024-byte alignment
-    const uint32_t raw_base = base + TC_STAGES * STAGE_BYTES;
+    const uint32_t raw_base = base + TC_XS * STAGE_BYTES;
     const uint32_t bar_base = raw_base + TC_RAW * RAW_BYTES;
     unsigned char *gen_base = smem_raw + (base - smem_u32(smem_raw));
-    auto full_bar = [&](int s) { return bar_base + 8u * s; };                              // dequantisers + x bytes -> MMA
-    auto empty_bar = [&](int s) { return bar_base + 8u * (TC_STAGES + s); };               // MMA done -> stage reusable
-    auto rawf_bar = [&](int s) { return bar_base + 8u * (2 * TC_STAGES + s); };            // nibbles landed
-    auto rawe_bar = [&](int s) { return bar_base + 8u * (2 * TC_STAGES + TC_RAW + s); };   // nibbles consumed
-    const uint32_t accum_bar = bar_base + 8u * (2 * TC_STAGES + 2 * TC_RAW);
+    float *s_xscale = reinterpret_cast<float *>(gen_base + TC_XS * STAGE_BYTES + TC_RAW * RAW_BYTES + 512);
+    auto xf_bar = [&](int s) { return bar_base + 8u * s; };                                 // activation tile landed
+    auto xe_bar = [&](int s) { return bar_base + 8u * (TC_XS + s); };                       // ... consumed by the MMAs
+    auto af_bar = [&](int s) { return bar_base + 8u * (2 * TC_XS + s); };                   // weight operand written
+    auto ae_bar = [&](int s) { return bar_base + 8u * (2 * TC_XS + TC_AS + s); };           // ... consumed by the MMAs
+    auto rawf_bar = [&](int s) { return bar_base + 8u * (2 * TC_XS + 2 * TC_AS + s); };     // nibbles landed
+    auto rawe_bar = [&](int s) { return bar_base + 8u * (2 * TC_XS + 2 * TC_AS + TC_RAW + s); };   // ... read by the dequantisers
+    const uint32_t accum_bar = bar_base + 8u * (2 * TC_XS + 2 * TC_AS + 2 * TC_RAW);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r0 = blockIdx.x * TC_ROWS, m0 = blockIdx.z * TC_MT;
@@ -119,13 +139,15 @@ gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     if (tid == 0) {
         s_abort = 0;
-        for (int s = 0; s < TC_STAGES; s++) { mbar_init(full_bar(s), TC_DEQ + 1); mbar_init(empty_bar(s), 1); }
-        for (int s = 0; s < TC_RAW; s++) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), TC_DEQ); }
+        for (int s = 0; s < TC_XS; s++) { mbar_init(xf_bar(s), 1); mbar_init(xe_bar(s), 1); }
+        for (int s = 0; s < TC_AS; s++) { mbar_init(af_bar(s), TC_DEQ / 32); mbar_init(ae_bar(s), 1); }   // one arrival per warp:
+        for (int s = 0; s < TC_RAW; s++) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), TC_DEQ / 32); }   // 512 arrivals on one word serialise
         mbar_init(accum_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) {   // the MMA warp owns the TMEM allocation
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TC_MT) : "memory");
+    if (tid < TC_MT) s_xscale[tid] = m0 + tid < M ? xscale[m0 + tid] : 0.f;
+    if (warp == TC_DEQ / 32) {   // the MMA warp owns the tensor-memory allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -134,131 +156,140 @@ gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const uint32_t tmem = s_tmem;
     volatile int *abort_flag = &s_abort;
 
-    if (warp < 8) {
+    if (warp < TC_DEQ / 32) {
         // ------------------------------------------------------------------ dequantisers
-        const int row = tid & 127, h = tid >> 7;                 // operand row and which word pair {2h, 2h+1}
+        const int row = tid & 127, qd = tid >> 7, b = qd >> 1, h = qd & 1;   // operand row, block of the stage, word pair {2h, 2h+1}
         const int grow = min(r0 + row, N - 1);
-        const __half2 *scp = reinterpret_cast<const __half2 *>(sc + (size_t)grow * k_groups * 4) + kb_begin;
+        const __half *scp = sc + (size_t)grow * k_groups * 4 + (size_t)kb_begin * 2 + b;
         // nibble tile rows are 64 bytes with SWIZZLE_64B: 16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3)
         const int rsw = (row >> 1) & 3;
         const int raw_off0 = row * 64 + (((2 * h) ^ rsw) << 4), raw_off1 = row * 64 + (((2 * h + 1) ^ rsw) << 4);
-        unsigned char *a_row = gen_base + (row >> 3) * 1024 + (row & 7) * 128;
-        __half2 d0 = n_kb > 0 ? scp[0] : __floats2half2_rn(0.f, 0.f);
-        __half2 d1 = n_kb > 1 ? scp[1] : d0;
+        // this thread's tensor-memory lane (= weight row) and the first column of its 4-column groups
+        const uint32_t a_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + TMEM_A + 16 * b + 4 * h;
+        __half d0 = n_kb > 0 ? scp[0] : __float2half(0.f);
+        __half d1 = n_kb > 1 ? scp[2] : d0;
         uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
         for (int kb = 0; kb < n_kb; kb++) {
-            const int st = kb % TC_STAGES, g = kb >> 1, slot = g % TC_RAW;
-            const __half2 d2n = (kb + 2 < n_kb) ? scp[kb + 2] : d1;      // scales two stages ahead
+            const int as = kb % TC_AS, g = kb >> 1, slot = g % TC_RAW;
+            const __half d2n = (kb + 2 < n_kb) ? scp[2 * (kb + 2)] : d1;      // scale two stages ahead
             if ((kb & 1) == 0) {
                 if (!mbar_wait(rawf_bar(slot), (g / TC_RAW) & 1, abort_flag)) break;
-                const unsigned char *rp = gen_base + TC_STAGES * STAGE_BYTES + slot * RAW_BYTES;
+                const unsigned char *rp = gen_base + TC_XS * STAGE_BYTES + slot * RAW_BYTES;
                 w0 = *reinterpret_cast<const uint4 *>(rp + raw_off0);    // word 2h   of blocks 0..3 of the group
                 w1 = *reinterpret_cast<const uint4 *>(rp + raw_off1);    // word 2h+1 of blocks 0..3
-                mbar_arrive(rawe_bar(slot));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(rawe_bar(slot));
             }
-            if (kb >= TC_STAGES && !mbar_wait(empty_bar(st), ((kb / TC_STAGES) - 1) & 1, abort_flag)) break;
-            const uint32_t wb[2][2] = {{(kb & 1) ? w0.z : w0.x, (kb & 1) ? w1.z : w1.x}, {(kb & 1) ? w0.w : w0.y, (kb & 1) ? w1.w : w1.y}};
-            unsigned char *a_hi = a_row + st * STAGE_BYTES, *a_lo = a_hi + A_TILE;
+            if (kb >= TC_AS && !mbar_wait(ae_bar(as), ((kb / TC_AS) - 1) & 1, abort_flag)) break;
+            // this thread's block of the stage is block 2*(kb&1) + b of the group
+            const uint32_t wa = (kb & 1) ? (b ? w0.w : w0.z) : (b ? w0.y : w0.x);
+            const uint32_t wc = (kb & 1) ? (b ? w1.w : w1.z) : (b ? w1.y : w1.x);
+            const uint32_t a_hi = a_lane + 64 * as, a_lo = a_hi + 32;
+            const __half2 dd = __half2half2(d0);
 #pragma unroll
-            for (int b = 0; b < 2; b++) {
-                const __half2 dd = __half2half2(b == 0 ? __low2half(d0) : __high2half(d0));
+            for (int nib = 0; nib < 2; nib++) {
+                __half2 q[4];
+                q[0] = nib2(wa >> (4 * nib)); q[1] = nib2(wa >> (4 * nib + 8));
+                q[2] = nib2(wc >> (4 * nib)); q[3] = nib2(wc >> (4 * nib + 8));
+                uint32_t hi[4], lo[4];
 #pragma unroll
-                for (int nib = 0; nib < 2; nib++) {
-                    __half2 q[4];
-                    q[0] = nib2(wb[b][0] >> (4 * nib)); q[1] = nib2(wb[b][0] >> (4 * nib + 8));
-                    q[2] = nib2(wb[b][1] >> (4 * nib)); q[3] = nib2(wb[b][1] >> (4 * nib + 8));
-                    uint32_t hi[4], lo[4];
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        const __half2 ph = __hmul2(q[e], dd);
-                        const __half2 pl = __hfma2(q[e], dd, __hneg2(ph));
-                        hi[e] = h2u(ph); lo[e] = h2u(pl);
-                    }
-                    const int off = ((4 * b + 2 * nib + h) ^ (row & 7)) << 4;   // 16-byte chunk of the 128-byte row, swizzled
-                    *reinterpret_cast<uint4 *>(a_hi + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                    *reinterpret_cast<uint4 *>(a_lo + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                for (int e = 0; e < 4; e++) {
+                    const __half2 ph = __hmul2(q[e], dd);
+                    const __half2 pl = __hfma2(q[e], dd, __hneg2(ph));
+                    hi[e] = h2u(ph); lo[e] = h2u(pl);
                 }
+                // k positions 32b + 16nib + 8h .. +7 of the stage = columns 16b + 8nib + 4h .. +3 (two fp16 per column)
+                tmem_st4(a_hi + 8 * nib, hi[0], hi[1], hi[2], hi[3]);
+                tmem_st4(a_lo + 8 * nib, lo[0], lo[1], lo[2], lo[3]);
             }
             d0 = d1; d1 = d2n;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
-            mbar_arrive(full_bar(st));
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(af_bar(as));
         }
-    } else if (warp == 9) {
+    } else if (warp == TC_DEQ / 32 + 1) {
         // ------------------------------------------------------------------ TMA producer (one thread)
         if (lane == 0) {
             for (int kb = 0; kb < n_kb; kb++) {
-                const int gkb = kb_begin + kb, st = kb % TC_STAGES;
+                const int gkb = kb_begin + kb, xs = kb % TC_XS;
                 if ((kb & 1) == 0) {
                     const int g = kb >> 1, slot = g % TC_RAW;
                     if (g >= TC_RAW && !mbar_wait(rawe_bar(slot), ((g / TC_RAW) - 1) & 1, abort_flag)) break;
                     mbar_arrive_expect_tx(rawf_bar(slot), RAW_BYTES);
                     tma_load_2d(raw_base + slot * RAW_BYTES, &map_w, (gkb >> 1) * 64, r0, rawf_bar(slot));
                 }
-                if (kb >= TC_STAGES && !mbar_wait(empty_bar(st), ((kb / TC_STAGES) - 1) & 1, abort_flag)) break;
-                mbar_arrive_expect_tx(full_bar(st), 2 * X_TILE);
-                const uint32_t xs = base + st * STAGE_BYTES + 2 * A_TILE;
-                tma_load_2d(xs, &map_xh, gkb * TC_BK, m0, full_bar(st));
-                tma_load_2d(xs + X_TILE, &map_xl, gkb * TC_BK, m0, full_bar(st));
+                if (kb >= TC_XS && !mbar_wait(xe_bar(xs), ((kb / TC_XS) - 1) & 1, abort_flag)) break;
+                mbar_arrive_expect_tx(xf_bar(xs), 2 * X_TILE);
+                const uint32_t dst = base + xs * STAGE_BYTES;
+                tma_load_2d(dst, &map_xh, gkb * TC_BK, m0, xf_bar(xs));
+                tma_load_2d(dst + X_TILE, &map_xl, gkb * TC_BK, m0, xf_bar(xs));
             }
         }
     } else if (lane == 0) {
-        // ------------------------------------------------------------------ MMA issue (one thread of warp 8)
-        bool ok = true;
-        for (int kb = 0; kb < n_kb && ok; kb++) {
-            const int st = kb % TC_STAGES;
-            ok = mbar_wait(full_bar(st), (kb / TC_STAGES) & 1, abort_flag);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t sa = base + st * STAGE_BYTES;
-            const uint64_t a_hi = umma_desc(sa), a_lo = umma_desc(sa + A_TILE);
-            const uint64_t x_hi = umma_desc(sa + 2 * A_TILE), x_lo = umma_desc(sa + 2 * A_TILE + X_TILE);
+        // ------------------------------------------------------------------ MMA issue (one thread)
+        // per K=16 step: [A_hi] x [x_hi; x_lo] (N=128) into columns 0-127, then [A_lo] x [x_hi] (N=64) into columns 0-63.
+        // This thread shares its scheduler with four busy dequantiser warps and every instruction of its dependent chain
+        // costs ~10 cycles, so the loop is unrolled over the activation ring with all descriptors, tensor-memory
+        // addresses and barrier addresses precomputed: ~30 instructions per stage instead of ~100.
+        uint64_t xdesc[TC_XS][TC_BK / 16];
 #pragma unroll
-            for (int k = 0; k < TC_BK / 16; k++) {
-                const uint64_t adv = (uint64_t)(k * 32 >> 4);     // 16 fp16 = 32 bytes along K inside the swizzle row
-                umma_f16(tmem, a_hi + adv, x_hi + adv, (kb > 0 || k > 0) ? 1u : 0u);
-                umma_f16(tmem, a_lo + adv, x_hi + adv, 1u);
-                umma_f16(tmem, a_hi + adv, x_lo + adv, 1u);
+        for (int s = 0; s < TC_XS; s++)
+#pragma unroll
+            for (int k = 0; k < TC_BK / 16; k++) xdesc[s][k] = umma_desc(base + s * STAGE_BYTES) + (uint64_t)(2 * k);   // +32 bytes of K per step
+        bool ok = true;
+        uint32_t first = 0u;
+        for (int kb0 = 0; kb0 < n_kb && ok; kb0 += TC_XS) {
+            const uint32_t px = (uint32_t)(kb0 / TC_XS) & 1u;          // parity of the activation ring for this round
+#pragma unroll
+            for (int s = 0; s < TC_XS; s++) {
+                const int kb = kb0 + s;
+                if (kb >= n_kb) break;
+                const int as = s % TC_AS;                               // TC_XS is a multiple of TC_AS
+                const uint32_t pa = (uint32_t)((kb0 / TC_AS) + s / TC_AS) & 1u;
+                ok = mbar_wait(xf_bar(s), px, abort_flag) && mbar_wait(af_bar(as), pa, abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_hi = tmem + TMEM_A + 64 * as, a_lo = a_hi + 32;
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; k++) {
+                    umma_f16_ts(tmem, a_hi + 8 * k, xdesc[s][k], UMMA_IDESC_N128, first);
+                    first = 1u;
+                    umma_f16_ts(tmem, a_lo + 8 * k, xdesc[s][k], UMMA_IDESC_N64, 1u);
+                }
+                umma_commit(xe_bar(s));       // arrive when the MMAs above have finished reading the stage
+                umma_commit(ae_bar(as));
             }
-            umma_commit(empty_bar(st));       // arrives when the MMAs above have finished reading the stage
         }
         if (ok) umma_commit(accum_bar);
     }
 
-    // ------------------------------------------------------------------ epilogue (warps 0-3: TMEM lanes 32*warp .. +31)
+    // ------------------------------------------------------------------ epilogue: warp w reads lane quadrant w&3, columns 16*(w>>2)..
     __syncwarp();
-    if (warp < 4) {
+    if (warp < TC_DEQ / 32) {
         bool ok = n_kb > 0 && mbar_wait(accum_bar, 0, abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             float *o = out + (size_t)blockIdx.y * part_stride;
-            const int n = r0 + warp * 32 + lane;
+            const int n = r0 + (warp & 3) * 32 + lane, c0 = (warp >> 2) * 16;
+            uint32_t v0[16], v1[16];
+            const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + c0;
+            VX_TMEM_LD16(v0, taddr);
+            VX_TMEM_LD16(v1, taddr + TC_MT);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (n < N) {
 #pragma unroll
-            for (int cc = 0; cc < TC_MT; cc += 32) {
-                uint32_t v[32];
-                const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + cc;
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
-                    "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
-                      "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
-                      "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-                      "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                    : "r"(taddr));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (n < N) {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int m = m0 + cc + j;
-                        if (m < M) o[(size_t)m * ld_out + n] = __uint_as_float(v[j]) * xscale[m];
-                    }
+                for (int j = 0; j < 16; j++) {
+                    const int m = m0 + c0 + j;
+                    if (m < M) o[(size_t)m * ld_out + n] = (__uint_as_float(v0[j]) + __uint_as_float(v1[j])) * s_xscale[c0 + j];
                 }
             }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 8) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_MT) : "memory");
+    if (warp == TC_DEQ / 32) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
     if (tid == 0 && s_abort) atomicExch(err_flag, VX_E_TIMEOUT);
 }
