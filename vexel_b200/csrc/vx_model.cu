@@ -53,7 +53,7 @@ struct vx_model {
     int4 *d_work[2] = {nullptr, nullptr}; int32_t *d_rws[2] = {nullptr, nullptr}; int32_t *d_n_work[2] = {nullptr, nullptr};
     float *d_partials = nullptr;
     float *d_cos = nullptr, *d_sin = nullptr, *d_freq = nullptr;
-    float *x = nullptr, *qkv = nullptr, *attn = nullptr, *h13 = nullptr, *act = nullptr, *parts = nullptr, *logits = nullptr;
+    float *x = nullptr, *qkv = nullptr, *attn = nullptr, *parts = nullptr, *logits = nullptr;
     size_t parts_cap = 0;
     VxSplit sp_h{}, sp_q{}, sp_f{};
     int32_t *d_out_tok = nullptr, *h_out_tok = nullptr;
@@ -382,32 +382,48 @@ add_norm_split_kernel(float *x, const float *parts, int n_parts, size_t part_str
 // ------------------------------------------------------------------ RoPE + KV append
 // qkv row = [q (Hq*D) | k (Hkv*D) | v (Hkv*D)] float32.  q and k are rotated in place (backend/cpu/cpu.go:226-303);
 // k and v are rounded to fp16 (round-to-nearest-even, as reshape_paged_kv_f16) and written to the row's pool slot.
-__global__ void rope_append_kernel(float *qkv, int ld, const float *cs, const float *sn, const int32_t *slot_map, __half *pool_layer,
-                                   int n_heads, int n_kv_heads, int D, int neox) {
+constexpr int ROPE_HEADS = 4;   // heads per CTA
+// src holds n_parts split-K partial results [n_parts][rows][ld] of the fused QKV projection; their sum is the row.
+// grid: (rows, ceil((Hq + 2*Hkv) / ROPE_HEADS)); the heads of a row are q heads, then k heads, then v heads.
+__global__ void __launch_bounds__(128)
+rope_append_kernel(const float *__restrict__ src, int n_parts, size_t part_stride, float *__restrict__ qkv, int ld,
+                   const float *__restrict__ cs, const float *__restrict__ sn, const int32_t *__restrict__ slot_map,
+                   __half *__restrict__ pool_layer, int n_heads, int n_kv_heads, int D, int neox) {
     const int t = blockIdx.x, half = D / 2;
-    float *rowp = qkv + (size_t)t * ld;
+    const int h0 = blockIdx.y * ROPE_HEADS, h1 = min(h0 + ROPE_HEADS, n_heads + 2 * n_kv_heads);
+    const float *srow = src + (size_t)t * ld;
+    float *drow = qkv + (size_t)t * ld;
     const float *c = cs + (size_t)t * half, *s = sn + (size_t)t * half;
     const int slot = slot_map[t];
     const size_t hs = (size_t)n_kv_heads * D, part = (size_t)BS * hs;
     __half *kdst = pool_layer + (size_t)(slot / BS) * 2 * part + (size_t)(slot % BS) * hs;
     __half *vdst = kdst + part;
-    const int qk_pairs = (n_heads + n_kv_heads) * half;
-    for (int idx = threadIdx.x; idx < qk_pairs; idx += blockDim.x) {
-        int hd = idx / half, j = idx % half;
-        float *v = rowp + (size_t)hd * D;            // q heads then k heads are contiguous in the row
-        int i0 = neox ? j : 2 * j, i1 = neox ? j + half : 2 * j + 1;
-        float a = v[i0], b = v[i1];
-        float r0 = __fsub_rn(__fmul_rn(a, c[j]), __fmul_rn(b, s[j]));
-        float r1 = __fadd_rn(__fmul_rn(a, s[j]), __fmul_rn(b, c[j]));
-        v[i0] = r0; v[i1] = r1;
-        if (hd >= n_heads) {
-            int kh = hd - n_heads;
-            kdst[(size_t)kh * D + i0] = __float2half_rn(r0);
-            kdst[(size_t)kh * D + i1] = __float2half_rn(r1);
+    const int n_pairs = (h1 - h0) * half;
+    for (int idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
+        const int hd = h0 + idx / half, j = idx % half;
+        if (hd < n_heads + n_kv_heads) {       // q or k head: rotate the pair (i0, i1)
+            const int i0 = neox ? j : 2 * j, i1 = neox ? j + half : 2 * j + 1;
+            const size_t o0 = (size_t)hd * D + i0, o1 = (size_t)hd * D + i1;
+            float a = 0.f, b = 0.f;
+            for (int p = 0; p < n_parts; p++) { a += srow[p * part_stride + o0]; b += srow[p * part_stride + o1]; }
+            const float r0 = __fsub_rn(__fmul_rn(a, c[j]), __fmul_rn(b, s[j]));
+            const float r1 = __fadd_rn(__fmul_rn(a, s[j]), __fmul_rn(b, c[j]));
+            drow[o0] = r0; drow[o1] = r1;
+            if (hd >= n_heads) {
+                const int kh = hd - n_heads;
+                kdst[(size_t)kh * D + i0] = __float2half_rn(r0);
+                kdst[(size_t)kh * D + i1] = __float2half_rn(r1);
+            }
+        } else {                                // v head: two consecutive elements
+            const int vh = hd - n_heads - n_kv_heads;
+            const size_t o = (size_t)hd * D + 2 * j;
+            float a = 0.f, b = 0.f;
+            for (int p = 0; p < n_parts; p++) { a += srow[p * part_stride + o]; b += srow[p * part_stride + o + 1]; }
+            drow[o] = a; drow[o + 1] = b;
+            vdst[(size_t)vh * D + 2 * j] = __float2half_rn(a);
+            vdst[(size_t)vh * D + 2 * j + 1] = __float2half_rn(b);
         }
     }
-    const float *vsrc = rowp + (size_t)(n_heads + n_kv_heads) * D;
-    for (int e = threadIdx.x; e < (int)hs; e += blockDim.x) vdst[e] = __float2half_rn(vsrc[e]);
 }
 
 // ------------------------------------------------------------------ gated activation (SwiGLU / GeGLU) + split
@@ -427,7 +443,8 @@ __device__ __forceinline__ float gate_act(float g, float u, int geglu) {
 }
 // h13 row = [gate (F) | up (F)]; act = activation(gate)*up is split for the W2 projection without touching memory in between
 template <int NC>
-__global__ void __launch_bounds__(VX_ROW_THREADS) act_split_kernel(const float *__restrict__ h13, int ffn, int geglu, VxSplit s) {
+__global__ void __launch_bounds__(VX_ROW_THREADS)
+act_split_kernel(const float *__restrict__ h13, int n_parts, size_t part_stride, int ffn, int geglu, VxSplit s) {
     __shared__ float red[32];
     const int r = blockIdx.x;
     const float *gr = h13 + (size_t)r * 2 * ffn, *ur = gr + ffn;
@@ -439,6 +456,10 @@ __global__ void __launch_bounds__(VX_ROW_THREADS) act_split_kernel(const float *
         v[c] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (k0 < ffn) {
             float4 g = *reinterpret_cast<const float4 *>(gr + k0), u = *reinterpret_cast<const float4 *>(ur + k0);
+            for (int p = 1; p < n_parts; p++) {     // split-K partials of the fused gate|up projection
+                const float4 g2 = *reinterpret_cast<const float4 *>(gr + p * part_stride + k0), u2 = *reinterpret_cast<const float4 *>(ur + p * part_stride + k0);
+                g.x += g2.x; g.y += g2.y; g.z += g2.z; g.w += g2.w; u.x += u2.x; u.y += u2.y; u.z += u2.z; u.w += u2.w;
+            }
             v[c] = make_float4(gate_act(g.x, u.x, geglu), gate_act(g.y, u.y, geglu), gate_act(g.z, u.z, geglu), gate_act(g.w, u.w, geglu));
         }
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[c].x), fabsf(v[c].y)), fmaxf(fabsf(v[c].z), fabsf(v[c].w))));
@@ -522,11 +543,12 @@ int add_norm_split(vx_model *m, int rows, const float *parts, int n_parts, size_
                    const float *w, const VxSplit &s, float *capture) {
     return add_norm_split_rows(m, m->x, rows, parts, n_parts, part_stride, part_ld, post_w, w, s, capture);
 }
-int act_split(vx_model *m, int rows) {
+int act_split(vx_model *m, int rows, int n_parts) {
     const int F = m->cfg.ffn;
+    const size_t pstride = (size_t)rows * 2 * F;
     int nc = ceil_div(m->sp_f.k_pad, VX_ROW_THREADS * 4);
     switch (nc) {
-#define VX_ACT_CASE(N) case N: act_split_kernel<N><<<rows, VX_ROW_THREADS, 0, m->c->stream>>>(m->h13, F, m->cfg.geglu, m->sp_f); break;
+#define VX_ACT_CASE(N) case N: act_split_kernel<N><<<rows, VX_ROW_THREADS, 0, m->c->stream>>>(m->parts, n_parts, pstride, F, m->cfg.geglu, m->sp_f); break;
         VX_ACT_CASE(1) VX_ACT_CASE(2) VX_ACT_CASE(3) VX_ACT_CASE(4) VX_ACT_CASE(5) VX_ACT_CASE(6) VX_ACT_CASE(7) VX_ACT_CASE(8)
 #undef VX_ACT_CASE
     default: return vx_fail(m->c, VX_E_UNSUPPORTED, "ffn size %d is not supported (max 32768)", F);
@@ -565,10 +587,14 @@ int forward(vx_model *m, int rows, int mode, int n_work_host[2], int logit_rows)
         // x += W2 output of the previous layer; normOut = RMSNorm(x) (block.go:836)
         VX_TRY(add_norm_split(m, rows, m->parts, np_prev, (size_t)rows * H, H, post_prev, L.attn_norm, m->sp_h,
                               m->capture_on ? m->capture + (size_t)l * cap_stride : nullptr));
-        VX_TRY(gemm_full(m, L.wqkv, m->sp_h, rows, m->qkv, nqkv));                     // block.go:841-854
-        rope_append_kernel<<<rows, 256, 0, c->stream>>>(m->qkv, nqkv, m->d_cos, m->d_sin, m->d_slot_map,
-                                                        m->pool + (size_t)l * m->layer_stride, Hq, Hkv, D, cf.rope_neox);   // block.go:858-868
-        VX_LAUNCH_CHECK(c);
+        int np_qkv = 1;
+        VX_TRY(gemm(m, L.wqkv, m->sp_h, rows, m->parts, nqkv, &np_qkv));               // block.go:841-854
+        {
+            dim3 rg(rows, ceil_div(Hq + 2 * Hkv, ROPE_HEADS));
+            rope_append_kernel<<<rg, 128, 0, c->stream>>>(m->parts, np_qkv, (size_t)rows * nqkv, m->qkv, nqkv, m->d_cos, m->d_sin, m->d_slot_map,
+                                                          m->pool + (size_t)l * m->layer_stride, Hq, Hkv, D, cf.rope_neox);   // block.go:858-868
+            VX_LAUNCH_CHECK(c);
+        }
         time_begin(m, 0);
         if (mode == 1) {
             VX_TRY(vxe_sdpa_strided(c, m->qkv, nqkv, m->qkv + qd, m->qkv + qd + kvd, m->attn, qd, rows, 0, 1, Hq, Hkv, D, nqkv, D, scale,
@@ -592,8 +618,9 @@ int forward(vx_model *m, int rows, int mode, int n_work_host[2], int logit_rows)
         // x += Wo output (post-attn norm first for Gemma 2); normOut = RMSNorm(x, ffn_norm) (block.go:985-997)
         VX_TRY(add_norm_split(m, rows, m->parts, np_o, (size_t)rows * H, H, cf.post_norms ? L.post_attn_norm : nullptr, L.ffn_norm,
                               m->sp_h, nullptr));
-        VX_TRY(gemm_full(m, L.w13, m->sp_h, rows, m->h13, 2 * F));                      // block.go:1045-1049
-        VX_TRY(act_split(m, rows));                                                     // block.go:1051-1057
+        int np_13 = 1;
+        VX_TRY(gemm(m, L.w13, m->sp_h, rows, m->parts, 2 * F, &np_13));                 // block.go:1045-1049
+        VX_TRY(act_split(m, rows, np_13));                                              // block.go:1051-1057
         VX_TRY(gemm(m, L.w2, m->sp_f, rows, m->parts, H, &np_prev));                    // block.go:1060
         post_prev = cf.post_norms ? L.post_ffn_norm : nullptr;
     }
@@ -820,8 +847,7 @@ int vx_model_create(vx_ctx *c, const vx_model_config *cfg, vx_model **out) {
         cudaStreamSynchronize(c->stream);
     }
     MA(model_alloc_t(m, (size_t)T * H, &m->x)); MA(model_alloc_t(m, (size_t)T * nqkv, &m->qkv));
-    MA(model_alloc_t(m, (size_t)T * qd, &m->attn)); MA(model_alloc_t(m, (size_t)T * 2 * F, &m->h13));
-    MA(model_alloc_t(m, (size_t)T * F, &m->act)); MA(model_alloc_t(m, (size_t)T * cfg->vocab, &m->logits));
+    MA(model_alloc_t(m, (size_t)T * qd, &m->attn)); MA(model_alloc_t(m, (size_t)T * cfg->vocab, &m->logits));
     m->parts_cap = (size_t)MAX_PARTS * T * std::max(std::max(H, nqkv), 2 * F);
     MA(model_alloc_t(m, m->parts_cap, &m->parts));
     MA(model_alloc_t(m, (size_t)T, &m->d_out_tok));
