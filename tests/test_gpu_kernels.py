@@ -161,12 +161,12 @@ def test_matmul_q4_0(be, m, n, k):
     be.ResetPool()
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 256, 256), (3, 200, 1024), (8, 1000, 4096), (20, 130, 512), (70, 384, 2048)])
 @pytest.mark.parametrize("type_id,quant,fn", [(capi.T_Q4_K, gs.quantize_q4_k, "MatMulQ4_K"), (capi.T_Q6_K, gs.quantize_q6_k, "MatMulQ6_K")])
-def test_matmul_kquants(be, type_id, quant, fn):
-    rng = np.random.default_rng(7)
-    m, n, k = 3, 200, 1024
+def test_matmul_kquants(be, type_id, quant, fn, m, n, k):
+    rng = np.random.default_rng(7 + m)
     w = rng.standard_normal((n, k)).astype(np.float32) * 0.02
-    raw = quant(w); a = rng.standard_normal((m, k)).astype(np.float32)
+    raw = quant(w); a = rng.standard_normal((m, k)).astype(np.float32) + np.float32(0.3)   # non-zero mean exercises the Q4_K minima
     da, dw, do = be.upload(a), be.upload(raw), be.Alloc(m * n * 4)
     getattr(be, fn)(da, dw, do, m, n, k)
     want = O.matmul_transposed(a, O.dequant(type_id, raw, n * k).reshape(n, k), m, n, k)   # the reference's CPU route for K-quants

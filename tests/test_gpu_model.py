@@ -184,6 +184,38 @@ def test_gemma2_style_layers(be):
     gm.close()
 
 
+@pytest.mark.parametrize("quant", ["q4_k_m", "q6_k"])
+def test_kquant_models(be, quant):
+    """Q4_K_M (attn_v / ffn_down / output in Q6_K, the rest Q4_K) and all-Q6_K weights through the device projections; the
+    oracle takes the reference's CPU route for K-quants (dequantise to float32, runtime/loader.go:214-271)."""
+    spec = gs.scaled(gs.C3_LLAMA3_8B, 3, 256, 8, 2, 64, 512, 1024, quant=quant)
+    om, gm = build_pair(be, spec, 11, max_blocks=64)
+    rng = np.random.default_rng(6)
+    prompts = {1: 21, 2: 50}
+    gm.set_capture(True)
+    nxt = {}
+    for s, n in prompts.items():
+        p = rng.integers(0, spec.vocab, n).astype(np.int32)
+        wl, wh = om.forward(s, p, 0, want_hidden=True)
+        tok, gl = gm.prefill(s, p, 0, want_logits=True)
+        h = gm.get_capture(n)
+        for l in range(spec.n_layers + 1):
+            assert rel_l2(h[l], wh[l]) < HIDDEN_TOL, (s, l, rel_l2(h[l], wh[l]))
+        assert rel_l2(gl, wl) < HIDDEN_TOL and tok == O.argmax(wl[0])
+        nxt[s] = tok
+    for step in range(12):
+        pos = [prompts[s] + step for s in (1, 2)]
+        out, gl = gm.decode_step([1, 2], [nxt[1], nxt[2]], pos, want_logits=True)
+        h = gm.get_capture(2)
+        for i, s in enumerate((1, 2)):
+            wl, wh = om.forward(s, np.int32([nxt[s]]), pos[i], want_hidden=True)
+            for l in range(spec.n_layers + 1):
+                assert rel_l2(h[l, i], wh[l, 0]) < HIDDEN_TOL, (step, s, l)
+            nxt[s] = O.argmax(wl[0])
+            assert int(out[i]) == nxt[s]
+    gm.close()
+
+
 def test_full_size_round_trip_properties(be):
     """Size-independent checks at the benchmark's shape (one Llama-2-7B-shaped layer stack is too slow for the oracle):
     device-synthesised Q4_0 weights dequantise to the oracle's bits, and synthetic KV fill + decode keep the pool invariants."""

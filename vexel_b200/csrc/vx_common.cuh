@@ -144,13 +144,16 @@ struct VxWeight {
     int n = 0, k = 0, k_pad = 0;
     void *qs = nullptr;     // Q4_0: [n][k_pad/128][4 lanes][4 words]; F32: raw
     void *sc = nullptr;     // Q4_0: half [n][k_pad/32]
-    void *aux = nullptr;
+    void *aux = nullptr;    // K-quants: super-block scales (half2 {d, dmin} or half d) [n][k/256]
+    void *hi = nullptr;     // Q6_K: top two bits [n][k_pad/128][4 lanes] uint2
     size_t bytes = 0;       // GGUF byte size (roofline accounting)
 };
+struct VxRepackLayout { size_t off[4]; size_t row_bytes[4]; size_t total; };   // arrays: qs, sc, aux, hi
 
 // launchers implemented in vx_quant.cu
-int vxq_repack(vx_ctx *c, int type, const void *raw_dev, int n, int k, VxWeight *w, void *qs_dst, void *sc_dst);
-size_t vxq_repack_bytes(int type, int n, int k, size_t *qs_bytes, size_t *sc_bytes);
+bool vxq_layout(int type, int n, int k, VxRepackLayout *L);
+int vxq_repack_rows(vx_ctx *c, int type, const void *raw_dev, int n_rows, int k, void *base, const VxRepackLayout &L, int row0);
+void vxq_weight_view(int type, int n, int k, void *base, const VxRepackLayout &L, VxWeight *w);
 int vxq_gemm(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out,
              float *parts, size_t parts_cap_floats);
 int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out, float *parts,

@@ -19,8 +19,10 @@ constexpr int BS = 16;   // tokens per KV block (runtime/decode.go:351)
 constexpr int MAX_PARTS = 8;
 constexpr int MAX_WORK = 32768;
 
+struct ColW { VxWeight w; int col; };      // a projection writing output columns [col, col + w.n)
 struct LayerW {
-    VxWeight wqkv, wo, w13, w2;
+    std::vector<ColW> wqkv;                // one fused Wq|Wk|Wv matrix when the three share a block format, else one per format run
+    VxWeight wo, w13, w2;
     float *attn_norm = nullptr, *ffn_norm = nullptr, *post_attn_norm = nullptr, *post_ffn_norm = nullptr;
 };
 struct RawTensor { int type = -1; void *dev = nullptr; size_t bytes = 0; };
@@ -386,7 +388,7 @@ constexpr int ROPE_HEADS = 4;   // heads per CTA
 // src holds n_parts split-K partial results [n_parts][rows][ld] of the fused QKV projection; their sum is the row.
 // grid: (rows, ceil((Hq + 2*Hkv) / ROPE_HEADS)); the heads of a row are q heads, then k heads, then v heads.
 __global__ void __launch_bounds__(128)
-rope_append_kernel(const float *__restrict__ src, int n_parts, size_t part_stride, float *__restrict__ qkv, int ld,
+rope_append_kernel(const float *src, int n_parts, size_t part_stride, float *qkv, int ld,   // src may alias qkv (n_parts == 1)
                    const float *__restrict__ cs, const float *__restrict__ sn, const int32_t *__restrict__ slot_map,
                    __half *__restrict__ pool_layer, int n_heads, int n_kv_heads, int D, int neox) {
     const int t = blockIdx.x, half = D / 2;
@@ -588,10 +590,16 @@ int forward(vx_model *m, int rows, int mode, int n_work_host[2], int logit_rows)
         VX_TRY(add_norm_split(m, rows, m->parts, np_prev, (size_t)rows * H, H, post_prev, L.attn_norm, m->sp_h,
                               m->capture_on ? m->capture + (size_t)l * cap_stride : nullptr));
         int np_qkv = 1;
-        VX_TRY(gemm(m, L.wqkv, m->sp_h, rows, m->parts, nqkv, &np_qkv));               // block.go:841-854
+        const float *qkv_src = m->parts;
+        if (L.wqkv.size() == 1) {
+            VX_TRY(gemm(m, L.wqkv[0].w, m->sp_h, rows, m->parts, nqkv, &np_qkv));      // block.go:841-854
+        } else {   // mixed block formats: one projection per format run, written side by side; RoPE then runs in place
+            for (const ColW &cw : L.wqkv) VX_TRY(gemm_full(m, cw.w, m->sp_h, rows, m->qkv + cw.col, nqkv));
+            qkv_src = m->qkv;
+        }
         {
             dim3 rg(rows, ceil_div(Hq + 2 * Hkv, ROPE_HEADS));
-            rope_append_kernel<<<rg, 128, 0, c->stream>>>(m->parts, np_qkv, (size_t)rows * nqkv, m->qkv, nqkv, m->d_cos, m->d_sin, m->d_slot_map,
+            rope_append_kernel<<<rg, 128, 0, c->stream>>>(qkv_src, np_qkv, (size_t)rows * nqkv, m->qkv, nqkv, m->d_cos, m->d_sin, m->d_slot_map,
                                                           m->pool + (size_t)l * m->layer_stride, Hq, Hkv, D, cf.rope_neox);   // block.go:858-868
             VX_LAUNCH_CHECK(c);
         }
@@ -925,27 +933,25 @@ int vx_model_finalize(vx_model *m) {
         *dst = (float *)r.dev; m->owned.push_back(r.dev); r.dev = nullptr;   // ownership moves to the model
         return VX_OK;
     };
-    // concatenated repack of up to three row groups sharing k
-    auto build = [&](std::initializer_list<RawTensor *> srcs, std::initializer_list<int> ns, int k, VxWeight *w) -> int {
+    // concatenated repack of row groups that share k and the block format
+    auto build = [&](std::vector<RawTensor *> srcs, std::vector<int> ns, int k, VxWeight *w) -> int {
         int n_total = 0;
         for (int n : ns) n_total += n;
+        const int type = srcs[0]->type;
         for (RawTensor *r : srcs) {
             if (!r->dev) return vx_fail(c, VX_E_BAD_ARG, "a projection tensor was never set");
-            if (r->type != VX_T_Q4_0) return vx_fail(c, VX_E_UNSUPPORTED, "projection type %d: only Q4_0 has a device kernel", r->type);
+            if (r->type != type) return vx_fail(c, VX_E_BAD_ARG, "internal: mixed block formats in one fused matrix");
         }
-        size_t qsb, scb;
-        size_t bytes = vxq_repack_bytes(VX_T_Q4_0, n_total, k, &qsb, &scb);
-        void *p; VX_TRY(model_alloc(m, bytes, &p));
-        char *qs = (char *)p, *sc = (char *)p + qsb;
-        int k_groups = ceil_div(k, 128), row = 0; size_t gg = 0;
-        auto it_n = ns.begin();
-        for (RawTensor *r : srcs) {
-            VxWeight tmp;
-            VX_TRY(vxq_repack(c, VX_T_Q4_0, r->dev, *it_n, k, &tmp, qs + (size_t)row * k_groups * 64, sc + (size_t)row * k_groups * 4 * sizeof(__half)));
-            gg += tmp.bytes; row += *it_n; ++it_n;
+        VxRepackLayout L;
+        if (!vxq_layout(type, n_total, k, &L)) return vx_fail(c, VX_E_UNSUPPORTED, "projection type %d: no device kernel (Q4_0, Q4_K, Q6_K)", type);
+        void *p; VX_TRY(model_alloc(m, L.total, &p));
+        int row = 0;
+        for (size_t i = 0; i < srcs.size(); i++) {
+            VX_TRY(vxq_repack_rows(c, type, srcs[i]->dev, ns[i], k, p, L, row));
+            row += ns[i];
         }
-        w->type = VX_T_Q4_0; w->n = n_total; w->k = k; w->k_pad = k_groups * 128; w->qs = qs; w->sc = sc; w->bytes = gg;
-        m->weight_bytes += gg;
+        vxq_weight_view(type, n_total, k, p, L, w);
+        m->weight_bytes += w->bytes;
         VX_CUDA(c, cudaStreamSynchronize(c->stream));
         for (RawTensor *r : srcs) { cudaFree(r->dev); r->dev = nullptr; }
         return VX_OK;
@@ -959,8 +965,20 @@ int vx_model_finalize(vx_model *m) {
         VX_TRY(norm_f32(raw_at(l, VX_W_POST_FFN_NORM), &L.post_ffn_norm));
         VX_REQUIRE(c, L.attn_norm && L.ffn_norm, "attn_norm / ffn_norm missing");
         if (cf.post_norms) VX_REQUIRE(c, L.post_attn_norm && L.post_ffn_norm, "post norms missing");
-        VX_TRY(build({&raw_at(l, VX_W_WQ), &raw_at(l, VX_W_WK), &raw_at(l, VX_W_WV)}, {qd, kvd, kvd}, cf.hidden, &L.wqkv));
+        {   // fuse consecutive Q/K/V tensors of the same block format (Q4_K_M keeps attn_v in Q6_K)
+            RawTensor *t3[3] = {&raw_at(l, VX_W_WQ), &raw_at(l, VX_W_WK), &raw_at(l, VX_W_WV)};
+            const int n3[3] = {qd, kvd, kvd};
+            for (int i = 0, col = 0; i < 3;) {
+                std::vector<RawTensor *> grp; std::vector<int> ns; int cols = 0, j = i;
+                for (; j < 3 && t3[j]->type == t3[i]->type; j++) { grp.push_back(t3[j]); ns.push_back(n3[j]); cols += n3[j]; }
+                ColW cw; cw.col = col;
+                VX_TRY(build(grp, ns, cf.hidden, &cw.w));
+                L.wqkv.push_back(cw);
+                col += cols; i = j;
+            }
+        }
         VX_TRY(build({&raw_at(l, VX_W_WO)}, {cf.hidden}, qd, &L.wo));
+        if (raw_at(l, VX_W_W1).type != raw_at(l, VX_W_W3).type) return vx_fail(c, VX_E_UNSUPPORTED, "ffn_gate and ffn_up must share a block format");
         VX_TRY(build({&raw_at(l, VX_W_W1), &raw_at(l, VX_W_W3)}, {cf.ffn, cf.ffn}, cf.hidden, &L.w13));
         VX_TRY(build({&raw_at(l, VX_W_W2)}, {cf.hidden}, cf.ffn, &L.w2));
         m->weight_bytes += (size_t)cf.hidden * 4 * (cf.post_norms ? 4 : 2);
@@ -979,7 +997,7 @@ int vx_model_finalize(vx_model *m) {
         void *dup; VX_CUDA(c, cudaMalloc(&dup, emb.bytes));
         VX_CUDA(c, cudaMemcpyAsync(dup, emb.dev, emb.bytes, cudaMemcpyDeviceToDevice, c->stream));
         copy.dev = dup;
-        VX_TRY(build({&copy}, {cf.vocab}, cf.hidden, &m->w_out));
+        VX_TRY(build({&copy}, {cf.vocab}, cf.hidden, &m->w_out));   // frees the duplicate
     }
     m->embed = emb; m->owned.push_back(emb.dev); emb.dev = nullptr;
     m->finalized = true;

@@ -119,25 +119,116 @@ __global__ void repack_q4_0_kernel(const uint8_t *__restrict__ raw, uint4 *__res
     qs[idx] = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-size_t vxq_repack_bytes(int type, int n, int k, size_t *qs_bytes, size_t *sc_bytes) {
-    if (type != VX_T_Q4_0) { *qs_bytes = *sc_bytes = 0; return 0; }
-    int k_groups = ceil_div(k, 128);
-    *qs_bytes = (size_t)n * k_groups * 64;
-    *sc_bytes = ((size_t)n * k_groups * 4 * sizeof(__half) + 255) & ~(size_t)255;
-    return *qs_bytes + *sc_bytes;
+// ------------------------------------------------------------------ repacked K-quant layouts
+// Q4_K (144 B / 256 weights).  Per row and 128-weight group G (half a super-block): uint4 slot[c] holding the nibble
+// words (64-group jj, 16-byte half t') = (0,0),(0,1),(1,0),(1,1), word c of each; the low nibbles of a 64-group are
+// sub-block 2j, the high nibbles sub-block 2j+1 (dequant.go:366-392).  sc: 8 bytes per group {sc[4], min[4]} in the
+// order u = 2jj + nib, unpacked from the 6-bit fields (dequant.go:400-409).  aux: half2 {d, dmin} per super-block.
+__global__ void repack_q4_k_kernel(const uint8_t *__restrict__ raw, uint4 *__restrict__ qs, uint2 *__restrict__ sc,
+                                   __half2 *__restrict__ aux, int n, int k_groups) {
+    long idx = blockIdx.x * (long)blockDim.x + threadIdx.x;
+    if (idx >= (long)n * k_groups * 4) return;
+    int c = (int)(idx & 3); long rg = idx >> 2;
+    int G = (int)(rg % k_groups); long r = rg / k_groups;
+    const uint8_t *blk = raw + ((size_t)r * (k_groups / 2) + G / 2) * 144;
+    const int hf = G & 1;
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint8_t *p = blk + 16 + 32 * (2 * hf + (i >> 1)) + 16 * (i & 1) + 4 * c;
+        w[i] = (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
+    }
+    qs[idx] = make_uint4(w[0], w[1], w[2], w[3]);
+    if (c == 0) {
+        uint32_t s4 = 0, m4 = 0;
+        for (int u = 0; u < 4; u++) {
+            uint8_t a, b2;
+            scale_min_k4(4 * hf + u, blk + 4, a, b2);
+            s4 |= (uint32_t)a << (8 * u); m4 |= (uint32_t)b2 << (8 * u);
+        }
+        sc[(size_t)r * k_groups + G] = make_uint2(s4, m4);
+        if (hf == 0) aux[(size_t)r * (k_groups / 2) + G / 2] =
+            __halves2half2(__ushort_as_half((unsigned short)(blk[0] | (blk[1] << 8))), __ushort_as_half((unsigned short)(blk[2] | (blk[3] << 8))));
+    }
+}
+// Q6_K (210 B / 256 weights).  Per row and 128-weight half G: element e = 16u + p (sub-block u, position p); lane c owns
+// p in {4c..4c+3}.  lo: uint4, word i byte b = low nibble: low 4 bits of element (u=2i, p=4c+b), high nibble: (u=2i+1, p=4c+b).
+// hi: uint2, byte u bits [2b+1:2b] = top 2 bits of element (u, 4c+b).  sc: the 8 int8 scales of the half.  aux: half d.
+__global__ void repack_q6_k_kernel(const uint8_t *__restrict__ raw, uint4 *__restrict__ lo, uint2 *__restrict__ hi, uint2 *__restrict__ sc,
+                                   __half *__restrict__ aux, int n, int k_groups) {
+    long idx = blockIdx.x * (long)blockDim.x + threadIdx.x;
+    if (idx >= (long)n * k_groups * 4) return;
+    int c = (int)(idx & 3); long rg = idx >> 2;
+    int G = (int)(rg % k_groups); long r = rg / k_groups;
+    const uint8_t *blk = raw + ((size_t)r * (k_groups / 2) + G / 2) * 210;
+    const int hf = G & 1;
+    const uint8_t *ql = blk + 64 * hf, *qh = blk + 128 + 32 * hf;
+    auto q6 = [&](int e) -> uint32_t {            // 0..63, dequant.go:300-308
+        int l = e & 31, qd = e >> 5;
+        uint32_t lo4 = (qd & 1) ? ql[l + 32] : ql[l];
+        lo4 = (qd & 2) ? (lo4 >> 4) : (lo4 & 0xF);
+        uint32_t hi2 = (qh[l] >> (2 * qd)) & 3;
+        return lo4 | (hi2 << 4);
+    };
+    uint32_t wl[4] = {0, 0, 0, 0}; uint32_t wh[2] = {0, 0};
+    for (int u = 0; u < 8; u++)
+        for (int b2 = 0; b2 < 4; b2++) {
+            uint32_t v = q6(16 * u + 4 * c + b2);
+            wl[u >> 1] |= (v & 0xF) << (8 * b2 + 4 * (u & 1));
+            wh[u >> 2] |= (v >> 4) << (8 * (u & 3) + 2 * b2);
+        }
+    lo[idx] = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+    hi[idx] = make_uint2(wh[0], wh[1]);
+    if (c == 0) {
+        const uint8_t *s8 = blk + 192 + 8 * hf;
+        sc[(size_t)r * k_groups + G] = make_uint2((uint32_t)s8[0] | ((uint32_t)s8[1] << 8) | ((uint32_t)s8[2] << 16) | ((uint32_t)s8[3] << 24),
+                                                  (uint32_t)s8[4] | ((uint32_t)s8[5] << 8) | ((uint32_t)s8[6] << 16) | ((uint32_t)s8[7] << 24));
+        if (hf == 0) aux[(size_t)r * (k_groups / 2) + G / 2] = __ushort_as_half((unsigned short)(blk[208] | (blk[209] << 8)));
+    }
 }
 
-int vxq_repack(vx_ctx *c, int type, const void *raw_dev, int n, int k, VxWeight *w, void *qs_dst, void *sc_dst) {
-    if (type != VX_T_Q4_0) return vx_fail(c, VX_E_UNSUPPORTED, "repack: only Q4_0 has an MMA layout (type %d)", type);
-    if (k % 32 != 0) return vx_fail(c, VX_E_BAD_ARG, "repack: k=%d is not a multiple of the 32-weight block", k);
-    int k_groups = ceil_div(k, 128);
-    long total = (long)n * k_groups * 4;
-    repack_q4_0_kernel<<<(unsigned)((total + 255) / 256), 256, 0, c->stream>>>((const uint8_t *)raw_dev, (uint4 *)qs_dst, (__half *)sc_dst,
-                                                                              n, k / 32, k_groups);
+// byte offsets of the four arrays of a repacked [n][k] matrix; every array is row-major by weight row
+bool vxq_layout(int type, int n, int k, VxRepackLayout *L) {
+    const size_t kg = (size_t)ceil_div(k, 128);
+    size_t rb[4] = {0, 0, 0, 0};
+    switch (type) {
+    case VX_T_Q4_0: rb[0] = kg * 64; rb[1] = kg * 8; break;
+    case VX_T_Q4_K: rb[0] = kg * 64; rb[1] = kg * 8; rb[2] = kg / 2 * 4; break;
+    case VX_T_Q6_K: rb[0] = kg * 64; rb[1] = kg * 8; rb[2] = kg / 2 * 2; rb[3] = kg * 32; break;
+    default: return false;
+    }
+    size_t off = 0;
+    for (int i = 0; i < 4; i++) { L->row_bytes[i] = rb[i]; L->off[i] = off; off += (rb[i] * n + 255) & ~(size_t)255; }
+    L->total = off;
+    return true;
+}
+
+// repacks n_rows raw GGUF rows into rows [row0, row0 + n_rows) of a layout computed for the whole (concatenated) matrix
+int vxq_repack_rows(vx_ctx *c, int type, const void *raw_dev, int n_rows, int k, void *base, const VxRepackLayout &L, int row0) {
+    const int blk = type == VX_T_Q4_0 ? 32 : 256;
+    if (k % blk != 0) return vx_fail(c, VX_E_BAD_ARG, "repack: k=%d is not a multiple of the %d-weight block", k, blk);
+    const int k_groups = ceil_div(k, 128);
+    char *b0 = (char *)base;
+    void *p[4];
+    for (int i = 0; i < 4; i++) p[i] = b0 + L.off[i] + L.row_bytes[i] * (size_t)row0;
+    long total = (long)n_rows * k_groups * 4;
+    unsigned grid = (unsigned)((total + 255) / 256);
+    switch (type) {
+    case VX_T_Q4_0: repack_q4_0_kernel<<<grid, 256, 0, c->stream>>>((const uint8_t *)raw_dev, (uint4 *)p[0], (__half *)p[1], n_rows, k / 32, k_groups); break;
+    case VX_T_Q4_K: repack_q4_k_kernel<<<grid, 256, 0, c->stream>>>((const uint8_t *)raw_dev, (uint4 *)p[0], (uint2 *)p[1], (__half2 *)p[2], n_rows, k_groups); break;
+    case VX_T_Q6_K: repack_q6_k_kernel<<<grid, 256, 0, c->stream>>>((const uint8_t *)raw_dev, (uint4 *)p[0], (uint2 *)p[3], (uint2 *)p[1], (__half *)p[2], n_rows, k_groups); break;
+    default: return vx_fail(c, VX_E_UNSUPPORTED, "repack: GGUF type %d has no MMA layout", type);
+    }
     VX_LAUNCH_CHECK(c);
-    w->type = type; w->n = n; w->k = k; w->k_pad = k_groups * 128; w->qs = qs_dst; w->sc = sc_dst;
-    w->bytes = (size_t)n * (k / 32) * 18;
     return VX_OK;
+}
+
+void vxq_weight_view(int type, int n, int k, void *base, const VxRepackLayout &L, VxWeight *w) {
+    char *b0 = (char *)base;
+    w->type = type; w->n = n; w->k = k; w->k_pad = ceil_div(k, 128) * 128;
+    w->qs = b0 + L.off[0]; w->sc = b0 + L.off[1]; w->aux = b0 + L.off[2]; w->hi = b0 + L.off[3];
+    const double bpw = type == VX_T_Q4_0 ? 18.0 / 32 : type == VX_T_Q4_K ? 144.0 / 256 : 210.0 / 256;
+    w->bytes = (size_t)((double)n * k * bpw);
 }
 
 // ------------------------------------------------------------------ activation split
@@ -222,16 +313,33 @@ constexpr int GEMM_ROWS = 128;      // weight rows per CTA (8 warps x 16)
 constexpr int GEMM_XLD = 144;       // smem row stride in halfs: 128 + 16 keeps 8-byte fragment loads conflict-free
 constexpr int GEMM_STAGES = 3;
 
+// 6-bit variant of nib2_to_half2: v carries the low nibbles (bits 0-3, 16-19), h6 the top two bits already at bits 4-5 and
+// 20-21 -> half2 {q0 - 32, q1 - 32}, exact
+__device__ __forceinline__ uint32_t q6_to_half2(uint32_t v, uint32_t h6) {
+    uint32_t h = (v & 0x000F000Fu) | h6 | 0x64006400u;      // 1024 + q
+    __half2 r = __hsub2(*reinterpret_cast<__half2 *>(&h), __floats2half2_rn(1056.f, 1056.f));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+
+enum { FMT_Q4_0 = 0, FMT_Q4_K = 1, FMT_Q6_K = 2 };
+struct GemmW { const uint4 *qs; const void *sc; const void *aux; const uint2 *hi; };
+
+// One kernel for the three block formats.  Per 128-weight group a warp runs eight K=16 MMA steps on exact small
+// integers (q-8, q, q-32 in fp16) against the fp16 activation split and applies the block scales in float32 outside the
+// MMA, so the only rounding is float32 accumulation as in the reference:
+//   Q4_0  y += d_b * S_b                               S_b = sum over a 32-block of (q-8)*x     (cpu.go:842-911)
+//   Q4_K  y += fl(d*sc_u) * S_u - fl(dmin*m_u) * X_u    S_u = sum q*x, X_u = sum x over sub-block u (dequant.go:342-396)
+//   Q6_K  y += fl(d*sc_u) * S_u                         S_u = sum (q-32)*x over a 16-weight sub-block (dequant.go:272-331)
 // grid: (ceil(N/128), split_k, ceil(M / (8*NT))).  out layout: [split][M][ld_out]
-template <int NT, int TERMS>
+template <int FMT, int NT, int TERMS>
 __global__ void __launch_bounds__(256, 2)
-gemm_q4_0_kernel(const uint4 *__restrict__ qs, const __half *__restrict__ sc, const __half *__restrict__ xh,
-                 const __half *__restrict__ xl, const float *__restrict__ xscale, float *__restrict__ out,
-                 int M, int N, int k_groups, int groups_per_split, int x_ld, int ld_out, size_t part_stride) {
+gemm_quant_kernel(GemmW W, const __half *__restrict__ xh, const __half *__restrict__ xl, const float *__restrict__ xscale,
+                  const float *__restrict__ xbsum, float *__restrict__ out, int M, int N, int k_groups, int groups_per_split,
+                  int x_ld, int ld_out, size_t part_stride) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int MT = 8 * NT;
-    constexpr int STAGE_HALFS = TERMS * MT * GEMM_XLD;
-    __half *xs = reinterpret_cast<__half *>(smem_raw);
+    constexpr int BS_FLOATS = FMT == FMT_Q4_K ? MT * 4 : 0;                 // per-32-block activation sums of the group
+    constexpr int STAGE_BYTES = TERMS * MT * GEMM_XLD * 2 + BS_FLOATS * 4;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
     const int m0 = blockIdx.z * MT;
@@ -240,20 +348,27 @@ gemm_q4_0_kernel(const uint4 *__restrict__ qs, const __half *__restrict__ sc, co
     const int n_iter = g_end - g_begin;
     const int r0 = blockIdx.x * GEMM_ROWS + warp * 16;
     const int rowA = min(r0 + g, N - 1), rowB = min(r0 + g + 8, N - 1);
-    const uint4 *qA = qs + ((size_t)rowA * k_groups) * 4 + c;
-    const uint4 *qB = qs + ((size_t)rowB * k_groups) * 4 + c;
-    const uint2 *sA = reinterpret_cast<const uint2 *>(sc + (size_t)rowA * k_groups * 4);
-    const uint2 *sB = reinterpret_cast<const uint2 *>(sc + (size_t)rowB * k_groups * 4);
+    const uint4 *qA = W.qs + ((size_t)rowA * k_groups) * 4 + c;
+    const uint4 *qB = W.qs + ((size_t)rowB * k_groups) * 4 + c;
+    const uint2 *sA = reinterpret_cast<const uint2 *>(W.sc) + (size_t)rowA * k_groups;
+    const uint2 *sB = reinterpret_cast<const uint2 *>(W.sc) + (size_t)rowB * k_groups;
+    const uint2 *hA = FMT == FMT_Q6_K ? W.hi + ((size_t)rowA * k_groups) * 4 + c : nullptr;
+    const uint2 *hB = FMT == FMT_Q6_K ? W.hi + ((size_t)rowB * k_groups) * 4 + c : nullptr;
 
     auto load_x = [&](int stage, int grp) {
-        // TERMS * MT rows of 256 bytes = 16 chunks of 16 bytes each
-        constexpr int CHUNKS = TERMS * MT * 16;
+        unsigned char *st = smem_raw + (size_t)stage * STAGE_BYTES;
+        constexpr int CHUNKS = TERMS * MT * 16;      // TERMS * MT rows of 256 bytes = 16 chunks of 16 bytes each
         for (int i = threadIdx.x; i < CHUNKS; i += 256) {
             int term = i / (MT * 16), rem = i % (MT * 16), r = rem >> 4, ch = rem & 15;
             int m = min(m0 + r, M - 1);
             const __half *src = (term == 0 ? xh : xl) + (size_t)m * x_ld + (size_t)grp * 128 + ch * 8;
-            cp_async16(xs + stage * STAGE_HALFS + (term * MT + r) * GEMM_XLD + ch * 8, src);
+            cp_async16(reinterpret_cast<__half *>(st) + (term * MT + r) * GEMM_XLD + ch * 8, src);
         }
+        if (FMT == FMT_Q4_K)
+            for (int r = threadIdx.x; r < MT; r += 256) {
+                int m = min(m0 + r, M - 1);
+                cp_async16(st + TERMS * MT * GEMM_XLD * 2 + r * 16, xbsum + (size_t)m * (x_ld / 32) + (size_t)grp * 4);
+            }
     };
 
     float acc[NT][4];
@@ -262,61 +377,135 @@ gemm_q4_0_kernel(const uint4 *__restrict__ qs, const __half *__restrict__ sc, co
 #pragma unroll
         for (int i = 0; i < 4; i++) acc[t][i] = 0.f;
 
-    // prologue: x stages and the first weight registers
 #pragma unroll
     for (int s = 0; s < GEMM_STAGES - 1; s++) {
         if (s < n_iter) load_x(s, g_begin + s);
         cp_async_commit();
     }
-    uint4 wA = make_uint4(0, 0, 0, 0), wB = wA; uint2 dA = make_uint2(0, 0), dB = dA;
-    if (n_iter > 0) { wA = __ldg(qA + (size_t)g_begin * 4); wB = __ldg(qB + (size_t)g_begin * 4); dA = __ldg(sA + g_begin); dB = __ldg(sB + g_begin); }
+    uint4 wA = make_uint4(0, 0, 0, 0), wB = wA; uint2 dA = make_uint2(0, 0), dB = dA, eA = dA, eB = dA;
+    if (n_iter > 0) {
+        wA = __ldg(qA + (size_t)g_begin * 4); wB = __ldg(qB + (size_t)g_begin * 4); dA = __ldg(sA + g_begin); dB = __ldg(sB + g_begin);
+        if (FMT == FMT_Q6_K) { eA = __ldg(hA + (size_t)g_begin * 4); eB = __ldg(hB + (size_t)g_begin * 4); }
+    }
 
     for (int it = 0; it < n_iter; it++) {
         const int grp = g_begin + it;
-        // prefetch the next group's weights into registers
-        uint4 nA = wA, nB = wB; uint2 ndA = dA, ndB = dB;
-        if (it + 1 < n_iter) { nA = __ldg(qA + (size_t)(grp + 1) * 4); nB = __ldg(qB + (size_t)(grp + 1) * 4); ndA = __ldg(sA + grp + 1); ndB = __ldg(sB + grp + 1); }
+        uint4 nA = wA, nB = wB; uint2 ndA = dA, ndB = dB, neA = eA, neB = eB;
+        if (it + 1 < n_iter) {      // prefetch the next group's weights into registers
+            nA = __ldg(qA + (size_t)(grp + 1) * 4); nB = __ldg(qB + (size_t)(grp + 1) * 4); ndA = __ldg(sA + grp + 1); ndB = __ldg(sB + grp + 1);
+            if (FMT == FMT_Q6_K) { neA = __ldg(hA + (size_t)(grp + 1) * 4); neB = __ldg(hB + (size_t)(grp + 1) * 4); }
+        }
+        // super-block scales (one or two halves per 256 weights); L1/L2 resident, read once per group
+        float supA = 0.f, supB = 0.f, supminA = 0.f, supminB = 0.f;
+        if (FMT == FMT_Q4_K) {
+            const __half2 a2 = reinterpret_cast<const __half2 *>(W.aux)[(size_t)rowA * (k_groups / 2) + (grp >> 1)];
+            const __half2 b2 = reinterpret_cast<const __half2 *>(W.aux)[(size_t)rowB * (k_groups / 2) + (grp >> 1)];
+            supA = __low2float(a2); supminA = __high2float(a2); supB = __low2float(b2); supminB = __high2float(b2);
+        } else if (FMT == FMT_Q6_K) {
+            supA = __half2float(reinterpret_cast<const __half *>(W.aux)[(size_t)rowA * (k_groups / 2) + (grp >> 1)]);
+            supB = __half2float(reinterpret_cast<const __half *>(W.aux)[(size_t)rowB * (k_groups / 2) + (grp >> 1)]);
+        }
         cp_async_wait<GEMM_STAGES - 2>();
         __syncthreads();
-        // refill the stage freed by the previous iteration
-        if (it + GEMM_STAGES - 1 < n_iter) load_x((it + GEMM_STAGES - 1) % GEMM_STAGES, grp + GEMM_STAGES - 1);
+        if (it + GEMM_STAGES - 1 < n_iter) load_x((it + GEMM_STAGES - 1) % GEMM_STAGES, grp + GEMM_STAGES - 1);   // refill the freed stage
         cp_async_commit();
 
-        const __half *xst = xs + (it % GEMM_STAGES) * STAGE_HALFS;
+        const unsigned char *stp = smem_raw + (size_t)(it % GEMM_STAGES) * STAGE_BYTES;
+        const __half *xst = reinterpret_cast<const __half *>(stp);
+        const float *bss = reinterpret_cast<const float *>(stp + TERMS * MT * GEMM_XLD * 2);
         const uint32_t wa[4] = {wA.x, wA.y, wA.z, wA.w}, wb[4] = {wB.x, wB.y, wB.z, wB.w};
         const uint32_t da[2] = {dA.x, dA.y}, db[2] = {dB.x, dB.y};
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            float blk[NT][4];
-#pragma unroll
-            for (int t = 0; t < NT; t++) { blk[t][0] = blk[t][1] = blk[t][2] = blk[t][3] = 0.f; }
-#pragma unroll
-            for (int nib = 0; nib < 2; nib++) {
-                uint32_t va = wa[i] >> (4 * nib), vb = wb[i] >> (4 * nib);
-                uint32_t a[4];
-                a[0] = nib2_to_half2(va); a[2] = nib2_to_half2(va >> 8);
-                a[1] = nib2_to_half2(vb); a[3] = nib2_to_half2(vb >> 8);
-#pragma unroll
-                for (int t = 0; t < NT; t++) {
-                    const __half *p = xst + (8 * t + g) * GEMM_XLD + 32 * i + 16 * nib + 4 * c;
-                    uint2 b = *reinterpret_cast<const uint2 *>(p);
-                    mma_f16(blk[t], a, b.x, b.y);
-                    if (TERMS == 2) {
-                        uint2 bl = *reinterpret_cast<const uint2 *>(p + MT * GEMM_XLD);
-                        mma_f16(blk[t], a, bl.x, bl.y);
-                    }
-                }
-            }
-            uint32_t dpa = da[i >> 1], dpb = db[i >> 1];
-            float fa = __half2float(__ushort_as_half((unsigned short)((i & 1) ? (dpa >> 16) : (dpa & 0xFFFF))));
-            float fb = __half2float(__ushort_as_half((unsigned short)((i & 1) ? (dpb >> 16) : (dpb & 0xFFFF))));
+        const uint32_t ea[2] = {eA.x, eA.y}, eb[2] = {eB.x, eB.y};
+
+        // one scaling unit = the MMA steps that share a scale: two for the 4-bit formats, one for Q6_K
+        auto run_steps = [&](float (&blk)[NT][4], const uint32_t (&a)[4], int xoff) {
 #pragma unroll
             for (int t = 0; t < NT; t++) {
-                acc[t][0] = fmaf(fa, blk[t][0], acc[t][0]); acc[t][1] = fmaf(fa, blk[t][1], acc[t][1]);
-                acc[t][2] = fmaf(fb, blk[t][2], acc[t][2]); acc[t][3] = fmaf(fb, blk[t][3], acc[t][3]);
+                const __half *p = xst + (8 * t + g) * GEMM_XLD + xoff + 4 * c;
+                uint2 b = *reinterpret_cast<const uint2 *>(p);
+                mma_f16(blk[t], a, b.x, b.y);
+                if (TERMS == 2) {
+                    uint2 bl = *reinterpret_cast<const uint2 *>(p + MT * GEMM_XLD);
+                    mma_f16(blk[t], a, bl.x, bl.y);
+                }
+            }
+        };
+        if (FMT == FMT_Q4_0) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {                       // block i of the group; word i holds its 32 nibbles' lane share
+                float blk[NT][4];
+#pragma unroll
+                for (int t = 0; t < NT; t++) { blk[t][0] = blk[t][1] = blk[t][2] = blk[t][3] = 0.f; }
+#pragma unroll
+                for (int nib = 0; nib < 2; nib++) {
+                    uint32_t va = wa[i] >> (4 * nib), vb = wb[i] >> (4 * nib);
+                    uint32_t a[4];
+                    a[0] = nib2_to_half2(va); a[2] = nib2_to_half2(va >> 8);
+                    a[1] = nib2_to_half2(vb); a[3] = nib2_to_half2(vb >> 8);
+                    run_steps(blk, a, 32 * i + 16 * nib);
+                }
+                uint32_t dpa = da[i >> 1], dpb = db[i >> 1];
+                float fa = __half2float(__ushort_as_half((unsigned short)((i & 1) ? (dpa >> 16) : (dpa & 0xFFFF))));
+                float fb = __half2float(__ushort_as_half((unsigned short)((i & 1) ? (dpb >> 16) : (dpb & 0xFFFF))));
+#pragma unroll
+                for (int t = 0; t < NT; t++) {
+                    acc[t][0] = fmaf(fa, blk[t][0], acc[t][0]); acc[t][1] = fmaf(fa, blk[t][1], acc[t][1]);
+                    acc[t][2] = fmaf(fb, blk[t][2], acc[t][2]); acc[t][3] = fmaf(fb, blk[t][3], acc[t][3]);
+                }
+            }
+        } else if (FMT == FMT_Q4_K) {
+#pragma unroll
+            for (int u = 0; u < 4; u++) {                       // sub-block u = 2*jj + nib of the group: elements 32u .. 32u+31
+                const int jj = u >> 1, nib = u & 1;
+                float blk[NT][4];
+#pragma unroll
+                for (int t = 0; t < NT; t++) { blk[t][0] = blk[t][1] = blk[t][2] = blk[t][3] = 0.f; }
+#pragma unroll
+                for (int tp = 0; tp < 2; tp++) {
+                    uint32_t va = wa[2 * jj + tp] >> (4 * nib), vb = wb[2 * jj + tp] >> (4 * nib);
+                    uint32_t a[4];       // unsigned nibbles: undo the -8 of nib2_to_half2 by using the raw magic form
+                    uint32_t ha = (va & 0x000F000Fu) | 0x64006400u, hb2 = ((va >> 8) & 0x000F000Fu) | 0x64006400u;
+                    uint32_t hc = (vb & 0x000F000Fu) | 0x64006400u, hd = ((vb >> 8) & 0x000F000Fu) | 0x64006400u;
+                    const __half2 k1024 = __floats2half2_rn(1024.f, 1024.f);
+                    __half2 r0 = __hsub2(*reinterpret_cast<__half2 *>(&ha), k1024), r2 = __hsub2(*reinterpret_cast<__half2 *>(&hb2), k1024);
+                    __half2 r1 = __hsub2(*reinterpret_cast<__half2 *>(&hc), k1024), r3 = __hsub2(*reinterpret_cast<__half2 *>(&hd), k1024);
+                    a[0] = *reinterpret_cast<uint32_t *>(&r0); a[2] = *reinterpret_cast<uint32_t *>(&r2);
+                    a[1] = *reinterpret_cast<uint32_t *>(&r1); a[3] = *reinterpret_cast<uint32_t *>(&r3);
+                    run_steps(blk, a, 32 * u + 16 * tp);
+                }
+                const float fa = __fmul_rn(supA, (float)((da[0] >> (8 * u)) & 0xFF)), ma = __fmul_rn(supminA, (float)((da[1] >> (8 * u)) & 0xFF));
+                const float fb = __fmul_rn(supB, (float)((db[0] >> (8 * u)) & 0xFF)), mb = __fmul_rn(supminB, (float)((db[1] >> (8 * u)) & 0xFF));
+#pragma unroll
+                for (int t = 0; t < NT; t++) {
+                    const float x0 = bss[(8 * t + 2 * c) * 4 + u], x1 = bss[(8 * t + 2 * c + 1) * 4 + u];
+                    acc[t][0] += fa * blk[t][0] - ma * x0; acc[t][1] += fa * blk[t][1] - ma * x1;
+                    acc[t][2] += fb * blk[t][2] - mb * x0; acc[t][3] += fb * blk[t][3] - mb * x1;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < 8; u++) {                       // 16-weight sub-block u: elements 16u .. 16u+15, one MMA step
+                float blk[NT][4];
+#pragma unroll
+                for (int t = 0; t < NT; t++) { blk[t][0] = blk[t][1] = blk[t][2] = blk[t][3] = 0.f; }
+                const uint32_t va = wa[u >> 1] >> (4 * (u & 1)), vb = wb[u >> 1] >> (4 * (u & 1));
+                const uint32_t ha = (ea[u >> 2] >> (8 * (u & 3))) & 0xFF, hb2 = (eb[u >> 2] >> (8 * (u & 3))) & 0xFF;
+                uint32_t a[4];
+                a[0] = q6_to_half2(va, ((ha & 0x03) << 4) | ((ha & 0x30) << 16));
+                a[2] = q6_to_half2(va >> 8, ((ha & 0x0C) << 2) | ((ha & 0xC0) << 14));
+                a[1] = q6_to_half2(vb, ((hb2 & 0x03) << 4) | ((hb2 & 0x30) << 16));
+                a[3] = q6_to_half2(vb >> 8, ((hb2 & 0x0C) << 2) | ((hb2 & 0xC0) << 14));
+                run_steps(blk, a, 16 * u);
+                const float fa = __fmul_rn(supA, (float)(int)(int8_t)((da[u >> 2] >> (8 * (u & 3))) & 0xFF));
+                const float fb = __fmul_rn(supB, (float)(int)(int8_t)((db[u >> 2] >> (8 * (u & 3))) & 0xFF));
+#pragma unroll
+                for (int t = 0; t < NT; t++) {
+                    acc[t][0] = fmaf(fa, blk[t][0], acc[t][0]); acc[t][1] = fmaf(fa, blk[t][1], acc[t][1]);
+                    acc[t][2] = fmaf(fb, blk[t][2], acc[t][2]); acc[t][3] = fmaf(fb, blk[t][3], acc[t][3]);
+                }
             }
         }
-        wA = nA; wB = nB; dA = ndA; dB = ndB;
+        wA = nA; wB = nB; dA = ndA; dB = ndB; eA = neA; eB = neB;
     }
     cp_async_wait<0>();
 
@@ -336,18 +525,31 @@ gemm_q4_0_kernel(const uint4 *__restrict__ qs, const __half *__restrict__ sc, co
     }
 }
 
-template <int NT, int TERMS>
+template <int FMT, int NT, int TERMS>
 static int gemm_launch_nt(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int split,
                           int gps, size_t part_stride) {
     constexpr int MT = 8 * NT;
-    size_t smem = (size_t)GEMM_STAGES * TERMS * MT * GEMM_XLD * sizeof(__half);
-    auto kern = gemm_q4_0_kernel<NT, TERMS>;
+    size_t smem = (size_t)GEMM_STAGES * (TERMS * MT * GEMM_XLD * sizeof(__half) + (FMT == FMT_Q4_K ? MT * 16 : 0));
+    auto kern = gemm_quant_kernel<FMT, NT, TERMS>;
     if (smem > 48 * 1024) VX_CUDA(c, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(ceil_div(w.n, GEMM_ROWS), split, ceil_div(m, MT));
-    kern<<<grid, 256, smem, c->stream>>>((const uint4 *)w.qs, (const __half *)w.sc, x.hi, x.lo, x.scale, out, m, w.n,
-                                         w.k_pad / 128, gps, x.k_pad, ld_out, part_stride);
+    GemmW W{(const uint4 *)w.qs, w.sc, w.aux, (const uint2 *)w.hi};
+    kern<<<grid, 256, smem, c->stream>>>(W, x.hi, x.lo, x.scale, x.bsum, out, m, w.n, w.k_pad / 128, gps, x.k_pad, ld_out, part_stride);
     VX_LAUNCH_CHECK(c);
     return VX_OK;
+}
+template <int FMT>
+static int gemm_launch_fmt(vx_ctx *c, int nt, int terms, const VxWeight &w, const VxSplit &x, int m, float *dst, int ld, int split, int gps,
+                           size_t pstride) {
+#define VX_GEMM_CASE(NTV)                                                                                   \
+    case NTV:                                                                                               \
+        return terms == 2 ? gemm_launch_nt<FMT, NTV, 2>(c, w, x, m, dst, ld, split, gps, pstride)           \
+                          : gemm_launch_nt<FMT, NTV, 1>(c, w, x, m, dst, ld, split, gps, pstride);
+    switch (nt) {
+        VX_GEMM_CASE(1) VX_GEMM_CASE(2) VX_GEMM_CASE(4) VX_GEMM_CASE(8)
+    }
+#undef VX_GEMM_CASE
+    return VX_E_BAD_ARG;
 }
 
 static int g_gemm_terms = 2;   // 2: x = hi + lo (float32-faithful); 1: fp16 activations only
@@ -356,9 +558,10 @@ static int g_tc_min_rows = 17;  // batches of at least this many rows use the tc
 // out receives [m][ld_out] when *n_parts_out == 1, otherwise `parts` holds [n_parts][m][w.n]
 int vxq_gemm(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out,
              float *parts, size_t parts_cap_floats) {
-    if (w.type != VX_T_Q4_0) return vx_fail(c, VX_E_UNSUPPORTED, "projection: weight type %d has no MMA kernel", w.type);
+    if (w.type != VX_T_Q4_0 && w.type != VX_T_Q4_K && w.type != VX_T_Q6_K)
+        return vx_fail(c, VX_E_UNSUPPORTED, "projection: weight type %d has no MMA kernel", w.type);
     if (x.k_pad != w.k_pad) return vx_fail(c, VX_E_BAD_ARG, "projection: activation row stride %d != weight k_pad %d", x.k_pad, w.k_pad);
-    if (g_tc_min_rows > 0 && m >= g_tc_min_rows && g_gemm_terms == 2)
+    if (w.type == VX_T_Q4_0 && g_tc_min_rows > 0 && m >= g_tc_min_rows && g_gemm_terms == 2)
         return vxq_gemm_tc(c, w, x, m, out, ld_out, n_parts_out, parts, parts_cap_floats);
     int k_groups = w.k_pad / 128;
     int nt = m <= 8 ? 1 : m <= 16 ? 2 : m <= 32 ? 4 : 8;
@@ -383,16 +586,11 @@ int vxq_gemm(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, 
     int ld = split > 1 ? w.n : ld_out;
     size_t pstride = (size_t)m * w.n;
     *n_parts_out = split;
-    int terms = g_gemm_terms;
-#define VX_GEMM_CASE(NTV)                                                                                   \
-    case NTV:                                                                                               \
-        return terms == 2 ? gemm_launch_nt<NTV, 2>(c, w, x, m, dst, ld, split, gps, pstride)                \
-                          : gemm_launch_nt<NTV, 1>(c, w, x, m, dst, ld, split, gps, pstride);
-    switch (nt) {
-        VX_GEMM_CASE(1) VX_GEMM_CASE(2) VX_GEMM_CASE(4) VX_GEMM_CASE(8)
+    switch (w.type) {
+    case VX_T_Q4_0: return gemm_launch_fmt<FMT_Q4_0>(c, nt, g_gemm_terms, w, x, m, dst, ld, split, gps, pstride);
+    case VX_T_Q4_K: return gemm_launch_fmt<FMT_Q4_K>(c, nt, g_gemm_terms, w, x, m, dst, ld, split, gps, pstride);
+    default:        return gemm_launch_fmt<FMT_Q6_K>(c, nt, g_gemm_terms, w, x, m, dst, ld, split, gps, pstride);
     }
-#undef VX_GEMM_CASE
-    return VX_E_BAD_ARG;
 }
 
 __global__ void reduce_parts_kernel(const float *__restrict__ parts, int n_parts, int m, int n, float *__restrict__ out, int ld_out) {
@@ -463,23 +661,26 @@ int vx_synth_q4_0(vx_ctx *c, vx_dptr dst, int64_t n, uint64_t seed, float sigma)
     return VX_OK;
 }
 
-// QuantizedMatMul.MatMulQ4_0 on raw GGUF bytes: repack + split into scratch, then the MMA kernel.
-int vx_matmul_q4_0(vx_ctx *c, vx_dptr a, vx_dptr b_raw, vx_dptr out, int m, int n, int k) {
+// QuantizedMatMul on raw GGUF bytes: repack + split into the context scratch, then the MMA kernel.
+static int matmul_quant(vx_ctx *c, int type, vx_dptr a, vx_dptr b_raw, vx_dptr out, int m, int n, int k) {
     if (!c) return VX_E_BAD_ARG;
     VxGuard g(c);
     if (m <= 0 || n <= 0) return VX_OK;
     VX_REQUIRE(c, a && b_raw && out, "nil device pointer");
-    VX_REQUIRE(c, k > 0 && k % 32 == 0, "k must be a positive multiple of 32");
-    size_t qsb, scb, hi, lo, so, bo; int kp;
-    size_t wbytes = vxq_repack_bytes(VX_T_Q4_0, n, k, &qsb, &scb);
+    const int blk = type == VX_T_Q4_0 ? 32 : 256;
+    if (k <= 0 || k % blk != 0) return vx_fail(c, VX_E_BAD_ARG, "k=%d must be a positive multiple of %d", k, blk);
+    VxRepackLayout L;
+    vxq_layout(type, n, k, &L);
+    size_t hi, lo, so, bo; int kp;
     size_t sbytes = vxq_split_bytes(m, k, &hi, &lo, &so, &bo, &kp);
     size_t parts_floats = (size_t)8 * m * n;
     void *base;
-    VX_TRY(vx_scratch(c, wbytes + sbytes + parts_floats * 4 + 1024, &base));
+    VX_TRY(vx_scratch(c, L.total + sbytes + parts_floats * 4 + 1024, &base));
     char *p = (char *)base;
+    VX_TRY(vxq_repack_rows(c, type, dp<void>(b_raw), n, k, p, L, 0));
     VxWeight w;
-    VX_TRY(vxq_repack(c, VX_T_Q4_0, dp<void>(b_raw), n, k, &w, p, p + qsb));
-    char *sp = p + wbytes;
+    vxq_weight_view(type, n, k, p, L, &w);
+    char *sp = p + L.total;
     VxSplit s{(__half *)(sp + hi), (__half *)(sp + lo), (float *)(sp + so), (float *)(sp + bo), kp};
     VX_TRY(vxq_split_rows(c, dp<float>(a), m, k, k, s));
     float *parts = (float *)(sp + sbytes);
@@ -488,22 +689,9 @@ int vx_matmul_q4_0(vx_ctx *c, vx_dptr a, vx_dptr b_raw, vx_dptr out, int m, int 
     if (np > 1) VX_TRY(vxq_reduce_parts(c, parts, np, m, n, dp<float>(out), n));
     return VX_OK;
 }
-
-// K-quant projections at the interface level: bit-exact dequantisation to float32 followed by the
-// float32 transposed matmul -- the reference's own CPU route for K-quants (runtime/loader.go:214-271).
-static int matmul_kquant(vx_ctx *c, int type, vx_dptr a, vx_dptr b_raw, vx_dptr out, int m, int n, int k) {
-    if (!c) return VX_E_BAD_ARG;
-    VxGuard g(c);
-    if (m <= 0 || n <= 0) return VX_OK;
-    VX_REQUIRE(c, a && b_raw && out, "nil device pointer");
-    VX_REQUIRE(c, k > 0 && k % 256 == 0, "k must be a positive multiple of 256");
-    void *base;
-    VX_TRY(vx_scratch(c, (size_t)n * k * 4, &base));
-    VX_TRY(dequant_launch(c, type, dp<void>(b_raw), (float *)base, (int64_t)n * k));
-    return vx_matmul_f32_t(c, a, (vx_dptr)(uintptr_t)base, out, m, n, k);
-}
-int vx_matmul_q4_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k) { return matmul_kquant(c, VX_T_Q4_K, a, b, out, m, n, k); }
-int vx_matmul_q6_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k) { return matmul_kquant(c, VX_T_Q6_K, a, b, out, m, n, k); }
+int vx_matmul_q4_0(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k) { return matmul_quant(c, VX_T_Q4_0, a, b, out, m, n, k); }
+int vx_matmul_q4_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k) { return matmul_quant(c, VX_T_Q4_K, a, b, out, m, n, k); }
+int vx_matmul_q6_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k) { return matmul_quant(c, VX_T_Q6_K, a, b, out, m, n, k); }
 
 int vx_set_tc_min_rows(int rows) { g_tc_min_rows = rows; return VX_OK; }
 int vx_set_gemm_terms(int terms) { if (terms == 1 || terms == 2) { g_gemm_terms = terms; return VX_OK; } return VX_E_BAD_ARG; }
