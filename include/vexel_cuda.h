@@ -222,6 +222,30 @@ int vx_set_gemm_terms(int terms);
 /* batches with at least this many rows run the projections on the tcgen05 kernel (default 17; 0 = always the mma.sync kernel) */
 int vx_set_tc_min_rows(int rows);
 
+/* ------------------------------------------------------------------ continuous-batching scheduler
+ * The host loop of inference/scheduler (Scheduler.step / runDecodeStep, scheduler/scheduler.go:168-483; Sequence state
+ * machine, scheduler/sequence.go:15-80) over vx_prefill / vx_decode_step, for embedders without the Go scheduler.  Greedy
+ * sampling; the batch is formed in arrival order; a prompt that does not fit the free blocks waits. */
+typedef struct vx_sched vx_sched;
+typedef struct {
+    int max_batch_size;   /* Config.MaxBatchSize, scheduler.go:23 */
+    int max_sequences;    /* Config.MaxSequences :24 (enforced here; 0 = unlimited) */
+    int max_tokens;       /* Config.MaxTokens :25 (0 = unlimited) */
+    int eos_token;        /* stop token id, < 0 = none */
+} vx_sched_config;
+typedef struct {          /* SchedulerMetrics, scheduler.go:30-38 */
+    int active_sequences, completed_sequences, total_tokens, prefill_tokens, decode_tokens;
+    double prefill_seconds, decode_seconds;
+} vx_sched_metrics;
+int vx_sched_create(vx_model *m, const vx_sched_config *cfg, vx_sched **out);
+int vx_sched_destroy(vx_sched *s);
+int vx_sched_add_sequence(vx_sched *s, int64_t id, const int32_t *prompt, int n_prompt, int max_tokens);   /* AddSequence :645-676 */
+int vx_sched_remove_sequence(vx_sched *s, int64_t id);                                                     /* RemoveSequence :690-698 */
+int vx_sched_step(vx_sched *s, int *n_active_out);                                                         /* step :168-203 */
+int vx_sched_poll(vx_sched *s, int64_t id, int32_t *out, int cap, int *n_out, int *finished);              /* TokenChan drain */
+int vx_sched_get_metrics(vx_sched *s, vx_sched_metrics *out);                                                /* Metrics :475-481 */
+int vx_model_max_blocks(vx_model *m);   /* physical blocks per layer of the model's pool */
+
 #ifdef __cplusplus
 }
 #endif

@@ -229,3 +229,44 @@ def test_full_size_round_trip_properties(be):
     assert np.array_equal(got.view(np.uint32), O.dequant(O.Q4_0, raw, n).view(np.uint32))
     assert abs(float(got.std()) - 0.02) < 0.003 and abs(float(got.mean())) < 1e-3
     be.Free(d_raw); be.ResetPool()
+
+
+def test_continuous_batching_trace(be):
+    """Requests arriving over time through the scheduler (max batch 4): every request's greedy stream equals the oracle's
+    stand-alone greedy decode of the same prompt, whatever batch it happened to share (scheduler/batched_decode_test.go idea)."""
+    spec = small_llama()
+    om, gm = build_pair(be, spec, 21, max_blocks=96, max_seqs=8, max_blocks_per_seq=16)
+    rng = np.random.default_rng(8)
+    n_req = 10
+    prompts = [rng.integers(0, spec.vocab, int(rng.integers(3, 60))).astype(np.int32) for _ in range(n_req)]
+    out_len = [int(rng.integers(4, 20)) for _ in range(n_req)]
+    arrive = sorted(int(x) for x in rng.integers(0, 25, n_req))          # scheduler step at which each request arrives
+    sched = capi.Scheduler(gm, max_batch_size=4, max_sequences=8)
+    got = {i: [] for i in range(n_req)}
+    done = set()
+    step = 0
+    while len(done) < n_req and step < 400:
+        for i in range(n_req):
+            if arrive[i] == step:
+                sched.AddSequence(100 + i, prompts[i], max_tokens=out_len[i])
+        sched.step()
+        for i in range(n_req):
+            if arrive[i] <= step and i not in done:
+                toks, fin = sched.poll(100 + i)
+                got[i].extend(int(t) for t in toks)
+                if fin:
+                    done.add(i)
+        step += 1
+    assert len(done) == n_req
+    agree = total = 0
+    for i in range(n_req):
+        want = [O.argmax(om.forward(500 + i, prompts[i], 0)[0])]
+        for s in range(out_len[i] - 1):
+            want.append(O.argmax(om.forward(500 + i, np.int32([want[-1]]), len(prompts[i]) + s)[0]))
+        assert len(got[i]) == out_len[i]
+        agree += sum(int(a == b) for a, b in zip(got[i], want)); total += out_len[i]
+    assert agree / total >= 0.99, (agree, total)
+    met = sched.Metrics()
+    assert met.completed_sequences == n_req and met.prefill_tokens == sum(len(p) for p in prompts)
+    assert met.decode_tokens == sum(out_len) - n_req and gm.pool_stats()[1] == gm.pool_stats()[0]   # every block returned
+    sched.close(); gm.close()

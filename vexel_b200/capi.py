@@ -33,6 +33,15 @@ class ModelConfig(C.Structure):
         ("max_blocks", C.c_int), ("max_seqs", C.c_int), ("max_batch_tokens", C.c_int), ("max_blocks_per_seq", C.c_int)]
 
 
+class SchedConfig(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("max_batch_size", "max_sequences", "max_tokens", "eos_token")]
+
+
+class SchedMetrics(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("active_sequences", "completed_sequences", "total_tokens", "prefill_tokens", "decode_tokens")] + [
+        ("prefill_seconds", C.c_double), ("decode_seconds", C.c_double)]
+
+
 _vp, _i, _i64, _f, _u64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_uint64, C.c_size_t
 _D = C.c_uint64  # vx_dptr
 
@@ -82,7 +91,11 @@ SIGNATURES = {
     "vx_model_kernel_time": [_vp, _i, _i, C.POINTER(_f), C.POINTER(_u64)],
     "vx_synth_q4_0": [_vp, _D, _i64, _u64, _f],
     "vx_pool_shuffle_free_list": [_vp, C.c_uint32], "vx_model_weight_bytes": [_vp, C.POINTER(_u64)],
-    "vx_set_gemm_terms": [_i], "vx_set_tc_min_rows": [_i],
+    "vx_set_gemm_terms": [_i], "vx_set_tc_min_rows": [_i], "vx_model_max_blocks": [_vp],
+    "vx_sched_create": [_vp, C.POINTER(SchedConfig), C.POINTER(_vp)], "vx_sched_destroy": [_vp],
+    "vx_sched_add_sequence": [_vp, _i64, _vp, _i, _i], "vx_sched_remove_sequence": [_vp, _i64],
+    "vx_sched_step": [_vp, C.POINTER(_i)], "vx_sched_poll": [_vp, _i64, _vp, _i, C.POINTER(_i), C.POINTER(_i)],
+    "vx_sched_get_metrics": [_vp, C.POINTER(SchedMetrics)],
 }
 _RESTYPE = {"vx_last_error": C.c_char_p}
 
@@ -324,3 +337,35 @@ class Model:
 
     def weight_bytes(self):
         b = C.c_uint64(); self._ck(self.lib.vx_model_weight_bytes(self.h, C.byref(b))); return b.value
+
+
+class Scheduler:
+    """vx_sched_*: the continuous-batching loop of inference/scheduler over the batched fast path."""
+
+    def __init__(self, model: Model, max_batch_size, max_sequences=0, max_tokens=0, eos_token=-1):
+        self.m, self.lib = model, model.lib
+        cfg = SchedConfig(max_batch_size, max_sequences, max_tokens, eos_token)
+        h = C.c_void_p()
+        model._ck(self.lib.vx_sched_create(model.h, C.byref(cfg), C.byref(h)))
+        self.h = h
+
+    def close(self):
+        if self.h:
+            self.lib.vx_sched_destroy(self.h); self.h = None
+
+    def AddSequence(self, seq_id, prompt, max_tokens=0):
+        p = np.ascontiguousarray(prompt, np.int32)
+        self.m._ck(self.lib.vx_sched_add_sequence(self.h, seq_id, _np_ptr(p), p.size, max_tokens))
+
+    def RemoveSequence(self, seq_id): self.m._ck(self.lib.vx_sched_remove_sequence(self.h, seq_id))
+
+    def step(self):
+        n = C.c_int(); self.m._ck(self.lib.vx_sched_step(self.h, C.byref(n))); return n.value
+
+    def poll(self, seq_id, cap=4096):
+        buf = np.empty(cap, np.int32); n, fin = C.c_int(), C.c_int()
+        self.m._ck(self.lib.vx_sched_poll(self.h, seq_id, _np_ptr(buf), cap, C.byref(n), C.byref(fin)))
+        return buf[:n.value].copy(), bool(fin.value)
+
+    def Metrics(self):
+        m = SchedMetrics(); self.m._ck(self.lib.vx_sched_get_metrics(self.h, C.byref(m))); return m

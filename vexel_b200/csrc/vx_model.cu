@@ -1300,6 +1300,8 @@ int vx_model_kernel_time(vx_model *m, int which, int enable, float *ms, uint64_t
     return VX_OK;
 }
 
+int vx_model_max_blocks(vx_model *m) { return m ? m->cfg.max_blocks : 0; }
+
 int vx_model_weight_bytes(vx_model *m, uint64_t *bytes) {
     if (!m || !bytes) return VX_E_BAD_ARG;
     *bytes = m->weight_bytes;
