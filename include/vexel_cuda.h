@@ -122,6 +122,15 @@ int vx_sdpa_paged_decode_multiquery(vx_ctx *, vx_dptr q, vx_dptr pool, vx_dptr b
                                     vx_dptr kv_lens_i32, int n_blocks, int block_size, int n_q_heads,
                                     int n_kv_heads, int head_dim, float scale, int query_len,
                                     int pool_is_f16);                                                    /* SDPAPagedDecodeMultiquery :463 */
+/* No counterpart in the reference.  vx_sdpa_paged_decode_f16 for callers that must not allocate while they attend (all
+ * HBM already given to the KV pool, a latency-critical section, a non-reentrant allocator): the split-K scratch is a fixed
+ * 4 MiB device array inside the library instead of the context's growable scratch, and the call makes no cudaMalloc /
+ * cudaFree / host heap allocation.  Sizes beyond the array (see the definition) are refused with VX_E_BAD_ARG.  The first
+ * call on a device resolves the array's address and should come before any stream capture; calls that overlap on the GPU
+ * share the array and race. */
+int vx_sdpa_paged_decode_f16_noalloc(vx_ctx *, vx_dptr q, vx_dptr pool, vx_dptr block_table_i32, vx_dptr out,
+                                     int n_blocks, int block_size, int n_q_heads, int n_kv_heads, int head_dim,
+                                     float scale, int tokens_in_last_block);
 /* the same paged kernel with the Gemma-2 variants the CPU branch applies
  * (runtime/block.go:925-953): softcap > 0 and/or kv_start (first attended position) per query */
 int vx_sdpa_paged_decode_ex(vx_ctx *, vx_dptr q, vx_dptr pool, vx_dptr block_table_i32, vx_dptr out,

@@ -71,6 +71,7 @@ SIGNATURES = {
     "vx_reshape_paged_kv_f16": [_vp, _D, _D, _D, _D, _i, _i, _i, _i, _i],
     "vx_sdpa_paged_decode": [_vp, _D, _D, _D, _D, _i, _i, _i, _i, _i, _f, _i],
     "vx_sdpa_paged_decode_f16": [_vp, _D, _D, _D, _D, _i, _i, _i, _i, _i, _f, _i],
+    "vx_sdpa_paged_decode_f16_noalloc": [_vp, _D, _D, _D, _D, _i, _i, _i, _i, _i, _f, _i],
     "vx_sdpa_paged_decode_batched": [_vp, _D, _D, C.POINTER(_D), _D, _i, _i, _i, _i, _i, _i, _f, C.POINTER(_i), _i],
     "vx_sdpa_paged_decode_multiquery": [_vp, _D, _D, _D, _D, _D, _i, _i, _i, _i, _i, _f, _i, _i],
     "vx_sdpa_paged_decode_ex": [_vp, _D, _D, _D, _D, _i, _i, _i, _i, _i, _i, _f, _f, _i],
@@ -231,6 +232,10 @@ class Backend:
 
     def SDPAPagedDecodeF16(self, q, pool, table, out, n_blocks, bs, hq, hkv, d, scale, tokens_in_last):
         self._ck(self.lib.vx_sdpa_paged_decode_f16(self.h, q, pool, table, out, n_blocks, bs, hq, hkv, d, scale, tokens_in_last))
+
+    def SDPAPagedDecodeF16NoAlloc(self, q, pool, table, out, n_blocks, bs, hq, hkv, d, scale, tokens_in_last):
+        """vx_sdpa_paged_decode_f16 with its scratch in a fixed device array: the call allocates nothing."""
+        self._ck(self.lib.vx_sdpa_paged_decode_f16_noalloc(self.h, q, pool, table, out, n_blocks, bs, hq, hkv, d, scale, tokens_in_last))
 
     def SDPAPagedDecodeBatched(self, q, pool, tables, out, batch, max_blocks, bs, hq, hkv, d, scale, seq_lens, f16=True):
         tb = (_D * batch)(*tables); sl = (_i * batch)(*seq_lens)

@@ -8,6 +8,8 @@
 // a CTA of four warps handles one work item for one KV head, each warp streaming whole 16-token pages
 // with 128-bit loads (a token's head slice is D*2 contiguous bytes), online softmax with warp shuffles,
 // then a four-way merge in shared memory.  Rows cut into several chunks are finished by a merge kernel.
+#include <algorithm>
+
 #include "vx_paged.cuh"
 
 // ------------------------------------------------------------------ scatter (ReshapePagedKV[F16])
@@ -330,6 +332,45 @@ static int paged_iface(vx_ctx *c, vx_dptr q, vx_dptr pool, int pool_is_f16, cons
     return vxp_attention(c, a);
 }
 
+// ------------------------------------------------------------------ decode attention without any allocation
+// Some callers must not allocate device memory when they attend: a serving process that has handed every free byte of
+// HBM to its KV pool, a host thread inside a latency-critical section, or an embedder whose allocator is not reentrant.
+// For them the split-K scratch of the paged decode (block-table pointer, row descriptors, work list, partial results)
+// lives in this fixed array.  Every GPU that loads the library holds these 4 MiB until the process exits.
+constexpr size_t VX_NOALLOC_SCRATCH_BYTES = 4u << 20;
+constexpr int VX_NOALLOC_MAX_WORK = 1024;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[VX_NOALLOC_SCRATCH_BYTES];
+// The array's name is a host-side stand-in in host code, not a device address: the address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static void *g_noalloc_dev_ptr[64] = {nullptr};
+
+struct NoAllocLayout { size_t tab, slot, ks, kl, rws, nw, work, part; };
+static NoAllocLayout noalloc_layout() {
+    NoAllocLayout L;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off += (bytes + 255) & ~(size_t)255; return o; };
+    L.tab = take(sizeof(void *)); L.slot = take(4); L.ks = take(4); L.kl = take(4); L.rws = take(8); L.nw = take(4);
+    L.work = take(sizeof(int4) * VX_NOALLOC_MAX_WORK); L.part = off;
+    return L;
+}
+// fills the single-row descriptors from kernel arguments (no host-to-device copy) and builds the work list
+__global__ void noalloc_setup_kernel(unsigned char *scratch, NoAllocLayout L, const int32_t *table, int kv_len, int block_size, int chunk_pages) {
+    __shared__ int tmp[33];
+    __shared__ int ovf;
+    if (threadIdx.x == 0) {
+        ovf = 0;
+        *reinterpret_cast<const int32_t **>(scratch + L.tab) = table;
+        *reinterpret_cast<int32_t *>(scratch + L.slot) = 0;
+        *reinterpret_cast<int32_t *>(scratch + L.ks) = 0;
+        *reinterpret_cast<int32_t *>(scratch + L.kl) = kv_len;
+    }
+    __syncthreads();
+    int n = vx_build_work(1, reinterpret_cast<const int32_t *>(scratch + L.ks), reinterpret_cast<const int32_t *>(scratch + L.kl), block_size,
+                          chunk_pages, reinterpret_cast<int4 *>(scratch + L.work), reinterpret_cast<int32_t *>(scratch + L.rws),
+                          VX_NOALLOC_MAX_WORK, &ovf, tmp);
+    if (threadIdx.x == 0) *reinterpret_cast<int32_t *>(scratch + L.nw) = n;
+}
+
 template <typename T>
 static int reshape_launch(vx_ctx *c, vx_dptr src, vx_dptr pool, vx_dptr pt, vx_dptr bo, int n_tokens, int hkv, int d, int bs, int is_v) {
     if (!c) return VX_E_BAD_ARG;
@@ -404,6 +445,51 @@ int vx_sdpa_paged_decode_multiquery(vx_ctx *c, vx_dptr q, vx_dptr pool, vx_dptr 
     std::vector<int> slot(query_len, 0);
     return paged_iface(c, q, pool, f16, &table, slot.data(), nullptr, nullptr, kv_lens, n_blocks * bs, out, query_len, 1, bs, hq, hkv, d,
                        scale, 0.f);
+}
+
+
+// Same result as vx_sdpa_paged_decode_f16, but the call allocates nothing: no cudaMalloc / cudaFree, no growth of the
+// context scratch, no host heap.  Limits: head_dim <= 256, n_q_heads * (head_dim + 2) * 4 bytes per split-K chunk must fit
+// the 4 MiB array (the number of chunks shrinks to fit; at worst one chunk per row), n_blocks <= 65536; anything larger is
+// refused with VX_E_BAD_ARG.  The first call on a device looks up the array's address (cudaGetSymbolAddress); make that
+// first call before starting a stream capture.  All calls share the one array, which keeps the previous call's contents
+// (nothing in it needs to start at zero: every field is written before it is read), so two calls that overlap on the GPU
+// -- different streams or contexts of one process -- race.
+int vx_sdpa_paged_decode_f16_noalloc(vx_ctx *c, vx_dptr q, vx_dptr pool, vx_dptr table, vx_dptr out, int n_blocks, int bs, int hq,
+                                     int hkv, int d, float scale, int til) {
+    if (!c) return VX_E_BAD_ARG;
+    VxGuard g(c);
+    VX_REQUIRE(c, q && pool && out && table, "nil device pointer");
+    VX_REQUIRE(c, n_blocks > 0 && n_blocks <= 65536 && bs > 0 && til > 0 && til <= bs, "bad block table arguments (n_blocks <= 65536)");
+    VX_REQUIRE(c, hq > 0 && hkv > 0 && hq % hkv == 0 && d > 0 && d <= 256, "bad head configuration (head_dim <= 256)");
+    VX_REQUIRE(c, c->device >= 0 && c->device < 64, "device index out of range");
+    if (!g_noalloc_dev_ptr[c->device]) {     // once per device, with that device current (VxGuard made it so)
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) return vx_cuda_fail(c, e, "cudaGetSymbolAddress(no-alloc scratch)");
+        g_noalloc_dev_ptr[c->device] = p;
+    }
+    unsigned char *sp = static_cast<unsigned char *>(g_noalloc_dev_ptr[c->device]);
+    const NoAllocLayout L = noalloc_layout();
+    const size_t per_chunk = (size_t)hq * (d + 2) * sizeof(float);
+    if (L.part + per_chunk > VX_NOALLOC_SCRATCH_BYTES)
+        return vx_fail(c, VX_E_BAD_ARG, "vx_sdpa_paged_decode_f16_noalloc: %d heads x head_dim %d exceed the %zu-byte scratch", hq, d, VX_NOALLOC_SCRATCH_BYTES);
+    const int kv_len = (n_blocks - 1) * bs + til;
+    int max_chunks = (int)std::min<size_t>((VX_NOALLOC_SCRATCH_BYTES - L.part) / per_chunk, (size_t)VX_NOALLOC_MAX_WORK);
+    int chunk_pages = max(4, ceil_div(n_blocks * hkv, 4 * c->sm_count));
+    if (ceil_div(n_blocks, chunk_pages) > max_chunks) chunk_pages = ceil_div(n_blocks, max_chunks);
+    noalloc_setup_kernel<<<1, 32, 0, c->stream>>>(sp, L, dp<int32_t>(table), kv_len, bs, chunk_pages);
+    VX_LAUNCH_CHECK(c);
+    VxAttnArgs a{};
+    a.q = dp<float>(q); a.q_row_stride = hq * d; a.pool = dp<void>(pool); a.pool_is_f16 = 1;
+    a.tables = reinterpret_cast<const int32_t *const *>(sp + L.tab); a.row_slot = reinterpret_cast<const int32_t *>(sp + L.slot);
+    a.row_kv_start = reinterpret_cast<const int32_t *>(sp + L.ks); a.row_kv_len = reinterpret_cast<const int32_t *>(sp + L.kl);
+    a.work = reinterpret_cast<const int4 *>(sp + L.work); a.n_work_dev = reinterpret_cast<const int32_t *>(sp + L.nw);
+    a.n_work = ceil_div(n_blocks, chunk_pages); a.row_work_start = reinterpret_cast<const int32_t *>(sp + L.rws);
+    a.partials = reinterpret_cast<float *>(sp + L.part);
+    a.out = dp<float>(out); a.out_row_stride = hq * d;
+    a.rows = 1; a.n_q_heads = hq; a.n_kv_heads = hkv; a.head_dim = d; a.block_size = bs; a.scale = scale; a.softcap = 0.f;
+    return vxp_attention(c, a);
 }
 
 }  // extern "C"
