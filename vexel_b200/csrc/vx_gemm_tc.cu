@@ -13,7 +13,7 @@
 //              A_lo*x_lo term is 2^-22 relative.  Two instructions instead of three: a single thread issues an MMA only
 //              every ~45 cycles, which bounds small-N shapes.  tcgen05.commit hands the stage buffers back.
 //   warps 0-15 epilogue: tcgen05.ld of the accumulator halves, add, scale by the row's power of two, store.
-// No TMA load uses cluster multicast.  Every mbarrier wait is bounded: on timeout the kernel raises an error word, skips
+// Every TMA load targets this CTA only.  Every mbarrier wait is bounded: on timeout the kernel raises an error word, skips
 // to the end, frees its tensor memory and returns, so a protocol bug cannot hang the GPU.
 #include <cuda.h>
 
@@ -66,7 +66,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (clock64() - t0 > WAIT_CLOCKS) { *abort_flag = 1; return false; }
     }
 }
-// 2-D tiled TMA load (no multicast) completing on an mbarrier of this CTA
+// 2-D tiled TMA load into this CTA, completing on one of its mbarriers
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
