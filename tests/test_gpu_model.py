@@ -270,3 +270,45 @@ def test_continuous_batching_trace(be):
     assert met.completed_sequences == n_req and met.prefill_tokens == sum(len(p) for p in prompts)
     assert met.decode_tokens == sum(out_len) - n_req and gm.pool_stats()[1] == gm.pool_stats()[0]   # every block returned
     sched.close(); gm.close()
+
+
+def test_c1_tinyllama_full_shape(be):
+    """The benchmark's CPU-runnable configuration at its real shape: TinyLlama-1.1B-shaped Q4_0 (22 layers, hidden 2048,
+    32 q / 4 kv heads, head_dim 64, FFN 5632, vocab 32000), seed-0 weights, 4 ragged sequences with prompts {17, 64, 130, 255},
+    prefill then batched greedy decode (steps bounded by VEXEL_C1_STEPS, default 8, to keep the oracle within a minute)."""
+    import os
+    steps = int(os.environ.get("VEXEL_C1_STEPS", "8"))
+    spec = gs.C1_TINYLLAMA
+    om, gm = build_pair(be, spec, 0, max_blocks=96, max_seqs=4, max_batch_tokens=256, max_blocks_per_seq=24)
+    rng = np.random.default_rng(1)
+    lens = {1: 17, 2: 64, 3: 130, 4: 255}
+    gm.set_capture(True)
+    nxt = {}
+    worst = 0.0
+    for s, n in lens.items():
+        p = rng.integers(0, spec.vocab, n).astype(np.int32)
+        wl, wh = om.forward(s, p, 0, want_hidden=True)
+        tok, gl = gm.prefill(s, p, 0, want_logits=True)
+        h = gm.get_capture(n)
+        for l in range(spec.n_layers + 1):
+            worst = max(worst, rel_l2(h[l], wh[l]))
+        assert rel_l2(gl, wl) < HIDDEN_TOL and tok == O.argmax(wl[0])
+        assert np.array_equal(gm.block_table(s), om.pool.table(0, s))
+        nxt[s] = tok
+    agree = total = 0
+    seqs = sorted(lens)
+    for step in range(steps):
+        pos = [lens[s] + step for s in seqs]
+        out = gm.decode_step(seqs, [nxt[s] for s in seqs], pos)
+        h = gm.get_capture(len(seqs))
+        for i, s in enumerate(seqs):
+            wl, wh = om.forward(s, np.int32([nxt[s]]), pos[i], want_hidden=True)
+            for l in range(spec.n_layers + 1):
+                worst = max(worst, rel_l2(h[l, i], wh[l, 0]))
+            nxt[s] = O.argmax(wl[0])
+            agree += int(out[i] == nxt[s]); total += 1
+            assert np.array_equal(gm.block_table(s), om.pool.table(0, s))
+    assert worst < HIDDEN_TOL, worst
+    assert agree / total >= 0.99, (agree, total)
+    print(f"C1 full shape: worst per-layer hidden rel-L2 {worst:.2e}, greedy agreement {agree}/{total}")
+    gm.close()

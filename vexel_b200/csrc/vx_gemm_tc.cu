@@ -2,16 +2,16 @@
 //
 // Shape ("swap-AB"): D[128 weight rows x batch] += A[128 x 64k] * B[batch x 64k]^T per pipeline stage, accumulator in tensor
 // memory, one CTA per (128-row weight tile, split-K slice, 64-row batch tile).
-//   warp 17    TMA producer: per stage the activation tiles x_hi and x_lo (64 rows x 128 B each, SWIZZLE_128B, stacked into
+//   warp 18    TMA producer: per stage the activation tiles x_hi and x_lo (64 rows x 128 B each, SWIZZLE_128B, stacked into
 //              one 128-row operand) and, every second stage, the packed nibbles of a 128-weight group (128 rows x 64 B,
 //              SWIZZLE_64B).
 //   warps 0-15 dequantisers: read their row's nibbles from shared memory, expand to fp16 and store the A operand straight
 //              into TENSOR MEMORY (tcgen05.st; lane = weight row, two fp16 per 32-bit column) as two terms with
 //              w = d*(q-8) = A_hi + A_lo exactly (A_hi = fp16 product, A_lo = fp16 FMA residual).  With A in shared
 //              memory every MMA re-read 4 KB of it and the kernel was bound by shared-memory traffic.
-//   warp 16    one elected thread issues, per K=16 step, A_hi x [x_hi; x_lo] (N=128) and A_lo x x_hi (N=64); the dropped
-//              A_lo*x_lo term is 2^-22 relative.  Two instructions instead of three: a single thread issues an MMA only
-//              every ~45 cycles, which bounds small-N shapes.  tcgen05.commit hands the stage buffers back.
+//   warps 16-17 one elected thread each issues, for its half of a stage's K=16 steps, A_hi x [x_hi; x_lo] (N=128) and
+//              A_lo x x_hi (N=64) into its own accumulator; the dropped A_lo*x_lo term is 2^-22 relative.  tcgen05.commit
+//              hands the stage back.
 //   warps 0-15 epilogue: tcgen05.ld of the accumulator halves, add, scale by the row's power of two, store.
 // Every TMA load targets this CTA only.  Every mbarrier wait is bounded: on timeout the kernel raises an error word, skips
 // to the end, frees its tensor memory and returns, so a protocol bug cannot hang the GPU.
@@ -24,19 +24,20 @@ namespace {
 constexpr int TC_ROWS = 128;          // weight rows per CTA (MMA M)
 constexpr int TC_MT = 64;             // batch rows per CTA
 constexpr int TC_BK = 64;             // k per stage = one 128-byte swizzle row of fp16
-constexpr int TC_XS = 8;              // activation-tile ring (shared memory)
-constexpr int TC_AS = 4;              // weight-operand ring (tensor memory)
+constexpr int TC_ST = 4;              // pipeline stages: activation tiles in shared memory, weight operand in tensor memory
+constexpr int TC_ISSUERS = 2;         // MMA-issuing threads (one per warp), each with its own accumulator
 constexpr int TC_RAW = 4;             // ring of 128-weight nibble groups (each feeds two stages)
 constexpr int TC_DEQ = 512;           // dequantiser threads: (row, block of the stage, word pair)
-constexpr int TC_THREADS = TC_DEQ + 64;
+constexpr int TC_THREADS = TC_DEQ + 32 * (TC_ISSUERS + 1);
 constexpr int X_TILE = TC_MT * 128;           // bytes of one fp16 activation tile (64 rows x 128 B)
 constexpr int STAGE_BYTES = 2 * X_TILE;       // x_hi rows 0-63 followed by x_lo rows 64-127: one 128-row K-major operand
 constexpr int RAW_BYTES = TC_ROWS * 64;       // packed nibbles of one 128-weight group
-constexpr int SMEM_BYTES = TC_XS * STAGE_BYTES + TC_RAW * RAW_BYTES + 1024 /*alignment*/ + 512 /*barriers*/ + 256 /*row scales*/;
-// tensor memory columns: accumulator [0,128): cols 0-63 = A_hi*x_hi + A_lo*x_hi, cols 64-127 = A_hi*x_lo;
-// weight stage s: A_hi at 128 + 64*s, A_lo 32 columns further (two fp16 per 32-bit column)
-constexpr int TMEM_A = 2 * TC_MT;
-constexpr int TMEM_COLS = 512;                // 128 + 4 * 64 = 384, rounded to the next power of two
+constexpr int SMEM_BYTES = TC_ST * STAGE_BYTES + TC_RAW * RAW_BYTES + 1024 /*alignment*/ + 512 /*barriers*/ + 256 /*row scales*/;
+// tensor memory columns: issuer j accumulates into [128j, 128j+128): cols 0-63 = A_hi*x_hi + A_lo*x_hi, cols 64-127 = A_hi*x_lo
+// for its K=16 steps; weight stage s: A_hi at TMEM_A + 64*s, A_lo 32 columns further (two fp16 per 32-bit column)
+constexpr int TMEM_A = TC_ISSUERS * 2 * TC_MT;
+constexpr int TMEM_COLS = 512;                // 2 * 128 + 4 * 64
+static_assert(TMEM_A + 64 * TC_ST <= TMEM_COLS, "tensor memory budget");
 constexpr long long WAIT_CLOCKS = 400000000LL;             // ~0.2 s at 2 GHz
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -120,17 +121,16 @@ gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;            // operand tiles need 1024-byte alignment
-    const uint32_t raw_base = base + TC_XS * STAGE_BYTES;
+    const uint32_t raw_base = base + TC_ST * STAGE_BYTES;
     const uint32_t bar_base = raw_base + TC_RAW * RAW_BYTES;
     unsigned char *gen_base = smem_raw + (base - smem_u32(smem_raw));
-    float *s_xscale = reinterpret_cast<float *>(gen_base + TC_XS * STAGE_BYTES + TC_RAW * RAW_BYTES + 512);
+    float *s_xscale = reinterpret_cast<float *>(gen_base + TC_ST * STAGE_BYTES + TC_RAW * RAW_BYTES + 512);
     auto xf_bar = [&](int s) { return bar_base + 8u * s; };                                 // activation tile landed
-    auto xe_bar = [&](int s) { return bar_base + 8u * (TC_XS + s); };                       // ... consumed by the MMAs
-    auto af_bar = [&](int s) { return bar_base + 8u * (2 * TC_XS + s); };                   // weight operand written
-    auto ae_bar = [&](int s) { return bar_base + 8u * (2 * TC_XS + TC_AS + s); };           // ... consumed by the MMAs
-    auto rawf_bar = [&](int s) { return bar_base + 8u * (2 * TC_XS + 2 * TC_AS + s); };     // nibbles landed
-    auto rawe_bar = [&](int s) { return bar_base + 8u * (2 * TC_XS + 2 * TC_AS + TC_RAW + s); };   // ... read by the dequantisers
-    const uint32_t accum_bar = bar_base + 8u * (2 * TC_XS + 2 * TC_AS + 2 * TC_RAW);
+    auto af_bar = [&](int s) { return bar_base + 8u * (TC_ST + s); };                       // weight operand written
+    auto e_bar = [&](int s) { return bar_base + 8u * (2 * TC_ST + s); };                    // stage consumed by every issuer's MMAs
+    auto rawf_bar = [&](int s) { return bar_base + 8u * (3 * TC_ST + s); };                 // nibbles landed
+    auto rawe_bar = [&](int s) { return bar_base + 8u * (3 * TC_ST + TC_RAW + s); };        // ... read by the dequantisers
+    const uint32_t accum_bar = bar_base + 8u * (3 * TC_ST + 2 * TC_RAW);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r0 = blockIdx.x * TC_ROWS, m0 = blockIdx.z * TC_MT;
@@ -139,10 +139,9 @@ gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     if (tid == 0) {
         s_abort = 0;
-        for (int s = 0; s < TC_XS; s++) { mbar_init(xf_bar(s), 1); mbar_init(xe_bar(s), 1); }
-        for (int s = 0; s < TC_AS; s++) { mbar_init(af_bar(s), TC_DEQ / 32); mbar_init(ae_bar(s), 1); }   // one arrival per warp:
+        for (int s = 0; s < TC_ST; s++) { mbar_init(xf_bar(s), 1); mbar_init(af_bar(s), TC_DEQ / 32); mbar_init(e_bar(s), TC_ISSUERS); }   // one arrival per warp:
         for (int s = 0; s < TC_RAW; s++) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), TC_DEQ / 32); }   // 512 arrivals on one word serialise
-        mbar_init(accum_bar, 1);
+        mbar_init(accum_bar, TC_ISSUERS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < TC_MT) s_xscale[tid] = m0 + tid < M ? xscale[m0 + tid] : 0.f;
@@ -170,17 +169,17 @@ gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         __half d1 = n_kb > 1 ? scp[2] : d0;
         uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
         for (int kb = 0; kb < n_kb; kb++) {
-            const int as = kb % TC_AS, g = kb >> 1, slot = g % TC_RAW;
+            const int as = kb % TC_ST, g = kb >> 1, slot = g % TC_RAW;
             const __half d2n = (kb + 2 < n_kb) ? scp[2 * (kb + 2)] : d1;      // scale two stages ahead
             if ((kb & 1) == 0) {
                 if (!mbar_wait(rawf_bar(slot), (g / TC_RAW) & 1, abort_flag)) break;
-                const unsigned char *rp = gen_base + TC_XS * STAGE_BYTES + slot * RAW_BYTES;
+                const unsigned char *rp = gen_base + TC_ST * STAGE_BYTES + slot * RAW_BYTES;
                 w0 = *reinterpret_cast<const uint4 *>(rp + raw_off0);    // word 2h   of blocks 0..3 of the group
                 w1 = *reinterpret_cast<const uint4 *>(rp + raw_off1);    // word 2h+1 of blocks 0..3
                 __syncwarp();
                 if (lane == 0) mbar_arrive(rawe_bar(slot));
             }
-            if (kb >= TC_AS && !mbar_wait(ae_bar(as), ((kb / TC_AS) - 1) & 1, abort_flag)) break;
+            if (kb >= TC_ST && !mbar_wait(e_bar(as), ((kb / TC_ST) - 1) & 1, abort_flag)) break;
             // this thread's block of the stage is block 2*(kb&1) + b of the group
             const uint32_t wa = (kb & 1) ? (b ? w0.w : w0.z) : (b ? w0.y : w0.x);
             const uint32_t wc = (kb & 1) ? (b ? w1.w : w1.z) : (b ? w1.y : w1.x);
@@ -208,18 +207,18 @@ gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(af_bar(as));
         }
-    } else if (warp == TC_DEQ / 32 + 1) {
+    } else if (warp == TC_DEQ / 32 + TC_ISSUERS) {
         // ------------------------------------------------------------------ TMA producer (one thread)
         if (lane == 0) {
             for (int kb = 0; kb < n_kb; kb++) {
-                const int gkb = kb_begin + kb, xs = kb % TC_XS;
+                const int gkb = kb_begin + kb, xs = kb % TC_ST;
                 if ((kb & 1) == 0) {
                     const int g = kb >> 1, slot = g % TC_RAW;
                     if (g >= TC_RAW && !mbar_wait(rawe_bar(slot), ((g / TC_RAW) - 1) & 1, abort_flag)) break;
                     mbar_arrive_expect_tx(rawf_bar(slot), RAW_BYTES);
                     tma_load_2d(raw_base + slot * RAW_BYTES, &map_w, (gkb >> 1) * 64, r0, rawf_bar(slot));
                 }
-                if (kb >= TC_XS && !mbar_wait(xe_bar(xs), ((kb / TC_XS) - 1) & 1, abort_flag)) break;
+                if (kb >= TC_ST && !mbar_wait(e_bar(xs), ((kb / TC_ST) - 1) & 1, abort_flag)) break;
                 mbar_arrive_expect_tx(xf_bar(xs), 2 * X_TILE);
                 const uint32_t dst = base + xs * STAGE_BYTES;
                 tma_load_2d(dst, &map_xh, gkb * TC_BK, m0, xf_bar(xs));
@@ -227,38 +226,37 @@ gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
         }
     } else if (lane == 0) {
-        // ------------------------------------------------------------------ MMA issue (one thread)
-        // per K=16 step: [A_hi] x [x_hi; x_lo] (N=128) into columns 0-127, then [A_lo] x [x_hi] (N=64) into columns 0-63.
-        // This thread shares its scheduler with four busy dequantiser warps and every instruction of its dependent chain
-        // costs ~10 cycles, so the loop is unrolled over the activation ring with all descriptors, tensor-memory
-        // addresses and barrier addresses precomputed: ~30 instructions per stage instead of ~100.
-        uint64_t xdesc[TC_XS][TC_BK / 16];
+        // ------------------------------------------------------------------ MMA issue (one thread per issuer warp)
+        // On a busy SM every tcgen05 instruction (mma or commit) costs its issuing thread ~80-100 cycles whatever its
+        // shape, so the K=16 steps of a stage are shared between TC_ISSUERS threads on different schedulers, each with
+        // its own accumulator (summed in the epilogue: the result stays deterministic), and a stage is released by a
+        // single commit per issuer.  Per step: [A_hi] x [x_hi; x_lo] (N=128), then [A_lo] x [x_hi] (N=64).
+        const int j = warp - TC_DEQ / 32;
+        constexpr int KS = (TC_BK / 16) / TC_ISSUERS;             // K=16 steps per issuer and stage
+        uint64_t xdesc[TC_ST][KS];
 #pragma unroll
-        for (int s = 0; s < TC_XS; s++)
+        for (int s = 0; s < TC_ST; s++)
 #pragma unroll
-            for (int k = 0; k < TC_BK / 16; k++) xdesc[s][k] = umma_desc(base + s * STAGE_BYTES) + (uint64_t)(2 * k);   // +32 bytes of K per step
+            for (int k = 0; k < KS; k++) xdesc[s][k] = umma_desc(base + s * STAGE_BYTES) + (uint64_t)(2 * (j * KS + k));   // +32 bytes of K per step
+        const uint32_t acc = tmem + 2 * TC_MT * j;
         bool ok = true;
         uint32_t first = 0u;
-        for (int kb0 = 0; kb0 < n_kb && ok; kb0 += TC_XS) {
-            const uint32_t px = (uint32_t)(kb0 / TC_XS) & 1u;          // parity of the activation ring for this round
+        for (int kb0 = 0; kb0 < n_kb && ok; kb0 += TC_ST) {
+            const uint32_t par = (uint32_t)(kb0 / TC_ST) & 1u;
 #pragma unroll
-            for (int s = 0; s < TC_XS; s++) {
-                const int kb = kb0 + s;
-                if (kb >= n_kb) break;
-                const int as = s % TC_AS;                               // TC_XS is a multiple of TC_AS
-                const uint32_t pa = (uint32_t)((kb0 / TC_AS) + s / TC_AS) & 1u;
-                ok = mbar_wait(xf_bar(s), px, abort_flag) && mbar_wait(af_bar(as), pa, abort_flag);
+            for (int s = 0; s < TC_ST; s++) {
+                if (kb0 + s >= n_kb) break;
+                ok = mbar_wait(xf_bar(s), par, abort_flag) && mbar_wait(af_bar(s), par, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_hi = tmem + TMEM_A + 64 * as, a_lo = a_hi + 32;
+                const uint32_t a_hi = tmem + TMEM_A + 64 * s + 8 * j * KS, a_lo = a_hi + 32;
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; k++) {
-                    umma_f16_ts(tmem, a_hi + 8 * k, xdesc[s][k], UMMA_IDESC_N128, first);
+                for (int k = 0; k < KS; k++) {
+                    umma_f16_ts(acc, a_hi + 8 * k, xdesc[s][k], UMMA_IDESC_N128, first);
                     first = 1u;
-                    umma_f16_ts(tmem, a_lo + 8 * k, xdesc[s][k], UMMA_IDESC_N64, 1u);
+                    umma_f16_ts(acc, a_lo + 8 * k, xdesc[s][k], UMMA_IDESC_N64, 1u);
                 }
-                umma_commit(xe_bar(s));       // arrive when the MMAs above have finished reading the stage
-                umma_commit(ae_bar(as));
+                umma_commit(e_bar(s));        // arrives when this issuer's MMAs have finished reading the stage
             }
         }
         if (ok) umma_commit(accum_bar);
@@ -272,16 +270,22 @@ gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (ok) {
             float *o = out + (size_t)blockIdx.y * part_stride;
             const int n = r0 + (warp & 3) * 32 + lane, c0 = (warp >> 2) * 16;
-            uint32_t v0[16], v1[16];
-            const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + c0;
-            VX_TMEM_LD16(v0, taddr);
-            VX_TMEM_LD16(v1, taddr + TC_MT);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float sum[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) sum[i] = 0.f;
+#pragma unroll
+            for (int part = 0; part < 2 * TC_ISSUERS; part++) {       // issuer accumulators x {x_hi, x_lo} halves, fixed order
+                uint32_t v[16];
+                VX_TMEM_LD16(v, tmem + ((uint32_t)((warp & 3) * 32) << 16) + part * TC_MT + c0);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 16; i++) sum[i] += __uint_as_float(v[i]);
+            }
             if (n < N) {
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    const int m = m0 + c0 + j;
-                    if (m < M) o[(size_t)m * ld_out + n] = (__uint_as_float(v0[j]) + __uint_as_float(v1[j])) * s_xscale[c0 + j];
+                for (int i = 0; i < 16; i++) {
+                    const int m = m0 + c0 + i;
+                    if (m < M) o[(size_t)m * ld_out + n] = sum[i] * s_xscale[c0 + i];
                 }
             }
         }
