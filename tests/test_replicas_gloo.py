@@ -1,0 +1,88 @@
+"""World-size-2 CPU runs (gloo) of the replica plumbing bench.py uses on N GPUs: request sharding, barrier,
+max-over-ranks timing and whole-job throughput, and the reference arm running on rank 0 only."""
+import json
+import os
+import socket
+import subprocess
+import sys
+import textwrap
+
+import numpy as np
+
+from vexel_b200 import replicas
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _launch(script, world=2, timeout=240):
+    port = _free_port()
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, WORLD_SIZE=str(world), RANK=str(r), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   PYTHONPATH=ROOT)
+        procs.append(subprocess.Popen([sys.executable, "-c", script], env=env, cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    outs = []
+    for p in procs:
+        o, e = p.communicate(timeout=timeout)
+        assert p.returncode == 0, e[-2000:]
+        outs.append(o)
+    return outs
+
+
+def test_shards_are_disjoint_and_cover():
+    ids = np.arange(1, 1001)
+    for world in (1, 2, 3, 8):
+        parts = [replicas.shard(ids, world, r) for r in range(world)]
+        assert sorted(np.concatenate(parts).tolist()) == ids.tolist()
+        for r, p in enumerate(parts):
+            assert all(replicas.owner_of(i, world) == r for i in p)
+            assert np.all(np.diff(p) > 0)          # arrival order kept
+    assert len({tuple(sorted(replicas.rank_seeds(r).items())) for r in range(8)}) == 8
+
+
+def test_single_process_passthrough():
+    assert replicas.max_over_ranks(None, 3.5) == 3.5
+    v, s = replicas.job_throughput(None, 640, 0.5)
+    assert v == 1280 and s == 0.5
+
+
+def test_two_ranks_gloo_throughput_and_sharding():
+    script = textwrap.dedent("""
+        import json, numpy as np
+        from vexel_b200 import replicas
+        world, rank, local = replicas.rank_env()
+        dist = replicas.init("gloo")
+        assert dist is not None and dist.get_world_size() == 2
+        mine = replicas.shard(np.arange(100, 131), world, rank)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine.tolist())
+        replicas.barrier(dist)
+        # rank 1 is the slow replica: 64 sequences x 10 steps each, 0.5 s and 0.8 s
+        value, slowest = replicas.job_throughput(dist, 64 * 10, 0.5 + 0.3 * rank)
+        mx = replicas.max_over_ranks(dist, 10.0 * (rank + 1))
+        print(json.dumps({"rank": rank, "value": value, "slowest": slowest, "mx": mx, "gathered": gathered}))
+        replicas.shutdown(dist)
+    """)
+    outs = [json.loads(o.strip().splitlines()[-1]) for o in _launch(script)]
+    for o in outs:
+        assert abs(o["slowest"] - 0.8) < 1e-12
+        assert abs(o["value"] - 2 * 640 / 0.8) < 1e-9          # all ranks' units over the slowest rank's time
+        assert o["mx"] == 20.0
+        flat = sorted(o["gathered"][0] + o["gathered"][1])
+        assert flat == list(range(100, 131))
+        assert not set(o["gathered"][0]) & set(o["gathered"][1])
+
+
+def test_reference_arm_runs_on_rank_zero_only():
+    """Rank 1 of the reference arm exits 0 without work or output (rank 0's timing is covered by the bench itself)."""
+    env = dict(os.environ, WORLD_SIZE="2", RANK="1", LOCAL_RANK="1", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()))
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "1"],
+                       env=env, cwd=ROOT, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert r.stdout.strip() == ""
