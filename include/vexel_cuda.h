@@ -184,6 +184,13 @@ int vx_pool_layer_ptr(vx_model *m, int layer, vx_dptr *out, size_t *bytes);
 /* test/bench helper: give a sequence `len` tokens of KV filled with deterministic f16 noise (no forward pass) */
 int vx_seq_fill_synthetic(vx_model *m, int64_t seq_id, int len, uint32_t seed);
 
+/* Sampler.Config plus the uniform draw of one Sample call (pkg/sampler/sampler.go:9-14, 49-76, 206-218).
+ * temperature 0 = greedy; top_k 0 = off; top_p 0 or >= 1 = off; u in [0,1) is what rng.Float32() returned. */
+typedef struct { float temperature; int32_t top_k; float top_p; float u; } vx_sample_params;
+/* Sampler.Sample for `rows` contiguous logits rows of n floats on the device (the rows are overwritten by
+ * their probabilities); synchronous like ArgmaxOps.Argmax.  out_tokens is a host array. */
+int vx_sample_rows(vx_ctx *, vx_dptr logits, int rows, int n, const vx_sample_params *params, int32_t *out_tokens);
+
 /* One scheduler step over a ragged batch: replaces Scheduler.runDecodeStep's per-sequence calls
  * (scheduler/scheduler.go:290-303 -> runtime/decode.go:612-654).  Row i of the batch is sequence
  * seq_ids[i] fed q_lens[i] tokens (NULL = 1 each; >1 = speculative verify, decode.go:1446-1569)
@@ -193,6 +200,14 @@ int vx_seq_fill_synthetic(vx_model *m, int64_t seq_id, int len, uint32_t seed);
 int vx_decode_step(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t *tokens,
                    const int32_t *positions, const int32_t *q_lens, int32_t *out_tokens,
                    float *logits);
+/* vx_prefill whose returned token is sampled (one record, for the last prompt position) */
+int vx_prefill_sampled(vx_model *m, int64_t seq_id, const int32_t *tokens, int n_tokens, int start_pos,
+                       const vx_sample_params *params, int32_t *out_token, float *logits);
+/* vx_decode_step with on-device sampling in place of Scheduler.sampleToken's host path (scheduler/scheduler.go:783-820):
+ * params holds one record per packed row. */
+int vx_decode_step_sampled(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t *tokens, const int32_t *positions,
+                           const int32_t *q_lens, const vx_sample_params *params, int32_t *out_tokens, float *logits);
+
 /* Greedy generation of n_steps tokens for a fixed batch with the token feedback kept on the device (no host
  * round trip between steps).  tokens/positions describe the first step as in vx_decode_step (one token per
  * sequence).  out_tokens (optional, host) receives [n_steps, n_seqs]; device_ms (optional) the CUDA-event time of
@@ -241,6 +256,10 @@ typedef struct {
     int max_sequences;    /* Config.MaxSequences :24 (enforced here; 0 = unlimited) */
     int max_tokens;       /* Config.MaxTokens :25 (0 = unlimited) */
     int eos_token;        /* stop token id, < 0 = none */
+    float temperature;    /* Config.SamplerConfig (sampler.Config :9-14): 0 = greedy */
+    int top_k;
+    float top_p;
+    uint64_t seed;        /* seeds the scheduler's own uniform generator (the reference seeds math/rand, whose stream is not reproduced) */
 } vx_sched_config;
 typedef struct {          /* SchedulerMetrics, scheduler.go:30-38 */
     int active_sequences, completed_sequences, total_tokens, prefill_tokens, decode_tokens;

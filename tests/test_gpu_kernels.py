@@ -343,3 +343,91 @@ def test_bad_arguments_are_reported_not_crashed(be):
     p = be.Alloc(1024); be.ResetPool(); p2 = be.Alloc(1024)
     assert p == p2              # pooled buffers are recycled by ResetPool
     be.ResetPool()
+
+
+# ------------------------------------------------------------------ sampler (pkg/sampler/sampler.go:49-218)
+def _sample_params(rows):
+    return np.zeros(rows, capi.SAMPLE_DTYPE)
+
+
+def test_sampler_reference_cases(be):
+    """The reference's own sampler tests (pkg/sampler/sampler_test.go:20-100) replayed with explicit draws."""
+    logits = np.array([0.1, 0.5, 0.2, 0.9, 0.3], np.float32)
+    draws = np.random.default_rng(42).random(64).astype(np.float32)
+    for (t, k, p, ok) in [(0.0, 0, 0.0, {3}), (1.0, 2, 0.0, {1, 3}), (1.0, 0, 0.5, None), (1.0, 0, 0.0, None)]:
+        rows = draws.size
+        par = _sample_params(rows); par["temperature"] = t; par["top_k"] = k; par["top_p"] = p; par["u"] = draws
+        d = be.upload(np.tile(logits, (rows, 1)))
+        got = be.SampleRows(d, rows, logits.size, par)
+        want = np.array([O.sample(logits, t, k, p, float(u)) for u in draws], np.int32)
+        assert np.array_equal(got, want)
+        if ok is not None:
+            assert set(got.tolist()) <= ok
+        be.ResetPool()
+
+
+@pytest.mark.parametrize("n", [1000, 32000, 128256])
+def test_sampler_matches_oracle(be, n):
+    rng = np.random.default_rng(n)
+    rows = 48
+    logits = (rng.standard_normal((rows, n)) * 2.5).astype(np.float32)
+    par = _sample_params(rows)
+    par["temperature"] = rng.choice([0.0, 0.7, 1.0, 1.3], rows).astype(np.float32)
+    par["top_k"] = rng.choice([0, 1, 40, 200, n, n + 5], rows)
+    par["top_p"] = rng.choice([0.0, 0.3, 0.9, 0.95, 1.0], rows).astype(np.float32)
+    par["u"] = rng.random(rows).astype(np.float32)
+    par["u"][0] = 0.0
+    d = be.upload(logits)
+    got = be.SampleRows(d, rows, n, par)
+    want = np.array([O.sample(logits[i], float(par["temperature"][i]), int(par["top_k"][i]), float(par["top_p"][i]), float(par["u"][i]))
+                     for i in range(rows)], np.int32)
+    assert np.array_equal(got, want), (got, want, par)
+    # the rows now hold the filtered, renormalised distribution
+    probs = be.download(d, rows * n).reshape(rows, n)
+    for i in range(rows):
+        if par["temperature"][i] == 0:
+            continue
+        assert abs(float(probs[i].astype(np.float64).sum()) - 1.0) < 2e-3     # float32 running sums, as in the reference
+        k = int(par["top_k"][i])
+        if 0 < k < n and not (0 < par["top_p"][i] < 1):
+            assert np.count_nonzero(probs[i]) == k          # continuous logits: no ties at the threshold
+    # the largest draw: float32 (reference) and float64 (here) running sums end a few ulps apart, so only the property
+    # is compared: the pick sits where the running sum has reached the draw, or is the last-index fallback (sampler.go:216-217)
+    par["u"] = np.float32(1.0) - np.float32(2.0 ** -24)
+    d = be.upload(logits)
+    got = be.SampleRows(d, rows, n, par)
+    probs = be.download(d, rows * n).reshape(rows, n).astype(np.float64)
+    for i in range(rows):
+        if par["temperature"][i] == 0:
+            assert got[i] == O.argmax(logits[i])
+            continue
+        cdf = np.cumsum(probs[i])
+        assert (probs[i][got[i]] > 0 and cdf[got[i]] >= 1.0 - 1e-5) or got[i] == n - 1, (i, got[i])
+    be.ResetPool()
+
+
+def test_sampler_topk_keeps_ties(be):
+    """Every value equal to the k-th largest survives top-k (sampler.go:127-136 compares with '<')."""
+    n = 4096
+    rng = np.random.default_rng(5)
+    logits = rng.integers(0, 6, (8, n)).astype(np.float32)          # six levels, hundreds of ties each
+    par = _sample_params(8); par["temperature"] = 1.0; par["top_k"] = 10; par["u"] = rng.random(8).astype(np.float32)
+    d = be.upload(logits)
+    got = be.SampleRows(d, 8, n, par)
+    want = np.array([O.sample(logits[i], 1.0, 10, 0.0, float(par["u"][i])) for i in range(8)], np.int32)
+    assert np.array_equal(got, want)
+    probs = be.download(d, 8 * n).reshape(8, n)
+    for i in range(8):
+        assert np.count_nonzero(probs[i]) == np.count_nonzero(logits[i] == 5.0)
+    # top-p over ties: the kept set is the top level only partly; its size is what the running sum dictates
+    par["top_k"] = 0; par["top_p"] = 0.05
+    d = be.upload(logits)
+    got = be.SampleRows(d, 8, n, par)
+    probs = be.download(d, 8 * n).reshape(8, n)
+    for i in range(8):
+        e = np.exp((logits[i] - 5.0).astype(np.float64)); p = (e / e.sum())
+        top = p.max(); need = int(math.floor(0.05 / top)) + 1
+        kept = np.nonzero(probs[i])[0]
+        assert abs(kept.size - need) <= 1 and np.all(logits[i][kept] == 5.0)
+        assert logits[i][got[i]] == 5.0 and probs[i][got[i]] > 0
+    be.ResetPool()

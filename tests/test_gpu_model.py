@@ -312,3 +312,68 @@ def test_c1_tinyllama_full_shape(be):
     assert agree / total >= 0.99, (agree, total)
     print(f"C1 full shape: worst per-layer hidden rel-L2 {worst:.2e}, greedy agreement {agree}/{total}")
     gm.close()
+
+
+@pytest.mark.parametrize("gemma", [False, True])
+def test_decode_step_sampled(be, gemma):
+    """On-device sampling after the step == the reference sampler applied to the logits the step returns
+    (scheduler.go:783-820 samples on the host from the copied logits; final softcap from model.go:340-349)."""
+    if gemma:
+        spec = gs.scaled(gs.C4_GEMMA2_9B, 2, 256, 4, 2, 64, 512, 1024, quant="q4_0", sliding_window=24)
+    else:
+        spec = small_llama(2)
+    _, gm = build_pair(be, spec, 4, max_blocks=64, cpu=False)
+    rng = np.random.default_rng(9)
+    seqs = np.array([1, 2, 3, 4], np.int64)
+    for s in seqs:
+        gm.prefill(int(s), rng.integers(0, spec.vocab, 5 + int(s)).astype(np.int32))
+    pos = np.array([gm.seq_len(int(s)) for s in seqs], np.int32)
+    toks = rng.integers(0, spec.vocab, 4).astype(np.int32)
+    for step in range(4):
+        par = np.zeros(4, capi.SAMPLE_DTYPE)
+        par["temperature"] = [0.0, 0.8, 1.0, 1.5]; par["top_k"] = [0, 20, 0, 5]; par["top_p"] = [0.0, 0.9, 0.5, 0.0]
+        par["u"] = rng.random(4).astype(np.float32)
+        out, logits = gm.decode_step_sampled(seqs, toks, pos, par, want_logits=True)
+        want = [O.sample(logits[i], float(par["temperature"][i]), int(par["top_k"][i]), float(par["top_p"][i]), float(par["u"][i]))
+                for i in range(4)]
+        assert out.tolist() == want
+        # the same step again without the logits copy (the soft-cap then happens inside the sampling kernel)
+        for sid, p0 in zip(seqs, pos):
+            gm.seq_truncate(int(sid), int(p0))
+        out2 = gm.decode_step_sampled(seqs, toks, pos, par)
+        assert out2.tolist() == want
+        toks = out.copy(); pos += 1
+    gm.close()
+
+
+def test_scheduler_sampling(be):
+    """Temperature sampling through the scheduler: a fixed seed reproduces the streams, top-k 1 equals greedy whatever the
+    temperature, and a warm temperature yields different streams for different seeds (pkg/sampler/sampler_test.go:33-75)."""
+    spec = small_llama(2)
+    _, gm = build_pair(be, spec, 21, max_blocks=96, max_seqs=8, max_blocks_per_seq=16, cpu=False)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, spec.vocab, int(rng.integers(3, 30))).astype(np.int32) for _ in range(5)]
+
+    def run(**kw):
+        sched = capi.Scheduler(gm, max_batch_size=4, max_sequences=8, **kw)
+        for i, p in enumerate(prompts):
+            sched.AddSequence(10 + i, p, max_tokens=12)
+        got = {i: [] for i in range(len(prompts))}
+        for _ in range(100):
+            sched.step()
+            fins = []
+            for i in got:
+                t, fin = sched.poll(10 + i); got[i].extend(int(x) for x in t); fins.append(fin)
+            if all(fins):
+                break
+        assert all(len(v) == 12 for v in got.values())
+        sched.close()
+        return got
+
+    greedy = run()
+    assert run(temperature=0.9, top_k=1, seed=5) == greedy
+    a = run(temperature=1.2, top_k=50, top_p=0.95, seed=7)
+    assert run(temperature=1.2, top_k=50, top_p=0.95, seed=7) == a
+    assert run(temperature=1.2, top_k=50, top_p=0.95, seed=8) != a
+    assert gm.pool_stats()[1] == gm.pool_stats()[0]
+    gm.close()

@@ -34,7 +34,8 @@ class ModelConfig(C.Structure):
 
 
 class SchedConfig(C.Structure):
-    _fields_ = [(n, C.c_int) for n in ("max_batch_size", "max_sequences", "max_tokens", "eos_token")]
+    _fields_ = [(n, C.c_int) for n in ("max_batch_size", "max_sequences", "max_tokens", "eos_token")] + [
+        ("temperature", C.c_float), ("top_k", C.c_int), ("top_p", C.c_float), ("seed", C.c_uint64)]
 
 
 class SchedMetrics(C.Structure):
@@ -46,6 +47,8 @@ _vp, _i, _i64, _f, _u64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_ui
 _D = C.c_uint64  # vx_dptr
 
 # name -> argtypes (every function returns int unless listed in _RESTYPE)
+SAMPLE_DTYPE = np.dtype([("temperature", np.float32), ("top_k", np.int32), ("top_p", np.float32), ("u", np.float32)])
+
 SIGNATURES = {
     "vx_init": [_i, C.POINTER(_vp)], "vx_destroy": [_vp], "vx_last_error": [_vp], "vx_device_index": [_vp],
     "vx_alloc": [_vp, _sz, C.POINTER(_D)], "vx_alloc_permanent": [_vp, _sz, C.POINTER(_D)], "vx_free": [_vp, _D],
@@ -84,7 +87,10 @@ SIGNATURES = {
     "vx_pool_layer_ptr": [_vp, _i, C.POINTER(_D), C.POINTER(_sz)],
     "vx_seq_fill_synthetic": [_vp, _i64, _i, C.c_uint32],
     "vx_decode_step": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp],
+    "vx_decode_step_sampled": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "vx_sample_rows": [_vp, _D, _i, _i, _vp, _vp],
     "vx_prefill": [_vp, _i64, _vp, _i, _i, _vp, _vp],
+    "vx_prefill_sampled": [_vp, _i64, _vp, _i, _i, _vp, _vp, _vp],
     "vx_decode_run": [_vp, _i, _vp, _vp, _vp, _i, _vp, C.POINTER(_f)],
     "vx_model_set_capture": [_vp, _i], "vx_model_get_capture": [_vp, _vp, _sz],
     "vx_model_get_packing": [_vp, _vp, _vp, _vp, _i, _i],
@@ -214,6 +220,11 @@ class Backend:
     def Argmax(self, x, n):
         r = C.c_int(); self._ck(self.lib.vx_argmax(self.h, x, n, C.byref(r))); return r.value
 
+    def SampleRows(self, logits, rows, n, params):
+        """Sampler.Sample on `rows` device logits rows; params = array of (temperature, top_k, top_p, u) records."""
+        params = np.ascontiguousarray(params, SAMPLE_DTYPE); out = np.empty(rows, np.int32)
+        self._ck(self.lib.vx_sample_rows(self.h, logits, rows, n, _np_ptr(params), _np_ptr(out))); return out
+
     def ArgmaxRows(self, x, rows, cols, out): self._ck(self.lib.vx_argmax_rows(self.h, x, rows, cols, out))
     def MatMulQ4_0(self, a, b, out, m, n, k): self._ck(self.lib.vx_matmul_q4_0(self.h, a, b, out, m, n, k))
     def MatMulQ4_K(self, a, b, out, m, n, k): self._ck(self.lib.vx_matmul_q4_k(self.h, a, b, out, m, n, k))
@@ -307,6 +318,19 @@ class Model:
                                         _np_ptr(ql), _np_ptr(out), _np_ptr(logits)))
         return (out, logits) if want_logits else out
 
+    def decode_step_sampled(self, seq_ids, tokens, positions, params, q_lens=None, want_logits=False):
+        """decode_step with one (temperature, top_k, top_p, u) record per packed row, sampled on the device."""
+        seq_ids = np.ascontiguousarray(seq_ids, np.int64); tokens = np.ascontiguousarray(tokens, np.int32)
+        positions = np.ascontiguousarray(positions, np.int32); params = np.ascontiguousarray(params, SAMPLE_DTYPE)
+        ql = None if q_lens is None else np.ascontiguousarray(q_lens, np.int32)
+        rows = tokens.size
+        assert params.size == rows
+        out = np.empty(rows, np.int32)
+        logits = np.empty((rows, self.cfg.vocab), np.float32) if want_logits else None
+        self._ck(self.lib.vx_decode_step_sampled(self.h, seq_ids.size, _np_ptr(seq_ids), _np_ptr(tokens), _np_ptr(positions),
+                                                _np_ptr(ql), _np_ptr(params), _np_ptr(out), _np_ptr(logits)))
+        return (out, logits) if want_logits else out
+
     def decode_run(self, seq_ids, tokens, positions, n_steps):
         """n_steps greedy steps with on-device token feedback; returns (tokens [n_steps, n_seqs], device ms)."""
         seq_ids = np.ascontiguousarray(seq_ids, np.int64); tokens = np.ascontiguousarray(tokens, np.int32)
@@ -347,9 +371,9 @@ class Model:
 class Scheduler:
     """vx_sched_*: the continuous-batching loop of inference/scheduler over the batched fast path."""
 
-    def __init__(self, model: Model, max_batch_size, max_sequences=0, max_tokens=0, eos_token=-1):
+    def __init__(self, model: Model, max_batch_size, max_sequences=0, max_tokens=0, eos_token=-1, temperature=0.0, top_k=0, top_p=0.0, seed=0):
         self.m, self.lib = model, model.lib
-        cfg = SchedConfig(max_batch_size, max_sequences, max_tokens, eos_token)
+        cfg = SchedConfig(max_batch_size, max_sequences, max_tokens, eos_token, temperature, top_k, top_p, seed)
         h = C.c_void_p()
         model._ck(self.lib.vx_sched_create(model.h, C.byref(cfg), C.byref(h)))
         self.h = h

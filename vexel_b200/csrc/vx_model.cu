@@ -59,6 +59,7 @@ struct vx_model {
     size_t parts_cap = 0;
     VxSplit sp_h{}, sp_q{}, sp_f{};
     int32_t *d_out_tok = nullptr, *h_out_tok = nullptr;
+    void *d_sample = nullptr;                    // per-row sampling parameters of the current step
     float *capture = nullptr; bool capture_on = false; int capture_rows = 0;
     int last_rows = 0, last_seqs = 0;
     uint64_t steps = 0;
@@ -491,6 +492,7 @@ __global__ void final_softcap_kernel(float *logits, long n, float cap) {   // ru
 
 // launchers living in other translation units
 int vxe_argmax_rows(vx_ctx *c, const float *x, int rows, int cols, int32_t *out);
+int vxs_sample_rows(vx_ctx *c, float *logits, long ld, int rows, int n, const void *d_params, float final_softcap, int32_t *d_out);
 int vxe_sdpa_strided(vx_ctx *c, const float *q, int q_ld, const float *k, const float *v, float *out, int out_ld, int rows, int kv_len,
                      int causal, int hq, int hkv, int d, long pos_stride, long head_stride, float scale, float softcap);
 
@@ -747,7 +749,7 @@ int enqueue_step(vx_model *m, const StepPlan &p, int mode, int logit_rows) {
 }
 
 int run_step(vx_model *m, int n_seqs, const int *slots, const int32_t *tokens, const int32_t *positions, const int32_t *q_lens,
-             int mode, int logit_rows_req, int32_t *out_tokens, float *logits) {
+             int mode, int logit_rows_req, int32_t *out_tokens, float *logits, const vx_sample_params *sample = nullptr) {
     vx_ctx *c = m->c; const vx_model_config &cf = m->cfg;
     StepPlan p;
     VX_TRY(plan_step(m, n_seqs, slots, positions, q_lens, &p));
@@ -762,8 +764,14 @@ int run_step(vx_model *m, int n_seqs, const int *slots, const int32_t *tokens, c
         final_softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(m->logits, n, cf.final_softcap);
         VX_LAUNCH_CHECK(c);
     }
-    VX_CUDA(c, cudaMemcpyAsync(m->h_out_tok, m->d_out_tok, sizeof(int32_t) * logit_rows, cudaMemcpyDeviceToHost, c->stream));
     if (logits) VX_CUDA(c, cudaMemcpyAsync(logits, m->logits, sizeof(float) * (size_t)logit_rows * cf.vocab, cudaMemcpyDeviceToHost, c->stream));
+    if (sample) {
+        // rows with temperature 0 keep the argmax; the others are drawn on the device from the logits in place
+        // (scheduler.go:783-820 copies the logits to the host and samples there)
+        VX_CUDA(c, cudaMemcpyAsync(m->d_sample, sample, sizeof(vx_sample_params) * (size_t)logit_rows, cudaMemcpyHostToDevice, c->stream));
+        VX_TRY(vxs_sample_rows(c, m->logits, cf.vocab, logit_rows, cf.vocab, m->d_sample, logits ? 0.f : cf.final_softcap, m->d_out_tok));
+    }
+    VX_CUDA(c, cudaMemcpyAsync(m->h_out_tok, m->d_out_tok, sizeof(int32_t) * logit_rows, cudaMemcpyDeviceToHost, c->stream));
     VX_TRY(check_status(m));   // synchronises the stream
     time_collect(m);
     if (out_tokens) memcpy(out_tokens, m->h_out_tok, sizeof(int32_t) * logit_rows);
@@ -859,6 +867,7 @@ int vx_model_create(vx_ctx *c, const vx_model_config *cfg, vx_model **out) {
     m->parts_cap = (size_t)MAX_PARTS * T * std::max(std::max(H, nqkv), 2 * F);
     MA(model_alloc_t(m, m->parts_cap, &m->parts));
     MA(model_alloc_t(m, (size_t)T, &m->d_out_tok));
+    { int32_t *sp = nullptr; MA(model_alloc_t(m, (size_t)T * 4, &sp)); m->d_sample = sp; }
     auto mk_split = [&](int k, VxSplit *s) {
         size_t hi, lo, so, bo; int kp;
         size_t bytes = vxq_split_bytes(T, k, &hi, &lo, &so, &bo, &kp);
@@ -1162,6 +1171,20 @@ int vx_decode_step(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_
     return run_step(m, n_seqs, slots.data(), tokens, positions, q_lens, 0, 0, out_tokens, logits);
 }
 
+// vx_decode_step followed by Sampler.Sample (pkg/sampler/sampler.go:49-76) on the device: one parameter record per
+// packed row, the uniform draw supplied by the caller.  Rows with temperature 0 are greedy.
+int vx_decode_step_sampled(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t *tokens, const int32_t *positions,
+                           const int32_t *q_lens, const vx_sample_params *params, int32_t *out_tokens, float *logits) {
+    if (!m) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    VX_REQUIRE(c, m->finalized, "model not finalized");
+    VX_REQUIRE(c, n_seqs > 0 && n_seqs <= m->cfg.max_seqs && seq_ids && tokens && positions && params, "bad arguments");
+    std::vector<int> slots(n_seqs);
+    for (int i = 0; i < n_seqs; i++) VX_TRY(get_slot(m, seq_ids[i], true, &slots[i]));
+    return run_step(m, n_seqs, slots.data(), tokens, positions, q_lens, 0, 0, out_tokens, logits, params);
+}
+
 // Greedy generation for a fixed batch with the token feedback kept on the device: step s+1 is fed the
 // argmax of step s without a host round trip.  Only the first step's inputs cross PCIe; all produced
 // tokens come back in one copy at the end.  device_ms (optional) is the CUDA-event time of the n_steps
@@ -1223,7 +1246,8 @@ int vx_decode_run(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t
     return VX_OK;
 }
 
-int vx_prefill(vx_model *m, int64_t id, const int32_t *tokens, int n_tokens, int start_pos, int32_t *out_token, float *logits) {
+static int prefill_impl(vx_model *m, int64_t id, const int32_t *tokens, int n_tokens, int start_pos, const vx_sample_params *sample,
+                        int32_t *out_token, float *logits) {
     if (!m) return VX_E_BAD_ARG;
     vx_ctx *c = m->c;
     VxGuard g(c);
@@ -1240,10 +1264,22 @@ int vx_prefill(vx_model *m, int64_t id, const int32_t *tokens, int n_tokens, int
         // the first chunk of a prompt that starts at 0 attends over its own float32 K/V (SDPAPrefill);
         // later chunks read the paged fp16 cache like the multi-query verify path
         int mode = (pos == 0) ? 1 : 0;
-        VX_TRY(run_step(m, 1, &slot, tokens + done, &pos, &ql, mode, 1, last ? out_token : nullptr, last ? logits : nullptr));
+        VX_TRY(run_step(m, 1, &slot, tokens + done, &pos, &ql, mode, 1, last ? out_token : nullptr, last ? logits : nullptr,
+                        last ? sample : nullptr));
         done += n;
     }
     return VX_OK;
+}
+
+int vx_prefill(vx_model *m, int64_t id, const int32_t *tokens, int n_tokens, int start_pos, int32_t *out_token, float *logits) {
+    return prefill_impl(m, id, tokens, n_tokens, start_pos, nullptr, out_token, logits);
+}
+
+// vx_prefill whose first generated token is drawn by Sampler.Sample from the last prompt position's logits
+int vx_prefill_sampled(vx_model *m, int64_t id, const int32_t *tokens, int n_tokens, int start_pos, const vx_sample_params *params,
+                       int32_t *out_token, float *logits) {
+    if (!params) return VX_E_BAD_ARG;
+    return prefill_impl(m, id, tokens, n_tokens, start_pos, params, out_token, logits);
 }
 
 int vx_model_set_capture(vx_model *m, int enable) {

@@ -4,8 +4,9 @@
 // sample their first token, then one decode step for every decoding sequence of the batch), same metrics.  Differences,
 // all deliberate: the batch is taken in arrival order (the reference iterates a Go map), the whole batch is ONE
 // vx_decode_step instead of a per-sequence loop, and a pending prompt that does not fit the free blocks waits
-// instead of stopping the scheduler loop (scheduler.go:134-136).  Sampling is greedy (first maximum); the reference's
-// temperature path needs the host sampler and the logits copy it already has.
+// instead of stopping the scheduler loop (scheduler.go:134-136).  Temperature 0 is greedy (first maximum); otherwise
+// tokens are drawn on the device by the sampler's rules with uniform draws from a generator seeded by the config
+// (the reference copies the logits to the host and draws from math/rand, scheduler.go:783-820).
 #include <chrono>
 #include <deque>
 
@@ -26,6 +27,14 @@ struct vx_sched {
     std::vector<Seq> seqs;            // arrival order
     vx_sched_metrics met{};
     std::mutex mu;
+    uint64_t rng = 0;
+    // splitmix64; the top 24 bits make a float in [0, 1) like rand.Float32
+    float uniform() {
+        uint64_t z = (rng += 0x9E3779B97F4A7C15ull);
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull; z = (z ^ (z >> 27)) * 0x94D049BB133111EBull; z ^= z >> 31;
+        return (float)(z >> 40) * (1.0f / 16777216.0f);
+    }
+    vx_sample_params draw() { return vx_sample_params{cfg.temperature, cfg.top_k, cfg.top_p, uniform()}; }
 };
 
 extern "C" {
@@ -33,7 +42,7 @@ extern "C" {
 int vx_sched_create(vx_model *m, const vx_sched_config *cfg, vx_sched **out) {
     if (!m || !cfg || !out || cfg->max_batch_size <= 0) return VX_E_BAD_ARG;
     vx_sched *s = new vx_sched();
-    s->m = m; s->cfg = *cfg;
+    s->m = m; s->cfg = *cfg; s->rng = cfg->seed;
     *out = s;
     return VX_OK;
 }
@@ -103,7 +112,9 @@ int vx_sched_step(vx_sched *s, int *n_active_out) {
         if (need > per_layer_free) continue;                                           // block-aware admission: wait for blocks
         auto t0 = clk::now();
         int32_t tok = 0;
-        int rc = vx_prefill(s->m, q->id, q->prompt.data(), (int)q->prompt.size(), 0, &tok, nullptr);
+        vx_sample_params sp = s->draw();
+        int rc = s->cfg.temperature == 0.f ? vx_prefill(s->m, q->id, q->prompt.data(), (int)q->prompt.size(), 0, &tok, nullptr)
+                                           : vx_prefill_sampled(s->m, q->id, q->prompt.data(), (int)q->prompt.size(), 0, &sp, &tok, nullptr);
         if (rc != VX_OK) return rc;
         q->position = (int)q->prompt.size();
         q->generated.push_back(tok);
@@ -119,7 +130,13 @@ int vx_sched_step(vx_sched *s, int *n_active_out) {
     if (dec.empty()) return VX_OK;
     auto t0 = clk::now();
     std::vector<int32_t> out(dec.size());
-    int rc = vx_decode_step(s->m, (int)dec.size(), ids.data(), toks.data(), pos.data(), nullptr, out.data(), nullptr);
+    int rc;
+    if (s->cfg.temperature == 0.f) rc = vx_decode_step(s->m, (int)dec.size(), ids.data(), toks.data(), pos.data(), nullptr, out.data(), nullptr);
+    else {
+        std::vector<vx_sample_params> sp(dec.size());
+        for (auto &p : sp) p = s->draw();
+        rc = vx_decode_step_sampled(s->m, (int)dec.size(), ids.data(), toks.data(), pos.data(), nullptr, sp.data(), out.data(), nullptr);
+    }
     if (rc != VX_OK) return rc;
     for (size_t i = 0; i < dec.size(); i++) {
         Seq &q = *dec[i];
