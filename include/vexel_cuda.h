@@ -171,6 +171,24 @@ int vx_model_destroy(vx_model *m);
 int vx_model_set_tensor(vx_model *m, int layer, int slot, int ggml_type, const void *data,
                         size_t bytes, int data_on_device);
 int vx_model_finalize(vx_model *m);    /* repack for the MMA kernels, fuse QKV and gate|up */
+int vx_model_get_config(vx_model *m, vx_model_config *out);
+
+/* GGUF files (pkg/gguf/gguf.go:246-501): header, metadata and tensor table parsed on the host, tensor data mapped.
+ * vx_gguf_open always returns a handle (close it); on failure vx_gguf_error says why, in the reference's words. */
+typedef struct vx_gguf vx_gguf;
+int vx_gguf_open(const char *path, vx_gguf **out);                                 /* gguf.Open :246 */
+int vx_gguf_close(vx_gguf *g);
+const char *vx_gguf_error(vx_gguf *g);
+int vx_gguf_tensor_count(vx_gguf *g);
+int vx_gguf_tensor_info(vx_gguf *g, int index, char *name, int name_cap, int *ggml_type, int *n_dims,
+                        uint64_t *ne4, uint64_t *file_offset, uint64_t *bytes);     /* TensorInfo :208-214; ne in GGUF order */
+int vx_gguf_meta(vx_gguf *g, const char *key, char *out, int cap);                  /* File.Metadata[key] as text; VX_E_NO_SEQ if absent */
+/* extractModelConfig (gguf.go:503-584) + ModelConfigFromGGUF (runtime/config.go:388-507): fills the architecture
+ * fields of *cfg and leaves max_blocks / max_seqs / max_batch_tokens / max_blocks_per_seq to the caller */
+int vx_gguf_model_config(vx_gguf *g, vx_model_config *cfg);
+/* LoadWeightsGGUF + CopyWeightsToDevice (runtime/loader.go:28-212, 507-708) into a model created from that config,
+ * followed by vx_model_finalize */
+int vx_model_load_gguf(vx_model *m, vx_gguf *g);
 
 /* GPUBlockPool sequence bookkeeping, device-resident (runtime/gpu_block_pool.go:129-190, 572-635) */
 int vx_seq_create(vx_model *m, int64_t seq_id);

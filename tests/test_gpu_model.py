@@ -377,3 +377,58 @@ def test_scheduler_sampling(be):
     assert run(temperature=1.2, top_k=50, top_p=0.95, seed=8) != a
     assert gm.pool_stats()[1] == gm.pool_stats()[0]
     gm.close()
+
+
+@pytest.mark.parametrize("case", ["llama_q4_0", "llama_q4_k_m_tied_q6k_embedding", "gemma2_q6_k"])
+def test_load_gguf_matches_tensor_by_tensor_build(be, case, tmp_path):
+    """A model streamed from a GGUF file produces the same bits as the one built tensor by tensor from the same bytes, and
+    follows the loader rules (runtime/loader.go:28-212, 597-600): block formats kept for projections, quantised embedding
+    expanded to float32, head tied to the embedding when output.weight is absent."""
+    if case == "llama_q4_0":
+        spec = small_llama(2); tie = False
+    elif case == "gemma2_q6_k":
+        spec = gs.scaled(gs.C4_GEMMA2_9B, 2, 256, 4, 2, 64, 512, 1024, quant="q6_k", sliding_window=24); tie = False
+    else:
+        spec = gs.scaled(gs.C3_LLAMA3_8B, 2, 256, 8, 2, 64, 512, 1024, quant="q4_k_m"); tie = True
+    tensors = list(gs.synth_tensors(spec, 13))
+    file_tensors = tensors
+    if tie:
+        # the file stores one Q6_K matrix used as embedding and, through the tie, as output head
+        emb_raw = [t for t in tensors if t[0] < 0 and t[1] == capi.G_OUTPUT][0][3]
+        file_tensors = [(l, s, capi.T_Q6_K, emb_raw) if (l < 0 and s == capi.G_EMBED) else (l, s, t, r) for l, s, t, r in tensors]
+        emb_f32 = O.dequant(capi.T_Q6_K, emb_raw, spec.vocab * spec.hidden).reshape(spec.vocab, spec.hidden)
+        tensors = [(l, s, capi.T_F32, emb_f32) if (l < 0 and s == capi.G_EMBED) else (l, s, t, r) for l, s, t, r in tensors]
+    path = str(tmp_path / "model.gguf")
+    gs.write_gguf(path, spec, file_tensors, tie_output=tie)
+    ga = capi.Model.from_gguf(be, path, max_blocks=64, max_seqs=8, max_batch_tokens=256, max_blocks_per_seq=64)
+    gb = capi.Model(be, gs.model_config(spec, 64, 8, 256, 64))
+    for layer, slot, t, raw in tensors:
+        gb.set_tensor(layer, slot, t, raw)
+    gb.finalize()
+    assert ga.weight_bytes() == gb.weight_bytes()
+    rng = np.random.default_rng(2)
+    p = rng.integers(0, spec.vocab, 37).astype(np.int32)
+    ta, la = ga.prefill(1, p, 0, want_logits=True)
+    tb, lb = gb.prefill(1, p, 0, want_logits=True)
+    assert ta == tb and np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+    cur = ta
+    for step in range(6):
+        oa, la = ga.decode_step([1], [cur], [37 + step], want_logits=True)
+        ob, lb = gb.decode_step([1], [cur], [37 + step], want_logits=True)
+        assert np.array_equal(la.view(np.uint32), lb.view(np.uint32)) and oa[0] == ob[0]
+        cur = int(oa[0])
+    ga.close(); gb.close()
+
+
+def test_load_gguf_reports_bad_tensors(be, tmp_path):
+    spec = small_llama(1)
+    tensors = list(gs.synth_tensors(spec, 1))
+    path = str(tmp_path / "short.gguf")
+    gs.write_gguf(path, spec, [t for t in tensors if not (t[0] == 0 and t[1] == capi.W_W2)])
+    with pytest.raises(RuntimeError, match="blk.0.ffn_down.weight not found"):
+        capi.Model.from_gguf(be, path, max_blocks=16)
+    wrong = gs.scaled(spec, 1, spec.hidden, spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.ffn * 2, spec.vocab)
+    path2 = str(tmp_path / "shape.gguf")
+    gs.write_gguf(path2, spec, tensors, meta_spec=wrong)     # metadata says ffn*2, tensors are ffn wide
+    with pytest.raises(RuntimeError, match="has shape"):
+        capi.Model.from_gguf(be, path2, max_blocks=16)

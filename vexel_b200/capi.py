@@ -87,6 +87,10 @@ SIGNATURES = {
     "vx_pool_layer_ptr": [_vp, _i, C.POINTER(_D), C.POINTER(_sz)],
     "vx_seq_fill_synthetic": [_vp, _i64, _i, C.c_uint32],
     "vx_decode_step": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp],
+    "vx_model_get_config": [_vp, _vp],
+    "vx_gguf_open": [C.c_char_p, C.POINTER(_vp)], "vx_gguf_close": [_vp], "vx_gguf_error": [_vp], "vx_gguf_tensor_count": [_vp],
+    "vx_gguf_tensor_info": [_vp, _i, C.c_char_p, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u64)],
+    "vx_gguf_meta": [_vp, C.c_char_p, C.c_char_p, _i], "vx_gguf_model_config": [_vp, _vp], "vx_model_load_gguf": [_vp, _vp],
     "vx_decode_step_sampled": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "vx_sample_rows": [_vp, _D, _i, _i, _vp, _vp],
     "vx_prefill": [_vp, _i64, _vp, _i, _i, _vp, _vp],
@@ -104,7 +108,7 @@ SIGNATURES = {
     "vx_sched_step": [_vp, C.POINTER(_i)], "vx_sched_poll": [_vp, _i64, _vp, _i, C.POINTER(_i), C.POINTER(_i)],
     "vx_sched_get_metrics": [_vp, C.POINTER(SchedMetrics)],
 }
-_RESTYPE = {"vx_last_error": C.c_char_p}
+_RESTYPE = {"vx_last_error": C.c_char_p, "vx_gguf_error": C.c_char_p}
 
 
 class Lib:
@@ -261,6 +265,51 @@ class Backend:
     def SynthQ4_0(self, dst, n_elements, seed, sigma): self._ck(self.lib.vx_synth_q4_0(self.h, dst, n_elements, seed, sigma))
 
 
+class GGUFError(RuntimeError):
+    pass
+
+
+class GGUF:
+    """A parsed GGUF file (gguf.Open, pkg/gguf/gguf.go:246): metadata, tensor table, architecture config.  Host only."""
+
+    def __init__(self, path):
+        self.lib = Lib.get().dll
+        h = C.c_void_p()
+        rc = self.lib.vx_gguf_open(os.fsencode(path), C.byref(h))
+        self.h = h
+        if rc != 0:
+            msg = self.lib.vx_gguf_error(h).decode(); self.close()
+            raise GGUFError(msg)
+
+    def close(self):
+        if self.h:
+            self.lib.vx_gguf_close(self.h); self.h = None
+
+    def _ck(self, rc):
+        if rc != 0:
+            raise GGUFError("%d: %s" % (rc, self.lib.vx_gguf_error(self.h).decode()))
+
+    def tensors(self):
+        """[(name, ggml type, dims in GGUF order, absolute file offset, bytes)]"""
+        out = []
+        for i in range(self.lib.vx_gguf_tensor_count(self.h)):
+            name = C.create_string_buffer(256); t, nd = C.c_int(), C.c_int()
+            ne = (C.c_uint64 * 4)(); off, nb = C.c_uint64(), C.c_uint64()
+            self._ck(self.lib.vx_gguf_tensor_info(self.h, i, name, 256, C.byref(t), C.byref(nd), ne, C.byref(off), C.byref(nb)))
+            out.append((name.value.decode(), t.value, tuple(ne[:nd.value]), off.value, nb.value))
+        return out
+
+    def meta(self, key):
+        buf = C.create_string_buffer(4096)
+        rc = self.lib.vx_gguf_meta(self.h, key.encode(), buf, 4096)
+        return None if rc == 5 else buf.value.decode()
+
+    def model_config(self, max_blocks, max_seqs, max_batch_tokens, max_blocks_per_seq) -> ModelConfig:
+        cfg = ModelConfig(max_blocks=max_blocks, max_seqs=max_seqs, max_batch_tokens=max_batch_tokens, max_blocks_per_seq=max_blocks_per_seq)
+        self._ck(self.lib.vx_gguf_model_config(self.h, C.byref(cfg)))
+        return cfg
+
+
 class Model:
     """The batched decode fast path (vx_model_* / vx_seq_* / vx_decode_step / vx_prefill)."""
 
@@ -269,6 +318,20 @@ class Model:
         h = C.c_void_p()
         be._ck(self.lib.vx_model_create(be.h, C.byref(cfg), C.byref(h)))
         self.h = h
+
+    @classmethod
+    def from_gguf(cls, be: Backend, path, max_blocks, max_seqs=8, max_batch_tokens=256, max_blocks_per_seq=64):
+        """initModel's load sequence (cmd/vexel/commands.go:35-142): parse, configure from metadata, stream weights to the device."""
+        g = GGUF(path)
+        try:
+            m = cls(be, g.model_config(max_blocks, max_seqs, max_batch_tokens, max_blocks_per_seq))
+            try:
+                m._ck(m.lib.vx_model_load_gguf(m.h, g.h))
+            except Exception:
+                m.close(); raise
+            return m
+        finally:
+            g.close()
 
     def close(self):
         if self.h:

@@ -158,6 +158,8 @@ int vxq_gemm(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, 
              float *parts, size_t parts_cap_floats);
 int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out, float *parts,
                 size_t parts_cap_floats);
+struct vx_model;
+extern "C" vx_ctx *vx_model_ctx(vx_model *m);     // the context a model lives in (internal)
 int vx_check_device_error(vx_ctx *c);   // after a stream synchronisation: reports and clears the sticky kernel error word
 int vxq_split_rows(vx_ctx *c, const float *x, int rows, int cols, int ld, const VxSplit &s);
 int vxq_reduce_parts(vx_ctx *c, const float *parts, int n_parts, int m, int n, float *out, int ld_out);

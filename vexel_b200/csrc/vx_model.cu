@@ -898,6 +898,14 @@ int vx_model_destroy(vx_model *m) {
     return VX_OK;
 }
 
+vx_ctx *vx_model_ctx(vx_model *m) { return m ? m->c : nullptr; }
+
+int vx_model_get_config(vx_model *m, vx_model_config *out) {
+    if (!m || !out) return VX_E_BAD_ARG;
+    *out = m->cfg;
+    return VX_OK;
+}
+
 int vx_model_set_tensor(vx_model *m, int layer, int slot, int type, const void *data, size_t bytes, int on_device) {
     if (!m) return VX_E_BAD_ARG;
     vx_ctx *c = m->c;

@@ -227,3 +227,78 @@ def weight_bytes(spec: ModelSpec) -> int:
     total += spec.vocab * spec.hidden * per[out_type]
     total += (spec.n_layers * (4 if spec.post_norms else 2) + 1) * spec.hidden * 4
     return int(total)
+
+
+# ---------------------------------------------------------------------------- GGUF v3 files
+_GGUF_NAMES = {  # slot -> tensor suffix under blk.N. (GetLayerTensorName, inference/pkg/gguf/loader.go:132-229)
+    capi.W_ATTN_NORM: "attn_norm.weight", capi.W_WQ: "attn_q.weight", capi.W_WK: "attn_k.weight", capi.W_WV: "attn_v.weight",
+    capi.W_WO: "attn_output.weight", capi.W_POST_ATTN_NORM: "post_attention_norm.weight", capi.W_FFN_NORM: "ffn_norm.weight",
+    capi.W_W1: "ffn_gate.weight", capi.W_W3: "ffn_up.weight", capi.W_W2: "ffn_down.weight", capi.W_POST_FFN_NORM: "post_ffw_norm.weight"}
+_GGUF_GLOBALS = {capi.G_EMBED: "token_embd.weight", capi.G_FINAL_NORM: "output_norm.weight", capi.G_OUTPUT: "output.weight"}
+_MT_U32, _MT_F32, _MT_STR, _MT_ARR = 4, 6, 8, 9
+
+
+def gguf_tensor_name(layer, slot):
+    return _GGUF_GLOBALS[slot] if layer < 0 else "blk.%d.%s" % (layer, _GGUF_NAMES[slot])
+
+
+def _gstr(s):
+    b = s.encode()
+    return np.uint64(len(b)).tobytes() + b
+
+
+def write_gguf(path, spec: ModelSpec, tensors, alignment=32, with_tokens=True, tie_output=False, version=3, meta_spec=None):
+    """Writes `tensors` (an iterable of (layer, slot, ggml type, raw ndarray), e.g. synth_tensors(spec, seed)) as a GGUF
+    file with the metadata keys inference/pkg/gguf/gguf.go:503-584 reads.  with_tokens adds a tokenizer.ggml.tokens
+    array of spec.vocab placeholder strings (the reference takes the vocabulary size from its length);
+    tie_output drops output.weight so that loaders fall back to the embedding; meta_spec (tests of error paths) lets
+    the metadata describe a different model than the tensor shapes."""
+    shape_spec, spec = spec, (meta_spec or spec)
+    a = spec.arch
+    kv = [("general.architecture", _MT_STR, a), ("general.alignment", _MT_U32, alignment),
+          (a + ".block_count", _MT_U32, spec.n_layers), (a + ".embedding_length", _MT_U32, spec.hidden),
+          (a + ".attention.head_count", _MT_U32, spec.n_heads), (a + ".attention.head_count_kv", _MT_U32, spec.n_kv_heads),
+          (a + ".feed_forward_length", _MT_U32, spec.ffn), (a + ".context_length", _MT_U32, 8192),
+          (a + ".rope.freq_base", _MT_F32, spec.rope_theta), (a + ".attention.layer_norm_rms_epsilon", _MT_F32, spec.rms_eps),
+          (a + ".attention.key_length", _MT_U32, spec.head_dim), (a + ".attention.value_length", _MT_U32, spec.head_dim)]
+    if spec.sliding_window:
+        kv.append((a + ".attention.sliding_window", _MT_U32, spec.sliding_window))
+    if spec.attn_softcap:
+        kv.append((a + ".attn_logit_softcapping", _MT_F32, spec.attn_softcap))
+    if spec.final_softcap:
+        kv.append((a + ".final_logit_softcapping", _MT_F32, spec.final_softcap))
+    items = []
+    for layer, slot, t, raw in tensors:
+        if tie_output and layer < 0 and slot == capi.G_OUTPUT:
+            continue
+        if layer < 0:
+            n, k = (1, shape_spec.hidden) if slot == capi.G_FINAL_NORM else (shape_spec.vocab, shape_spec.hidden)
+        else:
+            n, k = (slot_shape(shape_spec, slot) if slot in (capi.W_WQ, capi.W_WK, capi.W_WV, capi.W_WO, capi.W_W1, capi.W_W3, capi.W_W2)
+                    else (1, shape_spec.hidden))
+        dims = (k,) if n == 1 and raw.ndim == 1 else (k, n)                      # ne[0] is the innermost dimension
+        items.append((gguf_tensor_name(layer, slot), dims, t, np.ascontiguousarray(raw).view(np.uint8).reshape(-1)))
+    head = bytearray()
+    head += np.uint32(0x46554747).tobytes() + np.uint32(version).tobytes()
+    head += np.uint64(len(items)).tobytes() + np.uint64(len(kv) + (1 if with_tokens else 0)).tobytes()
+    for key, t, v in kv:
+        head += _gstr(key) + np.uint32(t).tobytes()
+        head += _gstr(v) if t == _MT_STR else (np.uint32(v).tobytes() if t == _MT_U32 else np.float32(v).tobytes())
+    if with_tokens:
+        head += _gstr("tokenizer.ggml.tokens") + np.uint32(_MT_ARR).tobytes() + np.uint32(_MT_STR).tobytes() + np.uint64(spec.vocab).tobytes()
+        head += b"".join(_gstr("t%d" % i) for i in range(spec.vocab))
+    off = 0
+    offsets = []
+    for name, dims, t, raw in items:
+        offsets.append(off)
+        off = (off + raw.size + alignment - 1) // alignment * alignment
+    for (name, dims, t, raw), o in zip(items, offsets):
+        head += _gstr(name) + np.uint32(len(dims)).tobytes() + b"".join(np.uint64(d).tobytes() for d in dims)
+        head += np.uint32(t).tobytes() + np.uint64(o).tobytes()
+    pad = (-len(head)) % alignment
+    with open(path, "wb") as f:
+        f.write(bytes(head) + b"\0" * pad)
+        pos = 0
+        for (name, dims, t, raw), o in zip(items, offsets):
+            f.write(b"\0" * (o - pos)); f.write(raw.tobytes()); pos = o + raw.size
+    return [(name, t, dims) for name, dims, t, raw in items]
