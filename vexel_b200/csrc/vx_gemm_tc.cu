@@ -57,12 +57,20 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// waits in hardware for the phase to complete or for a short time limit, whichever comes first; a thread parked here
+// takes no issue slots from the warps that share its scheduler (a test_wait spin loop does)
+__device__ __forceinline__ bool mbar_try_park(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(2000u) : "memory");
+    return ok != 0;
+}
 // bounded wait: false on timeout or when another thread of the CTA has already given up
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
-        if (mbar_try(bar, parity)) return true;
+        if (mbar_try_park(bar, parity)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_CLOCKS) { *abort_flag = 1; return false; }
     }
@@ -92,8 +100,10 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
     asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
                  ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+                   "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -139,7 +149,7 @@ gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     if (tid == 0) {
         s_abort = 0;
-        for (int s = 0; s < TC_ST; s++) { mbar_init(xf_bar(s), 1); mbar_init(af_bar(s), TC_DEQ / 32); mbar_init(e_bar(s), TC_ISSUERS); }   // one arrival per warp:
+        for (int s = 0; s < TC_ST; s++) { mbar_init(xf_bar(s), 1); mbar_init(af_bar(s), TC_DEQ / 64); mbar_init(e_bar(s), TC_ISSUERS); }   // one arrival per warp:
         for (int s = 0; s < TC_RAW; s++) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), TC_DEQ / 32); }   // 512 arrivals on one word serialise
         mbar_init(accum_bar, TC_ISSUERS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -157,51 +167,52 @@ gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
     if (warp < TC_DEQ / 32) {
         // ------------------------------------------------------------------ dequantisers
-        const int row = tid & 127, qd = tid >> 7, b = qd >> 1, h = qd & 1;   // operand row, block of the stage, word pair {2h, 2h+1}
+        // Two groups of eight warps take alternate stages, so the groups run out of phase and each scheduler always has
+        // warps of both in flight.  Within a group, warp w owns the 32 operand rows (= tensor-memory lanes) of quadrant
+        // w & 3 and the 32-weight block b of the stage: one thread turns one GGUF block of its row into 16 columns of
+        // fp16 pairs, written with one 16-column store each for the hi and the lo part.
+        const int grp = (warp >> 2) & 1, b = warp >> 3;
+        const int row = (warp & 3) * 32 + lane;
         const int grow = min(r0 + row, N - 1);
         const __half *scp = sc + (size_t)grow * k_groups * 4 + (size_t)kb_begin * 2 + b;
-        // nibble tile rows are 64 bytes with SWIZZLE_64B: 16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3)
+        // nibble tile rows are 64 bytes with SWIZZLE_64B: 16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3);
+        // chunk c holds word c of the four blocks of the 128-weight group, this thread's block is 2 * grp + b of it
         const int rsw = (row >> 1) & 3;
-        const int raw_off0 = row * 64 + (((2 * h) ^ rsw) << 4), raw_off1 = row * 64 + (((2 * h + 1) ^ rsw) << 4);
-        // this thread's tensor-memory lane (= weight row) and the first column of its 4-column groups
-        const uint32_t a_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + TMEM_A + 16 * b + 4 * h;
-        __half d0 = n_kb > 0 ? scp[0] : __float2half(0.f);
-        __half d1 = n_kb > 1 ? scp[2] : d0;
-        uint4 w0 = make_uint4(0, 0, 0, 0), w1 = w0;
-        for (int kb = 0; kb < n_kb; kb++) {
+        int raw_off[4];
+#pragma unroll
+        for (int c = 0; c < 4; c++) raw_off[c] = row * 64 + ((c ^ rsw) << 4) + 4 * (2 * grp + b);
+        const uint32_t a_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + TMEM_A + 16 * b;
+        __half d0 = grp < n_kb ? scp[2 * grp] : __float2half(0.f);
+        for (int kb = grp; kb < n_kb; kb += 2) {
             const int as = kb % TC_ST, g = kb >> 1, slot = g % TC_RAW;
-            const __half d2n = (kb + 2 < n_kb) ? scp[2 * (kb + 2)] : d1;      // scale two stages ahead
-            if ((kb & 1) == 0) {
-                if (!mbar_wait(rawf_bar(slot), (g / TC_RAW) & 1, abort_flag)) break;
-                const unsigned char *rp = gen_base + TC_ST * STAGE_BYTES + slot * RAW_BYTES;
-                w0 = *reinterpret_cast<const uint4 *>(rp + raw_off0);    // word 2h   of blocks 0..3 of the group
-                w1 = *reinterpret_cast<const uint4 *>(rp + raw_off1);    // word 2h+1 of blocks 0..3
-                __syncwarp();
-                if (lane == 0) mbar_arrive(rawe_bar(slot));
-            }
+            const __half d1 = (kb + 2 < n_kb) ? scp[2 * (kb + 2)] : d0;        // scale of this group's next stage
+            if (!mbar_wait(rawf_bar(slot), (g / TC_RAW) & 1, abort_flag)) break;
+            const unsigned char *rp = gen_base + TC_ST * STAGE_BYTES + slot * RAW_BYTES;
+            uint32_t w[4];
+#pragma unroll
+            for (int c = 0; c < 4; c++) w[c] = *reinterpret_cast<const uint32_t *>(rp + raw_off[c]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(rawe_bar(slot));
             if (kb >= TC_ST && !mbar_wait(e_bar(as), ((kb / TC_ST) - 1) & 1, abort_flag)) break;
-            // this thread's block of the stage is block 2*(kb&1) + b of the group
-            const uint32_t wa = (kb & 1) ? (b ? w0.w : w0.z) : (b ? w0.y : w0.x);
-            const uint32_t wc = (kb & 1) ? (b ? w1.w : w1.z) : (b ? w1.y : w1.x);
-            const uint32_t a_hi = a_lane + 64 * as, a_lo = a_hi + 32;
             const __half2 dd = __half2half2(d0);
+            uint32_t hi[16], lo[16];
 #pragma unroll
-            for (int nib = 0; nib < 2; nib++) {
-                __half2 q[4];
-                q[0] = nib2(wa >> (4 * nib)); q[1] = nib2(wa >> (4 * nib + 8));
-                q[2] = nib2(wc >> (4 * nib)); q[3] = nib2(wc >> (4 * nib + 8));
-                uint32_t hi[4], lo[4];
+            for (int nib = 0; nib < 2; nib++)
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const __half2 ph = __hmul2(q[e], dd);
-                    const __half2 pl = __hfma2(q[e], dd, __hneg2(ph));
-                    hi[e] = h2u(ph); lo[e] = h2u(pl);
-                }
-                // k positions 32b + 16nib + 8h .. +7 of the stage = columns 16b + 8nib + 4h .. +3 (two fp16 per column)
-                tmem_st4(a_hi + 8 * nib, hi[0], hi[1], hi[2], hi[3]);
-                tmem_st4(a_lo + 8 * nib, lo[0], lo[1], lo[2], lo[3]);
-            }
-            d0 = d1; d1 = d2n;
+                for (int c = 0; c < 4; c++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        // bytes e and e + 2 of word c: weights 16 nib + 4 c + {e, e + 2} of the block (the activation tiles
+                        // carry the same order of k within every four), exact product d * (q - 8) as an fp16 pair
+                        const __half2 q = nib2(w[c] >> (4 * nib + 8 * e));
+                        const __half2 ph = __hmul2(q, dd);
+                        const __half2 pl = __hfma2(q, dd, __hneg2(ph));
+                        hi[8 * nib + 2 * c + e] = h2u(ph); lo[8 * nib + 2 * c + e] = h2u(pl);
+                    }
+            // k positions 32 b .. 32 b + 31 of the stage = columns 16 b .. 16 b + 15 (two fp16 per column)
+            tmem_st16(a_lane + 64 * as, hi);
+            tmem_st16(a_lane + 64 * as + 32, lo);
+            d0 = d1;
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
