@@ -253,6 +253,9 @@ int vx_model_kernel_time(vx_model *m, int which, int enable, float *ms, uint64_t
 /* deterministic synthetic Q4_0 weights generated on the device: ~N(0, sigma) quantised with
  * d = signed-absmax / -8, q = clamp(round(x/d) + 8, 0, 15); writes GGUF Q4_0 blocks */
 int vx_synth_q4_0(vx_ctx *ctx, vx_dptr dst_raw, int64_t n_elements, uint64_t seed, float sigma);
+/* bench helper: valid Q4_K (type 12) or Q6_K (type 14) blocks with hashed payload and super-scales chosen for a
+ * dequantised standard deviation near sigma; for timing runs on K-quant model shapes */
+int vx_synth_kquant(vx_ctx *ctx, vx_dptr dst_raw, int ggml_type, int64_t n_elements, uint64_t seed, float sigma);
 /* bench helper: permute the pool's free list so that consecutive logical blocks land on scattered
  * physical blocks; only valid while no sequence holds blocks */
 int vx_pool_shuffle_free_list(vx_model *m, uint32_t seed);

@@ -100,7 +100,9 @@ SIGNATURES = {
     "vx_model_get_packing": [_vp, _vp, _vp, _vp, _i, _i],
     "vx_model_counters": [_vp, C.POINTER(_u64), C.POINTER(_u64)],
     "vx_model_kernel_time": [_vp, _i, _i, C.POINTER(_f), C.POINTER(_u64)],
+    "vx_synth_kquant": [_vp, _D, _i, _i64, _u64, _f],
     "vx_synth_q4_0": [_vp, _D, _i64, _u64, _f],
+    "vx_synth_kquant": [_vp, _D, _i, _i64, _u64, _f],
     "vx_pool_shuffle_free_list": [_vp, C.c_uint32], "vx_model_weight_bytes": [_vp, C.POINTER(_u64)],
     "vx_set_gemm_terms": [_i], "vx_set_tc_min_rows": [_i], "vx_model_max_blocks": [_vp],
     "vx_sched_create": [_vp, C.POINTER(SchedConfig), C.POINTER(_vp)], "vx_sched_destroy": [_vp],
@@ -263,6 +265,9 @@ class Backend:
         self._ck(self.lib.vx_sdpa_paged_decode_ex(self.h, q, pool, table, out, kv_start, kv_len, bs, hq, hkv, d, scale, softcap, int(f16)))
 
     def SynthQ4_0(self, dst, n_elements, seed, sigma): self._ck(self.lib.vx_synth_q4_0(self.h, dst, n_elements, seed, sigma))
+
+    def SynthKQuant(self, dst, type_id, n_elements, seed, sigma):
+        self._ck(self.lib.vx_synth_kquant(self.h, dst, type_id, n_elements, seed, sigma))
 
 
 class GGUFError(RuntimeError):

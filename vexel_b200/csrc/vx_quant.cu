@@ -661,6 +661,38 @@ int vx_synth_q4_0(vx_ctx *c, vx_dptr dst, int64_t n, uint64_t seed, float sigma)
     return VX_OK;
 }
 
+// Valid Q4_K / Q6_K blocks with hashed payload bytes, for benchmarks that need weights of a K-quant model's shape and
+// byte size without a host-side encoder in the loop.  Every byte pattern of the quant and scale fields is a valid
+// block; only the fp16 super-scales are chosen, so that the dequantised weights have a standard deviation near sigma
+// (Q4_K: w = d*sc*q - dmin*m with sc, m in [0,63], q in [0,15]; Q6_K: w = d*sc*q with sc in [-128,127], q in [-32,31]).
+__global__ void synth_kquant_kernel(uint8_t *__restrict__ dst, int64_t n_blocks, int type, uint64_t seed, float sigma) {
+    int64_t b = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    const int bytes = type == VX_T_Q4_K ? 144 : 210;
+    uint8_t *p = dst + b * bytes;
+    for (int i = 0; i < bytes; i += 8) {
+        uint64_t r = mix64(seed ^ mix64((uint64_t)b * 32 + i / 8));
+        for (int j = 0; j < 8 && i + j < bytes; j++) p[i + j] = (uint8_t)(r >> (8 * j));
+    }
+    if (type == VX_T_Q4_K) {
+        unsigned short d = __half_as_ushort(__float2half_rn(sigma / 200.f)), dm = __half_as_ushort(__float2half_rn(7.5f * sigma / 200.f));
+        p[0] = (uint8_t)(d & 0xFF); p[1] = (uint8_t)(d >> 8); p[2] = (uint8_t)(dm & 0xFF); p[3] = (uint8_t)(dm >> 8);
+    } else {
+        unsigned short d = __half_as_ushort(__float2half_rn(sigma / 1370.f));
+        p[208] = (uint8_t)(d & 0xFF); p[209] = (uint8_t)(d >> 8);
+    }
+}
+
+int vx_synth_kquant(vx_ctx *c, vx_dptr dst, int type, int64_t n, uint64_t seed, float sigma) {
+    if (!c) return VX_E_BAD_ARG;
+    VxGuard g(c);
+    VX_REQUIRE(c, dst && n > 0 && n % 256 == 0 && (type == VX_T_Q4_K || type == VX_T_Q6_K), "Q4_K or Q6_K, element count a positive multiple of 256");
+    int64_t nb = n / 256;
+    synth_kquant_kernel<<<(unsigned)ceil_div64(nb, 128), 128, 0, c->stream>>>(dp<uint8_t>(dst), nb, type, seed, sigma);
+    VX_LAUNCH_CHECK(c);
+    return VX_OK;
+}
+
 // QuantizedMatMul on raw GGUF bytes: repack + split into the context scratch, then the MMA kernel.
 static int matmul_quant(vx_ctx *c, int type, vx_dptr a, vx_dptr b_raw, vx_dptr out, int m, int n, int k) {
     if (!c) return VX_E_BAD_ARG;
