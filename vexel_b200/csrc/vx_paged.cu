@@ -223,6 +223,206 @@ paged_flash_kernel(VxAttnArgs a) {
     }
 }
 
+// ------------------------------------------------------------------ grouped-query variant on the tensor cores
+// With G query heads per KV head the dot products above cost G times the CUDA-core work per KV byte (at G = 8 more than
+// the FMA pipes can deliver at HBM speed) and a warp-shuffle reduction per head.  Here a warp turns one 16-token page into
+// two small matrix products on mma.sync.m16n8k16 with the 16 tokens as the M dimension and the group's heads as N = 8:
+//   S^T[16 tokens x 8 heads] = K[16 x D] . Q^T[D x 8]          K from shared memory (ldmatrix), Q^T in registers
+//   O^T[D x 8 heads]        += V^T[D x 16 tokens] . P^T[16 x 8]  V^T via ldmatrix.trans, P^T from S^T by four shuffles
+// K and V pages are staged through a per-warp double buffer with cp.async (16-byte chunks, XOR-swizzled rows so that
+// ldmatrix is conflict-free).  q and p are carried as exact fp16 hi + lo pairs (two MMAs each), K and V are fp16 already,
+// accumulation is float32: the result matches the float32 reference to rounding, like the CUDA-core kernel.
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void cp_async_16(uint32_t saddr, const void *g) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(saddr), "l"(g));
+}
+__device__ __forceinline__ uint32_t pack_hi_lo(float x, float y, uint32_t *lo) {     // exact split of two floats into fp16 hi, lo pairs
+    const __half hx = __float2half_rn(x), hy = __float2half_rn(y);
+    const __half2 h = __halves2half2(hx, hy);
+    const __half2 l = __floats2half2_rn(x - __half2float(hx), y - __half2float(hy));
+    *lo = *reinterpret_cast<const uint32_t *>(&l);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+template <int D, int G>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+paged_flash_mma_kernel(VxAttnArgs a) {
+    constexpr int KS = D / 16;                    // K=16 steps of the score product = 16-row tiles of the output product
+    constexpr int ROW_B = D * 2;                  // bytes of one token's head slice
+    constexpr int TILE_B = ATT_BS * ROW_B;        // one K (or V) page tile
+    constexpr int STAGE_B = 2 * TILE_B;           // K tile then V tile
+    constexpr int CPL = STAGE_B / 16 / 32;        // 16-byte chunks per lane and page
+    extern __shared__ __align__(128) unsigned char att_smem[];
+
+    const int wi = blockIdx.x;
+    if (wi >= *a.n_work_dev) return;
+    const int4 item = a.work[wi];
+    const int row = item.x, first_page = item.y, n_pages = item.z;
+    const int kvh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+    const int kv_start = a.row_kv_start ? a.row_kv_start[row] : 0, kv_len = a.row_kv_len[row];
+    const int32_t *table = a.tables[a.row_slot[row]];
+    const size_t hs = (size_t)a.n_kv_heads * D;
+    const __half *pool = (const __half *)a.pool;
+    const uint32_t stage0 = (uint32_t)__cvta_generic_to_shared(att_smem) + warp * 2 * STAGE_B;
+
+    // Q^T fragments: lane (g, c) holds head g (zero beyond the group), d = 16 ks + 2c, +1 and + 8, +9, as hi and lo halves
+    uint32_t qh[KS][2], ql[KS][2];
+    {
+        const float *qp = a.q + (size_t)row * a.q_row_stride + (size_t)(kvh * G + (g < G ? g : 0)) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            float2 v0 = make_float2(0.f, 0.f), v1 = v0;
+            if (g < G) { v0 = *reinterpret_cast<const float2 *>(qp + 16 * ks + 2 * c); v1 = *reinterpret_cast<const float2 *>(qp + 16 * ks + 2 * c + 8); }
+            qh[ks][0] = pack_hi_lo(v0.x, v0.y, &ql[ks][0]);
+            qh[ks][1] = pack_hi_lo(v1.x, v1.y, &ql[ks][1]);
+        }
+    }
+    float acc[KS][4];
+#pragma unroll
+    for (int i = 0; i < KS; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};     // heads 2c, 2c+1; l over this lane's tokens only
+
+    auto issue = [&](int page, int stage) {       // stages the K and V tiles of one page (all lanes)
+        const int blk = table[page];
+        const __half *kb = pool + (size_t)blk * 2 * ATT_BS * hs + (size_t)kvh * D;
+        const uint32_t sb = stage0 + stage * STAGE_B;
+#pragma unroll
+        for (int j = 0; j < CPL; j++) {
+            const int ci = lane + 32 * j;                    // chunk of the stage: [K | V][token][D/8 chunks]
+            const int isv = ci / (TILE_B / 16), r = ci % (TILE_B / 16), t = r / (D / 8), cc = r % (D / 8);
+            cp_async_16(sb + isv * TILE_B + t * ROW_B + ((cc ^ (t & 7)) << 4), kb + (size_t)isv * ATT_BS * hs + (size_t)t * hs + cc * 8);
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+
+    const int last_page = first_page + n_pages;
+    int page = first_page + warp, stage = 0;
+    if (page < last_page) issue(page, 0);
+    for (; page < last_page; page += ATT_WARPS, stage ^= 1) {
+        if (page + ATT_WARPS < last_page) { issue(page + ATT_WARPS, stage ^ 1); asm volatile("cp.async.wait_group 1;\n" ::); }
+        else asm volatile("cp.async.wait_group 0;\n" ::);
+        __syncwarp();
+        const uint32_t kb_s = stage0 + stage * STAGE_B, vb_s = kb_s + TILE_B;
+
+        // scores, transposed: rows = tokens g and g + 8, columns = heads 2c and 2c + 1
+        float st[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const int mj = lane >> 3, r = (lane & 7) + 8 * (mj & 1);           // ldmatrix row address of this lane
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                uint32_t ka[4];
+                ldsm_x4(ka, kb_s + r * ROW_B + (((2 * ks + (mj >> 1)) ^ (r & 7)) << 4));
+                mma_16816(st, ka, qh[ks][0], qh[ks][1]);
+                mma_16816(st, ka, ql[ks][0], ql[ks][1]);
+            }
+        }
+        const int pos0 = page * ATT_BS + g, pos1 = pos0 + 8;
+        const bool ok0 = pos0 >= kv_start && pos0 < kv_len, ok1 = pos1 >= kv_start && pos1 < kv_len;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float v = st[i] * a.scale;
+            if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
+            st[i] = ((i < 2) ? ok0 : ok1) ? v : -INFINITY;
+        }
+        float p[4];
+#pragma unroll
+        for (int hh = 0; hh < 2; hh++) {
+            float mx = fmaxf(st[hh], st[2 + hh]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m_run[hh], mx);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;            // page fully outside the window: p = 0, no rescale
+            const float corr = __expf(m_run[hh] - m_use);                    // exp(-inf) = 0 on the first page
+            p[hh] = st[hh] == -INFINITY ? 0.f : __expf(st[hh] - m_use);
+            p[2 + hh] = st[2 + hh] == -INFINITY ? 0.f : __expf(st[2 + hh] - m_use);
+            l_run[hh] = l_run[hh] * corr + p[hh] + p[2 + hh];
+#pragma unroll
+            for (int i = 0; i < KS; i++) { acc[i][hh] *= corr; acc[i][2 + hh] *= corr; }
+            m_run[hh] = m_new;
+        }
+        // P^T as the B operand: lane (g, c) needs head g at tokens 2c, 2c+1 (b0) and 2c+8, 2c+9 (b1); in the score layout
+        // token t, head h sits in lane (t & 7, h >> 1), register 2 (t >> 3) + (h & 1)
+        uint32_t xl0, xl1;
+        const uint32_t xh0 = pack_hi_lo(p[0], p[2], &xl0), xh1 = pack_hi_lo(p[1], p[3], &xl1);   // {token g, token g+8} of head 2c / 2c+1
+        const int srcA = (2 * c) * 4 + (g >> 1), srcB = (2 * c + 1) * 4 + (g >> 1);
+        const bool odd = g & 1;
+        uint32_t ah0 = __shfl_sync(0xffffffffu, xh0, srcA), ah1 = __shfl_sync(0xffffffffu, xh1, srcA);
+        uint32_t bh0 = __shfl_sync(0xffffffffu, xh0, srcB), bh1 = __shfl_sync(0xffffffffu, xh1, srcB);
+        uint32_t al0 = __shfl_sync(0xffffffffu, xl0, srcA), al1 = __shfl_sync(0xffffffffu, xl1, srcA);
+        uint32_t bl0 = __shfl_sync(0xffffffffu, xl0, srcB), bl1 = __shfl_sync(0xffffffffu, xl1, srcB);
+        const uint32_t ya_h = odd ? ah1 : ah0, yb_h = odd ? bh1 : bh0, ya_l = odd ? al1 : al0, yb_l = odd ? bl1 : bl0;
+        const uint32_t ph0 = __byte_perm(ya_h, yb_h, 0x5410), ph1 = __byte_perm(ya_h, yb_h, 0x7632);
+        const uint32_t pl0 = __byte_perm(ya_l, yb_l, 0x5410), pl1 = __byte_perm(ya_l, yb_l, 0x7632);
+        {
+            const int mj = lane >> 3, t = (lane & 7) + 8 * (mj >> 1);          // token row read by this lane
+#pragma unroll
+            for (int mt = 0; mt < KS; mt++) {
+                uint32_t va[4];
+                ldsm_x4_t(va, vb_s + t * ROW_B + (((2 * mt + (mj & 1)) ^ (t & 7)) << 4));
+                mma_16816(acc[mt], va, ph0, ph1);
+                mma_16816(acc[mt], va, pl0, pl1);
+            }
+        }
+        __syncwarp();                              // every lane is done with this stage before it is refilled
+    }
+
+    // this warp's partial result to shared memory (reusing the staging area), then the same 4-way merge as above
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) {
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 4);
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 8);
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 16);
+    }
+    __syncthreads();
+    float *sm_acc = reinterpret_cast<float *>(att_smem);                      // [warp][G][D]
+    float *sm_m = sm_acc + ATT_WARPS * G * D, *sm_l = sm_m + ATT_WARPS * G;    // [warp][G]
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) {
+        const int h = 2 * c + hh;
+        if (h < G) {
+            if (g == 0) { sm_m[warp * G + h] = m_run[hh]; sm_l[warp * G + h] = l_run[hh]; }
+#pragma unroll
+            for (int mt = 0; mt < KS; mt++) {
+                sm_acc[(warp * G + h) * D + 16 * mt + g] = acc[mt][hh];
+                sm_acc[(warp * G + h) * D + 16 * mt + g + 8] = acc[mt][2 + hh];
+            }
+        }
+    }
+    __syncthreads();
+    const bool single = (a.row_work_start[row + 1] - a.row_work_start[row]) == 1;
+    for (int idx = threadIdx.x; idx < G * D; idx += ATT_WARPS * 32) {
+        const int gi = idx / D, d = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++) M = fmaxf(M, sm_m[w * G + gi]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; w++) {
+            const float f = sm_m[w * G + gi] == -INFINITY ? 0.f : __expf(sm_m[w * G + gi] - M);
+            L = fmaf(sm_l[w * G + gi], f, L); O = fmaf(sm_acc[(w * G + gi) * D + d], f, O);
+        }
+        const int h = kvh * G + gi;
+        if (single) {
+            a.out[(size_t)row * a.out_row_stride + (size_t)h * D + d] = L > 0.f ? O / L : 0.f;
+        } else {
+            float *part = a.partials + ((size_t)wi * a.n_q_heads + h) * (D + 2);
+            part[d] = O;
+            if (d == 0) { part[D] = M; part[D + 1] = L; }
+        }
+    }
+}
+
 // rows cut into more than one chunk: out = sum_c O_c e^{m_c-M} / sum_c l_c e^{m_c-M}
 __global__ void paged_merge_kernel(VxAttnArgs a) {
     const int row = blockIdx.y, h = blockIdx.x, D = a.head_dim;
@@ -241,9 +441,32 @@ __global__ void paged_merge_kernel(VxAttnArgs a) {
     }
 }
 
+static int g_attn_mma = 1;     // grouped-query shapes use the tensor-core kernel (0 = the CUDA-core kernel, for comparison)
+
+template <int D, int G>
+static int flash_launch_mma(vx_ctx *c, const VxAttnArgs &a, dim3 grid) {
+    constexpr int SMEM = ATT_WARPS * 2 * 2 * ATT_BS * D * 2;      // per warp: two stages of a K and a V page tile
+    static_assert(SMEM >= (int)((ATT_WARPS * G * D + 2 * ATT_WARPS * G) * sizeof(float)), "merge buffers fit in the staging area");
+    static bool attr_done = false;
+    if (!attr_done) {
+        if (cudaFuncSetAttribute(paged_flash_mma_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
+        attr_done = true;
+    }
+    paged_flash_mma_kernel<D, G><<<grid, ATT_WARPS * 32, SMEM, c->stream>>>(a);
+    return 0;
+}
+
 template <int D>
 static int flash_launch_g(vx_ctx *c, const VxAttnArgs &a, int G) {
     dim3 grid(a.n_work, a.n_kv_heads);
+    if (g_attn_mma && G > 1) {
+        switch (G) {
+        case 2: return flash_launch_mma<D, 2>(c, a, grid);
+        case 4: return flash_launch_mma<D, 4>(c, a, grid);
+        case 8: return flash_launch_mma<D, 8>(c, a, grid);
+        default: return -1;
+        }
+    }
     switch (G) {
     case 1: paged_flash_kernel<D, 1><<<grid, ATT_WARPS * 32, 0, c->stream>>>(a); break;
     case 2: paged_flash_kernel<D, 2><<<grid, ATT_WARPS * 32, 0, c->stream>>>(a); break;
