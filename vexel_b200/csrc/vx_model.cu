@@ -671,7 +671,10 @@ int plan_chunks(vx_model *m, const std::vector<int> &kv_start, const std::vector
     long pages = 0;
     for (size_t i = 0; i < kv_len.size(); i++) pages += (kv_len[i] - 1) / BS - kv_start[i] / BS + 1;
     long target = 6L * m->c->sm_count;
-    int chunk = (int)std::min<long>(16, std::max<long>(4, (pages * m->cfg.n_kv_heads + target - 1) / target));
+    // grouped-query shapes have few KV heads, hence few CTAs per chunk: longer chunks amortise a CTA's start-up
+    // (block-table and query loads) and merge over more pages
+    const long max_chunk = m->cfg.n_heads > m->cfg.n_kv_heads ? 64 : 16;
+    int chunk = (int)std::min<long>(max_chunk, std::max<long>(4, (pages * m->cfg.n_kv_heads + target - 1) / target));
     for (;;) {
         long n = 0;
         for (size_t i = 0; i < kv_len.size(); i++) { int np = (kv_len[i] - 1) / BS - kv_start[i] / BS + 1; n += (np + chunk - 1) / chunk; }

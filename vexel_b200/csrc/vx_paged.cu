@@ -292,15 +292,23 @@ paged_flash_mma_kernel(VxAttnArgs a) {
     for (int i = 0; i < KS; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};     // heads 2c, 2c+1; l over this lane's tokens only
 
+    // cp.async plan of one page: chunk (t, cc) of the K and of the V tile, t = tl + RPI * jj.  Everything but the block base
+    // is fixed per lane: global offset g_off + jj * g_step (+ the V tile), shared offset from t and the swizzled chunk.
+    constexpr int CPR = D / 8;                    // 16-byte chunks per token row
+    constexpr int RPI = 32 / CPR;                 // token rows covered by one warp-wide copy
+    static_assert(CPL == 2 * (ATT_BS / RPI), "copy plan");
+    const int tl = lane / CPR, cc = lane % CPR;
+    const size_t g_off = (size_t)kvh * D + (size_t)tl * hs + cc * 8, g_step = (size_t)RPI * hs, g_v = (size_t)ATT_BS * hs;
     auto issue = [&](int page, int stage) {       // stages the K and V tiles of one page (all lanes)
         const int blk = table[page];
-        const __half *kb = pool + (size_t)blk * 2 * ATT_BS * hs + (size_t)kvh * D;
+        const __half *kb = pool + (size_t)blk * 2 * ATT_BS * hs + g_off;
         const uint32_t sb = stage0 + stage * STAGE_B;
 #pragma unroll
-        for (int j = 0; j < CPL; j++) {
-            const int ci = lane + 32 * j;                    // chunk of the stage: [K | V][token][D/8 chunks]
-            const int isv = ci / (TILE_B / 16), r = ci % (TILE_B / 16), t = r / (D / 8), cc = r % (D / 8);
-            cp_async_16(sb + isv * TILE_B + t * ROW_B + ((cc ^ (t & 7)) << 4), kb + (size_t)isv * ATT_BS * hs + (size_t)t * hs + cc * 8);
+        for (int jj = 0; jj < ATT_BS / RPI; jj++) {
+            const int t = tl + RPI * jj;
+            const uint32_t so = sb + t * ROW_B + ((cc ^ (t & 7)) << 4);
+            cp_async_16(so, kb + jj * g_step);
+            cp_async_16(so + TILE_B, kb + jj * g_step + g_v);
         }
         asm volatile("cp.async.commit_group;\n" ::);
     };
@@ -317,14 +325,22 @@ paged_flash_mma_kernel(VxAttnArgs a) {
         // scores, transposed: rows = tokens g and g + 8, columns = heads 2c and 2c + 1
         float st[4] = {0.f, 0.f, 0.f, 0.f};
         {
+            float st2[4] = {0.f, 0.f, 0.f, 0.f};                               // two accumulation chains halve the MMA latency chain
             const int mj = lane >> 3, r = (lane & 7) + 8 * (mj & 1);           // ldmatrix row address of this lane
+            const uint32_t krow = kb_s + r * ROW_B;
+            const int sw = r & 7, co = mj >> 1;
 #pragma unroll
-            for (int ks = 0; ks < KS; ks++) {
-                uint32_t ka[4];
-                ldsm_x4(ka, kb_s + r * ROW_B + (((2 * ks + (mj >> 1)) ^ (r & 7)) << 4));
+            for (int ks = 0; ks < KS; ks += 2) {
+                uint32_t ka[4], kc[4];
+                ldsm_x4(ka, krow + (((2 * ks + co) ^ sw) << 4));
+                ldsm_x4(kc, krow + (((2 * ks + 2 + co) ^ sw) << 4));
                 mma_16816(st, ka, qh[ks][0], qh[ks][1]);
+                mma_16816(st2, kc, qh[ks + 1][0], qh[ks + 1][1]);
                 mma_16816(st, ka, ql[ks][0], ql[ks][1]);
+                mma_16816(st2, kc, ql[ks + 1][0], ql[ks + 1][1]);
             }
+#pragma unroll
+            for (int i = 0; i < 4; i++) st[i] += st2[i];
         }
         const int pos0 = page * ATT_BS + g, pos1 = pos0 + 8;
         const bool ok0 = pos0 >= kv_start && pos0 < kv_len, ok1 = pos1 >= kv_start && pos1 < kv_len;
