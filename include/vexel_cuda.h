@@ -264,7 +264,8 @@ int vx_model_weight_bytes(vx_model *m, uint64_t *bytes);
 /* activation terms fed to the tensor cores by the projections: 2 = fp16 hi+lo split (float32-faithful,
  * default), 1 = single fp16 (half the MMA work, ~2e-4 relative rounding per projection) */
 int vx_set_gemm_terms(int terms);
-/* batches with at least this many rows run the projections on the tcgen05 kernel (default 17; 0 = always the mma.sync kernel) */
+/* batches with at least this many rows run the projections on the tcgen05 kernel (default 17, and never below 33 for Q4_K;
+ * 0 = always the mma.sync kernel) */
 int vx_set_tc_min_rows(int rows);
 
 /* ------------------------------------------------------------------ continuous-batching scheduler

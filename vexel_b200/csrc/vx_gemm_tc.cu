@@ -32,7 +32,12 @@ constexpr int TC_THREADS = TC_DEQ + 32 * (TC_ISSUERS + 1);
 constexpr int X_TILE = TC_MT * 128;           // bytes of one fp16 activation tile (64 rows x 128 B)
 constexpr int STAGE_BYTES = 2 * X_TILE;       // x_hi rows 0-63 followed by x_lo rows 64-127: one 128-row K-major operand
 constexpr int RAW_BYTES = TC_ROWS * 64;       // packed nibbles of one 128-weight group
-constexpr int SMEM_BYTES = TC_ST * STAGE_BYTES + TC_RAW * RAW_BYTES + 1024 /*alignment*/ + 512 /*barriers*/ + 256 /*row scales*/;
+constexpr int RAWH_BYTES = TC_ROWS * 32;      // Q6_K only: the top two bits of the same group
+constexpr int SMEM_BYTES = TC_ST * STAGE_BYTES + TC_RAW * (RAW_BYTES + RAWH_BYTES) + 1024 /*alignment*/ + 512 /*barriers*/ + 256 /*row scales*/;
+enum { TC_Q4_0 = 0, TC_Q4_K = 1, TC_Q6_K = 2 };
+// what the block formats need beyond the nibble tiles: scales (Q4_0: half per block; K-quants: 8 bytes per 128-weight group),
+// super-block scales (Q4_K: half2 {d, dmin}; Q6_K: half d), and the activations' per-32-block sums for the Q4_K minima
+struct TcAux { const void *sc; const void *aux; const float *xbsum; int bsum_ld; };
 // tensor memory columns: issuer j accumulates into [128j, 128j+128): cols 0-63 = A_hi*x_hi + A_lo*x_hi, cols 64-127 = A_hi*x_lo
 // for its K=16 steps; weight stage s: A_hi at TMEM_A + 64*s, A_lo 32 columns further (two fp16 per 32-bit column)
 constexpr int TMEM_A = TC_ISSUERS * 2 * TC_MT;
@@ -120,21 +125,39 @@ __device__ __forceinline__ __half2 nib2(uint32_t v) {
     return __hsub2(*reinterpret_cast<__half2 *>(&h), __floats2half2_rn(1032.f, 1032.f));
 }
 __device__ __forceinline__ uint32_t h2u(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+// unsigned variant -> half2 {q0, q1}
+__device__ __forceinline__ __half2 nibu2(uint32_t v) {
+    uint32_t h = (v & 0x000F000Fu) | 0x64006400u;
+    return __hsub2(*reinterpret_cast<__half2 *>(&h), __floats2half2_rn(1024.f, 1024.f));
+}
+// low nibbles in v (bits 0-3, 16-19), the two top bits already placed at bits 4-5 and 20-21 -> half2 {q0 - 32, q1 - 32}
+__device__ __forceinline__ __half2 q6h2(uint32_t v, uint32_t h6) {
+    uint32_t h = (v & 0x000F000Fu) | h6 | 0x64006400u;
+    return __hsub2(*reinterpret_cast<__half2 *>(&h), __floats2half2_rn(1056.f, 1056.f));
+}
+// a float32 scale as an fp16 pair (hi + lo carries 22 bits of it)
+__device__ __forceinline__ void split_scale(float d, __half2 *hi, __half2 *lo) {
+    const __half h = __float2half_rn(d);
+    *hi = __half2half2(h); *lo = __half2half2(__float2half_rn(d - __half2float(h)));
+}
 
 // grid: (ceil(N/128), split_k, ceil(M/64)); out layout [split][M][ld_out]; kb_per_split is even
+template <int FMT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_xh,
-                    const __grid_constant__ CUtensorMap map_xl, const __half *__restrict__ sc, const float *__restrict__ xscale,
-                    float *__restrict__ out, int M, int N, int k_groups, int kb_per_split, int ld_out, size_t part_stride,
-                    int *__restrict__ err_flag) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_xh,
+               const __grid_constant__ CUtensorMap map_xl, const TcAux aux, const float *__restrict__ xscale,
+               float *__restrict__ out, int M, int N, int k_groups, int kb_per_split, int ld_out, size_t part_stride,
+               int *__restrict__ err_flag) {
+    const __half *sc = reinterpret_cast<const __half *>(aux.sc);
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;            // operand tiles need 1024-byte alignment
     const uint32_t raw_base = base + TC_ST * STAGE_BYTES;
-    const uint32_t bar_base = raw_base + TC_RAW * RAW_BYTES;
+    const uint32_t rawh_base = raw_base + TC_RAW * RAW_BYTES;
+    const uint32_t bar_base = rawh_base + TC_RAW * RAWH_BYTES;
     unsigned char *gen_base = smem_raw + (base - smem_u32(smem_raw));
-    float *s_xscale = reinterpret_cast<float *>(gen_base + TC_ST * STAGE_BYTES + TC_RAW * RAW_BYTES + 512);
+    float *s_xscale = reinterpret_cast<float *>(gen_base + TC_ST * STAGE_BYTES + TC_RAW * (RAW_BYTES + RAWH_BYTES) + 512);
     auto xf_bar = [&](int s) { return bar_base + 8u * s; };                                 // activation tile landed
     auto af_bar = [&](int s) { return bar_base + 8u * (TC_ST + s); };                       // weight operand written
     auto e_bar = [&](int s) { return bar_base + 8u * (2 * TC_ST + s); };                    // stage consumed by every issuer's MMAs
@@ -174,49 +197,135 @@ gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int grp = (warp >> 2) & 1, b = warp >> 3;
         const int row = (warp & 3) * 32 + lane;
         const int grow = min(r0 + row, N - 1);
-        const __half *scp = sc + (size_t)grow * k_groups * 4 + (size_t)kb_begin * 2 + b;
         // nibble tile rows are 64 bytes with SWIZZLE_64B: 16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3);
-        // chunk c holds word c of the four blocks of the 128-weight group, this thread's block is 2 * grp + b of it
+        // chunk c holds word c of the four nibble words of the 128-weight group
         const int rsw = (row >> 1) & 3;
-        int raw_off[4];
-#pragma unroll
-        for (int c = 0; c < 4; c++) raw_off[c] = row * 64 + ((c ^ rsw) << 4) + 4 * (2 * grp + b);
         const uint32_t a_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + TMEM_A + 16 * b;
-        __half d0 = grp < n_kb ? scp[2 * grp] : __float2half(0.f);
-        for (int kb = grp; kb < n_kb; kb += 2) {
-            const int as = kb % TC_ST, g = kb >> 1, slot = g % TC_RAW;
-            const __half d1 = (kb + 2 < n_kb) ? scp[2 * (kb + 2)] : d0;        // scale of this group's next stage
-            if (!mbar_wait(rawf_bar(slot), (g / TC_RAW) & 1, abort_flag)) break;
-            const unsigned char *rp = gen_base + TC_ST * STAGE_BYTES + slot * RAW_BYTES;
-            uint32_t w[4];
+        if (FMT == TC_Q4_0) {
+            // this thread's GGUF block is 2 * grp + b of the group: word index = block index
+            const __half *scp = sc + (size_t)grow * k_groups * 4 + (size_t)kb_begin * 2 + b;
+            int raw_off[4];
 #pragma unroll
-            for (int c = 0; c < 4; c++) w[c] = *reinterpret_cast<const uint32_t *>(rp + raw_off[c]);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(rawe_bar(slot));
-            if (kb >= TC_ST && !mbar_wait(e_bar(as), ((kb / TC_ST) - 1) & 1, abort_flag)) break;
-            const __half2 dd = __half2half2(d0);
-            uint32_t hi[16], lo[16];
+            for (int c = 0; c < 4; c++) raw_off[c] = row * 64 + ((c ^ rsw) << 4) + 4 * (2 * grp + b);
+            __half d0 = grp < n_kb ? scp[2 * grp] : __float2half(0.f);
+            for (int kb = grp; kb < n_kb; kb += 2) {
+                const int as = kb % TC_ST, g = kb >> 1, slot = g % TC_RAW;
+                const __half d1 = (kb + 2 < n_kb) ? scp[2 * (kb + 2)] : d0;        // scale of this group's next stage
+                if (!mbar_wait(rawf_bar(slot), (g / TC_RAW) & 1, abort_flag)) break;
+                const unsigned char *rp = gen_base + TC_ST * STAGE_BYTES + slot * RAW_BYTES;
+                uint32_t w[4];
 #pragma unroll
-            for (int nib = 0; nib < 2; nib++)
+                for (int c = 0; c < 4; c++) w[c] = *reinterpret_cast<const uint32_t *>(rp + raw_off[c]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(rawe_bar(slot));
+                if (kb >= TC_ST && !mbar_wait(e_bar(as), ((kb / TC_ST) - 1) & 1, abort_flag)) break;
+                const __half2 dd = __half2half2(d0);
+                uint32_t hi[16], lo[16];
 #pragma unroll
-                for (int c = 0; c < 4; c++)
+                for (int nib = 0; nib < 2; nib++)
 #pragma unroll
-                    for (int e = 0; e < 2; e++) {
-                        // bytes e and e + 2 of word c: weights 16 nib + 4 c + {e, e + 2} of the block (the activation tiles
-                        // carry the same order of k within every four), exact product d * (q - 8) as an fp16 pair
-                        const __half2 q = nib2(w[c] >> (4 * nib + 8 * e));
-                        const __half2 ph = __hmul2(q, dd);
-                        const __half2 pl = __hfma2(q, dd, __hneg2(ph));
-                        hi[8 * nib + 2 * c + e] = h2u(ph); lo[8 * nib + 2 * c + e] = h2u(pl);
+                    for (int c = 0; c < 4; c++)
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            // bytes e and e + 2 of word c: weights 16 nib + 4 c + {e, e + 2} of the block (the activation tiles
+                            // carry the same order of k within every four), exact product d * (q - 8) as an fp16 pair
+                            const __half2 q = nib2(w[c] >> (4 * nib + 8 * e));
+                            const __half2 ph = __hmul2(q, dd);
+                            const __half2 pl = __hfma2(q, dd, __hneg2(ph));
+                            hi[8 * nib + 2 * c + e] = h2u(ph); lo[8 * nib + 2 * c + e] = h2u(pl);
+                        }
+                // k positions 32 b .. 32 b + 31 of the stage = columns 16 b .. 16 b + 15 (two fp16 per column)
+                tmem_st16(a_lane + 64 * as, hi);
+                tmem_st16(a_lane + 64 * as + 32, lo);
+                d0 = d1;
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(af_bar(as));
+            }
+        } else {
+            // K-quants.  The stage of parity grp is 64-weight half grp of the 128-weight group; this thread expands its 32
+            // weights 32 b .. 32 b + 31.  The float32 sub-block scale fl(d * sc) travels as an fp16 pair, so that
+            // A_hi + A_lo = (d1_hi + d1_lo) * q to 2^-22: A_hi = fp16(q * d1_hi), A_lo = its FMA residual + q * d1_lo.
+            //   Q4_K: sub-block u = 2 grp + b; words 2 grp and 2 grp + 1 of every chunk hold its positions 0-15 / 16-31 in the
+            //         nibble b.  w = d1 q - dm is carried as d1 (q - 8) + (8 d1 - dm): the centred first term keeps the
+            //         accumulator small (no cancellation against a large offset sum), the second is a constant per
+            //         sub-block and is applied in the epilogue to the activations' block sums.
+            //   Q6_K: word 2 grp + b of every chunk holds 16-weight sub-blocks 4 grp + 2 b (low nibbles) and + 1 (high nibbles);
+            //         the top two bits come from the second tile (byte u of the chunk's 8, two bits per position).
+            const uint2 *scq = reinterpret_cast<const uint2 *>(aux.sc) + (size_t)grow * k_groups + (kb_begin >> 1);
+            const int g_abs0 = kb_begin >> 1;
+            int raw_off[4], rawh_off[4];
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                raw_off[c] = row * 64 + ((c ^ rsw) << 4) + (FMT == TC_Q4_K ? 8 * grp : 4 * (2 * grp + b));
+                rawh_off[c] = row * 32 + c * 8 + 4 * grp + 2 * b;
+            }
+            auto sup = [&](int g) -> float2 {     // {d, dmin} (Q4_K) or {d, 0} (Q6_K) of the group's super-block
+                if (FMT == TC_Q4_K) return __half22float2(reinterpret_cast<const __half2 *>(aux.aux)[(size_t)grow * (k_groups / 2) + ((g_abs0 + g) >> 1)]);
+                return make_float2(__half2float(reinterpret_cast<const __half *>(aux.aux)[(size_t)grow * (k_groups / 2) + ((g_abs0 + g) >> 1)]), 0.f);
+            };
+            uint2 s8 = grp < n_kb ? scq[0] : make_uint2(0, 0);
+            float2 dsup = grp < n_kb ? sup(0) : make_float2(0.f, 0.f);
+            for (int kb = grp; kb < n_kb; kb += 2) {
+                const int as = kb % TC_ST, g = kb >> 1, slot = g % TC_RAW;
+                const uint2 s8n = (kb + 2 < n_kb) ? scq[g + 1] : s8;
+                const float2 dsn = (kb + 2 < n_kb) ? sup(g + 1) : dsup;
+                if (!mbar_wait(rawf_bar(slot), (g / TC_RAW) & 1, abort_flag)) break;
+                const unsigned char *rp = gen_base + TC_ST * STAGE_BYTES + slot * RAW_BYTES;
+                uint32_t w0[4], w1[4], hb[4];
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    if (FMT == TC_Q4_K) {
+                        const uint2 t = *reinterpret_cast<const uint2 *>(rp + raw_off[c]);
+                        w0[c] = t.x >> (4 * b); w1[c] = t.y >> (4 * b);           // positions 0-15 and 16-31, this sub-block's nibble
+                        hb[c] = 0;
+                    } else {
+                        const uint32_t t = *reinterpret_cast<const uint32_t *>(rp + raw_off[c]);
+                        w0[c] = t; w1[c] = t >> 4;                                 // sub-blocks 4 grp + 2 b and + 1
+                        hb[c] = *reinterpret_cast<const unsigned short *>(gen_base + TC_ST * STAGE_BYTES + TC_RAW * RAW_BYTES + slot * RAWH_BYTES + rawh_off[c]);
                     }
-            // k positions 32 b .. 32 b + 31 of the stage = columns 16 b .. 16 b + 15 (two fp16 per column)
-            tmem_st16(a_lane + 64 * as, hi);
-            tmem_st16(a_lane + 64 * as + 32, lo);
-            d0 = d1;
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(af_bar(as));
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(rawe_bar(slot));
+                if (kb >= TC_ST && !mbar_wait(e_bar(as), ((kb / TC_ST) - 1) & 1, abort_flag)) break;
+                __half2 dh[2], dl[2];
+                if (FMT == TC_Q4_K) {
+                    const int u = 2 * grp + b;
+                    split_scale(__fmul_rn(dsup.x, (float)((s8.x >> (8 * u)) & 0xFF)), &dh[0], &dl[0]);       // dequant.go:369-372
+                    dh[1] = dh[0]; dl[1] = dl[0];
+                } else {
+                    const uint32_t sw = grp ? s8.y : s8.x;                        // int8 scales of sub-blocks 4 grp .. 4 grp + 3
+                    split_scale(__fmul_rn(dsup.x, (float)(int)(signed char)((sw >> (16 * b)) & 0xFF)), &dh[0], &dl[0]);   // dequant.go:296-299
+                    split_scale(__fmul_rn(dsup.x, (float)(int)(signed char)((sw >> (16 * b + 8)) & 0xFF)), &dh[1], &dl[1]);
+                }
+                uint32_t hi[16], lo[16];
+#pragma unroll
+                for (int t = 0; t < 2; t++)
+#pragma unroll
+                    for (int c = 0; c < 4; c++)
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            const uint32_t v = (t ? w1[c] : w0[c]) >> (8 * e);
+                            __half2 q;
+                            if (FMT == TC_Q4_K) q = nib2(v);          // q - 8: the offset 8 * d1 joins the minimum in the epilogue
+                            else {
+                                const uint32_t h8 = (hb[c] >> (8 * t)) & 0xFF;
+                                q = q6h2(v, e ? (((h8 & 0x0C) << 2) | ((h8 & 0xC0) << 14)) : (((h8 & 0x03) << 4) | ((h8 & 0x30) << 16)));
+                            }
+                            const __half2 ph = __hmul2(q, dh[t]);
+                            __half2 pl = __hfma2(q, dh[t], __hneg2(ph));
+                            pl = __hfma2(q, dl[t], pl);
+                            hi[8 * t + 2 * c + e] = h2u(ph); lo[8 * t + 2 * c + e] = h2u(pl);
+                        }
+                tmem_st16(a_lane + 64 * as, hi);
+                tmem_st16(a_lane + 64 * as + 32, lo);
+                s8 = s8n; dsup = dsn;
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(af_bar(as));
+            }
         }
     } else if (warp == TC_DEQ / 32 + TC_ISSUERS) {
         // ------------------------------------------------------------------ TMA producer (one thread)
@@ -226,8 +335,9 @@ gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if ((kb & 1) == 0) {
                     const int g = kb >> 1, slot = g % TC_RAW;
                     if (g >= TC_RAW && !mbar_wait(rawe_bar(slot), ((g / TC_RAW) - 1) & 1, abort_flag)) break;
-                    mbar_arrive_expect_tx(rawf_bar(slot), RAW_BYTES);
+                    mbar_arrive_expect_tx(rawf_bar(slot), FMT == TC_Q6_K ? RAW_BYTES + RAWH_BYTES : RAW_BYTES);
                     tma_load_2d(raw_base + slot * RAW_BYTES, &map_w, (gkb >> 1) * 64, r0, rawf_bar(slot));
+                    if (FMT == TC_Q6_K) tma_load_2d(rawh_base + slot * RAWH_BYTES, &map_h, (gkb >> 1) * 32, r0, rawf_bar(slot));
                 }
                 if (kb >= TC_ST && !mbar_wait(e_bar(xs), ((kb / TC_ST) - 1) & 1, abort_flag)) break;
                 mbar_arrive_expect_tx(xf_bar(xs), 2 * X_TILE);
@@ -292,6 +402,28 @@ gemm_q4_0_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
                 for (int i = 0; i < 16; i++) sum[i] += __uint_as_float(v[i]);
             }
+            if (FMT == TC_Q4_K) {
+                // plus sum over this slice's sub-blocks of (8 fl(d * sc_u) - fl(dmin * m_u)) * (sum of the activations of the sub-block)
+                // (dequant.go:369-392: w = d1 * q - dm1)
+                const int gn = min(n, N - 1);
+                const uint2 *scq = reinterpret_cast<const uint2 *>(aux.sc) + (size_t)gn * k_groups + (kb_begin >> 1);
+                const __half2 *supq = reinterpret_cast<const __half2 *>(aux.aux) + (size_t)gn * (k_groups / 2);
+                for (int gi = 0; 2 * gi < n_kb; gi++) {
+                    const int gabs = (kb_begin >> 1) + gi;
+                    const uint2 sm8 = scq[gi];
+                    const float2 dd = __half22float2(supq[gabs >> 1]);
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const float d1 = __fmul_rn(dd.x, (float)((sm8.x >> (8 * u)) & 0xFF)), dm = __fmul_rn(dd.y, (float)((sm8.y >> (8 * u)) & 0xFF));
+                        const float ce = fmaf(8.f, d1, -dm);
+#pragma unroll
+                        for (int i = 0; i < 16; i++) {
+                            const int m = min(m0 + c0 + i, M - 1);
+                            sum[i] = fmaf(ce, aux.xbsum[(size_t)m * aux.bsum_ld + gabs * 4 + u], sum[i]);
+                        }
+                    }
+                }
+            }
             if (n < N) {
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
@@ -345,11 +477,13 @@ int make_map(vx_ctx *c, CUtensorMap *map, CUtensorMapDataType dt, int elem, cons
 int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out, float *parts,
                 size_t parts_cap_floats) {
     int *err_flag = c->d_int_result + 8;
-    if (w.type != VX_T_Q4_0) return vx_fail(c, VX_E_UNSUPPORTED, "tensor-core projection: weight type %d", w.type);
+    if (w.type != VX_T_Q4_0 && w.type != VX_T_Q4_K && w.type != VX_T_Q6_K) return vx_fail(c, VX_E_UNSUPPORTED, "tensor-core projection: weight type %d", w.type);
     if (x.k_pad != w.k_pad) return vx_fail(c, VX_E_BAD_ARG, "projection: activation row stride %d != weight k_pad %d", x.k_pad, w.k_pad);
     static bool attr_set = false;
     if (!attr_set) {
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_q4_0_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         attr_set = true;
     }
     const int k_groups = w.k_pad / 128;
@@ -373,7 +507,7 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
     int ld = split > 1 ? w.n : ld_out;
     *n_parts_out = split;
     // tensor maps: packed nibbles as bytes [n][k_groups*64], activations as fp16 [rows][k_pad]
-    CUtensorMap map_w, map_xh, map_xl;
+    CUtensorMap map_w, map_h, map_xh, map_xl;
     const uint64_t x_rows = (uint64_t)((m + 63) / 64) * 64;     // the split buffers are allocated in multiples of 64 rows
     VX_TRY(make_map(c, &map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w.qs, (uint64_t)k_groups * 64, (uint64_t)w.n, (uint64_t)k_groups * 64, 64,
                     TC_ROWS, CU_TENSOR_MAP_SWIZZLE_64B));
@@ -381,9 +515,20 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
                     CU_TENSOR_MAP_SWIZZLE_128B));
     VX_TRY(make_map(c, &map_xl, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x.lo, (uint64_t)x.k_pad, x_rows, (uint64_t)x.k_pad * 2, TC_BK, TC_MT,
                     CU_TENSOR_MAP_SWIZZLE_128B));
+    // Q6_K: the top two bits of every weight as bytes [n][k_groups*32]; the other formats pass the nibble map again (unused)
+    if (w.type == VX_T_Q6_K)
+        VX_TRY(make_map(c, &map_h, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w.hi, (uint64_t)k_groups * 32, (uint64_t)w.n, (uint64_t)k_groups * 32, 32,
+                        TC_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE));
+    else map_h = map_w;
     dim3 grid(ceil_div(w.n, TC_ROWS), split, ceil_div(m, TC_MT));
-    gemm_q4_0_tc_kernel<<<grid, TC_THREADS, SMEM_BYTES, c->stream>>>(map_w, map_xh, map_xl, (const __half *)w.sc, x.scale, dst, m, w.n, k_groups,
-                                                                    per * 2, ld, (size_t)m * w.n, err_flag);
+    const TcAux aux{w.sc, w.aux, x.bsum, x.k_pad / 32};
+    const size_t pstride = (size_t)m * w.n;
+    if (w.type == VX_T_Q4_0)
+        gemm_tc_kernel<TC_Q4_0><<<grid, TC_THREADS, SMEM_BYTES, c->stream>>>(map_w, map_h, map_xh, map_xl, aux, x.scale, dst, m, w.n, k_groups, per * 2, ld, pstride, err_flag);
+    else if (w.type == VX_T_Q4_K)
+        gemm_tc_kernel<TC_Q4_K><<<grid, TC_THREADS, SMEM_BYTES, c->stream>>>(map_w, map_h, map_xh, map_xl, aux, x.scale, dst, m, w.n, k_groups, per * 2, ld, pstride, err_flag);
+    else
+        gemm_tc_kernel<TC_Q6_K><<<grid, TC_THREADS, SMEM_BYTES, c->stream>>>(map_w, map_h, map_xh, map_xl, aux, x.scale, dst, m, w.n, k_groups, per * 2, ld, pstride, err_flag);
     VX_LAUNCH_CHECK(c);
     return VX_OK;
 }
