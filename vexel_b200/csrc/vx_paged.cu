@@ -253,8 +253,8 @@ __device__ __forceinline__ uint32_t pack_hi_lo(float x, float y, uint32_t *lo) {
     return *reinterpret_cast<const uint32_t *>(&h);
 }
 
-template <int D, int G>
-__global__ void __launch_bounds__(ATT_WARPS * 32)
+template <int D, int G, int NW>
+__global__ void __launch_bounds__(NW * 32)
 paged_flash_mma_kernel(VxAttnArgs a) {
     constexpr int KS = D / 16;                    // K=16 steps of the score product = 16-row tiles of the output product
     constexpr int ROW_B = D * 2;                  // bytes of one token's head slice
@@ -316,8 +316,8 @@ paged_flash_mma_kernel(VxAttnArgs a) {
     const int last_page = first_page + n_pages;
     int page = first_page + warp, stage = 0;
     if (page < last_page) issue(page, 0);
-    for (; page < last_page; page += ATT_WARPS, stage ^= 1) {
-        if (page + ATT_WARPS < last_page) { issue(page + ATT_WARPS, stage ^ 1); asm volatile("cp.async.wait_group 1;\n" ::); }
+    for (; page < last_page; page += NW, stage ^= 1) {
+        if (page + NW < last_page) { issue(page + NW, stage ^ 1); asm volatile("cp.async.wait_group 1;\n" ::); }
         else asm volatile("cp.async.wait_group 0;\n" ::);
         __syncwarp();
         const uint32_t kb_s = stage0 + stage * STAGE_B, vb_s = kb_s + TILE_B;
@@ -402,7 +402,7 @@ paged_flash_mma_kernel(VxAttnArgs a) {
     }
     __syncthreads();
     float *sm_acc = reinterpret_cast<float *>(att_smem);                      // [warp][G][D]
-    float *sm_m = sm_acc + ATT_WARPS * G * D, *sm_l = sm_m + ATT_WARPS * G;    // [warp][G]
+    float *sm_m = sm_acc + NW * G * D, *sm_l = sm_m + NW * G;    // [warp][G]
 #pragma unroll
     for (int hh = 0; hh < 2; hh++) {
         const int h = 2 * c + hh;
@@ -417,14 +417,14 @@ paged_flash_mma_kernel(VxAttnArgs a) {
     }
     __syncthreads();
     const bool single = (a.row_work_start[row + 1] - a.row_work_start[row]) == 1;
-    for (int idx = threadIdx.x; idx < G * D; idx += ATT_WARPS * 32) {
+    for (int idx = threadIdx.x; idx < G * D; idx += NW * 32) {
         const int gi = idx / D, d = idx % D;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; w++) M = fmaxf(M, sm_m[w * G + gi]);
+        for (int w = 0; w < NW; w++) M = fmaxf(M, sm_m[w * G + gi]);
         float L = 0.f, O = 0.f;
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; w++) {
+        for (int w = 0; w < NW; w++) {
             const float f = sm_m[w * G + gi] == -INFINITY ? 0.f : __expf(sm_m[w * G + gi] - M);
             L = fmaf(sm_l[w * G + gi], f, L); O = fmaf(sm_acc[(w * G + gi) * D + d], f, O);
         }
@@ -461,14 +461,16 @@ static int g_attn_mma = 1;     // grouped-query shapes use the tensor-core kerne
 
 template <int D, int G>
 static int flash_launch_mma(vx_ctx *c, const VxAttnArgs &a, dim3 grid) {
-    constexpr int SMEM = ATT_WARPS * 2 * 2 * ATT_BS * D * 2;      // per warp: two stages of a K and a V page tile
-    static_assert(SMEM >= (int)((ATT_WARPS * G * D + 2 * ATT_WARPS * G) * sizeof(float)), "merge buffers fit in the staging area");
+    // head_dim 256 doubles the staging buffers and the register file per warp: two warps per CTA keep three CTAs on an SM
+    constexpr int NW = D == 256 ? 2 : ATT_WARPS;
+    constexpr int SMEM = NW * 2 * 2 * ATT_BS * D * 2;      // per warp: two stages of a K and a V page tile
+    static_assert(SMEM >= (int)((NW * G * D + 2 * NW * G) * sizeof(float)), "merge buffers fit in the staging area");
     static bool attr_done = false;
     if (!attr_done) {
-        if (cudaFuncSetAttribute(paged_flash_mma_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
+        if (cudaFuncSetAttribute(paged_flash_mma_kernel<D, G, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
         attr_done = true;
     }
-    paged_flash_mma_kernel<D, G><<<grid, ATT_WARPS * 32, SMEM, c->stream>>>(a);
+    paged_flash_mma_kernel<D, G, NW><<<grid, NW * 32, SMEM, c->stream>>>(a);
     return 0;
 }
 
