@@ -181,3 +181,4 @@ struct VxAttnArgs {
     float scale, softcap;
 };
 int vxp_attention(vx_ctx *c, const VxAttnArgs &a);
+int vxp_attention_split(vx_ctx *c, const VxAttnArgs &a, const VxSplit *split, int n_max_chunks, bool *fused);

@@ -17,6 +17,10 @@
 // to the end, frees its tensor memory and returns, so a protocol bug cannot hang the GPU.
 #include <cuda.h>
 
+#include <map>
+#include <mutex>
+#include <tuple>
+
 #include "vx_common.cuh"
 
 namespace {
@@ -506,9 +510,29 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
     float *dst = split > 1 ? parts : out;
     int ld = split > 1 ? w.n : ld_out;
     *n_parts_out = split;
-    // tensor maps: packed nibbles as bytes [n][k_groups*64], activations as fp16 [rows][k_pad]
-    CUtensorMap map_w, map_h, map_xh, map_xl;
+    // tensor maps: packed nibbles as bytes [n][k_groups*64], activations as fp16 [rows][k_pad].  A decode step launches the
+    // same (weight, activation buffer, row count) combinations every time, so encoded maps are kept per combination instead
+    // of paying four driver calls per launch.
     const uint64_t x_rows = (uint64_t)((m + 63) / 64) * 64;     // the split buffers are allocated in multiples of 64 rows
+    struct MapKey {
+        const void *qs, *hi, *xh, *xl; uint64_t rows; int n, kg, kp;
+        bool operator<(const MapKey &o) const {
+            return std::tie(qs, hi, xh, xl, rows, n, kg, kp) < std::tie(o.qs, o.hi, o.xh, o.xl, o.rows, o.n, o.kg, o.kp);
+        }
+    };
+    struct MapSet { CUtensorMap w, h, xh, xl; };
+    static std::map<MapKey, MapSet> cache;
+    static std::mutex cache_mu;
+    const MapKey key{w.qs, w.type == VX_T_Q6_K ? w.hi : nullptr, x.hi, x.lo, x_rows, w.n, k_groups, x.k_pad};
+    MapSet ms;
+    bool have = false;
+    {
+        std::lock_guard<std::mutex> lk(cache_mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { ms = it->second; have = true; }
+    }
+    CUtensorMap &map_w = ms.w, &map_h = ms.h, &map_xh = ms.xh, &map_xl = ms.xl;
+    if (!have) {
     VX_TRY(make_map(c, &map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w.qs, (uint64_t)k_groups * 64, (uint64_t)w.n, (uint64_t)k_groups * 64, 64,
                     TC_ROWS, CU_TENSOR_MAP_SWIZZLE_64B));
     VX_TRY(make_map(c, &map_xh, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x.hi, (uint64_t)x.k_pad, x_rows, (uint64_t)x.k_pad * 2, TC_BK, TC_MT,
@@ -520,6 +544,10 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
         VX_TRY(make_map(c, &map_h, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w.hi, (uint64_t)k_groups * 32, (uint64_t)w.n, (uint64_t)k_groups * 32, 32,
                         TC_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE));
     else map_h = map_w;
+        std::lock_guard<std::mutex> lk(cache_mu);
+        if (cache.size() > 4096) cache.clear();     // buffers of destroyed models: start over rather than grow without bound
+        cache[key] = ms;
+    }
     dim3 grid(ceil_div(w.n, TC_ROWS), split, ceil_div(m, TC_MT));
     const TcAux aux{w.sc, w.aux, x.bsum, x.k_pad / 32};
     const size_t pstride = (size_t)m * w.n;

@@ -570,7 +570,7 @@ bool layer_slides(const vx_model_config &c, int layer) {   // runtime/block.go:4
 // mode 0: paged attention for every row (decode / verify / chunked prefill)
 // mode 1: causal attention over the fresh float32 K/V of this call (prefill from position 0, block.go:891-895)
 // logit_rows: how many trailing rows get logits (all rows, or 1 for prefill)
-int forward(vx_model *m, int rows, int mode, int n_work_host[2], int logit_rows) {
+int forward(vx_model *m, int rows, int mode, int n_work_host[2], const int chunk_pages[2], int logit_rows) {
     vx_ctx *c = m->c; const vx_model_config &cf = m->cfg;
     const int H = cf.hidden, Hq = cf.n_heads, Hkv = cf.n_kv_heads, D = cf.head_dim, F = cf.ffn;
     const int qd = Hq * D, kvd = Hkv * D, nqkv = qd + 2 * kvd;
@@ -606,6 +606,7 @@ int forward(vx_model *m, int rows, int mode, int n_work_host[2], int logit_rows)
             VX_LAUNCH_CHECK(c);
         }
         time_begin(m, 0);
+        bool split_done = false;
         if (mode == 1) {
             VX_TRY(vxe_sdpa_strided(c, m->qkv, nqkv, m->qkv + qd, m->qkv + qd + kvd, m->attn, qd, rows, 0, 1, Hq, Hkv, D, nqkv, D, scale,
                                     cf.attn_softcap));
@@ -619,10 +620,12 @@ int forward(vx_model *m, int rows, int mode, int n_work_host[2], int logit_rows)
             a.partials = m->d_partials; a.out = m->attn; a.out_row_stride = qd;
             a.rows = rows; a.n_q_heads = Hq; a.n_kv_heads = Hkv; a.head_dim = D; a.block_size = BS;
             a.scale = scale; a.softcap = cf.attn_softcap;
-            VX_TRY(vxp_attention(c, a));                                                // block.go:872 / 881-890
+            // at most this many split-K chunks per row: the table width bounds a row's pages
+            const int n_max = ceil_div(cf.max_blocks_per_seq, max(chunk_pages[wl], 1)) + 1;
+            VX_TRY(vxp_attention_split(c, a, &m->sp_q, n_max, &split_done));                // block.go:872 / 881-890
         }
         time_end(m, 0);
-        VX_TRY(vxq_split_rows(c, m->attn, rows, qd, qd, m->sp_q));
+        if (!split_done) VX_TRY(vxq_split_rows(c, m->attn, rows, qd, qd, m->sp_q));
         int np_o = 1;
         VX_TRY(gemm(m, L.wo, m->sp_q, rows, m->parts, H, &np_o));                       // block.go:983
         // x += Wo output (post-attn norm first for Gemma 2); normOut = RMSNorm(x, ffn_norm) (block.go:985-997)
@@ -746,7 +749,7 @@ int enqueue_step(vx_model *m, const StepPlan &p, int mode, int logit_rows) {
     VX_LAUNCH_CHECK(c);
     if (m->capture_on) m->capture_rows = p.rows;
     int n_work[2] = {p.n_work[0], p.n_work[1]};
-    VX_TRY(forward(m, p.rows, mode, n_work, logit_rows));
+    VX_TRY(forward(m, p.rows, mode, n_work, p.chunk, logit_rows));
     m->steps++;
     return VX_OK;
 }

@@ -459,6 +459,77 @@ __global__ void paged_merge_kernel(VxAttnArgs a) {
 
 static int g_attn_mma = 1;     // grouped-query shapes use the tensor-core kernel (0 = the CUDA-core kernel, for comparison)
 
+// Merge of the split-K chunks fused with the fp16 hi/lo split that feeds the output projection: one CTA per query row.
+// Phase 1, one thread per head: the chunk maxima and weights e^{m_c - M} / L into shared memory.  Phase 2, four consecutive
+// head dimensions per thread: the weighted sum of the chunk outputs with independent loads (rows written directly by a
+// single-chunk CTA are read back instead), then the row maximum, the power-of-two scale and the split store.  Replaces
+// paged_merge_kernel + split_rows_kernel; nothing but the projection reads the attention output on that path.
+template <int NC>
+__global__ void __launch_bounds__(VX_ROW_THREADS) paged_merge_split_kernel(VxAttnArgs a, VxSplit s, int cols, int n_max) {
+    extern __shared__ float fw[];                  // [n_q_heads][n_max] normalised chunk weights
+    __shared__ float red[32];
+    const int row = blockIdx.x, D = a.head_dim, Hq = a.n_q_heads;
+    const int w0 = a.row_work_start[row], n = a.row_work_start[row + 1] - w0;
+    if (n > 1) {
+        for (int h = threadIdx.x; h < Hq; h += VX_ROW_THREADS) {
+            const float *p0 = a.partials + ((size_t)w0 * Hq + h) * (D + 2) + D;
+            const size_t cs = (size_t)Hq * (D + 2);
+            float M = -INFINITY;
+            for (int c = 0; c < n; c++) M = fmaxf(M, p0[c * cs]);
+            float L = 0.f;
+            for (int c = 0; c < n; c++) {
+                const float mc = p0[c * cs];
+                const float f = mc == -INFINITY ? 0.f : __expf(mc - M);
+                fw[h * n_max + c] = f;
+                L = fmaf(p0[c * cs + 1], f, L);
+            }
+            const float inv = L > 0.f ? 1.0f / L : 0.f;
+            for (int c = 0; c < n; c++) fw[h * n_max + c] *= inv;
+        }
+        __syncthreads();
+    }
+    float4 v[NC];
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < NC; j++) {
+        const int k0 = (j * VX_ROW_THREADS + threadIdx.x) * 4;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k0 < cols) {
+            if (n > 1) {
+                const int h = k0 / D, d = k0 % D;
+                const float *pp = a.partials + ((size_t)w0 * Hq + h) * (D + 2) + d;
+                const size_t cs = (size_t)Hq * (D + 2);
+                const float *f = fw + h * n_max;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+                for (int c = 0; c < n; c++) {
+                    const float2 x0 = *reinterpret_cast<const float2 *>(pp + c * cs), x1 = *reinterpret_cast<const float2 *>(pp + c * cs + 2);
+                    const float fc = f[c];
+                    acc.x = fmaf(x0.x, fc, acc.x); acc.y = fmaf(x0.y, fc, acc.y); acc.z = fmaf(x1.x, fc, acc.z); acc.w = fmaf(x1.y, fc, acc.w);
+                }
+                v[j] = acc;
+            } else {
+                v[j] = *reinterpret_cast<const float4 *>(a.out + (size_t)row * a.out_row_stride + k0);
+            }
+        }
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
+    }
+    amax = block_max(amax, red);
+    float sc, inv;
+    vx_row_scale(amax, sc, inv);
+    if (threadIdx.x == 0) s.scale[row] = sc;
+    __half *hi = s.hi + (size_t)row * s.k_pad, *lo = s.lo + (size_t)row * s.k_pad;
+    float *bs = s.bsum + (size_t)row * (s.k_pad / 32);
+#pragma unroll
+    for (int j = 0; j < NC; j++) {
+        const int k0 = (j * VX_ROW_THREADS + threadIdx.x) * 4;
+        if (k0 < s.k_pad) {
+            const float t[4] = {v[j].x * inv, v[j].y * inv, v[j].z * inv, v[j].w * inv};
+            vx_split_store4(t, hi, lo, bs, k0);
+        }
+    }
+}
+
 template <int D, int G>
 static int flash_launch_mma(vx_ctx *c, const VxAttnArgs &a, dim3 grid) {
     // head_dim 256 doubles the staging buffers and the register file per warp: two warps per CTA keep three CTAs on an SM
@@ -495,7 +566,13 @@ static int flash_launch_g(vx_ctx *c, const VxAttnArgs &a, int G) {
     return 0;
 }
 
-int vxp_attention(vx_ctx *c, const VxAttnArgs &a) {
+int vxp_attention(vx_ctx *c, const VxAttnArgs &a) { return vxp_attention_split(c, a, nullptr, 0, nullptr); }
+
+// The same, optionally followed by the fp16 split of the attention output (split != nullptr): when the split-K merge and the
+// split can share one kernel, *fused is set and `split` holds the rows; otherwise the caller runs the split itself.
+// n_max_chunks bounds the chunks of one row.
+int vxp_attention_split(vx_ctx *c, const VxAttnArgs &a, const VxSplit *split, int n_max_chunks, bool *fused) {
+    if (fused) *fused = false;
     if (a.rows <= 0) return VX_OK;
     if (a.n_q_heads <= 0 || a.n_kv_heads <= 0 || a.n_q_heads % a.n_kv_heads != 0)
         return vx_fail(c, VX_E_BAD_ARG, "paged attention: %d q heads over %d kv heads", a.n_q_heads, a.n_kv_heads);
@@ -507,6 +584,19 @@ int vxp_attention(vx_ctx *c, const VxAttnArgs &a) {
         int rc = D == 64 ? flash_launch_g<64>(c, a, G) : D == 128 ? flash_launch_g<128>(c, a, G) : flash_launch_g<256>(c, a, G);
         if (rc == 0) {
             VX_LAUNCH_CHECK(c);
+            const int cols = a.n_q_heads * D;
+            const size_t fw_bytes = (size_t)a.n_q_heads * max(n_max_chunks, 1) * sizeof(float);
+            if (split && fused && n_max_chunks > 0 && fw_bytes <= 40 * 1024 && split->k_pad <= 8 * VX_ROW_THREADS * 4 && a.out_row_stride % 4 == 0) {
+                const int nc = ceil_div(split->k_pad, VX_ROW_THREADS * 4);
+                switch (nc) {
+#define VX_MS_CASE(N) case N: paged_merge_split_kernel<N><<<a.rows, VX_ROW_THREADS, fw_bytes, c->stream>>>(a, *split, cols, n_max_chunks); break;
+                    VX_MS_CASE(1) VX_MS_CASE(2) VX_MS_CASE(3) VX_MS_CASE(4) VX_MS_CASE(5) VX_MS_CASE(6) VX_MS_CASE(7) VX_MS_CASE(8)
+#undef VX_MS_CASE
+                }
+                VX_LAUNCH_CHECK(c);
+                *fused = true;
+                return VX_OK;
+            }
             dim3 mg(a.n_q_heads, a.rows);
             paged_merge_kernel<<<mg, min(D, 256), 0, c->stream>>>(a);
             VX_LAUNCH_CHECK(c);
