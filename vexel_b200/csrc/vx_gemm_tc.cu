@@ -176,7 +176,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     if (tid == 0) {
         s_abort = 0;
-        for (int s = 0; s < TC_ST; s++) { mbar_init(xf_bar(s), 1); mbar_init(af_bar(s), TC_DEQ / 64); mbar_init(e_bar(s), TC_ISSUERS); }   // one arrival per warp:
+        // xf_bar(s): "stage s ready" = the activation tile has landed (one arrival carrying its byte count) and the eight warps
+        // of the dequantiser group have written the weight operand: one probe per stage for the issuing threads
+        for (int s = 0; s < TC_ST; s++) { mbar_init(xf_bar(s), 1 + TC_DEQ / 64); mbar_init(af_bar(s), 1); mbar_init(e_bar(s), TC_ISSUERS); }   // one arrival per warp:
         for (int s = 0; s < TC_RAW; s++) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), TC_DEQ / 32); }   // 512 arrivals on one word serialise
         mbar_init(accum_bar, TC_ISSUERS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -245,7 +247,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(af_bar(as));
+                if (lane == 0) mbar_arrive(xf_bar(as));
             }
         } else {
             // K-quants.  The stage of parity grp is 64-weight half grp of the 128-weight group; this thread expands its 32
@@ -328,7 +330,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(af_bar(as));
+                if (lane == 0) mbar_arrive(xf_bar(as));
             }
         }
     } else if (warp == TC_DEQ / 32 + TC_ISSUERS) {
@@ -371,7 +373,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
             for (int s = 0; s < TC_ST; s++) {
                 if (kb0 + s >= n_kb) break;
-                ok = mbar_wait(xf_bar(s), par, abort_flag) && mbar_wait(af_bar(s), par, abort_flag);
+                ok = mbar_wait(xf_bar(s), par, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a_hi = tmem + TMEM_A + 64 * s + 8 * j * KS, a_lo = a_hi + 32;
