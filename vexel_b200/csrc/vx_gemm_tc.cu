@@ -1,18 +1,27 @@
-// Q4_0 projection on the 5th-generation tensor cores (tcgen05 + TMEM) for batches of 17 or more rows.
+// Quantised projections (GGUF Q4_0, Q4_K, Q6_K) on the 5th-generation tensor cores (tcgen05 + TMEM) for batches above the
+// measured crossover (17 rows; 33 for Q4_K).
 //
 // Shape ("swap-AB"): D[128 weight rows x batch] += A[128 x 64k] * B[batch x 64k]^T per pipeline stage, accumulator in tensor
 // memory, one CTA per (128-row weight tile, split-K slice, 64-row batch tile).
 //   warp 18    TMA producer: per stage the activation tiles x_hi and x_lo (64 rows x 128 B each, SWIZZLE_128B, stacked into
 //              one 128-row operand) and, every second stage, the packed nibbles of a 128-weight group (128 rows x 64 B,
-//              SWIZZLE_64B).
-//   warps 0-15 dequantisers: read their row's nibbles from shared memory, expand to fp16 and store the A operand straight
-//              into TENSOR MEMORY (tcgen05.st; lane = weight row, two fp16 per 32-bit column) as two terms with
-//              w = d*(q-8) = A_hi + A_lo exactly (A_hi = fp16 product, A_lo = fp16 FMA residual).  With A in shared
-//              memory every MMA re-read 4 KB of it and the kernel was bound by shared-memory traffic.
+//              SWIZZLE_64B; Q6_K also the 32-byte rows of top bits).  Its program order keeps the nibble ring at most ~2.5
+//              tiles ahead of the MMAs.
+//   warps 0-15 dequantisers, two groups of eight warps on alternate stages: a thread reads the 32 weights of one block /
+//              sub-block of its row from shared memory, expands them to an fp16 pair and stores the A operand straight
+//              into TENSOR MEMORY (one 32-column tcgen05.st; lane = weight row, two fp16 per 32-bit column):
+//              Q4_0  w = d (q - 8) = A_hi + A_lo exactly (fp16 product + FMA residual);
+//              Q4_K  d1 (q - 8) with d1 = fl(d sc) carried as an fp16 pair, the constant 8 d1 - fl(dmin m) per sub-block is
+//                    applied in the epilogue to the activations' 32-block sums;
+//              Q6_K  d1 (q - 32), one d1 per 16 weights.
+//              With A in shared memory every MMA re-read 4 KB of it and the kernel was bound by shared-memory traffic.
 //   warps 16-17 one elected thread each issues, for its half of a stage's K=16 steps, A_hi x [x_hi; x_lo] (N=128) and
-//              A_lo x x_hi (N=64) into its own accumulator; the dropped A_lo*x_lo term is 2^-22 relative.  tcgen05.commit
-//              hands the stage back.
-//   warps 0-15 epilogue: tcgen05.ld of the accumulator halves, add, scale by the row's power of two, store.
+//              A_lo x x_hi (N=64) into its own accumulator; the dropped A_lo*x_lo term is 2^-22 relative.  One mbarrier per
+//              stage says "ready" (activation bytes landed + eight dequantiser warps arrived); tcgen05.commit hands it back.
+//   warps 0-15 epilogue: tcgen05.ld of the four accumulator parts, add in a fixed order, scale by the row's power of two, store.
+// Measured dead ends, so that they are not tried again: four issuing threads taking turns per accumulator (slower: the cost
+// sits in the number of tcgen05 instructions the SM dispatches per stage, not in one thread's latency); a separate
+// producer thread for the nibbles running a full ring ahead (wrong sums on multi-tile batches).
 // Every TMA load targets this CTA only.  Every mbarrier wait is bounded: on timeout the kernel raises an error word, skips
 // to the end, frees its tensor memory and returns, so a protocol bug cannot hang the GPU.
 #include <cuda.h>
@@ -43,7 +52,8 @@ enum { TC_Q4_0 = 0, TC_Q4_K = 1, TC_Q6_K = 2 };
 // super-block scales (Q4_K: half2 {d, dmin}; Q6_K: half d), and the activations' per-32-block sums for the Q4_K minima
 struct TcAux { const void *sc; const void *aux; const float *xbsum; int bsum_ld; };
 // tensor memory columns: issuer j accumulates into [128j, 128j+128): cols 0-63 = A_hi*x_hi + A_lo*x_hi, cols 64-127 = A_hi*x_lo
-// for its K=16 steps; weight stage s: A_hi at TMEM_A + 64*s, A_lo 32 columns further (two fp16 per 32-bit column)
+// for its K=16 steps; weight stage s at TMEM_A + 64*s: [hi k0 k1 | lo k0 k1 | hi k2 k3 | lo k2 k3], 8 columns (two fp16 each)
+// per K=16 step
 constexpr int TMEM_A = TC_ISSUERS * 2 * TC_MT;
 constexpr int TMEM_COLS = 512;                // 2 * 128 + 4 * 64
 static_assert(TMEM_A + 64 * TC_ST <= TMEM_COLS, "tensor memory budget");
@@ -113,6 +123,14 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
                  ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
                    "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&a)[16], const uint32_t (&b)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 ::"r"(taddr), "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]), "r"(a[8]), "r"(a[9]),
+                   "r"(a[10]), "r"(a[11]), "r"(a[12]), "r"(a[13]), "r"(a[14]), "r"(a[15]), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(b[4]),
+                   "r"(b[5]), "r"(b[6]), "r"(b[7]), "r"(b[8]), "r"(b[9]), "r"(b[10]), "r"(b[11]), "r"(b[12]), "r"(b[13]), "r"(b[14]), "r"(b[15])
+                 : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -206,7 +224,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // nibble tile rows are 64 bytes with SWIZZLE_64B: 16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3);
         // chunk c holds word c of the four nibble words of the 128-weight group
         const int rsw = (row >> 1) & 3;
-        const uint32_t a_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + TMEM_A + 16 * b;
+        const uint32_t a_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + TMEM_A + 32 * b;
         if (FMT == TC_Q4_0) {
             // this thread's GGUF block is 2 * grp + b of the group: word index = block index
             const __half *scp = sc + (size_t)grow * k_groups * 4 + (size_t)kb_begin * 2 + b;
@@ -240,9 +258,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             const __half2 pl = __hfma2(q, dd, __hneg2(ph));
                             hi[8 * nib + 2 * c + e] = h2u(ph); lo[8 * nib + 2 * c + e] = h2u(pl);
                         }
-                // k positions 32 b .. 32 b + 31 of the stage = columns 16 b .. 16 b + 15 (two fp16 per column)
-                tmem_st16(a_lane + 64 * as, hi);
-                tmem_st16(a_lane + 64 * as + 32, lo);
+                tmem_st32(a_lane + 64 * as, hi, lo);       // columns 32 b .. +15 the hi parts of K=16 steps 2b, 2b+1, .. +31 their lo parts
                 d0 = d1;
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -324,8 +340,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             pl = __hfma2(q, dl[t], pl);
                             hi[8 * t + 2 * c + e] = h2u(ph); lo[8 * t + 2 * c + e] = h2u(pl);
                         }
-                tmem_st16(a_lane + 64 * as, hi);
-                tmem_st16(a_lane + 64 * as + 32, lo);
+                tmem_st32(a_lane + 64 * as, hi, lo);       // columns 32 b .. +15 the hi parts of K=16 steps 2b, 2b+1, .. +31 their lo parts
                 s8 = s8n; dsup = dsn;
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -376,7 +391,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 ok = mbar_wait(xf_bar(s), par, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_hi = tmem + TMEM_A + 64 * s + 8 * j * KS, a_lo = a_hi + 32;
+                // stage layout in tensor memory: [hi k0 k1 | lo k0 k1 | hi k2 k3 | lo k2 k3], 8 columns per K=16 step; issuer j owns steps 2j, 2j+1
+                const uint32_t a_hi = tmem + TMEM_A + 64 * s + 32 * j, a_lo = a_hi + 16;
 #pragma unroll
                 for (int k = 0; k < KS; k++) {
                     umma_f16_ts(acc, a_hi + 8 * k, xdesc[s][k], UMMA_IDESC_N128, first);
