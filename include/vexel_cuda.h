@@ -264,6 +264,10 @@ int vx_model_weight_bytes(vx_model *m, uint64_t *bytes);
 /* activation terms fed to the tensor cores by the projections: 2 = fp16 hi+lo split (float32-faithful,
  * default), 1 = single fp16 (half the MMA work, ~2e-4 relative rounding per projection) */
 int vx_set_gemm_terms(int terms);
+/* failure-path self-test: a kernel waits, with a limit of limit_us microseconds, on a barrier that is never signalled; it
+ * must return (reached_end = 1) and the next vx_sync must report VX_E_TIMEOUT while the context stays usable.  This is
+ * how every device-side wait of the library behaves when its peer never shows up; no counterpart in the reference. */
+int vx_selftest_bounded_wait(vx_ctx *ctx, int limit_us, int *reached_end);
 /* batches with at least this many rows run the projections on the tcgen05 kernel (default 17, and never below 33 for Q4_K;
  * 0 = always the mma.sync kernel) */
 int vx_set_tc_min_rows(int rows);

@@ -5,6 +5,7 @@ paged == contiguous within 1e-3 (backend/metal/paged_sdpa_test.go:23-37, 186-322
 (backend/metal/paged_batched_test.go), quantised matvec against a CPU reference (backend/metal/q4_kernel_test.go).
 Dequantisation and indexing are checked bit-exactly; float reductions within the stated tolerance.
 """
+import ctypes as C
 import math
 
 import numpy as np
@@ -430,4 +431,21 @@ def test_sampler_topk_keeps_ties(be):
         kept = np.nonzero(probs[i])[0]
         assert abs(kept.size - need) <= 1 and np.all(logits[i][kept] == 5.0)
         assert logits[i][got[i]] == 5.0 and probs[i][got[i]] > 0
+    be.ResetPool()
+
+
+def test_bounded_wait_gives_up_and_context_survives(be):
+    """Failure handling of device-side waits: a kernel that waits (2 ms limit) on a barrier nobody signals returns by itself,
+    the next synchronisation reports the timeout status, and the context keeps working afterwards."""
+    reached = C.c_int(0)
+    be._ck(be.lib.vx_selftest_bounded_wait(be.h, 2000, C.byref(reached)))
+    assert reached.value == 1
+    with pytest.raises(capi.VxError) as ei:
+        be.Sync()
+    assert ei.value.code == 6 and "wait gave up" in str(ei.value)         # VX_E_TIMEOUT
+    be.Sync()                                                              # the status word was cleared: no sticky failure
+    x = np.arange(1024, dtype=np.float32)
+    d = be.upload(x); o = be.Alloc(4096)
+    be.Add(d, d, o, 1024)
+    assert np.array_equal(be.download(o, 1024), x + x)
     be.ResetPool()

@@ -85,13 +85,35 @@ __device__ __forceinline__ bool mbar_try_park(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // bounded wait: false on timeout or when another thread of the CTA has already given up
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int *abort_flag, long long limit_clocks) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
         if (mbar_try_park(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_CLOCKS) { *abort_flag = 1; return false; }
+        if (clock64() - t0 > limit_clocks) { *abort_flag = 1; return false; }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    return mbar_wait_limit(bar, parity, abort_flag, WAIT_CLOCKS);
+}
+
+// Self-test of the give-up path: one CTA waits on an mbarrier that nothing ever arrives on, with a short limit, and must
+// come back with the error word set instead of spinning.
+__global__ void bounded_wait_selftest_kernel(long long limit_clocks, int *__restrict__ err_flag, int *__restrict__ reached_end) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const bool ok = mbar_wait_limit(smem_u32(&bar), 0, &s_abort, limit_clocks);     // every thread waits; the first to give up raises the flag
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (!ok || s_abort) atomicExch(err_flag, VX_E_TIMEOUT);
+        *reached_end = 1;
     }
 }
 // 2-D tiled TMA load into this CTA, completing on one of its mbarriers
@@ -494,6 +516,26 @@ int make_map(vx_ctx *c, CUtensorMap *map, CUtensorMapDataType dt, int elem, cons
 }
 
 }  // namespace
+
+// Runs the self-test kernel with a wait limit of `limit_us` microseconds (clamped to [10, 100000]).  The kernel's status is
+// reported by the next synchronising call (vx_sync returns VX_E_TIMEOUT), exactly as for the projection kernels; the
+// context stays usable.  *reached_end tells that the kernel ran to its last line.
+extern "C" int vx_selftest_bounded_wait(vx_ctx *c, int limit_us, int *reached_end) {
+    if (!c || !reached_end) return VX_E_BAD_ARG;
+    VxGuard g(c);
+    limit_us = max(10, min(limit_us, 100000));
+    int khz = 0;
+    VX_CUDA(c, cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, c->device));
+    const long long limit_clocks = (long long)limit_us * (khz > 0 ? khz : 1500000) / 1000;
+    int *d_flag = c->d_int_result + 9;
+    VX_CUDA(c, cudaMemsetAsync(d_flag, 0, 4, c->stream));
+    bounded_wait_selftest_kernel<<<1, 64, 0, c->stream>>>(limit_clocks, c->d_int_result + 8, d_flag);
+    VX_LAUNCH_CHECK(c);
+    VX_CUDA(c, cudaMemcpyAsync(c->h_int_result + 9, d_flag, 4, cudaMemcpyDeviceToHost, c->stream));
+    VX_CUDA(c, cudaStreamSynchronize(c->stream));
+    *reached_end = c->h_int_result[9];
+    return VX_OK;
+}
 
 // same contract as vxq_gemm (vx_quant.cu); the context's device error word receives VX_E_TIMEOUT if a bounded wait gave up
 int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out, float *parts,
