@@ -9,6 +9,8 @@
 #include <math.h>
 #include <string.h>
 
+#include <cooperative_groups.h>
+
 #include <algorithm>
 
 #include "vx_paged.cuh"
@@ -445,17 +447,24 @@ __device__ __forceinline__ float gate_act(float g, float u, int geglu) {
     return __fmul_rn(a, u);
 }
 // h13 row = [gate (F) | up (F)]; act = activation(gate)*up is split for the W2 projection without touching memory in between
+// One thread-block cluster per row: CL CTAs of 1024 threads share the row's columns (thread t of CTA q owns columns
+// ((c * CL + q) * 1024 + t) * 4 .. +3 of chunk c) and exchange their partial maxima through distributed shared memory, so a
+// thin batch spreads the float64 activation math over CL SMs instead of one.
 template <int NC>
 __global__ void __launch_bounds__(VX_ROW_THREADS)
 act_split_kernel(const float *__restrict__ h13, int n_parts, size_t part_stride, int ffn, int geglu, VxSplit s) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int CL = (int)cluster.num_blocks(), q = (int)cluster.block_rank();
     __shared__ float red[32];
-    const int r = blockIdx.x;
+    __shared__ float cl_amax;
+    const int r = blockIdx.x / CL;
     const float *gr = h13 + (size_t)r * 2 * ffn, *ur = gr + ffn;
     float4 v[NC];
     float amax = 0.f;
 #pragma unroll
     for (int c = 0; c < NC; c++) {
-        int k0 = (c * VX_ROW_THREADS + threadIdx.x) * 4;
+        int k0 = ((c * CL + q) * VX_ROW_THREADS + threadIdx.x) * 4;
         v[c] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (k0 < ffn) {
             float4 g = *reinterpret_cast<const float4 *>(gr + k0), u = *reinterpret_cast<const float4 *>(ur + k0);
@@ -468,14 +477,20 @@ act_split_kernel(const float *__restrict__ h13, int n_parts, size_t part_stride,
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[c].x), fabsf(v[c].y)), fmaxf(fabsf(v[c].z), fabsf(v[c].w))));
     }
     amax = block_max(amax, red);
+    if (CL > 1) {
+        if (threadIdx.x == 0) cl_amax = amax;
+        cluster.sync();
+        for (int o = 0; o < CL; o++) amax = fmaxf(amax, *cluster.map_shared_rank(&cl_amax, o));
+        cluster.sync();                            // nobody leaves while a peer may still read its maximum
+    }
     float sc, inv;
     vx_row_scale(amax, sc, inv);
-    if (threadIdx.x == 0) s.scale[r] = sc;
+    if (threadIdx.x == 0 && q == 0) s.scale[r] = sc;
     __half *hi = s.hi + (size_t)r * s.k_pad, *lo = s.lo + (size_t)r * s.k_pad;
     float *bs = s.bsum + (size_t)r * (s.k_pad / 32);
 #pragma unroll
     for (int c = 0; c < NC; c++) {
-        int k0 = (c * VX_ROW_THREADS + threadIdx.x) * 4;
+        int k0 = ((c * CL + q) * VX_ROW_THREADS + threadIdx.x) * 4;
         if (k0 < s.k_pad) {
             const float t[4] = {v[c].x * inv, v[c].y * inv, v[c].z * inv, v[c].w * inv};
             vx_split_store4(t, hi, lo, bs, k0);
@@ -550,9 +565,18 @@ int add_norm_split(vx_model *m, int rows, const float *parts, int n_parts, size_
 int act_split(vx_model *m, int rows, int n_parts) {
     const int F = m->cfg.ffn;
     const size_t pstride = (size_t)rows * 2 * F;
-    int nc = ceil_div(m->sp_f.k_pad, VX_ROW_THREADS * 4);
+    // cluster size: as many CTAs per row as keep the grid within about two waves of the GPU
+    int cl = 1;
+    while (cl < 4 && rows * cl * 2 <= 2 * m->c->sm_count && m->sp_f.k_pad > cl * VX_ROW_THREADS * 4) cl *= 2;
+    int nc = ceil_div(m->sp_f.k_pad, cl * VX_ROW_THREADS * 4);
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(rows * cl); lc.blockDim = dim3(VX_ROW_THREADS); lc.dynamicSmemBytes = 0; lc.stream = m->c->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = cl; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    lc.attrs = at; lc.numAttrs = 1;
+    const float *parts_c = m->parts;
     switch (nc) {
-#define VX_ACT_CASE(N) case N: act_split_kernel<N><<<rows, VX_ROW_THREADS, 0, m->c->stream>>>(m->parts, n_parts, pstride, F, m->cfg.geglu, m->sp_f); break;
+#define VX_ACT_CASE(N) case N: VX_CUDA(m->c, cudaLaunchKernelEx(&lc, act_split_kernel<N>, parts_c, n_parts, pstride, F, m->cfg.geglu, m->sp_f)); break;
         VX_ACT_CASE(1) VX_ACT_CASE(2) VX_ACT_CASE(3) VX_ACT_CASE(4) VX_ACT_CASE(5) VX_ACT_CASE(6) VX_ACT_CASE(7) VX_ACT_CASE(8)
 #undef VX_ACT_CASE
     default: return vx_fail(m->c, VX_E_UNSUPPORTED, "ffn size %d is not supported (max 32768)", F);
