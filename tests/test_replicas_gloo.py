@@ -86,3 +86,15 @@ def test_reference_arm_runs_on_rank_zero_only():
                        env=env, cwd=ROOT, capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stderr[-2000:]
     assert r.stdout.strip() == ""
+
+
+def test_trace_generator_is_deterministic_and_in_range():
+    from vexel_b200 import trace as tr
+    a1, p1, o1 = tr.make_trace(64, 40.0, 32000, seed=4)
+    a2, p2, o2 = tr.make_trace(64, 40.0, 32000, seed=4)
+    assert np.array_equal(a1, a2) and np.array_equal(o1, o2) and all(np.array_equal(x, y) for x, y in zip(p1, p2))
+    assert np.all(np.diff(a1) > 0) and 0.5 < a1[-1] / (64 / 40.0) < 2.0          # Poisson arrivals at ~40 per second
+    lens = np.array([len(p) for p in p1])
+    assert lens.min() >= 16 and lens.max() <= 8192 and 200 < np.median(lens) < 1200
+    assert o1.min() >= 32 and o1.max() <= 512
+    assert all(p.dtype == np.int32 and p.min() >= 0 and p.max() < 32000 for p in p1)
