@@ -432,3 +432,38 @@ def test_load_gguf_reports_bad_tensors(be, tmp_path):
     gs.write_gguf(path2, spec, tensors, meta_spec=wrong)     # metadata says ffn*2, tensors are ffn wide
     with pytest.raises(RuntimeError, match="has shape"):
         capi.Model.from_gguf(be, path2, max_blocks=16)
+
+
+@pytest.mark.parametrize("kind", ["llama_gqa", "llama_mha_d128", "gemma2_window"])
+def test_chunked_prefill_over_the_paged_cache(be, kind):
+    """A prompt longer than the step limit is fed in chunks (runtime/decode.go:961-1096 walks it through the same cache): the
+    first chunk attends over its fresh float32 K/V, the later ones over the fp16 pages — on the GPU through the multi-row
+    tensor-core kernel — and every chunk matches the oracle fed the same chunks."""
+    if kind == "llama_gqa":
+        spec = small_llama(2)
+    elif kind == "llama_mha_d128":
+        spec = gs.scaled(gs.C2_LLAMA2_7B, 2, 256, 2, 2, 128, 512, 1024)
+    else:
+        spec = gs.scaled(gs.C4_GEMMA2_9B, 2, 256, 4, 2, 64, 512, 1024, quant="q4_0", sliding_window=40)
+    om, gm = build_pair(be, spec, 17, max_blocks=64, max_seqs=4, max_batch_tokens=128, max_blocks_per_seq=32)
+    rng = np.random.default_rng(12)
+    n = 300
+    p = rng.integers(0, spec.vocab, n).astype(np.int32)
+    gm.set_capture(True)
+    tok, gl = gm.prefill(1, p, 0, want_logits=True)            # chunks of 128, 128 and 44 rows
+    for lo in (0, 128, 256):
+        wl, wh = om.forward(1, p[lo:lo + 128], lo, want_hidden=True)
+    if spec.final_softcap > 0:
+        O.lib().vo_final_softcap(wl.ctypes.data, wl.size, spec.final_softcap)
+    h = gm.get_capture(n - 256)                                # hidden states of the last chunk, every layer
+    for l in range(spec.n_layers + 1):
+        assert rel_l2(h[l], wh[l]) < HIDDEN_TOL, (l, rel_l2(h[l], wh[l]))
+    assert rel_l2(gl[0], wl[-1]) < HIDDEN_TOL and tok == O.argmax(wl[-1])
+    assert np.array_equal(gm.block_table(1), om.pool.table(0, 1))
+    # decode continues from the chunked prompt
+    out, gl = gm.decode_step([1], [tok], [n], want_logits=True)
+    wl, _ = om.forward(1, np.int32([tok]), n, want_hidden=True)
+    if spec.final_softcap > 0:
+        O.lib().vo_final_softcap(wl.ctypes.data, wl.size, spec.final_softcap)
+    assert rel_l2(gl[0], wl[0]) < HIDDEN_TOL and int(out[0]) == O.argmax(wl[0])
+    gm.close()

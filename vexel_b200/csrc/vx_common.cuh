@@ -181,4 +181,5 @@ struct VxAttnArgs {
     float scale, softcap;
 };
 int vxp_attention(vx_ctx *c, const VxAttnArgs &a);
+int vxp_prefill_rows(vx_ctx *c, const VxAttnArgs &a, int row0, int n_rows);   // VX_E_UNSUPPORTED when the shape has no such kernel
 int vxp_attention_split(vx_ctx *c, const VxAttnArgs &a, const VxSplit *split, int n_max_chunks, bool *fused);

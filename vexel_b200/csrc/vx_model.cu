@@ -646,7 +646,14 @@ int forward(vx_model *m, int rows, int mode, int n_work_host[2], const int chunk
             a.scale = scale; a.softcap = cf.attn_softcap;
             // at most this many split-K chunks per row: the table width bounds a row's pages
             const int n_max = ceil_div(cf.max_blocks_per_seq, max(chunk_pages[wl], 1)) + 1;
-            VX_TRY(vxp_attention_split(c, a, &m->sp_q, n_max, &split_done));                // block.go:872 / 881-890
+            // a long chunk of one sequence (chunked prefill, decode.go:1033-1060) walks the cache once per 64 rows instead of once per row
+            bool pf_done = false;
+            if (m->last_seqs == 1 && rows >= 32) {
+                int rc = vxp_prefill_rows(c, a, 0, rows);
+                if (rc == VX_OK) pf_done = true;
+                else if (rc != VX_E_UNSUPPORTED) return rc;
+            }
+            if (!pf_done) VX_TRY(vxp_attention_split(c, a, &m->sp_q, n_max, &split_done));  // block.go:872 / 881-890
         }
         time_end(m, 0);
         if (!split_done) VX_TRY(vxq_split_rows(c, m->attn, rows, qd, qd, m->sp_q));

@@ -459,6 +459,175 @@ __global__ void paged_merge_kernel(VxAttnArgs a) {
 
 static int g_attn_mma = 1;     // grouped-query shapes use the tensor-core kernel (0 = the CUDA-core kernel, for comparison)
 
+// ------------------------------------------------------------------ multi-row (chunked prefill) attention over the paged cache
+// A prompt chunk that does not start at position 0 attends over pages that earlier chunks wrote (runtime/decode.go:1033-1060
+// walks the prompt token by token through the same cache).  Running it through the decode kernels re-reads the whole cache
+// once per query row; here a CTA owns 64 consecutive rows of one sequence and one query head (a warp 16 rows), walks the
+// pages once in tiles of 64 tokens staged in shared memory, and does both products on mma.sync.m16n8k16 with the query
+// rows as M:   S[16 x 64] = Q . K^T   (K via ldmatrix),   O[16 x D] += P . V   (V via ldmatrix.trans, P straight from the
+// score accumulators).  q and p are exact fp16 hi + lo pairs, accumulation is float32; masks are per row
+// (kv_start <= t < kv_len), so causal order, sliding windows and ragged tails need no special cases.
+constexpr int PF_ROWS = 64;           // query rows per CTA
+constexpr int PF_TOK = 64;            // KV tokens per tile (four pages)
+
+template <int D>
+__global__ void __launch_bounds__(128)
+paged_prefill_mma_kernel(VxAttnArgs a, int row0, int n_rows) {
+    constexpr int KS = D / 16, ND = D / 8, ROW_B = D * 2, TILE_B = PF_TOK * ROW_B, STAGE_B = 2 * TILE_B;
+    constexpr int CPR = D / 8;                                // 16-byte chunks per token row
+    extern __shared__ __align__(128) unsigned char pf_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+    const int h = blockIdx.y, kvh = h / (a.n_q_heads / a.n_kv_heads);
+    const int rt0 = row0 + blockIdx.x * PF_ROWS, rt1 = min(row0 + n_rows, rt0 + PF_ROWS);      // this CTA's rows
+    const int rA = rt0 + warp * 16 + g, rB = rA + 8;                                            // this lane's two rows
+    const bool vA = rA < rt1, vB = rB < rt1;
+    const int32_t *table = a.tables[a.row_slot[rt0]];
+    const size_t hs = (size_t)a.n_kv_heads * D;
+    const __half *pool = (const __half *)a.pool;
+    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(pf_smem);
+
+    // the tile's token range: from the smallest window start to the largest length among its rows (rows are in position order)
+    const int t_begin = (a.row_kv_start ? a.row_kv_start[rt0] : 0) / ATT_BS * ATT_BS;
+    const int t_end = a.row_kv_len[rt1 - 1];
+    const int lenA = vA ? a.row_kv_len[rA] : 0, lenB = vB ? a.row_kv_len[rB] : 0;
+    const int stA = (vA && a.row_kv_start) ? a.row_kv_start[rA] : 0, stB = (vB && a.row_kv_start) ? a.row_kv_start[rB] : 0;
+
+    uint32_t qh[KS][4], ql[KS][4];
+    {
+        const float *qa = a.q + (size_t)(vA ? rA : rt0) * a.q_row_stride + (size_t)h * D;
+        const float *qb = a.q + (size_t)(vB ? rB : rt0) * a.q_row_stride + (size_t)h * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            const float2 a0 = *reinterpret_cast<const float2 *>(qa + 16 * ks + 2 * c), a2 = *reinterpret_cast<const float2 *>(qa + 16 * ks + 2 * c + 8);
+            const float2 b0 = *reinterpret_cast<const float2 *>(qb + 16 * ks + 2 * c), b2 = *reinterpret_cast<const float2 *>(qb + 16 * ks + 2 * c + 8);
+            qh[ks][0] = pack_hi_lo(a0.x, a0.y, &ql[ks][0]); qh[ks][1] = pack_hi_lo(b0.x, b0.y, &ql[ks][1]);
+            qh[ks][2] = pack_hi_lo(a2.x, a2.y, &ql[ks][2]); qh[ks][3] = pack_hi_lo(b2.x, b2.y, &ql[ks][3]);
+        }
+    }
+    float acc[ND][4];
+#pragma unroll
+    for (int i = 0; i < ND; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+    float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;        // l over this lane's columns only
+
+    auto issue = [&](int t0, int stage) {           // stages tokens t0 .. t0+63 (four pages) of K and V; all 128 threads
+        const uint32_t sb = sbase + stage * STAGE_B;
+#pragma unroll
+        for (int j = 0; j < 2 * PF_TOK * CPR / 128; j++) {
+            const int ci = threadIdx.x + 128 * j;
+            const int isv = ci / (PF_TOK * CPR), r = ci % (PF_TOK * CPR), t = r / CPR, cc = r % CPR;
+            const int tok = t0 + t;
+            const uint32_t so = isv * TILE_B + t * ROW_B + ((cc ^ (t & 7)) << 4);
+            if (tok < t_end) {
+                const int blk = table[tok / ATT_BS];
+                const __half *src = pool + (size_t)blk * 2 * ATT_BS * hs + (size_t)isv * ATT_BS * hs + (size_t)(tok % ATT_BS) * hs + (size_t)kvh * D + cc * 8;
+                cp_async_16(sb + so, src);
+            } else {
+                // beyond the last attended token: zeros, so that a masked probability of 0 never meets stale bytes that read as NaN
+                *reinterpret_cast<uint4 *>(pf_smem + stage * STAGE_B + so) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+
+    int stage = 0;
+    if (t_begin < t_end) issue(t_begin, 0);
+    for (int t0 = t_begin; t0 < t_end; t0 += PF_TOK, stage ^= 1) {
+        if (t0 + PF_TOK < t_end) { issue(t0 + PF_TOK, stage ^ 1); asm volatile("cp.async.wait_group 1;\n" ::); }
+        else asm volatile("cp.async.wait_group 0;\n" ::);
+        __syncthreads();
+        const uint32_t kb_s = sbase + stage * STAGE_B, vb_s = kb_s + TILE_B;
+        float st[PF_TOK / 8][4];
+#pragma unroll
+        for (int j = 0; j < PF_TOK / 8; j++) { st[j][0] = st[j][1] = st[j][2] = st[j][3] = 0.f; }
+        {
+            const int mj = lane >> 3;
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++)
+#pragma unroll
+                for (int j = 0; j < PF_TOK / 8; j += 2) {        // two token tiles per ldmatrix.x4
+                    const int t = 8 * (j + (mj >> 1)) + (lane & 7);
+                    uint32_t kf[4];
+                    ldsm_x4(kf, kb_s + t * ROW_B + (((2 * ks + (mj & 1)) ^ (t & 7)) << 4));
+                    mma_16816(st[j], qh[ks], kf[0], kf[1]); mma_16816(st[j], ql[ks], kf[0], kf[1]);
+                    mma_16816(st[j + 1], qh[ks], kf[2], kf[3]); mma_16816(st[j + 1], ql[ks], kf[2], kf[3]);
+                }
+        }
+        // scale, soft-cap, masks; running maxima per row (this lane: columns 8j + 2c, +1 of rows A and B)
+        float mxA = -INFINITY, mxB = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < PF_TOK / 8; j++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int tok = t0 + 8 * j + 2 * c + e;
+                float va = st[j][e] * a.scale, vb = st[j][2 + e] * a.scale;
+                if (a.softcap > 0.f) { va = a.softcap * tanhf(va / a.softcap); vb = a.softcap * tanhf(vb / a.softcap); }
+                va = (tok >= stA && tok < lenA) ? va : -INFINITY;
+                vb = (tok >= stB && tok < lenB) ? vb : -INFINITY;
+                st[j][e] = va; st[j][2 + e] = vb;
+                mxA = fmaxf(mxA, va); mxB = fmaxf(mxB, vb);
+            }
+        mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1)); mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+        mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1)); mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+        const float nA = fmaxf(mA, mxA), nB = fmaxf(mB, mxB);
+        const float uA = nA == -INFINITY ? 0.f : nA, uB = nB == -INFINITY ? 0.f : nB;
+        const float cA = __expf(mA - uA), cB = __expf(mB - uB);
+        mA = nA; mB = nB; lA *= cA; lB *= cB;
+#pragma unroll
+        for (int i = 0; i < ND; i++) { acc[i][0] *= cA; acc[i][1] *= cA; acc[i][2] *= cB; acc[i][3] *= cB; }
+        // P as the A operand of the second product, K=16 tokens per step: registers of score tiles 2kt and 2kt+1
+#pragma unroll
+        for (int kt = 0; kt < PF_TOK / 16; kt++) {
+            uint32_t ph[4], pl[4];
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                const int j = 2 * kt + half;
+                const float p0 = st[j][0] == -INFINITY ? 0.f : __expf(st[j][0] - uA), p1 = st[j][1] == -INFINITY ? 0.f : __expf(st[j][1] - uA);
+                const float p2 = st[j][2] == -INFINITY ? 0.f : __expf(st[j][2] - uB), p3 = st[j][3] == -INFINITY ? 0.f : __expf(st[j][3] - uB);
+                lA += p0 + p1; lB += p2 + p3;
+                ph[2 * half] = pack_hi_lo(p0, p1, &pl[2 * half]);
+                ph[2 * half + 1] = pack_hi_lo(p2, p3, &pl[2 * half + 1]);
+            }
+            const int mj = lane >> 3, t = 16 * kt + 8 * (mj & 1) + (lane & 7);
+#pragma unroll
+            for (int nd = 0; nd < ND; nd += 2) {             // two 8-wide d tiles per ldmatrix.x4.trans
+                uint32_t vf[4];
+                ldsm_x4_t(vf, vb_s + t * ROW_B + (((nd + (mj >> 1)) ^ (t & 7)) << 4));
+                mma_16816(acc[nd], ph, vf[0], vf[1]); mma_16816(acc[nd], pl, vf[0], vf[1]);
+                mma_16816(acc[nd + 1], ph, vf[2], vf[3]); mma_16816(acc[nd + 1], pl, vf[2], vf[3]);
+            }
+        }
+        __syncthreads();                             // the stage is refilled two iterations later by all threads
+    }
+    lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    const float iA = lA > 0.f ? 1.0f / lA : 0.f, iB = lB > 0.f ? 1.0f / lB : 0.f;
+#pragma unroll
+    for (int nd = 0; nd < ND; nd++) {
+        if (vA) *reinterpret_cast<float2 *>(a.out + (size_t)rA * a.out_row_stride + (size_t)h * D + 8 * nd + 2 * c) = make_float2(acc[nd][0] * iA, acc[nd][1] * iA);
+        if (vB) *reinterpret_cast<float2 *>(a.out + (size_t)rB * a.out_row_stride + (size_t)h * D + 8 * nd + 2 * c) = make_float2(acc[nd][2] * iB, acc[nd][3] * iB);
+    }
+}
+
+// rows [row0, row0 + n_rows) belong to one sequence, in position order; f16 pool, 16-token pages, head_dim 64 or 128
+int vxp_prefill_rows(vx_ctx *c, const VxAttnArgs &a, int row0, int n_rows) {
+    const int D = a.head_dim;
+    if (!(a.pool_is_f16 && a.block_size == ATT_BS && (D == 64 || D == 128) && a.q_row_stride % 2 == 0 && a.out_row_stride % 2 == 0 && n_rows > 0))
+        return VX_E_UNSUPPORTED;
+    dim3 grid(ceil_div(n_rows, PF_ROWS), a.n_q_heads);
+    const int smem = 2 * 2 * PF_TOK * D * 2;
+    if (D == 64) {
+        static bool done = false;
+        if (!done) { VX_CUDA(c, cudaFuncSetAttribute(paged_prefill_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); done = true; }
+        paged_prefill_mma_kernel<64><<<grid, 128, smem, c->stream>>>(a, row0, n_rows);
+    } else {
+        static bool done = false;
+        if (!done) { VX_CUDA(c, cudaFuncSetAttribute(paged_prefill_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); done = true; }
+        paged_prefill_mma_kernel<128><<<grid, 128, smem, c->stream>>>(a, row0, n_rows);
+    }
+    VX_LAUNCH_CHECK(c);
+    return VX_OK;
+}
+
 // Merge of the split-K chunks fused with the fp16 hi/lo split that feeds the output projection: one CTA per query row.
 // Phase 1, one thread per head: the chunk maxima and weights e^{m_c - M} / L into shared memory.  Phase 2, four consecutive
 // head dimensions per thread: the weighted sum of the chunk outputs with independent loads (rows written directly by a
