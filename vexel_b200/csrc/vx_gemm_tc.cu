@@ -35,18 +35,19 @@
 namespace {
 
 constexpr int TC_ROWS = 128;          // weight rows per CTA (MMA M)
-constexpr int TC_MT = 64;             // batch rows per CTA
+constexpr int TC_MT = 64;             // batch rows per CTA (decode); batches above 64 rows use 128-row tiles (template parameter MT)
 constexpr int TC_BK = 64;             // k per stage = one 128-byte swizzle row of fp16
 constexpr int TC_ST = 4;              // pipeline stages: activation tiles in shared memory, weight operand in tensor memory
 constexpr int TC_ISSUERS = 2;         // MMA-issuing threads (one per warp), each with its own accumulator
 constexpr int TC_RAW = 4;             // ring of 128-weight nibble groups (each feeds two stages)
 constexpr int TC_DEQ = 512;           // dequantiser threads: (row, block of the stage, word pair)
 constexpr int TC_THREADS = TC_DEQ + 32 * (TC_ISSUERS + 1);
-constexpr int X_TILE = TC_MT * 128;           // bytes of one fp16 activation tile (64 rows x 128 B)
-constexpr int STAGE_BYTES = 2 * X_TILE;       // x_hi rows 0-63 followed by x_lo rows 64-127: one 128-row K-major operand
+constexpr int x_tile_bytes(int mt) { return mt * 128; }          // one fp16 activation tile (mt rows x 128 B)
+constexpr int stage_bytes(int mt) { return 2 * x_tile_bytes(mt); }   // x_hi rows followed by x_lo rows: one 2*mt-row K-major operand
+constexpr int issuers_of(int mt) { return mt == 64 ? 2 : 1; }    // a 128-row tile needs the whole accumulator space for one issuer
 constexpr int RAW_BYTES = TC_ROWS * 64;       // packed nibbles of one 128-weight group
 constexpr int RAWH_BYTES = TC_ROWS * 32;      // Q6_K only: the top two bits of the same group
-constexpr int SMEM_BYTES = TC_ST * STAGE_BYTES + TC_RAW * (RAW_BYTES + RAWH_BYTES) + 1024 /*alignment*/ + 512 /*barriers*/ + 256 /*row scales*/;
+constexpr int smem_bytes(int mt) { return TC_ST * stage_bytes(mt) + TC_RAW * (RAW_BYTES + RAWH_BYTES) + 1024 /*alignment*/ + 512 /*barriers*/ + 512 /*row scales*/; }
 enum { TC_Q4_0 = 0, TC_Q4_K = 1, TC_Q6_K = 2 };
 // what the block formats need beyond the nibble tiles: scales (Q4_0: half per block; K-quants: 8 bytes per 128-weight group),
 // super-block scales (Q4_K: half2 {d, dmin}; Q6_K: half d), and the activations' per-32-block sums for the Q4_K minima
@@ -54,7 +55,7 @@ struct TcAux { const void *sc; const void *aux; const float *xbsum; int bsum_ld;
 // tensor memory columns: issuer j accumulates into [128j, 128j+128): cols 0-63 = A_hi*x_hi + A_lo*x_hi, cols 64-127 = A_hi*x_lo
 // for its K=16 steps; weight stage s at TMEM_A + 64*s: [hi k0 k1 | lo k0 k1 | hi k2 k3 | lo k2 k3], 8 columns (two fp16 each)
 // per K=16 step
-constexpr int TMEM_A = TC_ISSUERS * 2 * TC_MT;
+constexpr int TMEM_A = TC_ISSUERS * 2 * TC_MT;    // = 256 for both tile heights: 2 issuers x 128 columns, or 1 issuer x 256
 constexpr int TMEM_COLS = 512;                // 2 * 128 + 4 * 64
 static_assert(TMEM_A + 64 * TC_ST <= TMEM_COLS, "tensor memory budget");
 constexpr long long WAIT_CLOCKS = 400000000LL;             // ~0.2 s at 2 GHz
@@ -133,8 +134,7 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
     return d;
 }
 // instruction descriptors: D=f32, A=B=f16, both K-major, M=128, N = 128 (x_hi and x_lo stacked) or 64 (x_hi only)
-constexpr uint32_t UMMA_IDESC_N128 = (1u << 4) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
-constexpr uint32_t UMMA_IDESC_N64 = (1u << 4) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
+constexpr uint32_t umma_idesc(int n) { return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24); }
 
 // D[tmem_d] (+)= A[tmem_a] * B[smem desc]^T, the A operand read from tensor memory (8 columns of fp16 pairs per K=16)
 __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -186,12 +186,13 @@ __device__ __forceinline__ void split_scale(float d, __half2 *hi, __half2 *lo) {
 }
 
 // grid: (ceil(N/128), split_k, ceil(M/64)); out layout [split][M][ld_out]; kb_per_split is even
-template <int FMT>
+template <int FMT, int MT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_xh,
                const __grid_constant__ CUtensorMap map_xl, const TcAux aux, const float *__restrict__ xscale,
                float *__restrict__ out, int M, int N, int k_groups, int kb_per_split, int ld_out, size_t part_stride,
                int *__restrict__ err_flag) {
+    constexpr int X_TILE = x_tile_bytes(MT), STAGE_BYTES = stage_bytes(MT), NISS = issuers_of(MT);
     const __half *sc = reinterpret_cast<const __half *>(aux.sc);
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint32_t s_tmem;
@@ -210,7 +211,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t accum_bar = bar_base + 8u * (3 * TC_ST + 2 * TC_RAW);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int r0 = blockIdx.x * TC_ROWS, m0 = blockIdx.z * TC_MT;
+    const int r0 = blockIdx.x * TC_ROWS, m0 = blockIdx.z * MT;
     const int kb_begin = blockIdx.y * kb_per_split;
     const int n_kb = min(k_groups * 2, kb_begin + kb_per_split) - kb_begin;
 
@@ -218,12 +219,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         s_abort = 0;
         // xf_bar(s): "stage s ready" = the activation tile has landed (one arrival carrying its byte count) and the eight warps
         // of the dequantiser group have written the weight operand: one probe per stage for the issuing threads
-        for (int s = 0; s < TC_ST; s++) { mbar_init(xf_bar(s), 1 + TC_DEQ / 64); mbar_init(af_bar(s), 1); mbar_init(e_bar(s), TC_ISSUERS); }   // one arrival per warp:
+        for (int s = 0; s < TC_ST; s++) { mbar_init(xf_bar(s), 1 + TC_DEQ / 64); mbar_init(af_bar(s), 1); mbar_init(e_bar(s), NISS); }   // one arrival per warp:
         for (int s = 0; s < TC_RAW; s++) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), TC_DEQ / 32); }   // 512 arrivals on one word serialise
-        mbar_init(accum_bar, TC_ISSUERS);
+        mbar_init(accum_bar, NISS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (tid < TC_MT) s_xscale[tid] = m0 + tid < M ? xscale[m0 + tid] : 0.f;
+    if (tid < MT) s_xscale[tid] = m0 + tid < M ? xscale[m0 + tid] : 0.f;
     if (warp == TC_DEQ / 32) {   // the MMA warp owns the tensor-memory allocation
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -389,20 +390,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 tma_load_2d(dst + X_TILE, &map_xl, gkb * TC_BK, m0, xf_bar(xs));
             }
         }
-    } else if (lane == 0) {
+    } else if (lane == 0 && warp < TC_DEQ / 32 + NISS) {
         // ------------------------------------------------------------------ MMA issue (one thread per issuer warp)
         // On a busy SM every tcgen05 instruction (mma or commit) costs its issuing thread ~80-100 cycles whatever its
         // shape, so the K=16 steps of a stage are shared between TC_ISSUERS threads on different schedulers, each with
         // its own accumulator (summed in the epilogue: the result stays deterministic), and a stage is released by a
         // single commit per issuer.  Per step: [A_hi] x [x_hi; x_lo] (N=128), then [A_lo] x [x_hi] (N=64).
         const int j = warp - TC_DEQ / 32;
-        constexpr int KS = (TC_BK / 16) / TC_ISSUERS;             // K=16 steps per issuer and stage
+        constexpr int KS = (TC_BK / 16) / NISS;                   // K=16 steps per issuer and stage
         uint64_t xdesc[TC_ST][KS];
 #pragma unroll
         for (int s = 0; s < TC_ST; s++)
 #pragma unroll
             for (int k = 0; k < KS; k++) xdesc[s][k] = umma_desc(base + s * STAGE_BYTES) + (uint64_t)(2 * (j * KS + k));   // +32 bytes of K per step
-        const uint32_t acc = tmem + 2 * TC_MT * j;
+        const uint32_t acc = tmem + 2 * MT * j;
         bool ok = true;
         uint32_t first = 0u;
         for (int kb0 = 0; kb0 < n_kb && ok; kb0 += TC_ST) {
@@ -414,12 +415,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 // stage layout in tensor memory: [hi k0 k1 | lo k0 k1 | hi k2 k3 | lo k2 k3], 8 columns per K=16 step; issuer j owns steps 2j, 2j+1
-                const uint32_t a_hi = tmem + TMEM_A + 64 * s + 32 * j, a_lo = a_hi + 16;
+                const uint32_t a_hi0 = tmem + TMEM_A + 64 * s + 32 * j * (KS / 2);
 #pragma unroll
                 for (int k = 0; k < KS; k++) {
-                    umma_f16_ts(acc, a_hi + 8 * k, xdesc[s][k], UMMA_IDESC_N128, first);
+                    const uint32_t a_hi = a_hi0 + 32 * (k >> 1) + 8 * (k & 1), a_lo = a_hi + 16;
+                    umma_f16_ts(acc, a_hi, xdesc[s][k], umma_idesc(2 * MT), first);     // [x_hi; x_lo]: N = 2 MT
                     first = 1u;
-                    umma_f16_ts(acc, a_lo + 8 * k, xdesc[s][k], UMMA_IDESC_N64, 1u);
+                    umma_f16_ts(acc, a_lo, xdesc[s][k], umma_idesc(MT), 1u);            // x_hi only:   N = MT
                 }
                 umma_commit(e_bar(s));        // arrives when this issuer's MMAs have finished reading the stage
             }
@@ -434,18 +436,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
             float *o = out + (size_t)blockIdx.y * part_stride;
-            const int n = r0 + (warp & 3) * 32 + lane, c0 = (warp >> 2) * 16;
-            float sum[16];
+            constexpr int CW = MT / 4;                                // batch columns per warp group
+            const int n = r0 + (warp & 3) * 32 + lane, c0 = (warp >> 2) * CW;
+            float sum[CW];
 #pragma unroll
-            for (int i = 0; i < 16; i++) sum[i] = 0.f;
+            for (int i = 0; i < CW; i++) sum[i] = 0.f;
 #pragma unroll
-            for (int part = 0; part < 2 * TC_ISSUERS; part++) {       // issuer accumulators x {x_hi, x_lo} halves, fixed order
-                uint32_t v[16];
-                VX_TMEM_LD16(v, tmem + ((uint32_t)((warp & 3) * 32) << 16) + part * TC_MT + c0);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            for (int part = 0; part < 2 * NISS; part++)               // issuer accumulators x {x_hi, x_lo} halves, fixed order
 #pragma unroll
-                for (int i = 0; i < 16; i++) sum[i] += __uint_as_float(v[i]);
-            }
+                for (int cb = 0; cb < CW / 16; cb++) {
+                    uint32_t v[16];
+                    VX_TMEM_LD16(v, tmem + ((uint32_t)((warp & 3) * 32) << 16) + part * MT + c0 + 16 * cb);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 16; i++) sum[16 * cb + i] += __uint_as_float(v[i]);
+                }
             if (FMT == TC_Q4_K) {
                 // plus sum over this slice's sub-blocks of (8 fl(d * sc_u) - fl(dmin * m_u)) * (sum of the activations of the sub-block)
                 // (dequant.go:369-392: w = d1 * q - dm1)
@@ -461,7 +466,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const float d1 = __fmul_rn(dd.x, (float)((sm8.x >> (8 * u)) & 0xFF)), dm = __fmul_rn(dd.y, (float)((sm8.y >> (8 * u)) & 0xFF));
                         const float ce = fmaf(8.f, d1, -dm);
 #pragma unroll
-                        for (int i = 0; i < 16; i++) {
+                        for (int i = 0; i < CW; i++) {
                             const int m = min(m0 + c0 + i, M - 1);
                             sum[i] = fmaf(ce, aux.xbsum[(size_t)m * aux.bsum_ld + gabs * 4 + u], sum[i]);
                         }
@@ -470,7 +475,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
             if (n < N) {
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
+                for (int i = 0; i < CW; i++) {
                     const int m = m0 + c0 + i;
                     if (m < M) o[(size_t)m * ld_out + n] = sum[i] * s_xscale[c0 + i];
                 }
@@ -545,13 +550,19 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
     if (x.k_pad != w.k_pad) return vx_fail(c, VX_E_BAD_ARG, "projection: activation row stride %d != weight k_pad %d", x.k_pad, w.k_pad);
     static bool attr_set = false;
     if (!attr_set) {
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_0, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(64)));
+        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_K, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(64)));
+        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q6_K, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(64)));
+        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_0, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(128)));
+        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_K, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(128)));
+        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q6_K, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(128)));
         attr_set = true;
     }
+    // batches above 64 rows (prefill chunks, verify) take 128-row tiles: the MMA count per stage stays the same, so each
+    // dequantised weight tile and each tcgen05 instruction serves twice the rows
+    const int mt = m > 64 ? 128 : 64;
     const int k_groups = w.k_pad / 128;
-    const int tiles = ceil_div(w.n, TC_ROWS) * ceil_div(m, TC_MT);
+    const int tiles = ceil_div(w.n, TC_ROWS) * ceil_div(m, mt);
     // split-K (in whole 128-weight groups) for whole waves of one CTA per SM
     int split = 1;
     if (parts) {
@@ -575,15 +586,15 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
     // of paying four driver calls per launch.
     const uint64_t x_rows = (uint64_t)((m + 63) / 64) * 64;     // the split buffers are allocated in multiples of 64 rows
     struct MapKey {
-        const void *qs, *hi, *xh, *xl; uint64_t rows; int n, kg, kp;
+        const void *qs, *hi, *xh, *xl; uint64_t rows; int n, kg, kp, mt;
         bool operator<(const MapKey &o) const {
-            return std::tie(qs, hi, xh, xl, rows, n, kg, kp) < std::tie(o.qs, o.hi, o.xh, o.xl, o.rows, o.n, o.kg, o.kp);
+            return std::tie(qs, hi, xh, xl, rows, n, kg, kp, mt) < std::tie(o.qs, o.hi, o.xh, o.xl, o.rows, o.n, o.kg, o.kp, o.mt);
         }
     };
     struct MapSet { CUtensorMap w, h, xh, xl; };
     static std::map<MapKey, MapSet> cache;
     static std::mutex cache_mu;
-    const MapKey key{w.qs, w.type == VX_T_Q6_K ? w.hi : nullptr, x.hi, x.lo, x_rows, w.n, k_groups, x.k_pad};
+    const MapKey key{w.qs, w.type == VX_T_Q6_K ? w.hi : nullptr, x.hi, x.lo, x_rows, w.n, k_groups, x.k_pad, mt};
     MapSet ms;
     bool have = false;
     {
@@ -595,9 +606,9 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
     if (!have) {
     VX_TRY(make_map(c, &map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w.qs, (uint64_t)k_groups * 64, (uint64_t)w.n, (uint64_t)k_groups * 64, 64,
                     TC_ROWS, CU_TENSOR_MAP_SWIZZLE_64B));
-    VX_TRY(make_map(c, &map_xh, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x.hi, (uint64_t)x.k_pad, x_rows, (uint64_t)x.k_pad * 2, TC_BK, TC_MT,
+    VX_TRY(make_map(c, &map_xh, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x.hi, (uint64_t)x.k_pad, x_rows, (uint64_t)x.k_pad * 2, TC_BK, (uint32_t)mt,
                     CU_TENSOR_MAP_SWIZZLE_128B));
-    VX_TRY(make_map(c, &map_xl, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x.lo, (uint64_t)x.k_pad, x_rows, (uint64_t)x.k_pad * 2, TC_BK, TC_MT,
+    VX_TRY(make_map(c, &map_xl, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x.lo, (uint64_t)x.k_pad, x_rows, (uint64_t)x.k_pad * 2, TC_BK, (uint32_t)mt,
                     CU_TENSOR_MAP_SWIZZLE_128B));
     // Q6_K: the top two bits of every weight as bytes [n][k_groups*32]; the other formats pass the nibble map again (unused)
     if (w.type == VX_T_Q6_K)
@@ -608,15 +619,16 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
         if (cache.size() > 4096) cache.clear();     // buffers of destroyed models: start over rather than grow without bound
         cache[key] = ms;
     }
-    dim3 grid(ceil_div(w.n, TC_ROWS), split, ceil_div(m, TC_MT));
+    dim3 grid(ceil_div(w.n, TC_ROWS), split, ceil_div(m, mt));
     const TcAux aux{w.sc, w.aux, x.bsum, x.k_pad / 32};
     const size_t pstride = (size_t)m * w.n;
-    if (w.type == VX_T_Q4_0)
-        gemm_tc_kernel<TC_Q4_0><<<grid, TC_THREADS, SMEM_BYTES, c->stream>>>(map_w, map_h, map_xh, map_xl, aux, x.scale, dst, m, w.n, k_groups, per * 2, ld, pstride, err_flag);
-    else if (w.type == VX_T_Q4_K)
-        gemm_tc_kernel<TC_Q4_K><<<grid, TC_THREADS, SMEM_BYTES, c->stream>>>(map_w, map_h, map_xh, map_xl, aux, x.scale, dst, m, w.n, k_groups, per * 2, ld, pstride, err_flag);
-    else
-        gemm_tc_kernel<TC_Q6_K><<<grid, TC_THREADS, SMEM_BYTES, c->stream>>>(map_w, map_h, map_xh, map_xl, aux, x.scale, dst, m, w.n, k_groups, per * 2, ld, pstride, err_flag);
+#define VX_TC_LAUNCH(F, T) gemm_tc_kernel<F, T><<<grid, TC_THREADS, smem_bytes(T), c->stream>>>(map_w, map_h, map_xh, map_xl, aux, x.scale, dst, m, w.n, k_groups, per * 2, ld, pstride, err_flag)
+    if (mt == 64) {
+        if (w.type == VX_T_Q4_0) VX_TC_LAUNCH(TC_Q4_0, 64); else if (w.type == VX_T_Q4_K) VX_TC_LAUNCH(TC_Q4_K, 64); else VX_TC_LAUNCH(TC_Q6_K, 64);
+    } else {
+        if (w.type == VX_T_Q4_0) VX_TC_LAUNCH(TC_Q4_0, 128); else if (w.type == VX_T_Q4_K) VX_TC_LAUNCH(TC_Q4_K, 128); else VX_TC_LAUNCH(TC_Q6_K, 128);
+    }
+#undef VX_TC_LAUNCH
     VX_LAUNCH_CHECK(c);
     return VX_OK;
 }
