@@ -181,5 +181,7 @@ struct VxAttnArgs {
     float scale, softcap;
 };
 int vxp_attention(vx_ctx *c, const VxAttnArgs &a);
+int vxp_prefill_f32(vx_ctx *c, const float *q, int q_ld, const float *k, const float *v, long kv_ld, float *out, int out_ld, int n_rows,
+                    int hq, int hkv, int d, float scale, float softcap);
 int vxp_prefill_rows(vx_ctx *c, const VxAttnArgs &a, int row0, int n_rows);   // VX_E_UNSUPPORTED when the shape has no such kernel
 int vxp_attention_split(vx_ctx *c, const VxAttnArgs &a, const VxSplit *split, int n_max_chunks, bool *fused);

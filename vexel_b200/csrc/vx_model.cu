@@ -632,8 +632,10 @@ int forward(vx_model *m, int rows, int mode, int n_work_host[2], const int chunk
         time_begin(m, 0);
         bool split_done = false;
         if (mode == 1) {
-            VX_TRY(vxe_sdpa_strided(c, m->qkv, nqkv, m->qkv + qd, m->qkv + qd + kvd, m->attn, qd, rows, 0, 1, Hq, Hkv, D, nqkv, D, scale,
-                                    cf.attn_softcap));
+            int rc = vxp_prefill_f32(c, m->qkv, nqkv, m->qkv + qd, m->qkv + qd + kvd, nqkv, m->attn, qd, rows, Hq, Hkv, D, scale, cf.attn_softcap);
+            if (rc == VX_E_UNSUPPORTED)
+                rc = vxe_sdpa_strided(c, m->qkv, nqkv, m->qkv + qd, m->qkv + qd + kvd, m->attn, qd, rows, 0, 1, Hq, Hkv, D, nqkv, D, scale, cf.attn_softcap);
+            VX_TRY(rc);
         } else {
             const int wl = layer_slides(cf, l) ? 1 : 0;
             VxAttnArgs a{};

@@ -608,6 +608,152 @@ paged_prefill_mma_kernel(VxAttnArgs a, int row0, int n_rows) {
     }
 }
 
+// The first chunk of a prompt attends causally over its own freshly projected float32 K and V (runtime/block.go:891-895),
+// not over the fp16 cache.  Same tiling as above with the tiles built from the float32 rows: K and V are split into exact
+// fp16 hi + lo pairs on their way into shared memory and both products take three terms (hi*hi, lo*hi, hi*lo; the dropped
+// lo*lo term is 2^-22 relative), so the result matches the float32 arithmetic to rounding.
+template <int D>
+__global__ void __launch_bounds__(128)
+prefill_f32_mma_kernel(const float *__restrict__ q, int q_ld, const float *__restrict__ k, const float *__restrict__ v, long kv_ld,
+                       float *__restrict__ out, int out_ld, int n_rows, int n_q_heads, int n_kv_heads, float scale, float softcap) {
+    constexpr int KS = D / 16, ND = D / 8, ROW_B = D * 2, TILE_B = PF_TOK * ROW_B;
+    constexpr int CPR = D / 8;
+    extern __shared__ __align__(128) unsigned char pf_smem[];           // [K_hi | K_lo | V_hi | V_lo], one 64-token tile each
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+    const int h = blockIdx.y, kvh = h / (n_q_heads / n_kv_heads);
+    const int rt0 = blockIdx.x * PF_ROWS, rt1 = min(n_rows, rt0 + PF_ROWS);
+    const int rA = rt0 + warp * 16 + g, rB = rA + 8;
+    const bool vA = rA < rt1, vB = rB < rt1;
+    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(pf_smem);
+    const int t_end = rt1;                                                // causal: the last row sees tokens 0 .. rt1-1
+    const int lenA = vA ? rA + 1 : 0, lenB = vB ? rB + 1 : 0;
+
+    uint32_t qh[KS][4], ql[KS][4];
+    {
+        const float *qa = q + (size_t)(vA ? rA : rt0) * q_ld + (size_t)h * D, *qb = q + (size_t)(vB ? rB : rt0) * q_ld + (size_t)h * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            const float2 a0 = *reinterpret_cast<const float2 *>(qa + 16 * ks + 2 * c), a2 = *reinterpret_cast<const float2 *>(qa + 16 * ks + 2 * c + 8);
+            const float2 b0 = *reinterpret_cast<const float2 *>(qb + 16 * ks + 2 * c), b2 = *reinterpret_cast<const float2 *>(qb + 16 * ks + 2 * c + 8);
+            qh[ks][0] = pack_hi_lo(a0.x, a0.y, &ql[ks][0]); qh[ks][1] = pack_hi_lo(b0.x, b0.y, &ql[ks][1]);
+            qh[ks][2] = pack_hi_lo(a2.x, a2.y, &ql[ks][2]); qh[ks][3] = pack_hi_lo(b2.x, b2.y, &ql[ks][3]);
+        }
+    }
+    float acc[ND][4];
+#pragma unroll
+    for (int i = 0; i < ND; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+    float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
+
+    for (int t0 = 0; t0 < t_end; t0 += PF_TOK) {
+        // float32 rows -> fp16 hi / lo tiles (16-byte chunks of 8 dims, XOR-swizzled like the paged tiles)
+        for (int ci = threadIdx.x; ci < 2 * PF_TOK * CPR; ci += 128) {
+            const int isv = ci / (PF_TOK * CPR), r = ci % (PF_TOK * CPR), t = r / CPR, cc = r % CPR;
+            const int tok = t0 + t;
+            uint4 hi4 = make_uint4(0, 0, 0, 0), lo4 = hi4;
+            if (tok < t_end) {
+                const float *src = (isv ? v : k) + (size_t)tok * kv_ld + (size_t)kvh * D + cc * 8;
+                const float4 x0 = *reinterpret_cast<const float4 *>(src), x1 = *reinterpret_cast<const float4 *>(src + 4);
+                hi4.x = pack_hi_lo(x0.x, x0.y, &lo4.x); hi4.y = pack_hi_lo(x0.z, x0.w, &lo4.y);
+                hi4.z = pack_hi_lo(x1.x, x1.y, &lo4.z); hi4.w = pack_hi_lo(x1.z, x1.w, &lo4.w);
+            }
+            const uint32_t so = isv * 2 * TILE_B + t * ROW_B + ((cc ^ (t & 7)) << 4);
+            *reinterpret_cast<uint4 *>(pf_smem + so) = hi4;
+            *reinterpret_cast<uint4 *>(pf_smem + so + TILE_B) = lo4;
+        }
+        __syncthreads();
+        const uint32_t kh_s = sbase, kl_s = sbase + TILE_B, vh_s = sbase + 2 * TILE_B, vl_s = sbase + 3 * TILE_B;
+        float st[PF_TOK / 8][4];
+#pragma unroll
+        for (int j = 0; j < PF_TOK / 8; j++) { st[j][0] = st[j][1] = st[j][2] = st[j][3] = 0.f; }
+        {
+            const int mj = lane >> 3;
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++)
+#pragma unroll
+                for (int j = 0; j < PF_TOK / 8; j += 2) {
+                    const int t = 8 * (j + (mj >> 1)) + (lane & 7);
+                    const uint32_t off = t * ROW_B + (((2 * ks + (mj & 1)) ^ (t & 7)) << 4);
+                    uint32_t kf[4], kg[4];
+                    ldsm_x4(kf, kh_s + off); ldsm_x4(kg, kl_s + off);
+                    mma_16816(st[j], qh[ks], kf[0], kf[1]); mma_16816(st[j], ql[ks], kf[0], kf[1]); mma_16816(st[j], qh[ks], kg[0], kg[1]);
+                    mma_16816(st[j + 1], qh[ks], kf[2], kf[3]); mma_16816(st[j + 1], ql[ks], kf[2], kf[3]); mma_16816(st[j + 1], qh[ks], kg[2], kg[3]);
+                }
+        }
+        float mxA = -INFINITY, mxB = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < PF_TOK / 8; j++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int tok = t0 + 8 * j + 2 * c + e;
+                float va = st[j][e] * scale, vb = st[j][2 + e] * scale;
+                if (softcap > 0.f) { va = softcap * tanhf(va / softcap); vb = softcap * tanhf(vb / softcap); }
+                va = tok < lenA ? va : -INFINITY; vb = tok < lenB ? vb : -INFINITY;
+                st[j][e] = va; st[j][2 + e] = vb;
+                mxA = fmaxf(mxA, va); mxB = fmaxf(mxB, vb);
+            }
+        mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1)); mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+        mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1)); mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+        const float nA = fmaxf(mA, mxA), nB = fmaxf(mB, mxB);
+        const float uA = nA == -INFINITY ? 0.f : nA, uB = nB == -INFINITY ? 0.f : nB;
+        const float cA = __expf(mA - uA), cB = __expf(mB - uB);
+        mA = nA; mB = nB; lA *= cA; lB *= cB;
+#pragma unroll
+        for (int i = 0; i < ND; i++) { acc[i][0] *= cA; acc[i][1] *= cA; acc[i][2] *= cB; acc[i][3] *= cB; }
+#pragma unroll
+        for (int kt = 0; kt < PF_TOK / 16; kt++) {
+            uint32_t ph[4], pl[4];
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                const int j = 2 * kt + half;
+                const float p0 = st[j][0] == -INFINITY ? 0.f : __expf(st[j][0] - uA), p1 = st[j][1] == -INFINITY ? 0.f : __expf(st[j][1] - uA);
+                const float p2 = st[j][2] == -INFINITY ? 0.f : __expf(st[j][2] - uB), p3 = st[j][3] == -INFINITY ? 0.f : __expf(st[j][3] - uB);
+                lA += p0 + p1; lB += p2 + p3;
+                ph[2 * half] = pack_hi_lo(p0, p1, &pl[2 * half]);
+                ph[2 * half + 1] = pack_hi_lo(p2, p3, &pl[2 * half + 1]);
+            }
+            const int mj = lane >> 3, t = 16 * kt + 8 * (mj & 1) + (lane & 7);
+#pragma unroll
+            for (int nd = 0; nd < ND; nd += 2) {
+                const uint32_t off = t * ROW_B + (((nd + (mj >> 1)) ^ (t & 7)) << 4);
+                uint32_t vf[4], vg[4];
+                ldsm_x4_t(vf, vh_s + off); ldsm_x4_t(vg, vl_s + off);
+                mma_16816(acc[nd], ph, vf[0], vf[1]); mma_16816(acc[nd], pl, vf[0], vf[1]); mma_16816(acc[nd], ph, vg[0], vg[1]);
+                mma_16816(acc[nd + 1], ph, vf[2], vf[3]); mma_16816(acc[nd + 1], pl, vf[2], vf[3]); mma_16816(acc[nd + 1], ph, vg[2], vg[3]);
+            }
+        }
+        __syncthreads();
+    }
+    lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    const float iA = lA > 0.f ? 1.0f / lA : 0.f, iB = lB > 0.f ? 1.0f / lB : 0.f;
+#pragma unroll
+    for (int nd = 0; nd < ND; nd++) {
+        if (vA) *reinterpret_cast<float2 *>(out + (size_t)rA * out_ld + (size_t)h * D + 8 * nd + 2 * c) = make_float2(acc[nd][0] * iA, acc[nd][1] * iA);
+        if (vB) *reinterpret_cast<float2 *>(out + (size_t)rB * out_ld + (size_t)h * D + 8 * nd + 2 * c) = make_float2(acc[nd][2] * iB, acc[nd][3] * iB);
+    }
+}
+
+// causal attention of n_rows query rows over their own float32 K / V rows (row stride kv_ld floats, kv head h at h * D);
+// VX_E_UNSUPPORTED when the shape has no such kernel
+int vxp_prefill_f32(vx_ctx *c, const float *q, int q_ld, const float *k, const float *v, long kv_ld, float *out, int out_ld, int n_rows,
+                    int hq, int hkv, int d, float scale, float softcap) {
+    if (!((d == 64 || d == 128) && n_rows >= 16 && q_ld % 4 == 0 && kv_ld % 4 == 0 && out_ld % 2 == 0 && hkv > 0 && hq % hkv == 0)) return VX_E_UNSUPPORTED;
+    if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) != 0) return VX_E_UNSUPPORTED;
+    dim3 grid(ceil_div(n_rows, PF_ROWS), hq);
+    const int smem = 4 * PF_TOK * d * 2;
+    if (d == 64) {
+        static bool done = false;
+        if (!done) { VX_CUDA(c, cudaFuncSetAttribute(prefill_f32_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); done = true; }
+        prefill_f32_mma_kernel<64><<<grid, 128, smem, c->stream>>>(q, q_ld, k, v, kv_ld, out, out_ld, n_rows, hq, hkv, scale, softcap);
+    } else {
+        static bool done = false;
+        if (!done) { VX_CUDA(c, cudaFuncSetAttribute(prefill_f32_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); done = true; }
+        prefill_f32_mma_kernel<128><<<grid, 128, smem, c->stream>>>(q, q_ld, k, v, kv_ld, out, out_ld, n_rows, hq, hkv, scale, softcap);
+    }
+    VX_LAUNCH_CHECK(c);
+    return VX_OK;
+}
+
 // rows [row0, row0 + n_rows) belong to one sequence, in position order; f16 pool, 16-token pages, head_dim 64 or 128
 int vxp_prefill_rows(vx_ctx *c, const VxAttnArgs &a, int row0, int n_rows) {
     const int D = a.head_dim;
