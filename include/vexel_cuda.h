@@ -264,6 +264,8 @@ int vx_model_weight_bytes(vx_model *m, uint64_t *bytes);
 /* activation terms fed to the tensor cores by the projections: 2 = fp16 hi+lo split (float32-faithful,
  * default), 1 = single fp16 (half the MMA work, ~2e-4 relative rounding per projection) */
 int vx_set_gemm_terms(int terms);
+/* steps of a recurring shape are replayed from CUDA graphs (default on; 0 = launch every kernel individually) */
+int vx_set_graphs(int enable);
 /* failure-path self-test: a kernel waits, with a limit of limit_us microseconds, on a barrier that is never signalled; it
  * must return (reached_end = 1) and the next vx_sync must report VX_E_TIMEOUT while the context stays usable.  This is
  * how every device-side wait of the library behaves when its peer never shows up; no counterpart in the reference. */

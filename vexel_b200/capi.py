@@ -102,6 +102,7 @@ SIGNATURES = {
     "vx_model_kernel_time": [_vp, _i, _i, C.POINTER(_f), C.POINTER(_u64)],
     "vx_synth_kquant": [_vp, _D, _i, _i64, _u64, _f],
     "vx_selftest_bounded_wait": [_vp, _i, C.POINTER(_i)],
+    "vx_set_graphs": [_i],
     "vx_synth_q4_0": [_vp, _D, _i64, _u64, _f],
     "vx_synth_kquant": [_vp, _D, _i, _i64, _u64, _f],
     "vx_pool_shuffle_free_list": [_vp, C.c_uint32], "vx_model_weight_bytes": [_vp, C.POINTER(_u64)],

@@ -12,6 +12,8 @@
 #include <cooperative_groups.h>
 
 #include <algorithm>
+#include <map>
+#include <tuple>
 
 #include "vx_paged.cuh"
 
@@ -65,6 +67,16 @@ struct vx_model {
     float *capture = nullptr; bool capture_on = false; int capture_rows = 0;
     int last_rows = 0, last_seqs = 0;
     uint64_t steps = 0;
+    // CUDA graphs of whole steps, keyed by everything that shapes the launches (see enqueue_step)
+    struct GraphKey {
+        int n_seqs, rows, logit_rows, chunk0, chunk1, nw0, nw1;
+        bool operator<(const GraphKey &o) const {
+            return std::tie(n_seqs, rows, logit_rows, chunk0, chunk1, nw0, nw1) < std::tie(o.n_seqs, o.rows, o.logit_rows, o.chunk0, o.chunk1, o.nw0, o.nw1);
+        }
+    };
+    struct GraphEntry { cudaGraphExec_t exec = nullptr; int seen = 0; uint64_t launches = 0; };
+    std::map<GraphKey, GraphEntry> graphs;
+    uint64_t graph_replays = 0;
     int32_t *d_run_out = nullptr; size_t run_out_cap = 0;
     // kernel timing
     bool time_on[2] = {false, false}; float time_ms[2] = {0, 0}; uint64_t time_n[2] = {0, 0};
@@ -767,9 +779,11 @@ int plan_step(vx_model *m, int n_seqs, const int *slots, const int32_t *position
 }
 
 // Device half: packing kernel + the transformer stack, reading the step description already in d_step_in.
-int enqueue_step(vx_model *m, const StepPlan &p, int mode, int logit_rows) {
+static int g_graphs = 1;
+
+// pack kernel + the transformer stack for one planned step; n_work = grid sizes of the attention kernels
+int enqueue_kernels(vx_model *m, const StepPlan &p, int mode, int logit_rows, int n_work[2]) {
     vx_ctx *c = m->c; const vx_model_config &cf = m->cfg;
-    m->last_rows = p.rows; m->last_seqs = p.n_seqs;
     PackArgs pa{};
     pa.step_in = m->d_step_in; pa.n_seqs = p.n_seqs; pa.n_rows = p.rows;
     pa.tables = m->d_tables; pa.width = cf.max_blocks_per_seq; pa.seq_len = m->d_seq_len; pa.n_blocks = m->d_n_blocks;
@@ -780,9 +794,50 @@ int enqueue_step(vx_model *m, const StepPlan &p, int mode, int logit_rows) {
     pa.n_work0 = m->d_n_work[0]; pa.n_work1 = m->d_n_work[1]; pa.chunk0 = p.chunk[0]; pa.chunk1 = p.chunk[1]; pa.max_work = MAX_WORK;
     pack_kernel<<<1, 1024, 0, c->stream>>>(pa);
     VX_LAUNCH_CHECK(c);
+    return forward(m, p.rows, mode, n_work, p.chunk, logit_rows);
+}
+
+// A decode step is ~250-330 small launches, and a thin batch is bound by the host's launch rate rather than by the GPU.
+// Steps of the same shape are therefore replayed from a CUDA graph.  The key holds everything that shapes the launches:
+// sequence and row counts, the split-K chunk sizes, and the attention grids rounded up to a multiple of 32 work items
+// (CTAs beyond the device-side count return at once), so that a key survives many steps while the contexts grow.
+// The first step of a key runs eagerly (it also makes every lazy allocation and attribute call), the second is captured.
+int enqueue_step(vx_model *m, const StepPlan &p, int mode, int logit_rows) {
+    vx_ctx *c = m->c;
+    m->last_rows = p.rows; m->last_seqs = p.n_seqs;
     if (m->capture_on) m->capture_rows = p.rows;
     int n_work[2] = {p.n_work[0], p.n_work[1]};
-    VX_TRY(forward(m, p.rows, mode, n_work, p.chunk, logit_rows));
+    const bool can_graph = g_graphs && mode == 0 && !m->capture_on && !m->time_on[0] && !m->time_on[1];
+    if (can_graph) {
+        for (int i = 0; i < 2; i++) if (n_work[i] > 0) n_work[i] = std::min(MAX_WORK, (n_work[i] + 31) / 32 * 32);
+        const vx_model::GraphKey key{p.n_seqs, p.rows, logit_rows, p.chunk[0], p.chunk[1], n_work[0], n_work[1]};
+        if (m->graphs.size() > 256) {                    // shapes no longer in use: start over rather than grow without bound
+            for (auto &kv : m->graphs) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+            m->graphs.clear();
+        }
+        vx_model::GraphEntry &e = m->graphs[key];
+        if (!e.exec && e.seen >= 1 && e.seen < 1000000) {
+            const uint64_t l0 = c->launches;
+            cudaGraph_t g = nullptr;
+            bool ok = cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeRelaxed) == cudaSuccess;
+            int rc = ok ? enqueue_kernels(m, p, mode, logit_rows, n_work) : VX_OK;
+            if (ok) ok = cudaStreamEndCapture(c->stream, &g) == cudaSuccess && g != nullptr && rc == VX_OK;
+            if (ok) ok = cudaGraphInstantiate(&e.exec, g, 0) == cudaSuccess;
+            if (g) cudaGraphDestroy(g);
+            e.launches = c->launches - l0;
+            c->launches = l0;                            // nothing ran while capturing
+            if (!ok) { cudaGetLastError(); e.exec = nullptr; e.seen = 1000000; }     // this shape stays eager
+        }
+        if (e.exec) {
+            VX_CUDA(c, cudaGraphLaunch(e.exec, c->stream));
+            c->launches += e.launches;
+            m->graph_replays++;
+            m->steps++;
+            return VX_OK;
+        }
+        if (e.seen < 1000000) e.seen++;
+    }
+    VX_TRY(enqueue_kernels(m, p, mode, logit_rows, n_work));
     m->steps++;
     return VX_OK;
 }
@@ -933,6 +988,7 @@ int vx_model_destroy(vx_model *m) {
     if (m->h_out_tok) cudaFreeHost(m->h_out_tok);
     if (m->d_run_out) cudaFree(m->d_run_out);
     for (auto e : m->ev_pool) cudaEventDestroy(e);
+    for (auto &kv : m->graphs) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
     delete m;
     return VX_OK;
 }
@@ -1382,6 +1438,8 @@ int vx_model_kernel_time(vx_model *m, int which, int enable, float *ms, uint64_t
     }
     return VX_OK;
 }
+
+int vx_set_graphs(int enable) { g_graphs = enable != 0; return VX_OK; }
 
 int vx_model_max_blocks(vx_model *m) { return m ? m->cfg.max_blocks : 0; }
 
