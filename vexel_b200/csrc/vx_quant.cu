@@ -332,7 +332,7 @@ struct GemmW { const uint4 *qs; const void *sc; const void *aux; const uint2 *hi
 //   Q6_K  y += fl(d*sc_u) * S_u                         S_u = sum (q-32)*x over a 16-weight sub-block (dequant.go:272-331)
 // grid: (ceil(N/128), split_k, ceil(M / (8*NT))).  out layout: [split][M][ld_out]
 template <int FMT, int NT, int TERMS>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, NT == 1 ? 3 : 2)
 gemm_quant_kernel(GemmW W, const __half *__restrict__ xh, const __half *__restrict__ xl, const float *__restrict__ xscale,
                   const float *__restrict__ xbsum, float *__restrict__ out, int M, int N, int k_groups, int groups_per_split,
                   int x_ld, int ld_out, size_t part_stride) {
