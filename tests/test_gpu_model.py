@@ -467,3 +467,39 @@ def test_chunked_prefill_over_the_paged_cache(be, kind):
         O.lib().vo_final_softcap(wl.ctypes.data, wl.size, spec.final_softcap)
     assert rel_l2(gl[0], wl[0]) < HIDDEN_TOL and int(out[0]) == O.argmax(wl[0])
     gm.close()
+
+
+def test_ragged_step_at_page_boundaries(be):
+    """One step over a ragged batch whose sequences sit just below, on and just above page boundaries (16-token pages), with
+    a multi-row entry in the middle, repeated so that every sequence crosses a boundary; then the error path: a step that
+    needs more blocks than the pool has is refused and leaves lengths and tables untouched (gpu_block_pool.go:200-204)."""
+    spec = small_llama(2)
+    om, gm = build_pair(be, spec, 31, max_blocks=14, max_seqs=8, max_batch_tokens=64, max_blocks_per_seq=8)   # 13 blocks in use at the end
+    rng = np.random.default_rng(14)
+    lens = {1: 1, 2: 15, 3: 16, 4: 17, 5: 31, 6: 32}
+    for s, n in lens.items():
+        p = rng.integers(0, spec.vocab, n).astype(np.int32)
+        om.forward(s, p, 0); gm.prefill(s, p, 0)
+    for step in range(3):
+        ids = sorted(lens)
+        q_lens = [1, 1, 3, 1, 1, 1]                                  # sequence 3 verifies three tokens at once
+        toks = [rng.integers(0, spec.vocab, q).astype(np.int32) for q in q_lens]
+        out, logits = gm.decode_step(ids, np.concatenate(toks), [lens[s] for s in ids], q_lens=q_lens, want_logits=True)
+        row = 0
+        for s, q, t in zip(ids, q_lens, toks):
+            w = om.forward(s, t, lens[s], all_logits=True)
+            assert rel_l2(logits[row:row + q], w) < HIDDEN_TOL, (step, s)
+            assert [int(x) for x in out[row:row + q]] == [O.argmax(r) for r in w]
+            assert np.array_equal(gm.block_table(s), om.pool.table(0, s))
+            row += q; lens[s] += q
+    total, free, _ = gm.pool_stats()
+    before = {s: (gm.seq_len(s), gm.block_table(s).copy()) for s in lens}
+    with pytest.raises(capi.VxError) as ei:                          # 64 more tokens for one sequence need 4 blocks, one is free
+        gm.decode_step([1], rng.integers(0, spec.vocab, 64).astype(np.int32), [lens[1]], q_lens=[64])
+    assert ei.value.code == 4                                         # VX_E_OOM_BLOCKS
+    assert gm.pool_stats()[1] == free
+    for s in lens:
+        assert gm.seq_len(s) == before[s][0] and np.array_equal(gm.block_table(s), before[s][1])
+    out = gm.decode_step([2], [7], [lens[2]])                         # and the model still steps
+    assert int(out[0]) == O.argmax(om.forward(2, np.int32([7]), lens[2])[0])
+    gm.close()
