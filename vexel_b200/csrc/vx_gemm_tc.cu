@@ -461,15 +461,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     const int gabs = (kb_begin >> 1) + gi;
                     const uint2 sm8 = scq[gi];
                     const float2 dd = __half22float2(supq[gabs >> 1]);
+                    float ce[4];
 #pragma unroll
                     for (int u = 0; u < 4; u++) {
                         const float d1 = __fmul_rn(dd.x, (float)((sm8.x >> (8 * u)) & 0xFF)), dm = __fmul_rn(dd.y, (float)((sm8.y >> (8 * u)) & 0xFF));
-                        const float ce = fmaf(8.f, d1, -dm);
+                        ce[u] = fmaf(8.f, d1, -dm);
+                    }
 #pragma unroll
-                        for (int i = 0; i < CW; i++) {
-                            const int m = min(m0 + c0 + i, M - 1);
-                            sum[i] = fmaf(ce, aux.xbsum[(size_t)m * aux.bsum_ld + gabs * 4 + u], sum[i]);
-                        }
+                    for (int i = 0; i < CW; i++) {              // one 16-byte load brings the four sub-block sums of the group
+                        const int m = min(m0 + c0 + i, M - 1);
+                        const float4 bs = *reinterpret_cast<const float4 *>(aux.xbsum + (size_t)m * aux.bsum_ld + gabs * 4);
+                        sum[i] = fmaf(ce[0], bs.x, fmaf(ce[1], bs.y, fmaf(ce[2], bs.z, fmaf(ce[3], bs.w, sum[i]))));
                     }
                 }
             }
