@@ -577,9 +577,10 @@ int add_norm_split(vx_model *m, int rows, const float *parts, int n_parts, size_
 int act_split(vx_model *m, int rows, int n_parts) {
     const int F = m->cfg.ffn;
     const size_t pstride = (size_t)rows * 2 * F;
-    // cluster size: as many CTAs per row as keep the grid within about two waves of the GPU
+    // cluster size: a thin batch spreads each row over up to four SMs; from ~a third of the SMs in rows on, one CTA per row
+    // is faster (measured at 64 rows: 9 us alone against 12 us in clusters of four)
     int cl = 1;
-    while (cl < 4 && rows * cl * 2 <= 2 * m->c->sm_count && m->sp_f.k_pad > cl * VX_ROW_THREADS * 4) cl *= 2;
+    while (cl < 4 && rows * cl * 2 <= m->c->sm_count / 2 && m->sp_f.k_pad > cl * VX_ROW_THREADS * 4) cl *= 2;
     int nc = ceil_div(m->sp_f.k_pad, cl * VX_ROW_THREADS * 4);
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(rows * cl); lc.blockDim = dim3(VX_ROW_THREADS); lc.dynamicSmemBytes = 0; lc.stream = m->c->stream;

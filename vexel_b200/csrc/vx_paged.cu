@@ -781,25 +781,31 @@ int vxp_prefill_rows(vx_ctx *c, const VxAttnArgs &a, int row0, int n_rows) {
 // paged_merge_kernel + split_rows_kernel; nothing but the projection reads the attention output on that path.
 template <int NC>
 __global__ void __launch_bounds__(VX_ROW_THREADS) paged_merge_split_kernel(VxAttnArgs a, VxSplit s, int cols, int n_max) {
-    extern __shared__ float fw[];                  // [n_q_heads][n_max] normalised chunk weights
+    extern __shared__ float fw[];                  // [n_q_heads][n_max] normalised chunk weights, then [n_q_heads][n_max] chunk sums
     __shared__ float red[32];
     const int row = blockIdx.x, D = a.head_dim, Hq = a.n_q_heads;
     const int w0 = a.row_work_start[row], n = a.row_work_start[row + 1] - w0;
     if (n > 1) {
+        // chunk maxima and sums of all heads in one coalesced sweep, then one thread per head turns them into weights
+        float *ms = fw, *ls = fw + Hq * n_max;
+        for (int i = threadIdx.x; i < Hq * n; i += VX_ROW_THREADS) {
+            const int c = i / Hq, h = i % Hq;
+            const float *p0 = a.partials + ((size_t)(w0 + c) * Hq + h) * (D + 2) + D;
+            ms[h * n_max + c] = p0[0]; ls[h * n_max + c] = p0[1];
+        }
+        __syncthreads();
         for (int h = threadIdx.x; h < Hq; h += VX_ROW_THREADS) {
-            const float *p0 = a.partials + ((size_t)w0 * Hq + h) * (D + 2) + D;
-            const size_t cs = (size_t)Hq * (D + 2);
             float M = -INFINITY;
-            for (int c = 0; c < n; c++) M = fmaxf(M, p0[c * cs]);
+            for (int c = 0; c < n; c++) M = fmaxf(M, ms[h * n_max + c]);
             float L = 0.f;
             for (int c = 0; c < n; c++) {
-                const float mc = p0[c * cs];
+                const float mc = ms[h * n_max + c];
                 const float f = mc == -INFINITY ? 0.f : __expf(mc - M);
-                fw[h * n_max + c] = f;
-                L = fmaf(p0[c * cs + 1], f, L);
+                ms[h * n_max + c] = f;
+                L = fmaf(ls[h * n_max + c], f, L);
             }
             const float inv = L > 0.f ? 1.0f / L : 0.f;
-            for (int c = 0; c < n; c++) fw[h * n_max + c] *= inv;
+            for (int c = 0; c < n; c++) fw[h * n_max + c] = ms[h * n_max + c] * inv;
         }
         __syncthreads();
     }
@@ -900,7 +906,7 @@ int vxp_attention_split(vx_ctx *c, const VxAttnArgs &a, const VxSplit *split, in
         if (rc == 0) {
             VX_LAUNCH_CHECK(c);
             const int cols = a.n_q_heads * D;
-            const size_t fw_bytes = (size_t)a.n_q_heads * max(n_max_chunks, 1) * sizeof(float);
+            const size_t fw_bytes = 2 * (size_t)a.n_q_heads * max(n_max_chunks, 1) * sizeof(float);
             if (split && fused && n_max_chunks > 0 && fw_bytes <= 40 * 1024 && split->k_pad <= 8 * VX_ROW_THREADS * 4 && a.out_row_stride % 4 == 0) {
                 const int nc = ceil_div(split->k_pad, VX_ROW_THREADS * 4);
                 switch (nc) {
