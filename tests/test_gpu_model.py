@@ -503,3 +503,50 @@ def test_ragged_step_at_page_boundaries(be):
     out = gm.decode_step([2], [7], [lens[2]])                         # and the model still steps
     assert int(out[0]) == O.argmax(om.forward(2, np.int32([7]), lens[2])[0])
     gm.close()
+
+
+def test_sequence_calls_are_safe_against_a_running_step(be):
+    """AddSequence / RemoveSequence arrive from server goroutines while the scheduler loop steps (scheduler.go:645-698; the
+    reference guards the pool with a mutex, gpu_block_pool.go:46).  Here one thread decodes four sequences while another
+    creates, prefills and deletes other sequences through the same context; the decoded tokens must equal a quiet run."""
+    import threading
+    spec = small_llama(2)
+    _, gm = build_pair(be, spec, 41, max_blocks=128, max_seqs=16, max_blocks_per_seq=16, cpu=False)
+    rng = np.random.default_rng(15)
+    prompts = {s: rng.integers(0, spec.vocab, 10 + s).astype(np.int32) for s in (1, 2, 3, 4)}
+
+    def decode(ids, n_steps):
+        toks = np.array([gm.prefill(s, prompts[s], 0) for s in ids], np.int32)
+        pos = np.array([len(prompts[s]) for s in ids], np.int32)
+        hist = []
+        for _ in range(n_steps):
+            toks = gm.decode_step(ids, toks, pos); pos += 1; hist.append(toks.copy())
+        for s in ids:
+            gm.seq_delete(s)
+        return np.stack(hist)
+
+    quiet = decode([1, 2, 3, 4], 24)
+    errors, stop = [], threading.Event()
+
+    def churn():
+        r = np.random.default_rng(16)
+        i = 0
+        while not stop.is_set():
+            sid = 100 + (i % 8); i += 1
+            try:
+                gm.prefill(sid, r.integers(0, spec.vocab, int(r.integers(2, 40))).astype(np.int32), 0)
+                gm.decode_step([sid], [1], [gm.seq_len(sid)])
+                gm.seq_delete(sid)
+            except Exception as e:                                # noqa: BLE001
+                errors.append(e); return
+
+    t = threading.Thread(target=churn); t.start()
+    try:
+        busy = decode([1, 2, 3, 4], 24)
+    finally:
+        stop.set(); t.join()
+    assert not errors, errors
+    assert np.array_equal(quiet, busy)
+    total, free, _ = gm.pool_stats()
+    assert free == total
+    gm.close()
