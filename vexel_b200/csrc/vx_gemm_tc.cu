@@ -41,13 +41,22 @@ constexpr int TC_ST = 4;              // pipeline stages: activation tiles in sh
 constexpr int TC_ISSUERS = 2;         // MMA-issuing threads (one per warp), each with its own accumulator
 constexpr int TC_RAW = 4;             // ring of 128-weight nibble groups (each feeds two stages)
 constexpr int TC_DEQ = 512;           // dequantiser threads: (row, block of the stage, word pair)
-constexpr int TC_THREADS = TC_DEQ + 32 * (TC_ISSUERS + 1);
+constexpr int TC_THREADS = TC_DEQ + 32 * (TC_ISSUERS + 2);   // + TMA producer + helper warp (block sums of the Q4_K correction)
 constexpr int x_tile_bytes(int mt) { return mt * 128; }          // one fp16 activation tile (mt rows x 128 B)
 constexpr int stage_bytes(int mt) { return 2 * x_tile_bytes(mt); }   // x_hi rows followed by x_lo rows: one 2*mt-row K-major operand
 constexpr int issuers_of(int mt) { return mt == 64 ? 2 : 1; }    // a 128-row tile needs the whole accumulator space for one issuer
 constexpr int RAW_BYTES = TC_ROWS * 64;       // packed nibbles of one 128-weight group
 constexpr int RAWH_BYTES = TC_ROWS * 32;      // Q6_K only: the top two bits of the same group
-constexpr int smem_bytes(int mt) { return TC_ST * stage_bytes(mt) + TC_RAW * (RAW_BYTES + RAWH_BYTES) + 1024 /*alignment*/ + 512 /*barriers*/ + 512 /*row scales*/; }
+// Q4_K with 64-row batch tiles: the per-sub-block constants (8 d1 - dmin m) and the activations' block sums become two small
+// K-major fp16 operands (128-byte swizzled rows of 64 sub-blocks, hi and lo part each) so that the correction is a handful of
+// MMAs at the end of the K loop instead of 1024 FMAs per epilogue thread
+constexpr int CORR_U = 64;                                    // sub-blocks (K extent) of the correction operands
+constexpr int CORR_A_BYTES = TC_ROWS * 128;                   // one part of the constants: 128 weight rows x 64 halfs
+constexpr int CORR_B_BYTES = 64 * 128;                        // one part of the block sums: 64 batch rows x 64 halfs
+constexpr int corr_bytes(int fmt, int mt) { return (fmt == 1 && mt == 64) ? 2 * CORR_A_BYTES + 2 * CORR_B_BYTES : 0; }
+constexpr int smem_bytes(int fmt, int mt) {
+    return TC_ST * stage_bytes(mt) + TC_RAW * (RAW_BYTES + RAWH_BYTES) + corr_bytes(fmt, mt) + 1024 /*alignment*/ + 512 /*barriers*/ + 512 /*row scales*/;
+}
 enum { TC_Q4_0 = 0, TC_Q4_K = 1, TC_Q6_K = 2 };
 // what the block formats need beyond the nibble tiles: scales (Q4_0: half per block; K-quants: 8 bytes per 128-weight group),
 // super-block scales (Q4_K: half2 {d, dmin}; Q6_K: half d), and the activations' per-32-block sums for the Q4_K minima
@@ -141,6 +150,11 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
     asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
                  ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// both operands from shared memory
+__device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
                  ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
@@ -200,15 +214,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;            // operand tiles need 1024-byte alignment
     const uint32_t raw_base = base + TC_ST * STAGE_BYTES;
     const uint32_t rawh_base = raw_base + TC_RAW * RAW_BYTES;
-    const uint32_t bar_base = rawh_base + TC_RAW * RAWH_BYTES;
+    constexpr bool CORR = corr_bytes(FMT, MT) > 0;
+    const uint32_t corr_base = rawh_base + TC_RAW * RAWH_BYTES;          // [A_hi | A_lo | B_hi | B_lo], all 1024-byte aligned
+    const uint32_t bar_base = corr_base + corr_bytes(FMT, MT);
     unsigned char *gen_base = smem_raw + (base - smem_u32(smem_raw));
-    float *s_xscale = reinterpret_cast<float *>(gen_base + TC_ST * STAGE_BYTES + TC_RAW * (RAW_BYTES + RAWH_BYTES) + 512);
+    float *s_xscale = reinterpret_cast<float *>(gen_base + TC_ST * STAGE_BYTES + TC_RAW * (RAW_BYTES + RAWH_BYTES) + corr_bytes(FMT, MT) + 512);
+    unsigned char *corr_gen = gen_base + TC_ST * STAGE_BYTES + TC_RAW * (RAW_BYTES + RAWH_BYTES);
     auto xf_bar = [&](int s) { return bar_base + 8u * s; };                                 // activation tile landed
     auto af_bar = [&](int s) { return bar_base + 8u * (TC_ST + s); };                       // weight operand written
     auto e_bar = [&](int s) { return bar_base + 8u * (2 * TC_ST + s); };                    // stage consumed by every issuer's MMAs
     auto rawf_bar = [&](int s) { return bar_base + 8u * (3 * TC_ST + s); };                 // nibbles landed
     auto rawe_bar = [&](int s) { return bar_base + 8u * (3 * TC_ST + TC_RAW + s); };        // ... read by the dequantisers
     const uint32_t accum_bar = bar_base + 8u * (3 * TC_ST + 2 * TC_RAW);
+    const uint32_t corr_bar = accum_bar + 8u;                                                // block sums of the correction staged
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r0 = blockIdx.x * TC_ROWS, m0 = blockIdx.z * MT;
@@ -222,9 +240,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int s = 0; s < TC_ST; s++) { mbar_init(xf_bar(s), 1 + TC_DEQ / 64); mbar_init(af_bar(s), 1); mbar_init(e_bar(s), NISS); }   // one arrival per warp:
         for (int s = 0; s < TC_RAW; s++) { mbar_init(rawf_bar(s), 1); mbar_init(rawe_bar(s), TC_DEQ / 32); }   // 512 arrivals on one word serialise
         mbar_init(accum_bar, NISS);
+        mbar_init(corr_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < MT) s_xscale[tid] = m0 + tid < M ? xscale[m0 + tid] : 0.f;
+    // the tensor-core correction covers slices of up to CORR_U sub-blocks (32 stages); longer slices keep the epilogue loop
+    const bool corr_mma = CORR && n_kb * 2 <= CORR_U;
+    if (CORR) for (int i = tid; i < corr_bytes(FMT, MT) / 16; i += TC_THREADS) reinterpret_cast<uint4 *>(corr_gen)[i] = make_uint4(0, 0, 0, 0);
+    if (CORR) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (warp == TC_DEQ / 32) {   // the MMA warp owns the tensor-memory allocation
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -337,8 +360,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 __half2 dh[2], dl[2];
                 if (FMT == TC_Q4_K) {
                     const int u = 2 * grp + b;
-                    split_scale(__fmul_rn(dsup.x, (float)((s8.x >> (8 * u)) & 0xFF)), &dh[0], &dl[0]);       // dequant.go:369-372
+                    const float d1 = __fmul_rn(dsup.x, (float)((s8.x >> (8 * u)) & 0xFF));                  // dequant.go:369-372
+                    split_scale(d1, &dh[0], &dl[0]);
                     dh[1] = dh[0]; dl[1] = dl[0];
+                    if (CORR && corr_mma) {
+                        // constant of this sub-block, scaled by 2^10 to sit well inside the fp16 range (the block sums carry 2^-10)
+                        const float ce = fmaf(8.f, d1, -__fmul_rn(dsup.y, (float)((s8.y >> (8 * u)) & 0xFF))) * 1024.f;
+                        const __half ch = __float2half_rn(ce), cl = __float2half_rn(ce - __half2float(ch));
+                        const int ul = 2 * kb + b;                                 // sub-block index within the slice = K position
+                        const int off = row * 128 + (((ul >> 3) ^ (row & 7)) << 4) + (ul & 7) * 2;
+                        *reinterpret_cast<__half *>(corr_gen + off) = ch;
+                        *reinterpret_cast<__half *>(corr_gen + CORR_A_BYTES + off) = cl;
+                    }
                 } else {
                     const uint32_t sw = grp ? s8.y : s8.x;                        // int8 scales of sub-blocks 4 grp .. 4 grp + 3
                     split_scale(__fmul_rn(dsup.x, (float)(int)(signed char)((sw >> (16 * b)) & 0xFF)), &dh[0], &dl[0]);   // dequant.go:296-299
@@ -365,6 +398,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         }
                 tmem_st32(a_lane + 64 * as, hi, lo);       // columns 32 b .. +15 the hi parts of K=16 steps 2b, 2b+1, .. +31 their lo parts
                 s8 = s8n; dsup = dsn;
+                if (CORR) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the constants are read by the MMA unit
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
@@ -389,6 +423,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 tma_load_2d(dst, &map_xh, gkb * TC_BK, m0, xf_bar(xs));
                 tma_load_2d(dst + X_TILE, &map_xl, gkb * TC_BK, m0, xf_bar(xs));
             }
+        }
+    } else if (warp == TC_DEQ / 32 + TC_ISSUERS + 1) {
+        // ------------------------------------------------------------------ helper warp: the activations' 32-block sums of this
+        // slice as a K-major fp16 operand (hi and lo part, scaled by 2^-10), rows = batch rows, K = sub-blocks
+        if (CORR && corr_mma) {
+            const int U = n_kb * 2;
+            for (int i = lane; i < MT * U; i += 32) {
+                const int r = i / U, ul = i % U;
+                const int m = min(m0 + r, M - 1);
+                const float v = aux.xbsum[(size_t)m * aux.bsum_ld + (size_t)kb_begin * 2 + ul] * (1.0f / 1024.f);
+                const __half vh = __float2half_rn(v), vl = __float2half_rn(v - __half2float(vh));
+                const int off = r * 128 + (((ul >> 3) ^ (r & 7)) << 4) + (ul & 7) * 2;
+                *reinterpret_cast<__half *>(corr_gen + 2 * CORR_A_BYTES + off) = vh;
+                *reinterpret_cast<__half *>(corr_gen + 2 * CORR_A_BYTES + CORR_B_BYTES + off) = vl;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(corr_bar);
         }
     } else if (lane == 0 && warp < TC_DEQ / 32 + NISS) {
         // ------------------------------------------------------------------ MMA issue (one thread per issuer warp)
@@ -426,6 +478,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 umma_commit(e_bar(s));        // arrives when this issuer's MMAs have finished reading the stage
             }
         }
+        if (CORR && corr_mma && ok && j == 0) {
+            // every stage's "ready" barrier has been passed, so all constants are in place; wait for the block sums, then
+            // acc[:, 0:64] += C_hi B_hi + C_lo B_hi + C_hi B_lo over the slice's sub-blocks (K=16 per instruction)
+            ok = mbar_wait(corr_bar, 0, abort_flag);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t ah = umma_desc(corr_base), al = umma_desc(corr_base + CORR_A_BYTES);
+                const uint64_t bh = umma_desc(corr_base + 2 * CORR_A_BYTES), bl = umma_desc(corr_base + 2 * CORR_A_BYTES + CORR_B_BYTES);
+                const int steps = (n_kb * 2 + 15) / 16;
+                for (int k = 0; k < steps; k++) {
+                    umma_f16_ss(acc, ah + 2 * k, bh + 2 * k, umma_idesc(64), 1u);
+                    umma_f16_ss(acc, al + 2 * k, bh + 2 * k, umma_idesc(64), 1u);
+                    umma_f16_ss(acc, ah + 2 * k, bl + 2 * k, umma_idesc(64), 1u);
+                }
+            }
+        }
         if (ok) umma_commit(accum_bar);
     }
 
@@ -451,7 +519,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < 16; i++) sum[16 * cb + i] += __uint_as_float(v[i]);
                 }
-            if (FMT == TC_Q4_K) {
+            if (FMT == TC_Q4_K && !corr_mma) {
                 // plus sum over this slice's sub-blocks of (8 fl(d * sc_u) - fl(dmin * m_u)) * (sum of the activations of the sub-block)
                 // (dequant.go:369-392: w = d1 * q - dm1)
                 const int gn = min(n, N - 1);
@@ -552,12 +620,12 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
     if (x.k_pad != w.k_pad) return vx_fail(c, VX_E_BAD_ARG, "projection: activation row stride %d != weight k_pad %d", x.k_pad, w.k_pad);
     static bool attr_set = false;
     if (!attr_set) {
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_0, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(64)));
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_K, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(64)));
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q6_K, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(64)));
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_0, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(128)));
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_K, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(128)));
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q6_K, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(128)));
+        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_0, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(TC_Q4_0, 64)));
+        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_K, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(TC_Q4_K, 64)));
+        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q6_K, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(TC_Q6_K, 64)));
+        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_0, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(TC_Q4_0, 128)));
+        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_K, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(TC_Q4_K, 128)));
+        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q6_K, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(TC_Q6_K, 128)));
         attr_set = true;
     }
     // batches above 64 rows (prefill chunks, verify) take 128-row tiles: the MMA count per stage stays the same, so each
@@ -570,8 +638,11 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
     if (parts) {
         const int slots = c->sm_count;
         double best = 0.0;
+        // Q4_K with 64-row tiles: slices of at most 16 groups (32 stages) keep the minima correction on the tensor cores
+        const int s_min = (w.type == VX_T_Q4_K && mt == 64) ? min(8, ceil_div(k_groups, CORR_U / 4)) : 1;
         for (int s = 1; s <= 8 && s <= max(1, k_groups / 4); s++) {
             if ((size_t)s * m * w.n > parts_cap_floats) break;
+            if (s < s_min && (size_t)s_min * m * w.n <= parts_cap_floats) continue;
             int per = ceil_div(k_groups, s), s_eff = ceil_div(k_groups, per);
             long n_cta = (long)tiles * s_eff;
             double eff = (double)n_cta / (double)(ceil_div64(n_cta, slots) * slots) * ((double)k_groups / (double)(per * s_eff));
@@ -624,7 +695,7 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
     dim3 grid(ceil_div(w.n, TC_ROWS), split, ceil_div(m, mt));
     const TcAux aux{w.sc, w.aux, x.bsum, x.k_pad / 32};
     const size_t pstride = (size_t)m * w.n;
-#define VX_TC_LAUNCH(F, T) gemm_tc_kernel<F, T><<<grid, TC_THREADS, smem_bytes(T), c->stream>>>(map_w, map_h, map_xh, map_xl, aux, x.scale, dst, m, w.n, k_groups, per * 2, ld, pstride, err_flag)
+#define VX_TC_LAUNCH(F, T) gemm_tc_kernel<F, T><<<grid, TC_THREADS, smem_bytes(F, T), c->stream>>>(map_w, map_h, map_xh, map_xl, aux, x.scale, dst, m, w.n, k_groups, per * 2, ld, pstride, err_flag)
     if (mt == 64) {
         if (w.type == VX_T_Q4_0) VX_TC_LAUNCH(TC_Q4_0, 64); else if (w.type == VX_T_Q4_K) VX_TC_LAUNCH(TC_Q4_K, 64); else VX_TC_LAUNCH(TC_Q6_K, 64);
     } else {
