@@ -47,16 +47,18 @@ constexpr int stage_bytes(int mt) { return 2 * x_tile_bytes(mt); }   // x_hi row
 constexpr int issuers_of(int mt) { return mt == 64 ? 2 : 1; }    // a 128-row tile needs the whole accumulator space for one issuer
 constexpr int RAW_BYTES = TC_ROWS * 64;       // packed nibbles of one 128-weight group
 constexpr int RAWH_BYTES = TC_ROWS * 32;      // Q6_K only: the top two bits of the same group
-// Q4_K with 64-row batch tiles: the per-sub-block constants (8 d1 - dmin m) and the activations' block sums become two small
+// Q4_K: the per-sub-block constants (8 d1 - dmin m) and the activations' block sums become two small
 // K-major fp16 operands (128-byte swizzled rows of 64 sub-blocks, hi and lo part each) so that the correction is a handful of
 // MMAs at the end of the K loop instead of 1024 FMAs per epilogue thread
 constexpr int CORR_U = 64;                                    // sub-blocks (K extent) of the correction operands
 constexpr int CORR_A_BYTES = TC_ROWS * 128;                   // one part of the constants: 128 weight rows x 64 halfs
-constexpr int CORR_B_BYTES = 64 * 128;                        // one part of the block sums: 64 batch rows x 64 halfs
-constexpr int corr_bytes(int fmt, int mt) { return (fmt == 1 && mt == 64) ? 2 * CORR_A_BYTES + 2 * CORR_B_BYTES : 0; }
+constexpr int corr_b_bytes(int mt) { return mt * 128; }       // one part of the block sums: mt batch rows x 64 halfs
+constexpr int corr_bytes(int fmt, int mt) { return fmt == 1 ? 2 * CORR_A_BYTES + 2 * corr_b_bytes(mt) : 0; }
+constexpr int rawh_bytes(int fmt) { return fmt == 2 ? RAWH_BYTES : 0; }   // only Q6_K stages a second tile per group
 constexpr int smem_bytes(int fmt, int mt) {
-    return TC_ST * stage_bytes(mt) + TC_RAW * (RAW_BYTES + RAWH_BYTES) + corr_bytes(fmt, mt) + 1024 /*alignment*/ + 512 /*barriers*/ + 512 /*row scales*/;
+    return TC_ST * stage_bytes(mt) + TC_RAW * (RAW_BYTES + rawh_bytes(fmt)) + corr_bytes(fmt, mt) + 1024 /*alignment*/ + 512 /*barriers*/ + 512 /*row scales*/;
 }
+static_assert(smem_bytes(1, 128) <= 232448 && smem_bytes(2, 128) <= 232448, "shared memory budget of the 128-row variants");
 enum { TC_Q4_0 = 0, TC_Q4_K = 1, TC_Q6_K = 2 };
 // what the block formats need beyond the nibble tiles: scales (Q4_0: half per block; K-quants: 8 bytes per 128-weight group),
 // super-block scales (Q4_K: half2 {d, dmin}; Q6_K: half d), and the activations' per-32-block sums for the Q4_K minima
@@ -215,11 +217,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t raw_base = base + TC_ST * STAGE_BYTES;
     const uint32_t rawh_base = raw_base + TC_RAW * RAW_BYTES;
     constexpr bool CORR = corr_bytes(FMT, MT) > 0;
-    const uint32_t corr_base = rawh_base + TC_RAW * RAWH_BYTES;          // [A_hi | A_lo | B_hi | B_lo], all 1024-byte aligned
+    constexpr int CORR_B_BYTES = corr_b_bytes(MT);
+    const uint32_t corr_base = rawh_base + TC_RAW * rawh_bytes(FMT);     // [A_hi | A_lo | B_hi | B_lo], all 1024-byte aligned
     const uint32_t bar_base = corr_base + corr_bytes(FMT, MT);
     unsigned char *gen_base = smem_raw + (base - smem_u32(smem_raw));
-    float *s_xscale = reinterpret_cast<float *>(gen_base + TC_ST * STAGE_BYTES + TC_RAW * (RAW_BYTES + RAWH_BYTES) + corr_bytes(FMT, MT) + 512);
-    unsigned char *corr_gen = gen_base + TC_ST * STAGE_BYTES + TC_RAW * (RAW_BYTES + RAWH_BYTES);
+    float *s_xscale = reinterpret_cast<float *>(gen_base + TC_ST * STAGE_BYTES + TC_RAW * (RAW_BYTES + rawh_bytes(FMT)) + corr_bytes(FMT, MT) + 512);
+    unsigned char *corr_gen = gen_base + TC_ST * STAGE_BYTES + TC_RAW * (RAW_BYTES + rawh_bytes(FMT));
     auto xf_bar = [&](int s) { return bar_base + 8u * s; };                                 // activation tile landed
     auto af_bar = [&](int s) { return bar_base + 8u * (TC_ST + s); };                       // weight operand written
     auto e_bar = [&](int s) { return bar_base + 8u * (2 * TC_ST + s); };                    // stage consumed by every issuer's MMAs
@@ -480,7 +483,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         if (CORR && corr_mma && ok && j == 0) {
             // every stage's "ready" barrier has been passed, so all constants are in place; wait for the block sums, then
-            // acc[:, 0:64] += C_hi B_hi + C_lo B_hi + C_hi B_lo over the slice's sub-blocks (K=16 per instruction)
+            // acc[:, 0:MT] += C_hi B_hi + C_lo B_hi + C_hi B_lo over the slice's sub-blocks (K=16 per instruction)
             ok = mbar_wait(corr_bar, 0, abort_flag);
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -488,9 +491,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const uint64_t bh = umma_desc(corr_base + 2 * CORR_A_BYTES), bl = umma_desc(corr_base + 2 * CORR_A_BYTES + CORR_B_BYTES);
                 const int steps = (n_kb * 2 + 15) / 16;
                 for (int k = 0; k < steps; k++) {
-                    umma_f16_ss(acc, ah + 2 * k, bh + 2 * k, umma_idesc(64), 1u);
-                    umma_f16_ss(acc, al + 2 * k, bh + 2 * k, umma_idesc(64), 1u);
-                    umma_f16_ss(acc, ah + 2 * k, bl + 2 * k, umma_idesc(64), 1u);
+                    umma_f16_ss(acc, ah + 2 * k, bh + 2 * k, umma_idesc(MT), 1u);
+                    umma_f16_ss(acc, al + 2 * k, bh + 2 * k, umma_idesc(MT), 1u);
+                    umma_f16_ss(acc, ah + 2 * k, bl + 2 * k, umma_idesc(MT), 1u);
                 }
             }
         }
@@ -638,8 +641,8 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
     if (parts) {
         const int slots = c->sm_count;
         double best = 0.0;
-        // Q4_K with 64-row tiles: slices of at most 16 groups (32 stages) keep the minima correction on the tensor cores
-        const int s_min = (w.type == VX_T_Q4_K && mt == 64) ? min(8, ceil_div(k_groups, CORR_U / 4)) : 1;
+        // Q4_K: slices of at most 16 groups (32 stages) keep the minima correction on the tensor cores
+        const int s_min = w.type == VX_T_Q4_K ? min(8, ceil_div(k_groups, CORR_U / 4)) : 1;
         for (int s = 1; s <= 8 && s <= max(1, k_groups / 4); s++) {
             if ((size_t)s * m * w.n > parts_cap_floats) break;
             if (s < s_min && (size_t)s_min * m * w.n <= parts_cap_floats) continue;
