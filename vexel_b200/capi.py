@@ -106,7 +106,7 @@ SIGNATURES = {
     "vx_synth_q4_0": [_vp, _D, _i64, _u64, _f],
     "vx_synth_kquant": [_vp, _D, _i, _i64, _u64, _f],
     "vx_pool_shuffle_free_list": [_vp, C.c_uint32], "vx_model_weight_bytes": [_vp, C.POINTER(_u64)],
-    "vx_set_gemm_terms": [_i], "vx_set_tc_min_rows": [_i], "vx_model_max_blocks": [_vp],
+    "vx_set_gemm_terms": [_i], "vx_set_tc_min_rows": [_i], "vx_set_dependent_launch": [_i], "vx_model_max_blocks": [_vp],
     "vx_sched_create": [_vp, C.POINTER(SchedConfig), C.POINTER(_vp)], "vx_sched_destroy": [_vp],
     "vx_sched_add_sequence": [_vp, _i64, _vp, _i, _i], "vx_sched_remove_sequence": [_vp, _i64],
     "vx_sched_step": [_vp, C.POINTER(_i)], "vx_sched_poll": [_vp, _i64, _vp, _i, C.POINTER(_i), C.POINTER(_i)],

@@ -98,6 +98,25 @@ __device__ __forceinline__ float block_max(float v, float *red) {
     return r;
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------------
+// A kernel launched through vx_launch_dependent may start while its predecessor in the stream is still running: its CTAs
+// become resident as soon as every CTA of the predecessor has executed vx_pdl_trigger() (or exited).  Everything such a kernel
+// does before vx_pdl_wait() must be independent of the predecessor (barrier set-up, weight prefetch); vx_pdl_wait() returns
+// once the predecessor has completed and its writes are visible.  Both instructions are no-ops in a normal launch.
+__device__ __forceinline__ void vx_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void vx_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+extern int g_vx_pdl;     // 0 = plain stream order for every launch
+template <typename... KArgs, typename... Args>
+static inline cudaError_t vx_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = g_vx_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // ---- shared between translation units ---------------------------------------------------------
 // Activation rows prepared for the tensor-core projections: x = s * (hi + lo) with hi, lo fp16 and
 // s a power of two per row; element k is stored at position perm4(k) so that one 8-byte load gives

@@ -246,7 +246,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         mbar_init(corr_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (tid < MT) s_xscale[tid] = m0 + tid < M ? xscale[m0 + tid] : 0.f;
     // the tensor-core correction covers slices of up to CORR_U sub-blocks (32 stages); longer slices keep the epilogue loop
     const bool corr_mma = CORR && n_kb * 2 <= CORR_U;
     if (CORR) for (int i = tid; i < corr_bytes(FMT, MT) / 16; i += TC_THREADS) reinterpret_cast<uint4 *>(corr_gen)[i] = make_uint4(0, 0, 0, 0);
@@ -260,6 +259,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
     volatile int *abort_flag = &s_abort;
+    // Up to here nothing depended on the kernel before this one in the stream, and neither do the weights: the first two
+    // nibble tiles are requested before the wait for that kernel, whose tail then hides the set-up and the first DRAM latency.
+    constexpr int RAW_EARLY = 2;
+    if (warp == TC_DEQ / 32 + TC_ISSUERS && lane == 0) {
+        for (int g = 0; g < RAW_EARLY && 2 * g < n_kb; g++) {
+            mbar_arrive_expect_tx(rawf_bar(g), FMT == TC_Q6_K ? RAW_BYTES + RAWH_BYTES : RAW_BYTES);
+            tma_load_2d(raw_base + g * RAW_BYTES, &map_w, ((kb_begin >> 1) + g) * 64, r0, rawf_bar(g));
+            if (FMT == TC_Q6_K) tma_load_2d(rawh_base + g * RAWH_BYTES, &map_h, ((kb_begin >> 1) + g) * 32, r0, rawf_bar(g));
+        }
+    }
+    vx_pdl_wait();
+    if (tid < MT) s_xscale[tid] = m0 + tid < M ? xscale[m0 + tid] : 0.f;
+    __syncthreads();
 
     if (warp < TC_DEQ / 32) {
         // ------------------------------------------------------------------ dequantisers
@@ -413,7 +425,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (lane == 0) {
             for (int kb = 0; kb < n_kb; kb++) {
                 const int gkb = kb_begin + kb, xs = kb % TC_ST;
-                if ((kb & 1) == 0) {
+                if ((kb & 1) == 0 && (kb >> 1) >= RAW_EARLY) {
                     const int g = kb >> 1, slot = g % TC_RAW;
                     if (g >= TC_RAW && !mbar_wait(rawe_bar(slot), ((g / TC_RAW) - 1) & 1, abort_flag)) break;
                     mbar_arrive_expect_tx(rawf_bar(slot), FMT == TC_Q6_K ? RAW_BYTES + RAWH_BYTES : RAW_BYTES);
@@ -698,13 +710,15 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
     dim3 grid(ceil_div(w.n, TC_ROWS), split, ceil_div(m, mt));
     const TcAux aux{w.sc, w.aux, x.bsum, x.k_pad / 32};
     const size_t pstride = (size_t)m * w.n;
-#define VX_TC_LAUNCH(F, T) gemm_tc_kernel<F, T><<<grid, TC_THREADS, smem_bytes(F, T), c->stream>>>(map_w, map_h, map_xh, map_xl, aux, x.scale, dst, m, w.n, k_groups, per * 2, ld, pstride, err_flag)
+    cudaError_t le = cudaSuccess;
+#define VX_TC_LAUNCH(F, T) le = vx_launch_dependent(gemm_tc_kernel<F, T>, grid, dim3(TC_THREADS), (size_t)smem_bytes(F, T), c->stream, map_w, map_h, map_xh, map_xl, aux, (const float *)x.scale, dst, m, w.n, k_groups, per * 2, ld, pstride, err_flag)
     if (mt == 64) {
         if (w.type == VX_T_Q4_0) VX_TC_LAUNCH(TC_Q4_0, 64); else if (w.type == VX_T_Q4_K) VX_TC_LAUNCH(TC_Q4_K, 64); else VX_TC_LAUNCH(TC_Q6_K, 64);
     } else {
         if (w.type == VX_T_Q4_0) VX_TC_LAUNCH(TC_Q4_0, 128); else if (w.type == VX_T_Q4_K) VX_TC_LAUNCH(TC_Q4_K, 128); else VX_TC_LAUNCH(TC_Q6_K, 128);
     }
 #undef VX_TC_LAUNCH
+    if (le != cudaSuccess) return vx_cuda_fail(c, le, "projection launch");
     VX_LAUNCH_CHECK(c);
     return VX_OK;
 }

@@ -312,6 +312,7 @@ __global__ void __launch_bounds__(VX_ROW_THREADS)
 add_norm_split_kernel(float *x, const float *parts, int n_parts, size_t part_stride, int part_ld, const float *post_w, const float *w,
                       float eps, int hidden, VxSplit s, float *capture) {
     __shared__ float red[32];
+    vx_pdl_trigger();          // the projection that follows may become resident and fetch its first weights now
     const int r = blockIdx.x;
     float *xr = x + (size_t)r * hidden;
     float4 v[NC];
@@ -470,6 +471,7 @@ act_split_kernel(const float *__restrict__ h13, int n_parts, size_t part_stride,
     const int CL = (int)cluster.num_blocks(), q = (int)cluster.block_rank();
     __shared__ float red[32];
     __shared__ float cl_amax;
+    vx_pdl_trigger();          // the projection that follows may become resident and fetch its first weights now
     const int r = blockIdx.x / CL;
     const float *gr = h13 + (size_t)r * 2 * ffn, *ur = gr + ffn;
     float4 v[NC];

@@ -783,6 +783,7 @@ template <int NC>
 __global__ void __launch_bounds__(VX_ROW_THREADS) paged_merge_split_kernel(VxAttnArgs a, VxSplit s, int cols, int n_max) {
     extern __shared__ float fw[];                  // [n_q_heads][n_max] normalised chunk weights, then [n_q_heads][n_max] chunk sums
     __shared__ float red[32];
+    vx_pdl_trigger();          // the projection that follows may become resident and fetch its first weights now
     const int row = blockIdx.x, D = a.head_dim, Hq = a.n_q_heads;
     const int w0 = a.row_work_start[row], n = a.row_work_start[row + 1] - w0;
     if (n > 1) {

@@ -248,6 +248,7 @@ size_t vxq_split_bytes(int rows, int k, size_t *hi_off, size_t *lo_off, size_t *
 template <int NC>
 __global__ void __launch_bounds__(VX_ROW_THREADS) split_rows_kernel(const float *__restrict__ x, int cols, int ld, VxSplit s) {
     __shared__ float red[32];
+    vx_pdl_trigger();          // the projection that follows may become resident and fetch its first weights now
     const int row = blockIdx.x;
     const float *xr = x + (size_t)row * ld;
     float4 v[NC];
@@ -377,15 +378,17 @@ gemm_quant_kernel(GemmW W, const __half *__restrict__ xh, const __half *__restri
 #pragma unroll
         for (int i = 0; i < 4; i++) acc[t][i] = 0.f;
 
-#pragma unroll
-    for (int s = 0; s < GEMM_STAGES - 1; s++) {
-        if (s < n_iter) load_x(s, g_begin + s);
-        cp_async_commit();
-    }
+    // the first group's weights do not depend on the kernel before this one in the stream: request them before waiting for it
     uint4 wA = make_uint4(0, 0, 0, 0), wB = wA; uint2 dA = make_uint2(0, 0), dB = dA, eA = dA, eB = dA;
     if (n_iter > 0) {
         wA = __ldg(qA + (size_t)g_begin * 4); wB = __ldg(qB + (size_t)g_begin * 4); dA = __ldg(sA + g_begin); dB = __ldg(sB + g_begin);
         if (FMT == FMT_Q6_K) { eA = __ldg(hA + (size_t)g_begin * 4); eB = __ldg(hB + (size_t)g_begin * 4); }
+    }
+    vx_pdl_wait();
+#pragma unroll
+    for (int s = 0; s < GEMM_STAGES - 1; s++) {
+        if (s < n_iter) load_x(s, g_begin + s);
+        cp_async_commit();
     }
 
     for (int it = 0; it < n_iter; it++) {
@@ -534,7 +537,9 @@ static int gemm_launch_nt(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m,
     if (smem > 48 * 1024) VX_CUDA(c, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(ceil_div(w.n, GEMM_ROWS), split, ceil_div(m, MT));
     GemmW W{(const uint4 *)w.qs, w.sc, w.aux, (const uint2 *)w.hi};
-    kern<<<grid, 256, smem, c->stream>>>(W, x.hi, x.lo, x.scale, x.bsum, out, m, w.n, w.k_pad / 128, gps, x.k_pad, ld_out, part_stride);
+    cudaError_t le = vx_launch_dependent(kern, grid, dim3(256), smem, c->stream, W, (const __half *)x.hi, (const __half *)x.lo, (const float *)x.scale,
+                                         (const float *)x.bsum, out, m, w.n, w.k_pad / 128, gps, x.k_pad, ld_out, part_stride);
+    if (le != cudaSuccess) return vx_cuda_fail(c, le, "projection launch");
     VX_LAUNCH_CHECK(c);
     return VX_OK;
 }
@@ -553,6 +558,7 @@ static int gemm_launch_fmt(vx_ctx *c, int nt, int terms, const VxWeight &w, cons
 }
 
 static int g_gemm_terms = 2;   // 2: x = hi + lo (float32-faithful); 1: fp16 activations only
+int g_vx_pdl = 1;               // projections start under the tail of the kernel before them (programmatic dependent launch)
 static int g_tc_min_rows = 17;  // batches of at least this many rows use the tcgen05 kernel (0 = never)
 
 // out receives [m][ld_out] when *n_parts_out == 1, otherwise `parts` holds [n_parts][m][w.n]
@@ -729,6 +735,7 @@ int vx_matmul_q4_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, i
 int vx_matmul_q6_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k) { return matmul_quant(c, VX_T_Q6_K, a, b, out, m, n, k); }
 
 int vx_set_tc_min_rows(int rows) { g_tc_min_rows = rows; return VX_OK; }
+int vx_set_dependent_launch(int enable) { g_vx_pdl = enable != 0; return VX_OK; }
 int vx_set_gemm_terms(int terms) { if (terms == 1 || terms == 2) { g_gemm_terms = terms; return VX_OK; } return VX_E_BAD_ARG; }
 
 }  // extern "C"
