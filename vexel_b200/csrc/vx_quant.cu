@@ -300,6 +300,10 @@ __device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
     uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem));
 }
+__device__ __forceinline__ void cp_async8(void *smem, const void *gmem) {
+    uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(sa), "l"(gmem));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
@@ -312,7 +316,19 @@ __device__ __forceinline__ uint32_t nib2_to_half2(uint32_t v) {
 
 constexpr int GEMM_ROWS = 128;      // weight rows per CTA (8 warps x 16)
 constexpr int GEMM_XLD = 144;       // smem row stride in halfs: 128 + 16 keeps 8-byte fragment loads conflict-free
-constexpr int GEMM_STAGES = 3;
+// Depth of the cp.async ring (activation tile + the warps' weight words of one 128-weight group per stage).  Thin batches are
+// bound by how many weight bytes a CTA keeps in flight, so they get the deepest ring that still leaves three CTAs per SM.
+#ifndef VX_RING_MIN_NT
+#define VX_RING_MIN_NT 2
+#endif
+constexpr bool gemm_ring(int nt) { return nt >= VX_RING_MIN_NT; }      // 8-row tiles keep the next group's weights in registers instead
+constexpr int gemm_stages(int fmt, int nt) { return !gemm_ring(nt) ? 3 : nt == 1 ? (fmt == 2 ? 4 : 5) : nt == 2 ? 4 : nt == 4 ? (fmt == 2 ? 3 : 4) : 3; }
+constexpr int GEMM_W_BYTES = 8 * 64 * 16;     // per stage: 8 warps x (rows g and g + 8) x 32 lanes x 16 bytes of nibbles
+constexpr int GEMM_SC_BYTES = 8 * 16 * 8;     // 8 warps x 16 rows x 8 bytes of block / sub-block scales
+constexpr int gemm_h_bytes(int fmt) { return fmt == 2 ? 8 * 64 * 8 : 0; }   // Q6_K: the top two bits, 8 bytes per lane and row
+constexpr int gemm_stage_bytes(int fmt, int nt, int terms) {
+    return terms * 8 * nt * GEMM_XLD * 2 + (fmt == 1 ? 8 * nt * 16 : 0) + (gemm_ring(nt) ? GEMM_W_BYTES + GEMM_SC_BYTES + gemm_h_bytes(fmt) : 0);
+}
 
 // 6-bit variant of nib2_to_half2: v carries the low nibbles (bits 0-3, 16-19), h6 the top two bits already at bits 4-5 and
 // 20-21 -> half2 {q0 - 32, q1 - 32}, exact
@@ -340,7 +356,9 @@ gemm_quant_kernel(GemmW W, const __half *__restrict__ xh, const __half *__restri
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int MT = 8 * NT;
     constexpr int BS_FLOATS = FMT == FMT_Q4_K ? MT * 4 : 0;                 // per-32-block activation sums of the group
-    constexpr int STAGE_BYTES = TERMS * MT * GEMM_XLD * 2 + BS_FLOATS * 4;
+    constexpr int X_BYTES = TERMS * MT * GEMM_XLD * 2 + BS_FLOATS * 4;                  // activation part of a stage
+    constexpr int STAGE_BYTES = gemm_stage_bytes(FMT, NT, TERMS), GEMM_STAGES = gemm_stages(FMT, NT);
+    constexpr bool RING = gemm_ring(NT);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
     const int m0 = blockIdx.z * MT;
@@ -372,15 +390,37 @@ gemm_quant_kernel(GemmW W, const __half *__restrict__ xh, const __half *__restri
             }
     };
 
+    // the weight words of a group travel through the same ring: every lane copies the 16 bytes of its two rows (and lane c = 0
+    // the rows' 8 bytes of scales), so a CTA has GEMM_STAGES - 1 groups of weights in flight without holding them in registers
+    auto load_w = [&](int stage, int grp) {
+        unsigned char *st = smem_raw + (size_t)stage * STAGE_BYTES + X_BYTES;
+        cp_async16(st + (warp * 64 + lane) * 16, qA + (size_t)grp * 4);
+        cp_async16(st + (warp * 64 + 32 + lane) * 16, qB + (size_t)grp * 4);
+        if (c == 0) {
+            cp_async8(st + GEMM_W_BYTES + (warp * 16 + g) * 8, sA + grp);
+            cp_async8(st + GEMM_W_BYTES + (warp * 16 + 8 + g) * 8, sB + grp);
+        }
+        if (FMT == FMT_Q6_K) {
+            cp_async8(st + GEMM_W_BYTES + GEMM_SC_BYTES + (warp * 64 + lane) * 8, hA + (size_t)grp * 4);
+            cp_async8(st + GEMM_W_BYTES + GEMM_SC_BYTES + (warp * 64 + 32 + lane) * 8, hB + (size_t)grp * 4);
+        }
+    };
+
     float acc[NT][4];
 #pragma unroll
     for (int t = 0; t < NT; t++)
 #pragma unroll
         for (int i = 0; i < 4; i++) acc[t][i] = 0.f;
 
-    // the first group's weights do not depend on the kernel before this one in the stream: request them before waiting for it
+    // the weights do not depend on the kernel before this one in the stream: the ring's first groups are requested before the
+    // wait for that kernel (one commit group, older than every activation group)
     uint4 wA = make_uint4(0, 0, 0, 0), wB = wA; uint2 dA = make_uint2(0, 0), dB = dA, eA = dA, eB = dA;
-    if (n_iter > 0) {
+    if (RING) {
+#pragma unroll
+        for (int s = 0; s < GEMM_STAGES - 1; s++)
+            if (s < n_iter) load_w(s, g_begin + s);
+        cp_async_commit();
+    } else if (n_iter > 0) {
         wA = __ldg(qA + (size_t)g_begin * 4); wB = __ldg(qB + (size_t)g_begin * 4); dA = __ldg(sA + g_begin); dB = __ldg(sB + g_begin);
         if (FMT == FMT_Q6_K) { eA = __ldg(hA + (size_t)g_begin * 4); eB = __ldg(hB + (size_t)g_begin * 4); }
     }
@@ -394,7 +434,7 @@ gemm_quant_kernel(GemmW W, const __half *__restrict__ xh, const __half *__restri
     for (int it = 0; it < n_iter; it++) {
         const int grp = g_begin + it;
         uint4 nA = wA, nB = wB; uint2 ndA = dA, ndB = dB, neA = eA, neB = eB;
-        if (it + 1 < n_iter) {      // prefetch the next group's weights into registers
+        if (!RING && it + 1 < n_iter) {      // prefetch the next group's weights into registers
             nA = __ldg(qA + (size_t)(grp + 1) * 4); nB = __ldg(qB + (size_t)(grp + 1) * 4); ndA = __ldg(sA + grp + 1); ndB = __ldg(sB + grp + 1);
             if (FMT == FMT_Q6_K) { neA = __ldg(hA + (size_t)(grp + 1) * 4); neB = __ldg(hB + (size_t)(grp + 1) * 4); }
         }
@@ -410,11 +450,23 @@ gemm_quant_kernel(GemmW W, const __half *__restrict__ xh, const __half *__restri
         }
         cp_async_wait<GEMM_STAGES - 2>();
         __syncthreads();
-        if (it + GEMM_STAGES - 1 < n_iter) load_x((it + GEMM_STAGES - 1) % GEMM_STAGES, grp + GEMM_STAGES - 1);   // refill the freed stage
+        if (it + GEMM_STAGES - 1 < n_iter) {                 // refill the freed stage
+            if (RING) load_w((it + GEMM_STAGES - 1) % GEMM_STAGES, grp + GEMM_STAGES - 1);
+            load_x((it + GEMM_STAGES - 1) % GEMM_STAGES, grp + GEMM_STAGES - 1);
+        }
         cp_async_commit();
 
         const unsigned char *stp = smem_raw + (size_t)(it % GEMM_STAGES) * STAGE_BYTES;
         const __half *xst = reinterpret_cast<const __half *>(stp);
+        const unsigned char *wst = stp + X_BYTES;
+        if (RING) {
+            wA = *reinterpret_cast<const uint4 *>(wst + (warp * 64 + lane) * 16); wB = *reinterpret_cast<const uint4 *>(wst + (warp * 64 + 32 + lane) * 16);
+            dA = *reinterpret_cast<const uint2 *>(wst + GEMM_W_BYTES + (warp * 16 + g) * 8); dB = *reinterpret_cast<const uint2 *>(wst + GEMM_W_BYTES + (warp * 16 + 8 + g) * 8);
+            if (FMT == FMT_Q6_K) {
+                eA = *reinterpret_cast<const uint2 *>(wst + GEMM_W_BYTES + GEMM_SC_BYTES + (warp * 64 + lane) * 8);
+                eB = *reinterpret_cast<const uint2 *>(wst + GEMM_W_BYTES + GEMM_SC_BYTES + (warp * 64 + 32 + lane) * 8);
+            }
+        }
         const float *bss = reinterpret_cast<const float *>(stp + TERMS * MT * GEMM_XLD * 2);
         const uint32_t wa[4] = {wA.x, wA.y, wA.z, wA.w}, wb[4] = {wB.x, wB.y, wB.z, wB.w};
         const uint32_t da[2] = {dA.x, dA.y}, db[2] = {dB.x, dB.y};
@@ -508,7 +560,7 @@ gemm_quant_kernel(GemmW W, const __half *__restrict__ xh, const __half *__restri
                 }
             }
         }
-        wA = nA; wB = nB; dA = ndA; dB = ndB; eA = neA; eB = neB;
+        if (!RING) { wA = nA; wB = nB; dA = ndA; dB = ndB; eA = neA; eB = neB; }
     }
     cp_async_wait<0>();
 
@@ -532,7 +584,7 @@ template <int FMT, int NT, int TERMS>
 static int gemm_launch_nt(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int split,
                           int gps, size_t part_stride) {
     constexpr int MT = 8 * NT;
-    size_t smem = (size_t)GEMM_STAGES * (TERMS * MT * GEMM_XLD * sizeof(__half) + (FMT == FMT_Q4_K ? MT * 16 : 0));
+    size_t smem = (size_t)gemm_stages(FMT, NT) * gemm_stage_bytes(FMT, NT, TERMS);
     auto kern = gemm_quant_kernel<FMT, NT, TERMS>;
     if (smem > 48 * 1024) VX_CUDA(c, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(ceil_div(w.n, GEMM_ROWS), split, ceil_div(m, MT));
