@@ -651,20 +651,24 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
     const int mt = m > 64 ? 128 : 64;
     const int k_groups = w.k_pad / 128;
     const int tiles = ceil_div(w.n, TC_ROWS) * ceil_div(m, mt);
-    // split-K (in whole 128-weight groups) for whole waves of one CTA per SM
+    // split-K (in whole 128-weight groups).  Cost model in units of one pipeline stage: a CTA pays its stages plus a fixed
+    // set-up / drain / epilogue share (about eight stages' worth: the value was swept from 3 to 32 on three model shapes), CTAs run in waves of one per SM, and the
+    // partial sums cost their write and read (mostly L2).  The cheapest split wins, the smaller one on near-ties.
     int split = 1;
     if (parts) {
         const int slots = c->sm_count;
-        double best = 0.0;
+        constexpr double OVERHEAD_STAGES = 8.0, PART_STAGES_PER_FLOAT = 2.2e-6;
+        double best = 1e300;
         // Q4_K: slices of at most 16 groups (32 stages) keep the minima correction on the tensor cores
         const int s_min = w.type == VX_T_Q4_K ? min(8, ceil_div(k_groups, CORR_U / 4)) : 1;
         for (int s = 1; s <= 8 && s <= max(1, k_groups / 4); s++) {
             if ((size_t)s * m * w.n > parts_cap_floats) break;
             if (s < s_min && (size_t)s_min * m * w.n <= parts_cap_floats) continue;
-            int per = ceil_div(k_groups, s), s_eff = ceil_div(k_groups, per);
-            long n_cta = (long)tiles * s_eff;
-            double eff = (double)n_cta / (double)(ceil_div64(n_cta, slots) * slots) * ((double)k_groups / (double)(per * s_eff));
-            if (eff > best + 0.03) { best = eff; split = s; }
+            const int per = ceil_div(k_groups, s), s_eff = ceil_div(k_groups, per);
+            const long n_cta = (long)tiles * s_eff;
+            const double cost = (double)ceil_div64(n_cta, slots) * (2.0 * per + OVERHEAD_STAGES) +
+                                (s_eff > 1 ? PART_STAGES_PER_FLOAT * s_eff * (double)m * w.n : 0.0);
+            if (cost < best * 0.98) { best = cost; split = s; }
         }
     }
     int per = ceil_div(k_groups, split);
