@@ -76,7 +76,7 @@ struct vx_model {
     };
     struct GraphEntry { cudaGraphExec_t exec = nullptr; int seen = 0; uint64_t launches = 0; };
     std::map<GraphKey, GraphEntry> graphs;
-    uint64_t graph_replays = 0;
+    uint64_t graph_replays = 0, graph_updates = 0;
     int32_t *d_run_out = nullptr; size_t run_out_cap = 0;
     // kernel timing
     bool time_on[2] = {false, false}; float time_ms[2] = {0, 0}; uint64_t time_n[2] = {0, 0};
@@ -819,13 +819,28 @@ int enqueue_step(vx_model *m, const StepPlan &p, int mode, int logit_rows) {
             m->graphs.clear();
         }
         vx_model::GraphEntry &e = m->graphs[key];
-        if (!e.exec && e.seen >= 1 && e.seen < 1000000) {
+        // A key that differs from an instantiated one only in the attention grids (the contexts grew past a chunk boundary)
+        // takes that graph over: the step is captured again and the executable graph is updated in place, which costs a
+        // fraction of an eager step plus an instantiation.
+        vx_model::GraphEntry *sib = nullptr;
+        if (!e.exec && e.seen < 1000000)
+            for (auto &kv : m->graphs) {
+                const vx_model::GraphKey &k = kv.first;
+                if (kv.second.exec && k.n_seqs == key.n_seqs && k.rows == key.rows && k.logit_rows == key.logit_rows && k.chunk0 == key.chunk0 &&
+                    k.chunk1 == key.chunk1) { sib = &kv.second; break; }
+            }
+        if (!e.exec && (e.seen >= 1 || sib) && e.seen < 1000000) {
             const uint64_t l0 = c->launches;
             cudaGraph_t g = nullptr;
             bool ok = cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeRelaxed) == cudaSuccess;
             int rc = ok ? enqueue_kernels(m, p, mode, logit_rows, n_work) : VX_OK;
             if (ok) ok = cudaStreamEndCapture(c->stream, &g) == cudaSuccess && g != nullptr && rc == VX_OK;
-            if (ok) ok = cudaGraphInstantiate(&e.exec, g, 0) == cudaSuccess;
+            if (ok && sib) {
+                cudaGraphExecUpdateResultInfo info;
+                if (cudaGraphExecUpdate(sib->exec, g, &info) == cudaSuccess) { e.exec = sib->exec; sib->exec = nullptr; sib->seen = 1; m->graph_updates++; }
+                else { cudaGetLastError(); cudaGraphExecDestroy(sib->exec); sib->exec = nullptr; sib->seen = 1; }   // not updatable (a kernel changed): instantiate below
+            }
+            if (ok && !e.exec) ok = cudaGraphInstantiate(&e.exec, g, 0) == cudaSuccess;
             if (g) cudaGraphDestroy(g);
             e.launches = c->launches - l0;
             c->launches = l0;                            // nothing ran while capturing
