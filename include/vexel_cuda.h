@@ -247,6 +247,9 @@ int vx_model_get_packing(vx_model *m, int32_t *cu_seqlens, int32_t *slot_mapping
                          int n_seqs, int n_rows);
 /* counters: kernels launched and steps run since creation */
 int vx_model_counters(vx_model *m, uint64_t *kernel_launches, uint64_t *steps);
+/* steps replayed from a CUDA graph so far, and how many times an executable graph was taken over by in-place update
+ * because only the attention grids had changed */
+int vx_model_graph_stats(vx_model *m, uint64_t *replays, uint64_t *takeovers);
 /* timing of the dominant kernel class inside vx_decode_step (CUDA events on the context's stream):
  * which: 0 = paged attention, 1 = quantised projections.  Returns accumulated ms and launch count. */
 int vx_model_kernel_time(vx_model *m, int which, int enable, float *ms, uint64_t *launches);

@@ -550,3 +550,39 @@ def test_sequence_calls_are_safe_against_a_running_step(be):
     total, free, _ = gm.pool_stats()
     assert free == total
     gm.close()
+
+
+def test_graph_replay_and_takeover_equal_eager_steps(be):
+    """Steps of a recurring shape are replayed from CUDA graphs, and when the contexts outgrow the attention grid of a graph
+    the executable graph is updated in place.  Forty sequences step from 56 to 80 tokens (the split-K chunk is four 16-token
+    pages, so every sequence gains a work item at 65 tokens and the rounded grid goes from 64 to 96 items); the tokens must
+    equal those of the same steps launched kernel by kernel after a rollback (TruncateSequence, gpu_block_pool.go:162-190)."""
+    spec = small_llama(2)
+    _, gm = build_pair(be, spec, 51, max_blocks=40 * 6 + 8, max_seqs=40, max_batch_tokens=64, max_blocks_per_seq=6, cpu=False)
+    rng = np.random.default_rng(16)
+    ids = list(range(1, 41))
+    first = []
+    for s in ids:
+        first.append(gm.prefill(s, rng.integers(0, spec.vocab, 56).astype(np.int32), 0))
+
+    def run():
+        toks, lens, outs = np.int32(first), [56] * 40, []
+        for _ in range(24):
+            toks = np.int32(gm.decode_step(ids, toks, lens))
+            outs.append(toks.copy()); lens = [n + 1 for n in lens]
+        return np.stack(outs)
+
+    r0, t0 = gm.graph_stats()
+    with_graphs = run()
+    r1, t1 = gm.graph_stats()
+    assert r1 - r0 >= 18 and t1 - t0 >= 1, (r1 - r0, t1 - t0)       # most steps replayed, at least one takeover
+    for s in ids:
+        gm.seq_truncate(s, 56)
+    be.lib.vx_set_graphs(0)
+    try:
+        eager = run()
+        assert gm.graph_stats()[0] == r1
+    finally:
+        be.lib.vx_set_graphs(1)
+    assert np.array_equal(with_graphs, eager)
+    gm.close()

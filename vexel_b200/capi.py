@@ -99,6 +99,7 @@ SIGNATURES = {
     "vx_model_set_capture": [_vp, _i], "vx_model_get_capture": [_vp, _vp, _sz],
     "vx_model_get_packing": [_vp, _vp, _vp, _vp, _i, _i],
     "vx_model_counters": [_vp, C.POINTER(_u64), C.POINTER(_u64)],
+    "vx_model_graph_stats": [_vp, C.POINTER(_u64), C.POINTER(_u64)],
     "vx_model_kernel_time": [_vp, _i, _i, C.POINTER(_f), C.POINTER(_u64)],
     "vx_synth_kquant": [_vp, _D, _i, _i64, _u64, _f],
     "vx_selftest_bounded_wait": [_vp, _i, C.POINTER(_i)],
@@ -429,6 +430,9 @@ class Model:
 
     def counters(self):
         a, b = C.c_uint64(), C.c_uint64(); self._ck(self.lib.vx_model_counters(self.h, C.byref(a), C.byref(b))); return a.value, b.value
+
+    def graph_stats(self):
+        a, b = C.c_uint64(), C.c_uint64(); self._ck(self.lib.vx_model_graph_stats(self.h, C.byref(a), C.byref(b))); return a.value, b.value
 
     def kernel_time(self, which, enable=-1):
         ms, n = C.c_float(), C.c_uint64()

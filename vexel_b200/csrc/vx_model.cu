@@ -1445,6 +1445,13 @@ int vx_model_counters(vx_model *m, uint64_t *launches, uint64_t *steps) {
     return VX_OK;
 }
 
+int vx_model_graph_stats(vx_model *m, uint64_t *replays, uint64_t *takeovers) {
+    if (!m) return VX_E_BAD_ARG;
+    if (replays) *replays = m->graph_replays;
+    if (takeovers) *takeovers = m->graph_updates;
+    return VX_OK;
+}
+
 int vx_model_kernel_time(vx_model *m, int which, int enable, float *ms, uint64_t *launches) {
     if (!m || which < 0 || which > 1) return VX_E_BAD_ARG;
     VxGuard g(m->c);
