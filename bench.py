@@ -51,42 +51,6 @@ def measured_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
-def synth_weights_on_device(be, model, spec, seed):
-    """Random weights of the model's shape and block formats, generated by CUDA kernels straight into GGUF blocks (Q4_0 by the
-    benchmark's quantisation rule from N(0, sigma) draws; Q4_K / Q6_K as valid blocks with hashed payload).  The token
-    embedding is kept in Q4_0 for every workload: it is read B rows per step and is not part of the timed traffic."""
-    ones = np.ones(spec.hidden, np.float32)
-    proj_types, _, out_type = gs.tensor_types(spec)
-    per_elem = {capi.T_Q4_0: 18 / 32, capi.T_Q4_K: 144 / 256, capi.T_Q6_K: 210 / 256}
-    big = max(spec.vocab * spec.hidden, spec.ffn * spec.hidden)
-    d_tmp = be.AllocPermanent(int(big * max(per_elem.values())) + 256)
-    n_t = 0
-
-    def q(layer, slot, n, k, t):
-        nonlocal n_t
-        if t == capi.T_Q4_0:
-            be.SynthQ4_0(d_tmp, n * k, seed * 100003 + n_t, spec.sigma)
-        else:
-            be.SynthKQuant(d_tmp, t, n * k, seed * 100003 + n_t, spec.sigma)
-        model.set_tensor(layer, slot, t, (d_tmp, int(n * k * per_elem[t])))
-        n_t += 1
-
-    q(-1, capi.G_EMBED, spec.vocab, spec.hidden, capi.T_Q4_0)
-    for layer in range(spec.n_layers):
-        model.set_tensor(layer, capi.W_ATTN_NORM, capi.T_F32, ones)
-        model.set_tensor(layer, capi.W_FFN_NORM, capi.T_F32, ones)
-        if spec.post_norms:
-            model.set_tensor(layer, capi.W_POST_ATTN_NORM, capi.T_F32, ones)
-            model.set_tensor(layer, capi.W_POST_FFN_NORM, capi.T_F32, ones)
-        for slot in (capi.W_WQ, capi.W_WK, capi.W_WV, capi.W_WO, capi.W_W1, capi.W_W3, capi.W_W2):
-            n, k = gs.slot_shape(spec, slot)
-            q(layer, slot, n, k, proj_types[slot])
-    model.set_tensor(-1, capi.G_FINAL_NORM, capi.T_F32, ones)
-    q(-1, capi.G_OUTPUT, spec.vocab, spec.hidden, out_type)
-    be.Free(d_tmp)
-    model.finalize()
-
-
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -238,7 +202,7 @@ def trace_arm(args):
     kv_block_bytes = spec.kv_bytes_per_token() * 16
     max_blocks = int(min(120e9 // kv_block_bytes, 256 * (max_ctx // 16 + 2)))         # as much pool as ~120 GB allows; admission handles the rest
     model = capi.Model(be, gs.model_config(spec, max_blocks, max_seqs=256, max_batch_tokens=256, max_blocks_per_seq=max_ctx // 16 + 2))
-    synth_weights_on_device(be, model, spec, seed=0)
+    gs.synth_weights_on_device(be, model, spec, seed=0)
     res = tr.replay(model, arrivals, prompts, olen, max_batch=256)
     line = {"metric": "trace decode tok/s", "value": res["tok_per_s"], "unit": "tok/s", "n_gpus": 1, "higher_is_better": True, "data": "synthetic",
             "config": {"workload": f"{spec.name}: {args.trace} requests, Poisson {args.trace_rate}/s, prompts lognormal(ln 512, 0.8) clipped to "
@@ -316,7 +280,7 @@ def main():
     if args.no_graphs:
         be.lib.vx_set_graphs(0)
     model = capi.Model(be, gs.model_config(spec, max_blocks, max_seqs=B, max_batch_tokens=max(B, 8), max_blocks_per_seq=blocks_per_seq))
-    synth_weights_on_device(be, model, spec, seed=seeds["weights"])
+    gs.synth_weights_on_device(be, model, spec, seed=seeds["weights"])
     model.shuffle_free_list(seeds["free_list"])               # physical blocks shuffled randomly in the pool
     seqs = np.arange(1, B + 1, dtype=np.int64)
     for i, s in enumerate(seqs):

@@ -125,9 +125,11 @@ int vx_sdpa_paged_decode_multiquery(vx_ctx *, vx_dptr q, vx_dptr pool, vx_dptr b
 /* No counterpart in the reference.  vx_sdpa_paged_decode_f16 for callers that must not allocate while they attend (all
  * HBM already given to the KV pool, a latency-critical section, a non-reentrant allocator): the split-K scratch is a fixed
  * 4 MiB device array inside the library instead of the context's growable scratch, and the call makes no cudaMalloc /
- * cudaFree / host heap allocation.  Sizes beyond the array (see the definition) are refused with VX_E_BAD_ARG.  The first
- * call on a device resolves the array's address and should come before any stream capture; calls that overlap on the GPU
- * share the array and race. */
+ * cudaFree / host heap allocation.  Sizes beyond the array (see the definition; also n_blocks > 65536 or a block size above
+ * 16384) are refused with VX_E_BAD_ARG.  The first call on a device resolves the array's address and may make the driver
+ * load this library's kernels for that device, which is driver-side work that can allocate: make one warm-up call per
+ * device before the section that must not allocate, and before any stream capture.  Calls that overlap on the GPU share
+ * the array and race. */
 int vx_sdpa_paged_decode_f16_noalloc(vx_ctx *, vx_dptr q, vx_dptr pool, vx_dptr block_table_i32, vx_dptr out,
                                      int n_blocks, int block_size, int n_q_heads, int n_kv_heads, int head_dim,
                                      float scale, int tokens_in_last_block);
@@ -199,6 +201,9 @@ int vx_seq_len(vx_model *m, int64_t seq_id, int *out_len);
 int vx_seq_block_table(vx_model *m, int64_t seq_id, int32_t *out, int cap, int *out_n); /* device -> host copy */
 int vx_pool_stats(vx_model *m, int *total_blocks, int *free_blocks, int *shared_blocks);  /* BlockStats :610-625 */
 int vx_pool_layer_ptr(vx_model *m, int layer, vx_dptr *out, size_t *bytes);
+/* GPUBlockPool.freeList (runtime/gpu_block_pool.go:36, 200-219) as the stack it is, bottom first: the next block handed out
+ * is the last entry.  *n_out = number of free blocks per layer. */
+int vx_pool_free_list(vx_model *m, int32_t *out, int cap, int *n_out);
 /* test/bench helper: give a sequence `len` tokens of KV filled with deterministic f16 noise (no forward pass) */
 int vx_seq_fill_synthetic(vx_model *m, int64_t seq_id, int len, uint32_t seed);
 
@@ -218,6 +223,21 @@ int vx_sample_rows(vx_ctx *, vx_dptr logits, int rows, int n, const vx_sample_pa
 int vx_decode_step(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t *tokens,
                    const int32_t *positions, const int32_t *q_lens, int32_t *out_tokens,
                    float *logits);
+/* vx_decode_step with options, for the two callers the plain call cannot serve.
+ *  - Speculative verify with hidden states (VerifySpeculativeWithPagedKVAndHidden, runtime/decode.go:1446-1569): pass
+ *    `hidden` (host, [output rows, hidden] float32) to receive the post-final-norm hidden state of every output row
+ *    (decode.go:1543-1557), next to the logits.
+ *  - A scheduler step that mixes decoding sequences with prompt chunks (Scheduler.runDecodeStep + runBatchedPrefill,
+ *    scheduler/scheduler.go:245-303, 486-550, as ONE packed step): VX_STEP_PROMPT_ROWS makes multi-row entries prompt chunks
+ *    (PrefillWithPagedKV semantics, decode.go:961-1096: an entry that starts at position 0 attends over its fresh float32 K/V;
+ *    later chunks read the pages), VX_STEP_LAST_ROWS limits the outputs (tokens, logits, hidden, sampling records) to the last
+ *    row of every entry, n_seqs rows in batch order.
+ * params (optional): one sampling record per output row, as in vx_decode_step_sampled. */
+#define VX_STEP_LAST_ROWS 1
+#define VX_STEP_PROMPT_ROWS 2
+int vx_decode_step_ex(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t *tokens, const int32_t *positions,
+                      const int32_t *q_lens, int flags, const vx_sample_params *params, int32_t *out_tokens, float *logits,
+                      float *hidden);
 /* vx_prefill whose returned token is sampled (one record, for the last prompt position) */
 int vx_prefill_sampled(vx_model *m, int64_t seq_id, const int32_t *tokens, int n_tokens, int start_pos,
                        const vx_sample_params *params, int32_t *out_token, float *logits);
@@ -282,8 +302,11 @@ int vx_set_dependent_launch(int enable);
 
 /* ------------------------------------------------------------------ continuous-batching scheduler
  * The host loop of inference/scheduler (Scheduler.step / runDecodeStep, scheduler/scheduler.go:168-483; Sequence state
- * machine, scheduler/sequence.go:15-80) over vx_prefill / vx_decode_step, for embedders without the Go scheduler.  Greedy
- * sampling; the batch is formed in arrival order; a prompt that does not fit the free blocks waits. */
+ * machine, scheduler/sequence.go:15-80) over vx_decode_step_ex, for embedders without the Go scheduler.  Every iteration
+ * is ONE packed step: the decoding sequences plus the next chunk of each prompt being read, up to the model's
+ * max_batch_tokens.  The batch is formed in arrival order; a request is admitted when the pool can hold its prompt plus its
+ * token limit, waits otherwise (taking no batch slot), and is refused if it could never fit; requests without a limit
+ * reserve their prompt and may be preempted when the pool runs dry. */
 typedef struct vx_sched vx_sched;
 typedef struct {
     int max_batch_size;   /* Config.MaxBatchSize, scheduler.go:23 */
@@ -304,8 +327,14 @@ int vx_sched_destroy(vx_sched *s);
 int vx_sched_add_sequence(vx_sched *s, int64_t id, const int32_t *prompt, int n_prompt, int max_tokens);   /* AddSequence :645-676 */
 int vx_sched_remove_sequence(vx_sched *s, int64_t id);                                                     /* RemoveSequence :690-698 */
 int vx_sched_step(vx_sched *s, int *n_active_out);                                                         /* step :168-203 */
-int vx_sched_poll(vx_sched *s, int64_t id, int32_t *out, int cap, int *n_out, int *finished);              /* TokenChan drain */
+/* TokenChan drain (sequence.go:70-80).  *finished: 0 = still running, 1 = ended and drained, 2 = ended because the request
+ * was refused: its prompt plus token limit can never fit the block pool or one block table (where the reference stops its
+ * whole loop with an allocation error, scheduler.go:134-136).  Once an end has been reported the request is forgotten. */
+int vx_sched_poll(vx_sched *s, int64_t id, int32_t *out, int cap, int *n_out, int *finished);
 int vx_sched_get_metrics(vx_sched *s, vx_sched_metrics *out);                                                /* Metrics :475-481 */
+/* how many times a sequence was preempted to free blocks (its tokens are read again later), and how many requests were
+ * refused; no counterpart in the reference, whose loop ends on the first allocation failure */
+int vx_sched_get_pressure(vx_sched *s, uint64_t *preemptions, uint64_t *refused);
 int vx_model_max_blocks(vx_model *m);   /* physical blocks per layer of the model's pool */
 
 #ifdef __cplusplus

@@ -55,6 +55,7 @@ def lib():
             "vo_pool_store_kv": (i32, [vp, i32, i64, i32, vp, vp, i32]),
             "vo_pool_seq_len": (i32, [vp, i64]), "vo_pool_table": (i32, [vp, i32, i64, vp, i32]),
             "vo_pool_free_blocks": (i32, [vp, i32]), "vo_pool_layer_data": (vp, [vp, i32]),
+            "vo_pool_set_free_list": (i32, [vp, vp, i32]),
             "vo_pool_attention": (i32, [vp, i32, i64, vp, vp, i32, f32, f32, i32, i32]),
             "vo_model_create": (vp, [C.POINTER(Config)]), "vo_model_destroy": (None, [vp]),
             "vo_model_set_layer_tensor": (i32, [vp, i32, i32, i32, vp]),
@@ -206,7 +207,13 @@ class Pool:
     def seq_len(self, s): return self.L.vo_pool_seq_len(self.h, s)
     def free_blocks(self, layer=0): return self.L.vo_pool_free_blocks(self.h, layer)
 
+    def set_free_list(self, ids):
+        ids = np.ascontiguousarray(ids, np.int32)
+        assert self.L.vo_pool_set_free_list(self.h, _p(ids), ids.size) == 0
+
     def store_kv(self, layer, s, start, k, v, n_tok):
+        if k is None:                      # allocate the blocks of [start, start + n_tok) without writing them
+            return self.L.vo_pool_store_kv(self.h, layer, s, start, None, None, n_tok)
         k, v = _f32(k), _f32(v)
         return self.L.vo_pool_store_kv(self.h, layer, s, start, _p(k), _p(v), n_tok)
 

@@ -650,7 +650,7 @@ int vo_pool_store_kv(vo_pool *p, int layer, int64_t id, int start_pos, const flo
         p->refcnt[layer][b] = 1;
         s->tables[layer][s->n_blocks[layer]++] = b;
     }
-    for (int i = 0; i < n_tok; i++) {
+    for (int i = 0; k && v && i < n_tok; i++) {   /* k == NULL: allocate the blocks only (test set-up copies whole pages in) */
         int pos = start_pos + i;
         int32_t blk = s->tables[layer][pos / p->block_size], off = pos % p->block_size;
         size_t hs = (size_t)p->n_kv_heads * p->head_dim;
@@ -674,6 +674,17 @@ int vo_pool_table(vo_pool *p, int layer, int64_t id, int32_t *out, int cap) {
     return n;
 }
 int vo_pool_free_blocks(vo_pool *p, int layer) { return p->n_free[layer]; }
+/* Test set-up: replace every layer's free stack (bottom first) while no sequence holds a block.  The reference starts from
+ * the ascending list (gpu_block_pool.go:114-116); a serving pool that has run for a while hands out blocks in whatever
+ * order they came back, and tests reproduce such an order on both sides with this. */
+int vo_pool_set_free_list(vo_pool *p, const int32_t *ids, int n) {
+    if (n != p->max_blocks) return -1;
+    for (int l = 0; l < p->n_layers; l++) {
+        if (p->n_free[l] != p->max_blocks) return -2;
+        memcpy(p->free_list[l], ids, sizeof(int32_t) * (size_t)n);
+    }
+    return 0;
+}
 void *vo_pool_layer_data(vo_pool *p, int layer) { return p->data[layer]; }
 
 /* runtime/gpu_block_pool.go:337-389 (kv_len<=0 -> seq_len), attention math as vo_sdpa_paged */

@@ -100,6 +100,7 @@ int  vo_pool_store_kv(vo_pool *p, int layer, int64_t seq, int start_pos, const f
 int  vo_pool_seq_len(vo_pool *p, int64_t seq);
 int  vo_pool_table(vo_pool *p, int layer, int64_t seq, int32_t *out, int cap); /* returns n blocks */
 int  vo_pool_free_blocks(vo_pool *p, int layer);
+int  vo_pool_set_free_list(vo_pool *p, const int32_t *ids, int n);      /* test set-up: same hand-out order on both sides */
 void *vo_pool_layer_data(vo_pool *p, int layer);
 int  vo_pool_attention(vo_pool *p, int layer, int64_t seq, const float *q, float *out,
                        int n_q_heads, float scale, float softcap, int window,

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 from oracle import oracle as O
-from tests.helpers import build_pair, rel_l2
+from tests.helpers import build_pair, oracle_config, rel_l2
 from vexel_b200 import capi, gguf_synth as gs
 
 pytestmark = pytest.mark.gpu
@@ -76,10 +76,10 @@ def test_free_running_greedy_agreement(be):
     spec = small_llama()
     om, gm = build_pair(be, spec, 3, max_blocks=64, max_blocks_per_seq=24)
     rng = np.random.default_rng(2)
-    prompt = rng.integers(0, spec.vocab, 40).astype(np.int32)
+    prompt = rng.integers(0, spec.vocab, 40).astype(np.int32)                  # 40 + 257 tokens fit 19 of the 24 table entries
     a = O.argmax(om.forward(7, prompt, 0)[0]); b = gm.prefill(7, prompt, 0)
     got, want = [b], [a]
-    for step in range(64):
+    for step in range(256):                                       # the bar: >= 99 % over 256 free-running steps
         a = O.argmax(om.forward(7, np.int32([want[-1]]), 40 + step)[0])
         b = int(gm.decode_step([7], [got[-1]], [40 + step])[0])
         want.append(a); got.append(b)
@@ -275,9 +275,10 @@ def test_continuous_batching_trace(be):
 def test_c1_tinyllama_full_shape(be):
     """The benchmark's CPU-runnable configuration at its real shape: TinyLlama-1.1B-shaped Q4_0 (22 layers, hidden 2048,
     32 q / 4 kv heads, head_dim 64, FFN 5632, vocab 32000), seed-0 weights, 4 ragged sequences with prompts {17, 64, 130, 255},
-    prefill then batched greedy decode (steps bounded by VEXEL_C1_STEPS, default 8, to keep the oracle within a minute)."""
+    prefill then 64 batched greedy decode steps (VEXEL_C1_STEPS shortens the run while iterating: the oracle needs ~0.2 s per
+    token on eight cores)."""
     import os
-    steps = int(os.environ.get("VEXEL_C1_STEPS", "8"))
+    steps = int(os.environ.get("VEXEL_C1_STEPS", "64"))
     spec = gs.C1_TINYLLAMA
     om, gm = build_pair(be, spec, 0, max_blocks=96, max_seqs=4, max_batch_tokens=256, max_blocks_per_seq=24)
     rng = np.random.default_rng(1)
@@ -586,3 +587,190 @@ def test_graph_replay_and_takeover_equal_eager_steps(be):
         be.lib.vx_set_graphs(1)
     assert np.array_equal(with_graphs, eager)
     gm.close()
+
+
+def test_verify_returns_post_norm_hidden_states(be):
+    """VerifySpeculativeWithPagedKVAndHidden (runtime/decode.go:1446-1569) returns, next to the logits, the hidden state of
+    every verified token after the final norm (:1543-1557) -- what the Medusa heads read.  vx_decode_step_ex hands them out
+    for a ragged verify batch, from graph-replayed steps too, and with VX_STEP_LAST_ROWS only for the last row of each entry."""
+    spec = small_llama()
+    om = O.Model(oracle_config(spec, 64))
+    gm = capi.Model(be, gs.model_config(spec, 64, 8, 256, 64))
+    rng = np.random.default_rng(21)
+    final_w = (0.5 + rng.random(spec.hidden)).astype(np.float32)                # a final norm that is not all ones
+    for layer, slot, t, raw in gs.synth_tensors(spec, 9):
+        if layer < 0 and slot == capi.G_FINAL_NORM:
+            raw = final_w
+        (om.set_global(slot, t, raw) if layer < 0 else om.set_layer(layer, slot, t, raw))
+        gm.set_tensor(layer, slot, t, raw)
+    gm.finalize()
+    for s, n in [(1, 30), (2, 47), (3, 9)]:
+        p = rng.integers(0, spec.vocab, n).astype(np.int32)
+        om.forward(s, p, 0); gm.prefill(s, p, 0)
+    lens = {1: 30, 2: 47, 3: 9}
+    ids, q_lens = [1, 2, 3], [5, 1, 3]
+    r0 = gm.graph_stats()[0]
+    for rep in range(4):                                                        # the same shape four times: the later ones replay a graph
+        toks = [rng.integers(0, spec.vocab, q).astype(np.int32) for q in q_lens]
+        out, logits, hidden = gm.decode_step_ex(ids, np.concatenate(toks), [lens[s] for s in ids], q_lens=q_lens, want_logits=True, want_hidden=True)
+        row = 0
+        for s, q, t in zip(ids, q_lens, toks):
+            wl, wh = om.forward(s, t, lens[s], all_logits=True, want_hidden=True)
+            want_hidden = O.rmsnorm(wh[-1], final_w, spec.rms_eps)               # decode.go:1543: RMSNorm(state, FinalNorm)
+            assert rel_l2(hidden[row:row + q], want_hidden) < HIDDEN_TOL, (rep, s)
+            assert rel_l2(logits[row:row + q], wl) < HIDDEN_TOL
+            assert [int(x) for x in out[row:row + q]] == [O.argmax(r) for r in wl]
+            row += q
+        for s in ids:                                                           # roll every sequence back (reject all drafts)
+            om.pool.truncate(s, lens[s]); gm.seq_truncate(s, lens[s])
+    assert gm.graph_stats()[0] - r0 >= 2                                        # hidden states did not force eager steps
+    # last rows only: one output row per entry
+    toks = [rng.integers(0, spec.vocab, q).astype(np.int32) for q in q_lens]
+    out, logits, hidden = gm.decode_step_ex(ids, np.concatenate(toks), [lens[s] for s in ids], q_lens=q_lens, last_rows=True,
+                                            want_logits=True, want_hidden=True)
+    assert out.shape == (3,) and logits.shape == (3, spec.vocab) and hidden.shape == (3, spec.hidden)
+    for i, (s, q, t) in enumerate(zip(ids, q_lens, toks)):
+        wl, wh = om.forward(s, t, lens[s], all_logits=True, want_hidden=True)
+        assert rel_l2(hidden[i], O.rmsnorm(wh[-1], final_w, spec.rms_eps)[-1]) < HIDDEN_TOL
+        assert rel_l2(logits[i], wl[-1]) < HIDDEN_TOL and int(out[i]) == O.argmax(wl[-1])
+    gm.close()
+
+
+def test_mixed_prompt_chunks_and_decode_rows_in_one_step(be):
+    """A scheduler step that carries decoding sequences and prompt chunks together (scheduler.go:245-303 + 486-550 as one
+    packed call): a fresh prompt (attends over its float32 K/V like PrefillWithPagedKV from position 0), the second chunk of a
+    longer prompt (>= 32 rows: the multi-row kernel over the pages) and two decode rows; outputs for the last row of each."""
+    spec = small_llama(2)
+    om, gm = build_pair(be, spec, 33, max_blocks=96, max_seqs=8, max_batch_tokens=160, max_blocks_per_seq=16)
+    rng = np.random.default_rng(22)
+    pa = rng.integers(0, spec.vocab, 25).astype(np.int32); pb = rng.integers(0, spec.vocab, 70).astype(np.int32)
+    pc = rng.integers(0, spec.vocab, 110).astype(np.int32); pd = rng.integers(0, spec.vocab, 41).astype(np.int32)
+    ta = gm.prefill(1, pa, 0); om.forward(1, pa, 0)
+    tb = gm.prefill(2, pb, 0); om.forward(2, pb, 0)
+    gm.prefill(3, pc[:50], 0); om.forward(3, pc[:50], 0)                          # first chunk of a long prompt, fed earlier
+    ids = [1, 3, 4, 2]
+    toks = [np.int32([ta]), pc[50:], pd, np.int32([tb])]
+    pos = [25, 50, 0, 70]
+    out, logits, _ = gm.decode_step_ex(ids, np.concatenate(toks), pos, q_lens=[1, 60, 41, 1], last_rows=True, prompt_rows=True, want_logits=True)
+    for i, (s, t, p0) in enumerate(zip(ids, toks, pos)):
+        wl = om.forward(s, t, p0)                                                 # the oracle's prefill / decode of the same rows
+        assert rel_l2(logits[i], wl[-1]) < HIDDEN_TOL, (s, rel_l2(logits[i], wl[-1]))
+        assert int(out[i]) == O.argmax(wl[-1])
+        assert np.array_equal(gm.block_table(s), om.pool.table(0, s)) and gm.seq_len(s) == om.pool.seq_len(s)
+    gm.close()
+
+
+def test_scheduler_refuses_what_can_never_fit_and_reuses_ids(be):
+    """A request whose prompt plus token limit exceeds the pool (or one block table) ends with status 2 instead of waiting
+    for ever, without taking a batch slot from the others (the reference stops its loop with an allocation error,
+    scheduler.go:134-136); and the id of a finished request can be used again."""
+    spec = small_llama(2)
+    om, gm = build_pair(be, spec, 21, max_blocks=24, max_seqs=4, max_batch_tokens=64, max_blocks_per_seq=8)
+    rng = np.random.default_rng(23)
+    sched = capi.Scheduler(gm, max_batch_size=2, max_sequences=8)
+    big = rng.integers(0, spec.vocab, 100).astype(np.int32)                      # 100 + 60 tokens need 10 blocks: table width is 8
+    ok = rng.integers(0, spec.vocab, 20).astype(np.int32)
+    sched.AddSequence(1, big, max_tokens=60)
+    sched.AddSequence(2, ok, max_tokens=6)
+    got, status = [], {}
+    for _ in range(40):
+        sched.step()
+        for sid in (1, 2):
+            if sid not in status:
+                t, st = sched.poll_status(sid)
+                if sid == 2: got.extend(int(x) for x in t)
+                if st: status[sid] = st
+        if len(status) == 2:
+            break
+    assert status == {1: 2, 2: 1} and len(got) == 6
+    assert sched.pressure()[1] == 1
+    want = [O.argmax(om.forward(50, ok, 0)[0])]
+    for i in range(5):
+        want.append(O.argmax(om.forward(50, np.int32([want[-1]]), 20 + i)[0]))
+    assert got == want
+    # the finished id 2 again, with another prompt: served as a new request
+    ok2 = rng.integers(0, spec.vocab, 11).astype(np.int32)
+    sched.AddSequence(2, ok2, max_tokens=3)
+    got2 = []
+    for _ in range(20):
+        sched.step()
+        t, st = sched.poll_status(2); got2.extend(int(x) for x in t)
+        if st: break
+    assert st == 1 and len(got2) == 3 and got2[0] == O.argmax(om.forward(51, ok2, 0)[0])
+    assert gm.pool_stats()[1] == gm.pool_stats()[0]
+    sched.close(); gm.close()
+
+
+def test_scheduler_completes_every_request_when_the_pool_is_too_small(be):
+    """Twelve requests whose prompts and outputs together need several times the pool: admission holds requests back until
+    the blocks for their whole life are free, so no step ever fails on blocks and every request completes with the tokens
+    of a stand-alone greedy decode.  A second run without token limits (nothing to reserve) exercises preemption: the
+    youngest sequence gives its blocks back and is read again later; the streams stay the same."""
+    spec = small_llama(2)
+    om, gm = build_pair(be, spec, 27, max_blocks=20, max_seqs=6, max_batch_tokens=48, max_blocks_per_seq=10)
+    rng = np.random.default_rng(24)
+    n_req = 12
+    prompts = [rng.integers(0, spec.vocab, int(rng.integers(5, 70))).astype(np.int32) for _ in range(n_req)]
+    out_len = [int(rng.integers(8, 40)) for _ in range(n_req)]                  # up to 110 tokens = 7 blocks each; the pool has 20
+    want = []
+    for i in range(n_req):
+        w = [O.argmax(om.forward(900 + i, prompts[i], 0)[0])]
+        for j in range(out_len[i] - 1):
+            w.append(O.argmax(om.forward(900 + i, np.int32([w[-1]]), len(prompts[i]) + j)[0]))
+        want.append(w)
+        om.pool.delete_seq(900 + i)                                             # the oracle's pool is as small as the device's
+
+    def run(limit_known):
+        sched = capi.Scheduler(gm, max_batch_size=6, max_sequences=0, max_tokens=0)
+        for i in range(n_req):
+            sched.AddSequence(100 + i, prompts[i], max_tokens=out_len[i] if limit_known else 0)
+        got = {i: [] for i in range(n_req)}
+        done = set()
+        for _ in range(3000):
+            sched.step()
+            for i in range(n_req):
+                if i in done: continue
+                t, st = sched.poll_status(100 + i); got[i].extend(int(x) for x in t)
+                if not limit_known and len(got[i]) >= out_len[i]:
+                    sched.RemoveSequence(100 + i); done.add(i)                  # the client hangs up once it has what it wanted
+                elif st:
+                    assert st == 1; done.add(i)
+            if len(done) == n_req: break
+        assert len(done) == n_req
+        pre = sched.pressure()[0]
+        sched.close()
+        return got, pre
+
+    got, pre = run(True)
+    assert pre == 0                                                             # reservations: nobody had to be preempted
+    agree = sum(int(a == b) for i in range(n_req) for a, b in zip(got[i], want[i])); total = sum(out_len)
+    assert all(len(got[i]) == out_len[i] for i in range(n_req)) and agree / total >= 0.99, (agree, total)
+    assert gm.pool_stats()[1] == gm.pool_stats()[0]
+    got, pre = run(False)
+    assert pre >= 1                                                             # without limits the pool ran dry and somebody was preempted
+    agree = sum(int(a == b) for i in range(n_req) for a, b in zip(got[i][:out_len[i]], want[i]))
+    assert agree / total >= 0.99, (agree, total)
+    assert gm.pool_stats()[1] == gm.pool_stats()[0]
+    gm.close()
+
+
+def test_second_device_runs_the_large_shared_memory_kernels(lib_built):
+    """One process, one context per GPU (the layout of a Go server that drives several devices): the kernels that need more
+    than 48 KiB of dynamic shared memory must be set up on every device, not only on the first one that used them."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from vexel_b200 import Backend
+    outs = []
+    for dev in (0, 1):
+        b = Backend(dev)
+        spec = gs.scaled(gs.C3_LLAMA3_8B, 1, 256, 8, 2, 128, 512, 1024, quant="q4_0")     # head_dim 128, groups of four: 64 KiB attention kernel
+        _, gm = build_pair(b, spec, 5, max_blocks=64, max_seqs=24, max_batch_tokens=64, cpu=False)
+        rng = np.random.default_rng(3)
+        ids = list(range(1, 21))
+        first = [gm.prefill(s, rng.integers(0, spec.vocab, 40).astype(np.int32), 0) for s in ids]      # 40-row prefill kernels
+        toks, logits = gm.decode_step(ids, first, [40] * 20, want_logits=True)                       # 20 rows: tcgen05 projections
+        outs.append((np.array(first), toks.copy(), logits.copy()))
+        gm.close(); b.close()
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+    assert np.array_equal(outs[0][2].view(np.uint32), outs[1][2].view(np.uint32))

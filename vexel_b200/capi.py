@@ -47,6 +47,7 @@ _vp, _i, _i64, _f, _u64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_ui
 _D = C.c_uint64  # vx_dptr
 
 # name -> argtypes (every function returns int unless listed in _RESTYPE)
+STEP_LAST_ROWS, STEP_PROMPT_ROWS = 1, 2
 SAMPLE_DTYPE = np.dtype([("temperature", np.float32), ("top_k", np.int32), ("top_p", np.float32), ("u", np.float32)])
 
 SIGNATURES = {
@@ -85,8 +86,10 @@ SIGNATURES = {
     "vx_seq_block_table": [_vp, _i64, _vp, _i, C.POINTER(_i)],
     "vx_pool_stats": [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)],
     "vx_pool_layer_ptr": [_vp, _i, C.POINTER(_D), C.POINTER(_sz)],
+    "vx_pool_free_list": [_vp, _vp, _i, C.POINTER(_i)],
     "vx_seq_fill_synthetic": [_vp, _i64, _i, C.c_uint32],
     "vx_decode_step": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp],
+    "vx_decode_step_ex": [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp],
     "vx_model_get_config": [_vp, _vp],
     "vx_gguf_open": [C.c_char_p, C.POINTER(_vp)], "vx_gguf_close": [_vp], "vx_gguf_error": [_vp], "vx_gguf_tensor_count": [_vp],
     "vx_gguf_tensor_info": [_vp, _i, C.c_char_p, _i, C.POINTER(_i), C.POINTER(_i), C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u64)],
@@ -112,6 +115,7 @@ SIGNATURES = {
     "vx_sched_add_sequence": [_vp, _i64, _vp, _i, _i], "vx_sched_remove_sequence": [_vp, _i64],
     "vx_sched_step": [_vp, C.POINTER(_i)], "vx_sched_poll": [_vp, _i64, _vp, _i, C.POINTER(_i), C.POINTER(_i)],
     "vx_sched_get_metrics": [_vp, C.POINTER(SchedMetrics)],
+    "vx_sched_get_pressure": [_vp, C.POINTER(_u64), C.POINTER(_u64)],
 }
 _RESTYPE = {"vx_last_error": C.c_char_p, "vx_gguf_error": C.c_char_p}
 
@@ -374,6 +378,11 @@ class Model:
         a, b, c = C.c_int(), C.c_int(), C.c_int()
         self._ck(self.lib.vx_pool_stats(self.h, C.byref(a), C.byref(b), C.byref(c))); return a.value, b.value, c.value
 
+    def free_list(self):
+        """the per-layer free list, bottom of the stack first (the next block handed out is the last entry)"""
+        buf = np.empty(self.cfg.max_blocks, np.int32); n = C.c_int()
+        self._ck(self.lib.vx_pool_free_list(self.h, _np_ptr(buf), buf.size, C.byref(n))); return buf[:n.value].copy()
+
     def pool_layer(self, layer):
         p, n = _D(), C.c_size_t()
         self._ck(self.lib.vx_pool_layer_ptr(self.h, layer, C.byref(p), C.byref(n))); return p.value, n.value
@@ -388,6 +397,24 @@ class Model:
         self._ck(self.lib.vx_decode_step(self.h, seq_ids.size, _np_ptr(seq_ids), _np_ptr(tokens), _np_ptr(positions),
                                         _np_ptr(ql), _np_ptr(out), _np_ptr(logits)))
         return (out, logits) if want_logits else out
+
+    def decode_step_ex(self, seq_ids, tokens, positions, q_lens=None, last_rows=False, prompt_rows=False, params=None,
+                       want_logits=False, want_hidden=False):
+        """vx_decode_step_ex: returns (tokens, logits or None, post-final-norm hidden states or None) for the output rows --
+        every packed row, or with last_rows the last row of each batch entry."""
+        seq_ids = np.ascontiguousarray(seq_ids, np.int64); tokens = np.ascontiguousarray(tokens, np.int32)
+        positions = np.ascontiguousarray(positions, np.int32)
+        ql = None if q_lens is None else np.ascontiguousarray(q_lens, np.int32)
+        rows = seq_ids.size if last_rows else tokens.size
+        par = None if params is None else np.ascontiguousarray(params, SAMPLE_DTYPE)
+        assert par is None or par.size == rows
+        out = np.empty(rows, np.int32)
+        logits = np.empty((rows, self.cfg.vocab), np.float32) if want_logits else None
+        hidden = np.empty((rows, self.cfg.hidden), np.float32) if want_hidden else None
+        flags = (STEP_LAST_ROWS if last_rows else 0) | (STEP_PROMPT_ROWS if prompt_rows else 0)
+        self._ck(self.lib.vx_decode_step_ex(self.h, seq_ids.size, _np_ptr(seq_ids), _np_ptr(tokens), _np_ptr(positions), _np_ptr(ql),
+                                           flags, _np_ptr(par), _np_ptr(out), _np_ptr(logits), _np_ptr(hidden)))
+        return out, logits, hidden
 
     def decode_step_sampled(self, seq_ids, tokens, positions, params, q_lens=None, want_logits=False):
         """decode_step with one (temperature, top_k, top_p, u) record per packed row, sampled on the device."""
@@ -470,5 +497,15 @@ class Scheduler:
         self.m._ck(self.lib.vx_sched_poll(self.h, seq_id, _np_ptr(buf), cap, C.byref(n), C.byref(fin)))
         return buf[:n.value].copy(), bool(fin.value)
 
+    def poll_status(self, seq_id, cap=4096):
+        """(tokens, status): 0 running, 1 ended, 2 refused (the request could never fit the block pool)."""
+        buf = np.empty(cap, np.int32); n, fin = C.c_int(), C.c_int()
+        self.m._ck(self.lib.vx_sched_poll(self.h, seq_id, _np_ptr(buf), cap, C.byref(n), C.byref(fin)))
+        return buf[:n.value].copy(), fin.value
+
     def Metrics(self):
         m = SchedMetrics(); self.m._ck(self.lib.vx_sched_get_metrics(self.h, C.byref(m))); return m
+
+    def pressure(self):
+        a, b = C.c_uint64(), C.c_uint64()
+        self.m._ck(self.lib.vx_sched_get_pressure(self.h, C.byref(a), C.byref(b))); return a.value, b.value

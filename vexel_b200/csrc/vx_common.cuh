@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <mutex>
 #include <string>
 #include <unordered_map>
@@ -60,6 +61,19 @@ int vx_scratch(vx_ctx *c, size_t bytes, void **out);   // grows the interface-le
         int rc__ = (expr);                                                        \
         if (rc__ != VX_OK) return rc__;                                           \
     } while (0)
+
+// cudaFuncSetAttribute changes the calling device's copy of a kernel only, and one process may drive a context per GPU:
+// a call site keeps one of these (static) and asks it once per device, with that device current.
+struct VxPerDevice {
+    std::atomic<unsigned long long> mask{0};
+    template <typename K> cudaError_t max_dynamic_smem(const vx_ctx *c, K kernel, int bytes) {
+        const bool tracked = c->device >= 0 && c->device < 64;
+        if (tracked && ((mask.load(std::memory_order_acquire) >> c->device) & 1ull)) return cudaSuccess;
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e == cudaSuccess && tracked) mask.fetch_or(1ull << c->device, std::memory_order_release);
+        return e;
+    }
+};
 
 template <typename T> static inline T *dp(vx_dptr p) { return reinterpret_cast<T *>(static_cast<uintptr_t>(p)); }
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

@@ -636,15 +636,14 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
     int *err_flag = c->d_int_result + 8;
     if (w.type != VX_T_Q4_0 && w.type != VX_T_Q4_K && w.type != VX_T_Q6_K) return vx_fail(c, VX_E_UNSUPPORTED, "tensor-core projection: weight type %d", w.type);
     if (x.k_pad != w.k_pad) return vx_fail(c, VX_E_BAD_ARG, "projection: activation row stride %d != weight k_pad %d", x.k_pad, w.k_pad);
-    static bool attr_set = false;
-    if (!attr_set) {
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_0, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(TC_Q4_0, 64)));
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_K, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(TC_Q4_K, 64)));
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q6_K, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(TC_Q6_K, 64)));
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_0, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(TC_Q4_0, 128)));
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q4_K, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(TC_Q4_K, 128)));
-        VX_CUDA(c, cudaFuncSetAttribute(gemm_tc_kernel<TC_Q6_K, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(TC_Q6_K, 128)));
-        attr_set = true;
+    {
+        static VxPerDevice a0, a1, a2, a3, a4, a5;
+        VX_CUDA(c, a0.max_dynamic_smem(c, gemm_tc_kernel<TC_Q4_0, 64>, smem_bytes(TC_Q4_0, 64)));
+        VX_CUDA(c, a1.max_dynamic_smem(c, gemm_tc_kernel<TC_Q4_K, 64>, smem_bytes(TC_Q4_K, 64)));
+        VX_CUDA(c, a2.max_dynamic_smem(c, gemm_tc_kernel<TC_Q6_K, 64>, smem_bytes(TC_Q6_K, 64)));
+        VX_CUDA(c, a3.max_dynamic_smem(c, gemm_tc_kernel<TC_Q4_0, 128>, smem_bytes(TC_Q4_0, 128)));
+        VX_CUDA(c, a4.max_dynamic_smem(c, gemm_tc_kernel<TC_Q4_K, 128>, smem_bytes(TC_Q4_K, 128)));
+        VX_CUDA(c, a5.max_dynamic_smem(c, gemm_tc_kernel<TC_Q6_K, 128>, smem_bytes(TC_Q6_K, 128)));
     }
     // batches above 64 rows (prefill chunks, verify) take 128-row tiles: the MMA count per stage stays the same, so each
     // dequantised weight tile and each tcgen05 instruction serves twice the rows

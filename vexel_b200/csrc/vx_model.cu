@@ -55,7 +55,9 @@ struct vx_model {
     // ---- per-step buffers
     int32_t *d_step_in = nullptr, *h_step_in = nullptr;   // pinned staging + device copy
     int32_t *d_cu = nullptr, *d_row_slot = nullptr, *d_row_pos = nullptr, *d_slot_map = nullptr, *d_row_kv_len = nullptr,
-            *d_row_kv_start = nullptr;
+            *d_row_kv_start = nullptr, *d_row_route = nullptr, *d_last_row = nullptr;
+    float *d_hidden = nullptr;                   // post-final-norm hidden states of the output rows of the last step
+    bool fast_attn_shape = false;                // the paged attention kernels that walk work lists cover this head shape
     int4 *d_work[2] = {nullptr, nullptr}; int32_t *d_rws[2] = {nullptr, nullptr}; int32_t *d_n_work[2] = {nullptr, nullptr};
     float *d_partials = nullptr;
     float *d_cos = nullptr, *d_sin = nullptr, *d_freq = nullptr;
@@ -69,9 +71,10 @@ struct vx_model {
     uint64_t steps = 0;
     // CUDA graphs of whole steps, keyed by everything that shapes the launches (see enqueue_step)
     struct GraphKey {
-        int n_seqs, rows, logit_rows, chunk0, chunk1, nw0, nw1;
+        int n_seqs, rows, logit_rows, chunk0, chunk1, nw0, nw1, out_flags;
         bool operator<(const GraphKey &o) const {
-            return std::tie(n_seqs, rows, logit_rows, chunk0, chunk1, nw0, nw1) < std::tie(o.n_seqs, o.rows, o.logit_rows, o.chunk0, o.chunk1, o.nw0, o.nw1);
+            return std::tie(n_seqs, rows, logit_rows, chunk0, chunk1, nw0, nw1, out_flags) <
+                   std::tie(o.n_seqs, o.rows, o.logit_rows, o.chunk0, o.chunk1, o.nw0, o.nw1, o.out_flags);
         }
     };
     struct GraphEntry { cudaGraphExec_t exec = nullptr; int seen = 0; uint64_t launches = 0; };
@@ -194,9 +197,11 @@ __global__ void shuffle_free_list_kernel(int32_t *free_list, int32_t *tmp, int n
 }
 
 // ------------------------------------------------------------------ the packing kernel (one CTA)
-// step_in = [n_seqs slots][n_seqs q_lens][n_seqs positions][n_rows tokens]
+// step_in = [n_seqs slots][n_seqs q_lens][n_seqs positions][n_seqs routes][n_rows tokens]
+// route of a batch entry: 0 = its rows go through the split-K work lists, otherwise another attention kernel serves them
 struct PackArgs {
     const int32_t *step_in; int n_seqs, n_rows;
+    int32_t *row_route, *last_row;
     int32_t *tables; int width; int32_t *seq_len, *n_blocks, *free_list, *free_top, *refcnt, *status;
     int32_t *cu, *row_slot, *row_pos, *slot_map, *row_kv_len, *row_kv_start;
     int window;                          // 0 = no sliding layers
@@ -205,7 +210,7 @@ struct PackArgs {
 __global__ void __launch_bounds__(1024) pack_kernel(PackArgs a) {
     __shared__ int tmp[33];
     __shared__ int s_err, s_ovf;
-    const int32_t *slots = a.step_in, *qlens = a.step_in + a.n_seqs, *positions = a.step_in + 2 * a.n_seqs;
+    const int32_t *slots = a.step_in, *qlens = a.step_in + a.n_seqs, *positions = a.step_in + 2 * a.n_seqs, *routes = a.step_in + 3 * a.n_seqs;
     if (threadIdx.x == 0) { s_err = 0; s_ovf = 0; }
     __syncthreads();
     // pass A: validate, prefix sums of q_len (rows) and of newly needed blocks; nothing is modified yet
@@ -233,7 +238,16 @@ __global__ void __launch_bounds__(1024) pack_kernel(PackArgs a) {
         if (need_base > *a.free_top) s_err = VX_E_OOM_BLOCKS;
     }
     __syncthreads();
-    if (s_err) { if (threadIdx.x == 0) *a.status = s_err; return; }
+    if (s_err) {
+        // a refused step must not touch anybody's KV: the kernels that follow see no work items and no pool slot
+        for (int t = threadIdx.x; t <= a.n_rows; t += blockDim.x) {
+            a.rws0[t] = 0; a.rws1[t] = 0;
+            if (t < a.n_rows) { a.slot_map[t] = -1; a.row_kv_len[t] = 0; a.row_kv_start[t] = 0; a.row_route[t] = 0; a.row_pos[t] = 0; a.row_slot[t] = slots[0]; }
+        }
+        for (int i = threadIdx.x; i < a.n_seqs; i += blockDim.x) a.last_row[i] = 0;
+        if (threadIdx.x == 0) { *a.status = s_err; *a.n_work0 = 0; *a.n_work1 = 0; }
+        return;
+    }
     // pass B: pop blocks in batch order (sequence i takes the pops numbered [off_i, off_i + need_i) from the end of the stack)
     const int top = *a.free_top;
     __syncthreads();
@@ -255,18 +269,19 @@ __global__ void __launch_bounds__(1024) pack_kernel(PackArgs a) {
         int lo = 0, hi = a.n_seqs;                       // last i with cu[i] <= t
         while (hi - lo > 1) { int mid = (lo + hi) >> 1; if (a.cu[mid] <= t) lo = mid; else hi = mid; }
         int s = slots[lo], pos = positions[lo] + (t - a.cu[lo]);
-        a.row_slot[t] = s; a.row_pos[t] = pos;
+        a.row_slot[t] = s; a.row_pos[t] = pos; a.row_route[t] = routes[lo];
         a.slot_map[t] = a.tables[(size_t)s * a.width + pos / BS] * BS + pos % BS;
         a.row_kv_len[t] = pos + 1;
     }
+    for (int i = threadIdx.x; i < a.n_seqs; i += blockDim.x) a.last_row[i] = a.cu[i] + qlens[i] - 1;
     __syncthreads();
     for (int t = threadIdx.x; t < a.n_rows; t += blockDim.x)
         a.row_kv_start[t] = a.window > 0 ? max(0, a.row_pos[t] + 1 - a.window) : 0;   // runtime/block.go:925-929
     __syncthreads();
-    int n0 = vx_build_work(a.n_rows, nullptr, a.row_kv_len, BS, a.chunk0, a.work0, a.rws0, a.max_work, &s_ovf, tmp);
+    int n0 = vx_build_work(a.n_rows, nullptr, a.row_kv_len, a.row_route, BS, a.chunk0, a.work0, a.rws0, a.max_work, &s_ovf, tmp);
     if (threadIdx.x == 0) *a.n_work0 = n0;
     if (a.window > 0) {
-        int n1 = vx_build_work(a.n_rows, a.row_kv_start, a.row_kv_len, BS, a.chunk1, a.work1, a.rws1, a.max_work, &s_ovf, tmp);
+        int n1 = vx_build_work(a.n_rows, a.row_kv_start, a.row_kv_len, a.row_route, BS, a.chunk1, a.work1, a.rws1, a.max_work, &s_ovf, tmp);
         if (threadIdx.x == 0) *a.n_work1 = n1;
     }
     __syncthreads();
@@ -307,14 +322,17 @@ __global__ void embed_kernel(const int32_t *tokens, const void *table, int type,
 // ------------------------------------------------------------------ residual add + RMSNorm + split
 // x[row] += (post_w ? rmsnorm(sum parts)*post_w : sum parts);  y = rmsnorm(x)*w;  y -> fp16 hi/lo (+ per-block sums).
 // n_parts == 0 skips the add; w == nullptr skips the norm/split.  One CTA of 1024 threads per row, row in registers.
+// row_idx (optional, only with n_parts == 0): CTA r reads row row_idx[r] of x and writes split row r (the final norm of
+// the last row of every sequence).  normed_out (optional): the normalised row as float32 [r][hidden], which is the
+// post-final-norm hidden state VerifySpeculativeWithPagedKVAndHidden returns (runtime/decode.go:1543-1557).
 template <int NC>
 __global__ void __launch_bounds__(VX_ROW_THREADS)
 add_norm_split_kernel(float *x, const float *parts, int n_parts, size_t part_stride, int part_ld, const float *post_w, const float *w,
-                      float eps, int hidden, VxSplit s, float *capture) {
+                      float eps, int hidden, VxSplit s, float *capture, const int32_t *row_idx, float *normed_out) {
     __shared__ float red[32];
     vx_pdl_trigger();          // the projection that follows may become resident and fetch its first weights now
     const int r = blockIdx.x;
-    float *xr = x + (size_t)r * hidden;
+    float *xr = x + (size_t)(row_idx ? row_idx[r] : r) * hidden;
     float4 v[NC];
     const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -378,6 +396,7 @@ add_norm_split_kernel(float *x, const float *parts, int n_parts, size_t part_str
             float4 ww = *reinterpret_cast<const float4 *>(w + k0);
             v[c].x = __fmul_rn(__fdiv_rn(v[c].x, rms), ww.x); v[c].y = __fmul_rn(__fdiv_rn(v[c].y, rms), ww.y);
             v[c].z = __fmul_rn(__fdiv_rn(v[c].z, rms), ww.z); v[c].w = __fmul_rn(__fdiv_rn(v[c].w, rms), ww.w);
+            if (normed_out) *reinterpret_cast<float4 *>(normed_out + (size_t)r * hidden + k0) = v[c];
         }
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[c].x), fabsf(v[c].y)), fmaxf(fabsf(v[c].z), fabsf(v[c].w))));
     }
@@ -413,6 +432,7 @@ rope_append_kernel(const float *src, int n_parts, size_t part_stride, float *qkv
     float *drow = qkv + (size_t)t * ld;
     const float *c = cs + (size_t)t * half, *s = sn + (size_t)t * half;
     const int slot = slot_map[t];
+    if (slot < 0) return;                      // the packing kernel refused the step: nothing may reach the pool
     const size_t hs = (size_t)n_kv_heads * D, part = (size_t)BS * hs;
     __half *kdst = pool_layer + (size_t)(slot / BS) * 2 * part + (size_t)(slot % BS) * hs;
     __half *vdst = kdst + part;
@@ -564,11 +584,12 @@ int gemm_full(vx_model *m, const VxWeight &w, const VxSplit &x, int rows, float 
 }
 
 int add_norm_split_rows(vx_model *m, float *x, int rows, const float *parts, int n_parts, size_t part_stride, int part_ld,
-                        const float *post_w, const float *w, const VxSplit &s, float *capture) {
+                        const float *post_w, const float *w, const VxSplit &s, float *capture, const int32_t *row_idx = nullptr,
+                        float *normed_out = nullptr) {
     const int H = m->cfg.hidden;
     if (H > 8192) return vx_fail(m->c, VX_E_UNSUPPORTED, "hidden size %d > 8192", H);
-    if (H > 4096) add_norm_split_kernel<2><<<rows, VX_ROW_THREADS, 0, m->c->stream>>>(x, parts, n_parts, part_stride, part_ld, post_w, w, m->cfg.rms_eps, H, s, capture);
-    else add_norm_split_kernel<1><<<rows, VX_ROW_THREADS, 0, m->c->stream>>>(x, parts, n_parts, part_stride, part_ld, post_w, w, m->cfg.rms_eps, H, s, capture);
+    if (H > 4096) add_norm_split_kernel<2><<<rows, VX_ROW_THREADS, 0, m->c->stream>>>(x, parts, n_parts, part_stride, part_ld, post_w, w, m->cfg.rms_eps, H, s, capture, row_idx, normed_out);
+    else add_norm_split_kernel<1><<<rows, VX_ROW_THREADS, 0, m->c->stream>>>(x, parts, n_parts, part_stride, part_ld, post_w, w, m->cfg.rms_eps, H, s, capture, row_idx, normed_out);
     VX_LAUNCH_CHECK(m->c);
     return VX_OK;
 }
@@ -605,16 +626,23 @@ bool layer_slides(const vx_model_config &c, int layer) {   // runtime/block.go:4
     return c.window_alternating ? (layer % 2 == 1) : true;
 }
 
+// Rows of one batch entry that do not go through the split-K work lists.
+//   route 1: causal attention over the fresh float32 K/V of this call (a prompt that starts at position 0, block.go:891-895)
+//   route 2: the multi-row tensor-core kernel over the pages (a long chunk of one sequence, decode.go:1033-1060)
+struct RowRange { int row0, n, route; };
+enum { OUT_LAST_ROWS = 1, OUT_HIDDEN = 2 };     // output flags of a step (also part of the graph key)
+
 // The transformer stack over `rows` packed query rows whose packing arrays are already on the device.
-// mode 0: paged attention for every row (decode / verify / chunked prefill)
-// mode 1: causal attention over the fresh float32 K/V of this call (prefill from position 0, block.go:891-895)
-// logit_rows: how many trailing rows get logits (all rows, or 1 for prefill)
-int forward(vx_model *m, int rows, int mode, int n_work_host[2], const int chunk_pages[2], int logit_rows) {
+// special: the row ranges served by the prefill kernels; every other row (plain_rows of them) takes paged decode attention.
+// Outputs (logits, tokens, optionally post-norm hidden states) are produced for logit_rows rows: the trailing rows, or with
+// OUT_LAST_ROWS the last row of each of the logit_rows (= n_seqs) batch entries.
+int forward(vx_model *m, int rows, const std::vector<RowRange> &special, int plain_rows, int n_work_host[2], const int chunk_pages[2],
+            int logit_rows, int out_flags) {
     vx_ctx *c = m->c; const vx_model_config &cf = m->cfg;
     const int H = cf.hidden, Hq = cf.n_heads, Hkv = cf.n_kv_heads, D = cf.head_dim, F = cf.ffn;
     const int qd = Hq * D, kvd = Hkv * D, nqkv = qd + 2 * kvd;
     const float scale = (float)(1.0 / sqrt((double)D));   // block.go:862
-    const int32_t *tokens = m->d_step_in + 3 * m->last_seqs;
+    const int32_t *tokens = m->d_step_in + 4 * m->last_seqs;
     embed_kernel<<<rows, 256, 0, c->stream>>>(tokens, m->embed.dev, m->embed.type, m->x, H, cf.vocab, cf.embed_scale);
     VX_LAUNCH_CHECK(c);
     {
@@ -646,12 +674,7 @@ int forward(vx_model *m, int rows, int mode, int n_work_host[2], const int chunk
         }
         time_begin(m, 0);
         bool split_done = false;
-        if (mode == 1) {
-            int rc = vxp_prefill_f32(c, m->qkv, nqkv, m->qkv + qd, m->qkv + qd + kvd, nqkv, m->attn, qd, rows, Hq, Hkv, D, scale, cf.attn_softcap);
-            if (rc == VX_E_UNSUPPORTED)
-                rc = vxe_sdpa_strided(c, m->qkv, nqkv, m->qkv + qd, m->qkv + qd + kvd, m->attn, qd, rows, 0, 1, Hq, Hkv, D, nqkv, D, scale, cf.attn_softcap);
-            VX_TRY(rc);
-        } else {
+        {
             const int wl = layer_slides(cf, l) ? 1 : 0;
             VxAttnArgs a{};
             a.q = m->qkv; a.q_row_stride = nqkv; a.pool = m->pool + (size_t)l * m->layer_stride; a.pool_is_f16 = 1;
@@ -661,16 +684,23 @@ int forward(vx_model *m, int rows, int mode, int n_work_host[2], const int chunk
             a.partials = m->d_partials; a.out = m->attn; a.out_row_stride = qd;
             a.rows = rows; a.n_q_heads = Hq; a.n_kv_heads = Hkv; a.head_dim = D; a.block_size = BS;
             a.scale = scale; a.softcap = cf.attn_softcap;
+            for (const RowRange &r : special) {
+                if (r.route == 1) {
+                    const float *q = m->qkv + (size_t)r.row0 * nqkv;
+                    float *o = m->attn + (size_t)r.row0 * qd;
+                    int rc = vxp_prefill_f32(c, q, nqkv, q + qd, q + qd + kvd, nqkv, o, qd, r.n, Hq, Hkv, D, scale, cf.attn_softcap);
+                    if (rc == VX_E_UNSUPPORTED)
+                        rc = vxe_sdpa_strided(c, q, nqkv, q + qd, q + qd + kvd, o, qd, r.n, 0, 1, Hq, Hkv, D, nqkv, D, scale, cf.attn_softcap);
+                    VX_TRY(rc);
+                } else {
+                    // a long chunk of one sequence walks the cache once per 64 rows instead of once per row
+                    VX_TRY(vxp_prefill_rows(c, a, r.row0, r.n));
+                }
+            }
             // at most this many split-K chunks per row: the table width bounds a row's pages
             const int n_max = ceil_div(cf.max_blocks_per_seq, max(chunk_pages[wl], 1)) + 1;
-            // a long chunk of one sequence (chunked prefill, decode.go:1033-1060) walks the cache once per 64 rows instead of once per row
-            bool pf_done = false;
-            if (m->last_seqs == 1 && rows >= 32) {
-                int rc = vxp_prefill_rows(c, a, 0, rows);
-                if (rc == VX_OK) pf_done = true;
-                else if (rc != VX_E_UNSUPPORTED) return rc;
-            }
-            if (!pf_done) VX_TRY(vxp_attention_split(c, a, &m->sp_q, n_max, &split_done));  // block.go:872 / 881-890
+            // rows served above have no work items; the merge reads their finished output rows back
+            if (plain_rows > 0) VX_TRY(vxp_attention_split(c, a, &m->sp_q, n_max, &split_done));  // block.go:872 / 881-890
         }
         time_end(m, 0);
         if (!split_done) VX_TRY(vxq_split_rows(c, m->attn, rows, qd, qd, m->sp_q));
@@ -686,11 +716,13 @@ int forward(vx_model *m, int rows, int mode, int n_work_host[2], const int chunk
         post_prev = cf.post_norms ? L.post_ffn_norm : nullptr;
     }
     // last residual add, then the final norm on the rows that need logits (decode.go:442, 1057-1086)
-    const int r0 = rows - logit_rows;
+    const bool last_rows = (out_flags & OUT_LAST_ROWS) != 0;
+    const int r0 = last_rows ? 0 : rows - logit_rows;
     VX_TRY(add_norm_split(m, rows, m->parts, np_prev, (size_t)rows * H, H, post_prev, nullptr, m->sp_h,
                           m->capture_on ? m->capture + (size_t)cf.n_layers * cap_stride : nullptr));
-    // norm + split only the logit rows, written to split rows [0, logit_rows)
-    VX_TRY(add_norm_split_rows(m, m->x + (size_t)r0 * H, logit_rows, nullptr, 0, 0, 0, nullptr, m->final_norm, m->sp_h, nullptr));
+    // norm + split only the logit rows (the trailing ones, or the last row of every entry), written to split rows [0, logit_rows)
+    VX_TRY(add_norm_split_rows(m, m->x + (size_t)r0 * H, logit_rows, nullptr, 0, 0, 0, nullptr, m->final_norm, m->sp_h, nullptr,
+                               last_rows ? m->d_last_row : nullptr, (out_flags & OUT_HIDDEN) ? m->d_hidden : nullptr));
     VX_TRY(gemm_full(m, m->w_out, m->sp_h, logit_rows, m->logits, cf.vocab));           // model.go:352-422
     VX_TRY(vxe_argmax_rows(c, m->logits, logit_rows, cf.vocab, m->d_out_tok));          // sampler.go:79-90
     return VX_OK;
@@ -739,13 +771,14 @@ __global__ void advance_step_kernel(int32_t *step_in, int n_seqs, const int32_t 
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_seqs) return;
     step_in[2 * n_seqs + i] += 1;
-    step_in[3 * n_seqs + i] = prev_tokens[i];
+    step_in[4 * n_seqs + i] = prev_tokens[i];
 }
 
-// Host half of a step: validation and admission control against the host mirror, split-K planning, then the
-// mirror update.  No device state is touched; on failure nothing has changed.
-struct StepPlan { int n_seqs, rows, chunk[2], n_work[2]; };
-int plan_step(vx_model *m, int n_seqs, const int *slots, const int32_t *positions, const int32_t *q_lens, StepPlan *p) {
+// Host half of a step: validation and admission control against the host mirror, attention routes, split-K planning, then
+// the mirror update.  No device state is touched; on failure nothing has changed.
+struct StepPlan { int n_seqs = 0, rows = 0, chunk[2] = {4, 4}, n_work[2] = {0, 0}, plain_rows = 0; std::vector<RowRange> special; std::vector<int> routes; };
+constexpr int PF_MIN_ROWS = 32;      // from this many rows of one sequence on, the multi-row kernel beats per-row decode attention
+int plan_step(vx_model *m, int n_seqs, const int *slots, const int32_t *positions, const int32_t *q_lens, bool prompt_rows, StepPlan *p) {
     vx_ctx *c = m->c; const vx_model_config &cf = m->cfg;
     int rows = 0;
     for (int i = 0; i < n_seqs; i++) rows += q_lens ? q_lens[i] : 1;
@@ -754,6 +787,9 @@ int plan_step(vx_model *m, int n_seqs, const int *slots, const int32_t *position
     std::vector<int> kv_len, kv_start0, kv_start1;
     std::vector<char> seen(cf.max_seqs, 0);
     kv_len.reserve(rows);
+    p->special.clear(); p->routes.assign(n_seqs, 0);
+    const bool pf_rows_ok = cf.head_dim == 64 || cf.head_dim == 128;
+    int row0 = 0, n_special_rows = 0;
     for (int i = 0; i < n_seqs; i++) {
         int s = slots[i], ql = q_lens ? q_lens[i] : 1;
         if (ql <= 0) return vx_fail(c, VX_E_BAD_ARG, "q_len[%d] = %d", i, ql);
@@ -764,14 +800,29 @@ int plan_step(vx_model *m, int n_seqs, const int *slots, const int32_t *position
         int nb_new = (positions[i] + ql + BS - 1) / BS;
         if (nb_new > cf.max_blocks_per_seq) return vx_fail(c, VX_E_OOM_BLOCKS, "sequence would need %d blocks (table width %d)", nb_new, cf.max_blocks_per_seq);
         need += std::max(0, nb_new - m->h_n_blocks[s]);
-        for (int j = 0; j < ql; j++) kv_len.push_back(positions[i] + j + 1);
+        if (prompt_rows && positions[i] == 0) p->routes[i] = 1;
+        else if (ql >= PF_MIN_ROWS && pf_rows_ok) p->routes[i] = 2;
+        if (p->routes[i]) n_special_rows += ql;
+        row0 += ql;
     }
     if (need > m->h_free) return vx_fail(c, VX_E_OOM_BLOCKS, "no free blocks: need %ld, have %d (max=%d)", need, m->h_free, cf.max_blocks);
-    kv_start0.assign(rows, 0); kv_start1.assign(rows, 0);
-    if (cf.sliding_window > 0) for (int t = 0; t < rows; t++) kv_start1[t] = std::max(0, kv_len[t] - cf.sliding_window);
+    // a head shape outside the work-list kernels falls back to a kernel that serves every row: no mixing with the prefill routes
+    if (!m->fast_attn_shape && n_special_rows != rows) { p->routes.assign(n_seqs, 0); n_special_rows = 0; }
+    row0 = 0;
+    for (int i = 0; i < n_seqs; i++) {
+        int ql = q_lens ? q_lens[i] : 1;
+        if (p->routes[i]) p->special.push_back(RowRange{row0, ql, p->routes[i]});
+        else for (int j = 0; j < ql; j++) kv_len.push_back(positions[i] + j + 1);
+        row0 += ql;
+    }
+    p->plain_rows = rows - n_special_rows;
+    kv_start0.assign(kv_len.size(), 0); kv_start1.assign(kv_len.size(), 0);
+    if (cf.sliding_window > 0) for (size_t t = 0; t < kv_len.size(); t++) kv_start1[t] = std::max(0, kv_len[t] - cf.sliding_window);
     p->n_seqs = n_seqs; p->rows = rows; p->chunk[0] = p->chunk[1] = 4; p->n_work[0] = p->n_work[1] = 0;
-    p->n_work[0] = plan_chunks(m, kv_start0, kv_len, &p->chunk[0]);
-    if (cf.sliding_window > 0) p->n_work[1] = plan_chunks(m, kv_start1, kv_len, &p->chunk[1]);
+    if (p->plain_rows > 0) {
+        p->n_work[0] = plan_chunks(m, kv_start0, kv_len, &p->chunk[0]);
+        if (cf.sliding_window > 0) p->n_work[1] = plan_chunks(m, kv_start1, kv_len, &p->chunk[1]);
+    }
     for (int i = 0; i < n_seqs; i++) {
         int s = slots[i], ql = q_lens ? q_lens[i] : 1;
         int nb_new = (positions[i] + ql + BS - 1) / BS;
@@ -781,11 +832,26 @@ int plan_step(vx_model *m, int n_seqs, const int *slots, const int32_t *position
     return VX_OK;
 }
 
+// After a step failed between the planning and its synchronisation the host mirror may be ahead of or behind the device
+// (the packing kernel refuses a step as a whole, a launch error can strike after it ran): read the device state back.
+void resync_mirror(vx_model *m) {
+    vx_ctx *c = m->c;
+    cudaStreamSynchronize(c->stream);
+    std::vector<int32_t> len(m->cfg.max_seqs), nb(m->cfg.max_seqs);
+    int32_t top = m->h_free;
+    bool ok = cudaMemcpy(len.data(), m->d_seq_len, 4 * len.size(), cudaMemcpyDeviceToHost) == cudaSuccess &&
+              cudaMemcpy(nb.data(), m->d_n_blocks, 4 * nb.size(), cudaMemcpyDeviceToHost) == cudaSuccess &&
+              cudaMemcpy(&top, m->d_free_top, 4, cudaMemcpyDeviceToHost) == cudaSuccess;
+    if (!ok) { cudaGetLastError(); return; }
+    for (int s = 0; s < m->cfg.max_seqs; s++) { m->h_seq_len[s] = len[s]; m->h_n_blocks[s] = nb[s]; }
+    m->h_free = top;
+}
+
 // Device half: packing kernel + the transformer stack, reading the step description already in d_step_in.
 static int g_graphs = 1;
 
 // pack kernel + the transformer stack for one planned step; n_work = grid sizes of the attention kernels
-int enqueue_kernels(vx_model *m, const StepPlan &p, int mode, int logit_rows, int n_work[2]) {
+int enqueue_kernels(vx_model *m, const StepPlan &p, int out_flags, int logit_rows, int n_work[2]) {
     vx_ctx *c = m->c; const vx_model_config &cf = m->cfg;
     PackArgs pa{};
     pa.step_in = m->d_step_in; pa.n_seqs = p.n_seqs; pa.n_rows = p.rows;
@@ -793,11 +859,12 @@ int enqueue_kernels(vx_model *m, const StepPlan &p, int mode, int logit_rows, in
     pa.free_list = m->d_free_list; pa.free_top = m->d_free_top; pa.refcnt = m->d_refcnt; pa.status = m->d_status;
     pa.cu = m->d_cu; pa.row_slot = m->d_row_slot; pa.row_pos = m->d_row_pos; pa.slot_map = m->d_slot_map;
     pa.row_kv_len = m->d_row_kv_len; pa.row_kv_start = m->d_row_kv_start; pa.window = cf.sliding_window;
+    pa.row_route = m->d_row_route; pa.last_row = m->d_last_row;
     pa.work0 = m->d_work[0]; pa.work1 = m->d_work[1]; pa.rws0 = m->d_rws[0]; pa.rws1 = m->d_rws[1];
     pa.n_work0 = m->d_n_work[0]; pa.n_work1 = m->d_n_work[1]; pa.chunk0 = p.chunk[0]; pa.chunk1 = p.chunk[1]; pa.max_work = MAX_WORK;
     pack_kernel<<<1, 1024, 0, c->stream>>>(pa);
     VX_LAUNCH_CHECK(c);
-    return forward(m, p.rows, mode, n_work, p.chunk, logit_rows);
+    return forward(m, p.rows, p.special, p.plain_rows, n_work, p.chunk, logit_rows, out_flags);
 }
 
 // A decode step is ~250-330 small launches, and a thin batch is bound by the host's launch rate rather than by the GPU.
@@ -805,15 +872,16 @@ int enqueue_kernels(vx_model *m, const StepPlan &p, int mode, int logit_rows, in
 // sequence and row counts, the split-K chunk sizes, and the attention grids rounded up to a multiple of 32 work items
 // (CTAs beyond the device-side count return at once), so that a key survives many steps while the contexts grow.
 // The first step of a key runs eagerly (it also makes every lazy allocation and attribute call), the second is captured.
-int enqueue_step(vx_model *m, const StepPlan &p, int mode, int logit_rows) {
+int enqueue_step(vx_model *m, const StepPlan &p, int out_flags, int logit_rows) {
     vx_ctx *c = m->c;
     m->last_rows = p.rows; m->last_seqs = p.n_seqs;
     if (m->capture_on) m->capture_rows = p.rows;
     int n_work[2] = {p.n_work[0], p.n_work[1]};
-    const bool can_graph = g_graphs && mode == 0 && !m->capture_on && !m->time_on[0] && !m->time_on[1];
+    // steps with prefill routes launch one kernel per routed entry, so their launch sequence is not a function of the key
+    const bool can_graph = g_graphs && p.special.empty() && !m->capture_on && !m->time_on[0] && !m->time_on[1];
     if (can_graph) {
         for (int i = 0; i < 2; i++) if (n_work[i] > 0) n_work[i] = std::min(MAX_WORK, (n_work[i] + 31) / 32 * 32);
-        const vx_model::GraphKey key{p.n_seqs, p.rows, logit_rows, p.chunk[0], p.chunk[1], n_work[0], n_work[1]};
+        const vx_model::GraphKey key{p.n_seqs, p.rows, logit_rows, p.chunk[0], p.chunk[1], n_work[0], n_work[1], out_flags};
         if (m->graphs.size() > 256) {                    // shapes no longer in use: start over rather than grow without bound
             for (auto &kv : m->graphs) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
             m->graphs.clear();
@@ -827,13 +895,13 @@ int enqueue_step(vx_model *m, const StepPlan &p, int mode, int logit_rows) {
             for (auto &kv : m->graphs) {
                 const vx_model::GraphKey &k = kv.first;
                 if (kv.second.exec && k.n_seqs == key.n_seqs && k.rows == key.rows && k.logit_rows == key.logit_rows && k.chunk0 == key.chunk0 &&
-                    k.chunk1 == key.chunk1) { sib = &kv.second; break; }
+                    k.chunk1 == key.chunk1 && k.out_flags == key.out_flags) { sib = &kv.second; break; }
             }
         if (!e.exec && (e.seen >= 1 || sib) && e.seen < 1000000) {
             const uint64_t l0 = c->launches;
             cudaGraph_t g = nullptr;
             bool ok = cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeRelaxed) == cudaSuccess;
-            int rc = ok ? enqueue_kernels(m, p, mode, logit_rows, n_work) : VX_OK;
+            int rc = ok ? enqueue_kernels(m, p, out_flags, logit_rows, n_work) : VX_OK;
             if (ok) ok = cudaStreamEndCapture(c->stream, &g) == cudaSuccess && g != nullptr && rc == VX_OK;
             if (ok && sib) {
                 cudaGraphExecUpdateResultInfo info;
@@ -855,28 +923,30 @@ int enqueue_step(vx_model *m, const StepPlan &p, int mode, int logit_rows) {
         }
         if (e.seen < 1000000) e.seen++;
     }
-    VX_TRY(enqueue_kernels(m, p, mode, logit_rows, n_work));
+    VX_TRY(enqueue_kernels(m, p, out_flags, logit_rows, n_work));
     m->steps++;
     return VX_OK;
 }
 
-int run_step(vx_model *m, int n_seqs, const int *slots, const int32_t *tokens, const int32_t *positions, const int32_t *q_lens,
-             int mode, int logit_rows_req, int32_t *out_tokens, float *logits, const vx_sample_params *sample = nullptr) {
+// step flags of the C ABI (vexel_cuda.h) -> what the stack has to produce
+int run_step_planned(vx_model *m, const StepPlan &p, int n_seqs, const int *slots, const int32_t *tokens, const int32_t *positions,
+                     const int32_t *q_lens, int out_flags, int logit_rows, int32_t *out_tokens, float *logits, const vx_sample_params *sample,
+                     float *hidden) {
     vx_ctx *c = m->c; const vx_model_config &cf = m->cfg;
-    StepPlan p;
-    VX_TRY(plan_step(m, n_seqs, slots, positions, q_lens, &p));
     int32_t *h = m->h_step_in;
-    for (int i = 0; i < n_seqs; i++) { h[i] = slots[i]; h[n_seqs + i] = q_lens ? q_lens[i] : 1; h[2 * n_seqs + i] = positions[i]; }
-    memcpy(h + 3 * n_seqs, tokens, sizeof(int32_t) * p.rows);
-    VX_CUDA(c, cudaMemcpyAsync(m->d_step_in, h, sizeof(int32_t) * (3 * n_seqs + p.rows), cudaMemcpyHostToDevice, c->stream));
-    int logit_rows = logit_rows_req > 0 ? logit_rows_req : p.rows;
-    VX_TRY(enqueue_step(m, p, mode, logit_rows));
+    for (int i = 0; i < n_seqs; i++) {
+        h[i] = slots[i]; h[n_seqs + i] = q_lens ? q_lens[i] : 1; h[2 * n_seqs + i] = positions[i]; h[3 * n_seqs + i] = p.routes[i];
+    }
+    memcpy(h + 4 * n_seqs, tokens, sizeof(int32_t) * p.rows);
+    VX_CUDA(c, cudaMemcpyAsync(m->d_step_in, h, sizeof(int32_t) * (4 * n_seqs + p.rows), cudaMemcpyHostToDevice, c->stream));
+    VX_TRY(enqueue_step(m, p, out_flags, logit_rows));
     if (logits && cf.final_softcap > 0.f) {
         long n = (long)logit_rows * cf.vocab;
         final_softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(m->logits, n, cf.final_softcap);
         VX_LAUNCH_CHECK(c);
     }
     if (logits) VX_CUDA(c, cudaMemcpyAsync(logits, m->logits, sizeof(float) * (size_t)logit_rows * cf.vocab, cudaMemcpyDeviceToHost, c->stream));
+    if (hidden) VX_CUDA(c, cudaMemcpyAsync(hidden, m->d_hidden, sizeof(float) * (size_t)logit_rows * cf.hidden, cudaMemcpyDeviceToHost, c->stream));
     if (sample) {
         // rows with temperature 0 keep the argmax; the others are drawn on the device from the logits in place
         // (scheduler.go:783-820 copies the logits to the host and samples there)
@@ -888,6 +958,21 @@ int run_step(vx_model *m, int n_seqs, const int *slots, const int32_t *tokens, c
     time_collect(m);
     if (out_tokens) memcpy(out_tokens, m->h_out_tok, sizeof(int32_t) * logit_rows);
     return VX_OK;
+}
+
+// flags: VX_STEP_* of the C ABI.  logit_rows_req > 0: outputs for that many trailing rows only (prefill: 1).
+int run_step(vx_model *m, int n_seqs, const int *slots, const int32_t *tokens, const int32_t *positions, const int32_t *q_lens,
+             int flags, int logit_rows_req, int32_t *out_tokens, float *logits, const vx_sample_params *sample = nullptr,
+             float *hidden = nullptr) {
+    StepPlan p;
+    VX_TRY(plan_step(m, n_seqs, slots, positions, q_lens, (flags & VX_STEP_PROMPT_ROWS) != 0, &p));
+    int out_flags = hidden ? OUT_HIDDEN : 0;
+    int logit_rows = p.rows;
+    if (logit_rows_req > 0) logit_rows = logit_rows_req;
+    else if (flags & VX_STEP_LAST_ROWS) { logit_rows = n_seqs; if (n_seqs != p.rows) out_flags |= OUT_LAST_ROWS; }   // no gather when every entry has one row
+    int rc = run_step_planned(m, p, n_seqs, slots, tokens, positions, q_lens, out_flags, logit_rows, out_tokens, logits, sample, hidden);
+    if (rc != VX_OK) resync_mirror(m);
+    return rc;
 }
 
 int get_slot(vx_model *m, int64_t id, bool create, int *slot) {
@@ -949,13 +1034,19 @@ int vx_model_create(vx_ctx *c, const vx_model_config *cfg, vx_model **out) {
     m->h_seq_len.assign(cfg->max_seqs, 0); m->h_n_blocks.assign(cfg->max_seqs, 0);
     for (int s = cfg->max_seqs - 1; s >= 0; s--) m->free_slots.push_back(s);
     // ---- step buffers
-    const size_t step_ints = (size_t)3 * cfg->max_seqs + T;
+    const size_t step_ints = (size_t)4 * cfg->max_seqs + T;
     MA(model_alloc_t(m, step_ints, &m->d_step_in));
     if (cudaMallocHost(&m->h_step_in, step_ints * 4) != cudaSuccess || cudaMallocHost(&m->h_out_tok, (size_t)(T + 8) * 4) != cudaSuccess) return fail(VX_E_OOM);
     MA(model_alloc_t(m, (size_t)cfg->max_seqs + 1, &m->d_cu));
     MA(model_alloc_t(m, (size_t)T, &m->d_row_slot)); MA(model_alloc_t(m, (size_t)T, &m->d_row_pos));
     MA(model_alloc_t(m, (size_t)T, &m->d_slot_map)); MA(model_alloc_t(m, (size_t)T, &m->d_row_kv_len));
-    MA(model_alloc_t(m, (size_t)std::max(T, cfg->max_seqs), &m->d_row_kv_start));
+    MA(model_alloc_t(m, (size_t)std::max(T, cfg->max_seqs) + 1, &m->d_row_kv_start));
+    MA(model_alloc_t(m, (size_t)T, &m->d_row_route)); MA(model_alloc_t(m, (size_t)cfg->max_seqs, &m->d_last_row));
+    MA(model_alloc_t(m, (size_t)T * H, &m->d_hidden));
+    {
+        const int G = cfg->n_heads / cfg->n_kv_heads;
+        m->fast_attn_shape = (D == 64 || D == 128 || D == 256) && (G == 1 || G == 2 || G == 4 || G == 8) && (nqkv % 4 == 0);
+    }
     for (int i = 0; i < 2; i++) {
         MA(model_alloc_t(m, (size_t)MAX_WORK, &m->d_work[i]));
         MA(model_alloc_t(m, (size_t)T + 1, &m->d_rws[i]));
@@ -1238,6 +1329,21 @@ int vx_pool_stats(vx_model *m, int *total, int *free_blocks, int *shared) {
     return VX_OK;
 }
 
+// the free list as the stack it is, bottom first: the next block handed out is the last entry (gpu_block_pool.go:200-208)
+int vx_pool_free_list(vx_model *m, int32_t *out, int cap, int *n_out) {
+    if (!m || !n_out) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    VX_TRY(refresh_free(m));
+    *n_out = m->h_free;
+    const int n = std::min(m->h_free, cap);
+    if (out && n > 0) {
+        VX_CUDA(c, cudaMemcpyAsync(out, m->d_free_list, 4 * (size_t)n, cudaMemcpyDeviceToHost, c->stream));
+        VX_CUDA(c, cudaStreamSynchronize(c->stream));
+    }
+    return VX_OK;
+}
+
 int vx_pool_layer_ptr(vx_model *m, int layer, vx_dptr *out, size_t *bytes) {
     if (!m || !out || layer < 0 || layer >= m->cfg.n_layers) return VX_E_BAD_ARG;
     *out = (vx_dptr)(uintptr_t)(m->pool + (size_t)layer * m->layer_stride);
@@ -1292,6 +1398,24 @@ int vx_decode_step(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_
     return run_step(m, n_seqs, slots.data(), tokens, positions, q_lens, 0, 0, out_tokens, logits);
 }
 
+// vx_decode_step with options.  flags: VX_STEP_LAST_ROWS = outputs (tokens, logits, hidden, sampling records) cover the last
+// row of every batch entry only, n_seqs rows in batch order; VX_STEP_PROMPT_ROWS = multi-row entries are prompt chunks
+// (PrefillWithPagedKV, runtime/decode.go:961-1096): an entry that starts at position 0 attends over its fresh float32 K/V.
+// hidden (optional, host): post-final-norm hidden states of the output rows, [rows, hidden] float32, what
+// VerifySpeculativeWithPagedKVAndHidden hands to the Medusa heads (runtime/decode.go:1543-1557).
+int vx_decode_step_ex(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t *tokens, const int32_t *positions,
+                      const int32_t *q_lens, int flags, const vx_sample_params *params, int32_t *out_tokens, float *logits, float *hidden) {
+    if (!m) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    VX_REQUIRE(c, m->finalized, "model not finalized");
+    VX_REQUIRE(c, n_seqs > 0 && n_seqs <= m->cfg.max_seqs && seq_ids && tokens && positions, "bad arguments");
+    VX_REQUIRE(c, (flags & ~(VX_STEP_LAST_ROWS | VX_STEP_PROMPT_ROWS)) == 0, "unknown step flag");
+    std::vector<int> slots(n_seqs);
+    for (int i = 0; i < n_seqs; i++) VX_TRY(get_slot(m, seq_ids[i], true, &slots[i]));
+    return run_step(m, n_seqs, slots.data(), tokens, positions, q_lens, flags, 0, out_tokens, logits, params, hidden);
+}
+
 // vx_decode_step followed by Sampler.Sample (pkg/sampler/sampler.go:49-76) on the device: one parameter record per
 // packed row, the uniform draw supplied by the caller.  Rows with temperature 0 are greedy.
 int vx_decode_step_sampled(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t *tokens, const int32_t *positions,
@@ -1334,8 +1458,8 @@ int vx_decode_run(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t
         m->run_out_cap = (size_t)n_steps * n_seqs;
     }
     int32_t *h = m->h_step_in;
-    for (int i = 0; i < n_seqs; i++) { h[i] = slots[i]; h[n_seqs + i] = 1; h[2 * n_seqs + i] = positions[i]; h[3 * n_seqs + i] = tokens[i]; }
-    VX_CUDA(c, cudaMemcpyAsync(m->d_step_in, h, sizeof(int32_t) * 4 * n_seqs, cudaMemcpyHostToDevice, c->stream));
+    for (int i = 0; i < n_seqs; i++) { h[i] = slots[i]; h[n_seqs + i] = 1; h[2 * n_seqs + i] = positions[i]; h[3 * n_seqs + i] = 0; h[4 * n_seqs + i] = tokens[i]; }
+    VX_CUDA(c, cudaMemcpyAsync(m->d_step_in, h, sizeof(int32_t) * 5 * n_seqs, cudaMemcpyHostToDevice, c->stream));
     cudaEvent_t e0, e1;
     VX_CUDA(c, cudaEventCreate(&e0)); VX_CUDA(c, cudaEventCreate(&e1));
     cudaEventRecord(e0, c->stream);
@@ -1343,7 +1467,7 @@ int vx_decode_run(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t
     int rc = VX_OK;
     for (int st = 0; st < n_steps && rc == VX_OK; st++) {
         StepPlan p;
-        rc = plan_step(m, n_seqs, slots.data(), pos.data(), nullptr, &p);
+        rc = plan_step(m, n_seqs, slots.data(), pos.data(), nullptr, false, &p);
         if (rc != VX_OK) break;
         if (st > 0) {
             advance_step_kernel<<<ceil_div(n_seqs, 256), 256, 0, c->stream>>>(m->d_step_in, n_seqs, m->d_out_tok);
@@ -1361,6 +1485,7 @@ int vx_decode_run(vx_model *m, int n_seqs, const int64_t *seq_ids, const int32_t
     cudaEventElapsedTime(&ms, e0, e1);
     cudaEventDestroy(e0); cudaEventDestroy(e1);
     if (device_ms) *device_ms = ms;
+    if (rc != VX_OK || rc2 != VX_OK) resync_mirror(m);
     if (rc != VX_OK) return rc;
     if (rc2 != VX_OK) return rc2;
     if (out_tokens) VX_CUDA(c, cudaMemcpy(out_tokens, m->d_run_out, sizeof(int32_t) * (size_t)n_steps * n_seqs, cudaMemcpyDeviceToHost));
@@ -1384,8 +1509,7 @@ static int prefill_impl(vx_model *m, int64_t id, const int32_t *tokens, int n_to
         bool last = done + n == n_tokens;
         // the first chunk of a prompt that starts at 0 attends over its own float32 K/V (SDPAPrefill);
         // later chunks read the paged fp16 cache like the multi-query verify path
-        int mode = (pos == 0) ? 1 : 0;
-        VX_TRY(run_step(m, 1, &slot, tokens + done, &pos, &ql, mode, 1, last ? out_token : nullptr, last ? logits : nullptr,
+        VX_TRY(run_step(m, 1, &slot, tokens + done, &pos, &ql, VX_STEP_PROMPT_ROWS, 1, last ? out_token : nullptr, last ? logits : nullptr,
                         last ? sample : nullptr));
         done += n;
     }

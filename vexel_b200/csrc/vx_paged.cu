@@ -742,12 +742,12 @@ int vxp_prefill_f32(vx_ctx *c, const float *q, int q_ld, const float *k, const f
     dim3 grid(ceil_div(n_rows, PF_ROWS), hq);
     const int smem = 4 * PF_TOK * d * 2;
     if (d == 64) {
-        static bool done = false;
-        if (!done) { VX_CUDA(c, cudaFuncSetAttribute(prefill_f32_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); done = true; }
+        static VxPerDevice attr;
+        VX_CUDA(c, attr.max_dynamic_smem(c, prefill_f32_mma_kernel<64>, smem));
         prefill_f32_mma_kernel<64><<<grid, 128, smem, c->stream>>>(q, q_ld, k, v, kv_ld, out, out_ld, n_rows, hq, hkv, scale, softcap);
     } else {
-        static bool done = false;
-        if (!done) { VX_CUDA(c, cudaFuncSetAttribute(prefill_f32_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); done = true; }
+        static VxPerDevice attr;
+        VX_CUDA(c, attr.max_dynamic_smem(c, prefill_f32_mma_kernel<128>, smem));
         prefill_f32_mma_kernel<128><<<grid, 128, smem, c->stream>>>(q, q_ld, k, v, kv_ld, out, out_ld, n_rows, hq, hkv, scale, softcap);
     }
     VX_LAUNCH_CHECK(c);
@@ -762,12 +762,12 @@ int vxp_prefill_rows(vx_ctx *c, const VxAttnArgs &a, int row0, int n_rows) {
     dim3 grid(ceil_div(n_rows, PF_ROWS), a.n_q_heads);
     const int smem = 2 * 2 * PF_TOK * D * 2;
     if (D == 64) {
-        static bool done = false;
-        if (!done) { VX_CUDA(c, cudaFuncSetAttribute(paged_prefill_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); done = true; }
+        static VxPerDevice attr;
+        VX_CUDA(c, attr.max_dynamic_smem(c, paged_prefill_mma_kernel<64>, smem));
         paged_prefill_mma_kernel<64><<<grid, 128, smem, c->stream>>>(a, row0, n_rows);
     } else {
-        static bool done = false;
-        if (!done) { VX_CUDA(c, cudaFuncSetAttribute(paged_prefill_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); done = true; }
+        static VxPerDevice attr;
+        VX_CUDA(c, attr.max_dynamic_smem(c, paged_prefill_mma_kernel<128>, smem));
         paged_prefill_mma_kernel<128><<<grid, 128, smem, c->stream>>>(a, row0, n_rows);
     }
     VX_LAUNCH_CHECK(c);
@@ -858,11 +858,8 @@ static int flash_launch_mma(vx_ctx *c, const VxAttnArgs &a, dim3 grid) {
     constexpr int NW = D == 256 ? 2 : ATT_WARPS;
     constexpr int SMEM = NW * 2 * 2 * ATT_BS * D * 2;      // per warp: two stages of a K and a V page tile
     static_assert(SMEM >= (int)((NW * G * D + 2 * NW * G) * sizeof(float)), "merge buffers fit in the staging area");
-    static bool attr_done = false;
-    if (!attr_done) {
-        if (cudaFuncSetAttribute(paged_flash_mma_kernel<D, G, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
-        attr_done = true;
-    }
+    static VxPerDevice attr;
+    if (attr.max_dynamic_smem(c, paged_flash_mma_kernel<D, G, NW>, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
     paged_flash_mma_kernel<D, G, NW><<<grid, NW * 32, SMEM, c->stream>>>(a);
     return 0;
 }
@@ -939,7 +936,7 @@ __global__ void iface_build_work_kernel(int rows, const int32_t *kv_start, const
     __shared__ int ovf;
     if (threadIdx.x == 0) ovf = 0;
     __syncthreads();
-    int n = vx_build_work(rows, kv_start, kv_len, block_size, chunk_pages, work, row_work_start, max_work, &ovf, tmp);
+    int n = vx_build_work(rows, kv_start, kv_len, nullptr, block_size, chunk_pages, work, row_work_start, max_work, &ovf, tmp);
     if (threadIdx.x == 0) *n_work = n;
 }
 
@@ -995,7 +992,7 @@ constexpr int VX_NOALLOC_MAX_WORK = 1024;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[VX_NOALLOC_SCRATCH_BYTES];
 // The array's name is a host-side stand-in in host code, not a device address: the address comes from
 // cudaGetSymbolAddress, asked once per device with that device current.
-static void *g_noalloc_dev_ptr[64] = {nullptr};
+static std::atomic<void *> g_noalloc_dev_ptr[64];     // zero-initialised; contexts on different threads may race to fill an entry with the same value
 
 struct NoAllocLayout { size_t tab, slot, ks, kl, rws, nw, work, part; };
 static NoAllocLayout noalloc_layout() {
@@ -1018,7 +1015,7 @@ __global__ void noalloc_setup_kernel(unsigned char *scratch, NoAllocLayout L, co
         *reinterpret_cast<int32_t *>(scratch + L.kl) = kv_len;
     }
     __syncthreads();
-    int n = vx_build_work(1, reinterpret_cast<const int32_t *>(scratch + L.ks), reinterpret_cast<const int32_t *>(scratch + L.kl), block_size,
+    int n = vx_build_work(1, reinterpret_cast<const int32_t *>(scratch + L.ks), reinterpret_cast<const int32_t *>(scratch + L.kl), nullptr, block_size,
                           chunk_pages, reinterpret_cast<int4 *>(scratch + L.work), reinterpret_cast<int32_t *>(scratch + L.rws),
                           VX_NOALLOC_MAX_WORK, &ovf, tmp);
     if (threadIdx.x == 0) *reinterpret_cast<int32_t *>(scratch + L.nw) = n;
@@ -1104,8 +1101,10 @@ int vx_sdpa_paged_decode_multiquery(vx_ctx *c, vx_dptr q, vx_dptr pool, vx_dptr 
 // Same result as vx_sdpa_paged_decode_f16, but the call allocates nothing: no cudaMalloc / cudaFree, no growth of the
 // context scratch, no host heap.  Limits: head_dim <= 256, n_q_heads * (head_dim + 2) * 4 bytes per split-K chunk must fit
 // the 4 MiB array (the number of chunks shrinks to fit; at worst one chunk per row), n_blocks <= 65536; anything larger is
-// refused with VX_E_BAD_ARG.  The first call on a device looks up the array's address (cudaGetSymbolAddress); make that
-// first call before starting a stream capture.  All calls share the one array, which keeps the previous call's contents
+// refused with VX_E_BAD_ARG (so is a block size above 16384, which keeps kv_len inside an int).  The first call on a device
+// looks up the array's address (cudaGetSymbolAddress) and may make the driver load this library's kernels for that device,
+// which can allocate inside the driver: make one warm-up call per device outside the section that must not allocate, and
+// before starting a stream capture.  All calls share the one array, which keeps the previous call's contents
 // (nothing in it needs to start at zero: every field is written before it is read), so two calls that overlap on the GPU
 // -- different streams or contexts of one process -- race.
 int vx_sdpa_paged_decode_f16_noalloc(vx_ctx *c, vx_dptr q, vx_dptr pool, vx_dptr table, vx_dptr out, int n_blocks, int bs, int hq,
@@ -1113,16 +1112,17 @@ int vx_sdpa_paged_decode_f16_noalloc(vx_ctx *c, vx_dptr q, vx_dptr pool, vx_dptr
     if (!c) return VX_E_BAD_ARG;
     VxGuard g(c);
     VX_REQUIRE(c, q && pool && out && table, "nil device pointer");
-    VX_REQUIRE(c, n_blocks > 0 && n_blocks <= 65536 && bs > 0 && til > 0 && til <= bs, "bad block table arguments (n_blocks <= 65536)");
+    VX_REQUIRE(c, n_blocks > 0 && n_blocks <= 65536 && bs > 0 && bs <= 16384 && til > 0 && til <= bs,
+               "bad block table arguments (n_blocks <= 65536, block size <= 16384)");
     VX_REQUIRE(c, hq > 0 && hkv > 0 && hq % hkv == 0 && d > 0 && d <= 256, "bad head configuration (head_dim <= 256)");
     VX_REQUIRE(c, c->device >= 0 && c->device < 64, "device index out of range");
-    if (!g_noalloc_dev_ptr[c->device]) {     // once per device, with that device current (VxGuard made it so)
-        void *p = nullptr;
-        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-        if (e != cudaSuccess || !p) return vx_cuda_fail(c, e, "cudaGetSymbolAddress(no-alloc scratch)");
-        g_noalloc_dev_ptr[c->device] = p;
+    void *sym = g_noalloc_dev_ptr[c->device].load(std::memory_order_acquire);
+    if (!sym) {     // once per device, with that device current (VxGuard made it so)
+        cudaError_t e = cudaGetSymbolAddress(&sym, g_noalloc_scratch);
+        if (e != cudaSuccess || !sym) return vx_cuda_fail(c, e, "cudaGetSymbolAddress(no-alloc scratch)");
+        g_noalloc_dev_ptr[c->device].store(sym, std::memory_order_release);
     }
-    unsigned char *sp = static_cast<unsigned char *>(g_noalloc_dev_ptr[c->device]);
+    unsigned char *sp = static_cast<unsigned char *>(sym);
     const NoAllocLayout L = noalloc_layout();
     const size_t per_chunk = (size_t)hq * (d + 2) * sizeof(float);
     if (L.part + per_chunk > VX_NOALLOC_SCRATCH_BYTES)

@@ -28,7 +28,8 @@ __device__ __forceinline__ int vx_block_excl_scan(int v, int *tmp, int *total) {
 // first_page..last_page are cut into chunks of chunk_pages.  work[i] = (row, first page, page count,
 // chunk index within the row); row_work_start[r] = index of the row's first chunk.  Must be called by
 // every thread of the block.  Returns the number of work items (clamped to max_work, *overflow set).
-__device__ __forceinline__ int vx_build_work(int rows, const int32_t *kv_start, const int32_t *kv_len, int block_size,
+// row_route (optional): rows with a non-zero entry are served by another attention kernel and get no work items.
+__device__ __forceinline__ int vx_build_work(int rows, const int32_t *kv_start, const int32_t *kv_len, const int32_t *row_route, int block_size,
                                              int chunk_pages, int4 *work, int32_t *row_work_start, int max_work,
                                              int *overflow, int *scan_tmp) {
     int base = 0;
@@ -37,7 +38,7 @@ __device__ __forceinline__ int vx_build_work(int rows, const int32_t *kv_start, 
         int fp = 0, np = 0, nc = 0;
         if (r < rows) {
             int ks = kv_start ? kv_start[r] : 0, kl = kv_len[r];
-            if (kl > ks) {
+            if (kl > ks && !(row_route && row_route[r] != 0)) {
                 fp = ks / block_size;
                 np = (kl - 1) / block_size - fp + 1;
                 nc = (np + chunk_pages - 1) / chunk_pages;

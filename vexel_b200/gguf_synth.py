@@ -205,6 +205,50 @@ def synth_tensors(spec: ModelSpec, seed=0):
     yield -1, capi.G_OUTPUT, out_type, qmat(spec.vocab, spec.hidden, out_type)
 
 
+def synth_weights_on_device(be, model, spec, seed, sink=None):
+    """Random weights of the model's shape and block formats, generated by CUDA kernels straight into GGUF blocks (Q4_0 by the
+    benchmark's quantisation rule from N(0, sigma) draws; Q4_K / Q6_K as valid blocks with hashed payload).  The token
+    embedding is kept in Q4_0 for every workload: it is read B rows per step and is not part of the timed traffic.
+    sink(layer, slot, type, raw) -- optional -- receives every tensor as host data too (uint8 GGUF bytes, or the float32
+    norm vectors), so that a checker can be given the same model."""
+    ones = np.ones(spec.hidden, np.float32)
+    proj_types, _, out_type = tensor_types(spec)
+    per_elem = {capi.T_Q4_0: 18 / 32, capi.T_Q4_K: 144 / 256, capi.T_Q6_K: 210 / 256}
+    big = max(spec.vocab * spec.hidden, spec.ffn * spec.hidden)
+    d_tmp = be.AllocPermanent(int(big * max(per_elem.values())) + 256)
+    n_t = 0
+
+    def q(layer, slot, n, k, t):
+        nonlocal n_t
+        if t == capi.T_Q4_0:
+            be.SynthQ4_0(d_tmp, n * k, seed * 100003 + n_t, spec.sigma)
+        else:
+            be.SynthKQuant(d_tmp, t, n * k, seed * 100003 + n_t, spec.sigma)
+        nbytes = int(n * k * per_elem[t])
+        model.set_tensor(layer, slot, t, (d_tmp, nbytes))
+        if sink is not None:
+            sink(layer, slot, t, be.download(d_tmp, nbytes, np.uint8))
+        n_t += 1
+
+    def norm(layer, slot):
+        model.set_tensor(layer, slot, capi.T_F32, ones)
+        if sink is not None:
+            sink(layer, slot, capi.T_F32, ones)
+
+    q(-1, capi.G_EMBED, spec.vocab, spec.hidden, capi.T_Q4_0)
+    for layer in range(spec.n_layers):
+        norm(layer, capi.W_ATTN_NORM); norm(layer, capi.W_FFN_NORM)
+        if spec.post_norms:
+            norm(layer, capi.W_POST_ATTN_NORM); norm(layer, capi.W_POST_FFN_NORM)
+        for slot in (capi.W_WQ, capi.W_WK, capi.W_WV, capi.W_WO, capi.W_W1, capi.W_W3, capi.W_W2):
+            n, k = slot_shape(spec, slot)
+            q(layer, slot, n, k, proj_types[slot])
+    norm(-1, capi.G_FINAL_NORM)
+    q(-1, capi.G_OUTPUT, spec.vocab, spec.hidden, out_type)
+    be.Free(d_tmp)
+    model.finalize()
+
+
 def model_config(spec: ModelSpec, max_blocks, max_seqs, max_batch_tokens, max_blocks_per_seq) -> capi.ModelConfig:
     return capi.ModelConfig(
         n_layers=spec.n_layers, hidden=spec.hidden, n_heads=spec.n_heads, n_kv_heads=spec.n_kv_heads,
