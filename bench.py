@@ -28,9 +28,10 @@ from vexel_b200 import capi, gguf_synth as gs, replicas  # noqa: E402
 
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one paged_flash_kernel launch divided by its algorithmic bytes,
-# from the ncu capture summarised in profiles/ (None until a capture has been taken)
-ATTN_TRAFFIC_RATIO = 1.0137   # profiles/paged_flash_kernel_llama2-7b_B64.md: 1.2256 GB DRAM traffic / 1.2090 GB algorithmic (traffic grows with the KV bytes)
+# dram__bytes_read.sum + dram__bytes_write.sum of one paged attention launch divided by its algorithmic bytes, from one ncu
+# capture of a smaller case of the same kernel (1.2256 GB of DRAM traffic for 1.2090 GB of KV); the traffic grows in
+# proportion to the KV bytes, so the figure reported per run is this ratio times the launch's algorithmic bytes
+ATTN_TRAFFIC_RATIO = 1.0137
 
 WORKLOADS = {
     "llama2-7b-q4_0": gs.C2_LLAMA2_7B,
@@ -97,71 +98,102 @@ class ClockSampler:
         return out
 
 
-def cpu_baseline(spec, seconds_target=15.0, sample_layers=2, sample_seqs=4, ctx=1088, threads=None):
-    """The CPU port of the reference's decode path (oracle/), timed on this host's cores on a bounded sample:
-    `sample_layers` layers + the output head of the named shape, `sample_seqs` sequences at context `ctx`, decoded one
-    sequence at a time as the reference's batched path does (runtime/decode.go:623-654).  Layer time is scaled to the
-    full depth.  Random Q4_0 bytes stand in for the weights (timing does not depend on the values)."""
-    from oracle import oracle as O
-    threads = threads or os.cpu_count() or 1
-    O.lib().vo_set_threads(threads)
-    rng = np.random.default_rng(0)
-    small = gs.scaled(spec, sample_layers, spec.hidden, spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.ffn, spec.vocab)
-    max_blocks = sample_seqs * ((ctx + 64) // 16 + 2)
-    cfg = O.Config(n_layers=small.n_layers, hidden=small.hidden, n_heads=small.n_heads, n_kv_heads=small.n_kv_heads,
-                   head_dim=small.head_dim, ffn=small.ffn, vocab=small.vocab, rms_eps=small.rms_eps, rope_theta=small.rope_theta,
-                   rope_neox=0, geglu=0, post_norms=0, embed_scale=0.0, attn_softcap=0.0, final_softcap=0.0, sliding_window=0,
-                   window_alternating=0, max_blocks=max_blocks, kv_f16=1)
-    om = O.Model(cfg)
+class CpuPort:
+    """The CPU port of the reference's decode path (oracle/) set up for timing: the named shape at FULL depth when its
+    weights are Q4_0 (the reference multiplies those straight from the blocks, backend/cpu/cpu.go:842-911), `n_seqs`
+    sequences with contexts drawn like the benchmark's, decoded one sequence at a time as the reference's batched path does
+    (runtime/decode.go:623-654) -- so its tok/s does not depend on how many sequences share a step.  K-quant shapes would need
+    their float32 expansion (the reference's CPU route for them, runtime/loader.go:214-271), which for the larger models does
+    not fit a host: those keep a `layers`-deep slice and scale its layer time.  Random block bytes stand in for the weights
+    and a repeated noise pattern for the KV pages: timing does not depend on the values."""
 
-    def rand_q4(n, k):
-        raw = rng.integers(0, 256, (n, k // 32, 18), dtype=np.uint8)
-        raw[:, :, 0:2] = np.array([0.0045], np.float16).view(np.uint8)     # d ~ 0.02 * 1.8 / 8
-        return raw
+    def __init__(self, spec, n_seqs, ctx_min, ctx_max, threads=None, slice_layers=2):
+        from oracle import oracle as O
+        self.O, self.spec = O, spec
+        self.threads = threads or os.cpu_count() or 1
+        O.lib().vo_set_threads(self.threads)
+        rng = np.random.default_rng(0)
+        self.full_depth = spec.quant == "q4_0"
+        self.layers = spec.n_layers if self.full_depth else min(slice_layers, spec.n_layers)
+        self.ctx = np.random.default_rng(replicas.GLOBAL_WORKLOAD_SEED).integers(ctx_min, ctx_max + 1, n_seqs)
+        max_blocks = int(sum((int(c) + 4096) // 16 + 2 for c in self.ctx))
+        cfg = O.Config(n_layers=self.layers, hidden=spec.hidden, n_heads=spec.n_heads, n_kv_heads=spec.n_kv_heads,
+                       head_dim=spec.head_dim, ffn=spec.ffn, vocab=spec.vocab, rms_eps=spec.rms_eps, rope_theta=spec.rope_theta,
+                       rope_neox=0, geglu=int(spec.geglu), post_norms=int(spec.post_norms), embed_scale=spec.embed_scale,
+                       attn_softcap=spec.attn_softcap, final_softcap=spec.final_softcap, sliding_window=spec.sliding_window,
+                       window_alternating=int(spec.window_alternating), max_blocks=max_blocks, kv_f16=1)
+        self.om = om = O.Model(cfg)
+        proj_types, _, out_type = gs.tensor_types(spec)
+        blk = {capi.T_Q4_0: (32, 18), capi.T_Q4_K: (256, 144), capi.T_Q6_K: (256, 210)}
 
-    ones = np.ones(spec.hidden, np.float32)
-    om.set_global(O.G_EMBED, O.Q4_0, rand_q4(spec.vocab, spec.hidden))
-    om.set_global(O.G_OUTPUT, O.Q4_0, rand_q4(spec.vocab, spec.hidden))
-    om.set_global(O.G_FINAL_NORM, O.F32, ones)
-    slots = {O.T_WQ: capi.W_WQ, O.T_WK: capi.W_WK, O.T_WV: capi.W_WV, O.T_WO: capi.W_WO, O.T_W1: capi.W_W1, O.T_W3: capi.W_W3, O.T_W2: capi.W_W2}
-    for layer in range(sample_layers):
-        om.set_layer(layer, O.T_ATTN_NORM, O.F32, ones); om.set_layer(layer, O.T_FFN_NORM, O.F32, ones)
-        for oslot, gslot in slots.items():
-            n, k = gs.slot_shape(spec, gslot)
-            om.set_layer(layer, oslot, O.Q4_0, rand_q4(n, k))
-    kvd = spec.n_kv_heads * spec.head_dim
-    kv = (rng.random((ctx, kvd), dtype=np.float32) - 0.5) * 0.2
-    for s in range(sample_seqs):
-        om.pool.create_seq(s + 1)
-        for layer in range(sample_layers):
-            om.pool.store_kv(layer, s + 1, 0, kv, kv, ctx)
-    import ctypes as C
-    L = O.lib()
-    tok = np.int32([7])
-    logits = np.empty((1, spec.vocab), np.float32)
+        def rand_blocks(n, k, t):
+            per, nbytes = blk[t]
+            raw = rng.integers(0, 256, (n, k // per, nbytes), dtype=np.uint8)
+            d = np.array([0.0045 if t == capi.T_Q4_0 else 0.0003], np.float16).view(np.uint8)     # block scales of N(0, 0.02) weights
+            if t == capi.T_Q6_K: raw[:, :, 208:210] = d
+            else: raw[:, :, 0:2] = d
+            if t == capi.T_Q4_K: raw[:, :, 2:4] = d
+            return raw
 
-    def run(with_head, pos):
+        ones = np.ones(spec.hidden, np.float32)
+        om.set_global(capi.G_EMBED, capi.T_Q4_0, rand_blocks(spec.vocab, spec.hidden, capi.T_Q4_0))
+        om.set_global(capi.G_OUTPUT, out_type, rand_blocks(spec.vocab, spec.hidden, out_type))
+        om.set_global(capi.G_FINAL_NORM, capi.T_F32, ones)
+        for layer in range(self.layers):
+            for slot in (capi.W_ATTN_NORM, capi.W_FFN_NORM) + ((capi.W_POST_ATTN_NORM, capi.W_POST_FFN_NORM) if spec.post_norms else ()):
+                om.set_layer(layer, slot, capi.T_F32, ones)
+            for slot in (capi.W_WQ, capi.W_WK, capi.W_WV, capi.W_WO, capi.W_W1, capi.W_W3, capi.W_W2):
+                n, k = gs.slot_shape(spec, slot)
+                om.set_layer(layer, slot, proj_types[slot], rand_blocks(n, k, proj_types[slot]))
+        pattern = ((rng.random(1 << 16, dtype=np.float32) - 0.5) * 0.2).astype(np.float16).view(np.uint16)
+        for layer in range(self.layers):
+            data = om.pool.layer_data(layer)
+            whole = data.size // pattern.size * pattern.size
+            data[:whole].reshape(-1, pattern.size)[:] = pattern
+            data[whole:] = pattern[:data.size - whole]
+            for i in range(n_seqs):
+                if layer == 0: om.pool.create_seq(i + 1)
+                om.pool.store_kv(layer, i + 1, 0, None, None, int(self.ctx[i]))       # pages allocated, contents = the pattern
+        self.pos = self.ctx.astype(np.int64).copy()
+        self.logits = np.empty((1, spec.vocab), np.float32)
+        self.tok = np.int32([7])
+        self.next_seq = 0
+
+    def decode(self, n_tokens):
+        """One new token for each of the next n_tokens sequences (round robin); returns the seconds it took."""
+        import ctypes as C
+        L = self.O.lib()
         t0 = time.perf_counter()
-        for s in range(sample_seqs):
-            L.vo_model_forward(om.h, s + 1, tok.ctypes.data_as(C.c_void_p), 1, pos, 0,
-                               logits.ctypes.data_as(C.c_void_p) if with_head else None, None)
+        for _ in range(n_tokens):
+            i = self.next_seq; self.next_seq = (i + 1) % len(self.ctx)
+            rc = L.vo_model_forward(self.om.h, i + 1, self.tok.ctypes.data_as(C.c_void_p), 1, int(self.pos[i]), 0,
+                                    self.logits.ctypes.data_as(C.c_void_p), None)
+            assert rc == 0, rc
+            self.pos[i] += 1
         return time.perf_counter() - t0
 
-    t_layers, t_total, steps, pos = [], [], 0, ctx
-    t_begin = time.perf_counter()
-    while steps < 1 or (time.perf_counter() - t_begin) < seconds_target * 0.6:
-        t_layers.append(run(False, pos)); pos += 1
-        t_total.append(run(True, pos)); pos += 1
-        steps += 1
-        if steps >= 8:
-            break
-    tl, tt = min(t_layers), min(t_total)
-    t_head = max(tt - tl, 0.0)
-    per_token = (tl / sample_layers * spec.n_layers + t_head) / sample_seqs
-    return {"value": 1.0 / per_token, "unit": "tok/s", "cores": threads, "kind": "port",
-            "sample": f"{sample_layers} of {spec.n_layers} layers + output head of the {spec.name} shape, {sample_seqs} sequences at context {ctx}, "
-                      f"{steps} timed decode steps, layer time scaled to {spec.n_layers} layers; C port of the reference CPU path "
-                      f"(inference/backend/cpu/cpu.go arithmetic, sequences decoded one at a time), OpenMP over output elements"}
+    def scale(self):
+        """tokens/s of the whole model per tokens/s measured: 1 at full depth, otherwise the slice's share of the layers (the head
+        is counted as part of the slice, which flatters the CPU a little)."""
+        return 1.0 if self.full_depth else self.layers / self.spec.n_layers
+
+    def describe(self, what):
+        depth = (f"all {self.spec.n_layers} layers + output head" if self.full_depth
+                 else f"{self.layers} of {self.spec.n_layers} layers + output head, layer time scaled to full depth")
+        return (f"{what}; {self.spec.name} shape, {depth}, contexts ~U[{int(self.ctx.min())},{int(self.ctx.max())}] drawn like the benchmark's; "
+                f"C port of the reference CPU path (inference/backend/cpu/cpu.go arithmetic, sequences decoded one at a time as "
+                f"runtime/decode.go:623-654 does), OpenMP over output elements")
+
+
+def cpu_baseline(spec, ctx_min, ctx_max, seconds_target=15.0):
+    """Bounded CPU sample timed beside the GPU number: a few sequences of the workload, one token each, until the time is up."""
+    port = CpuPort(spec, n_seqs=4, ctx_min=ctx_min, ctx_max=ctx_max)
+    port.decode(1)                                         # warm the caches and the thread pool
+    n, secs = 0, 0.0
+    while n < 4 or (secs < seconds_target and n < 64):
+        secs += port.decode(1); n += 1
+    return {"value": n / secs * port.scale(), "unit": "tok/s", "cores": port.threads, "kind": "port",
+            "sample": port.describe(f"{n} tokens decoded over 4 sequences in {secs:.1f} s")}
 
 
 def dist_setup(n_gpus):
@@ -170,21 +202,30 @@ def dist_setup(n_gpus):
 
 
 def reference_arm(args):
-    """Times the CPU port of the reference's path with all host threads, on a bounded sample of the same workload."""
+    """Times the CPU port of the reference's path with all host threads.  A step = one new token for each sequence of a bounded
+    sample of the batch (the reference loops over the sequences of a batch, so its tok/s is the same for any batch size); the
+    sample is sized from the first token's time so that W + K steps end within a few minutes."""
     world, rank, _ = replicas.rank_env()
     if rank != 0:
         return
     spec = WORKLOADS[args.workload]
-    vals = []
-    base = None
-    for _ in range(max(1, min(args.steps, 3))):
-        base = cpu_baseline(spec, seconds_target=20.0)
-        vals.append(base["value"])
-    v = float(np.median(vals))
-    base["value"] = v
-    line = {"impl": "reference", "metric": "decode tok/s", "value": v, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": args.batch / v * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic", "config": {"workload": f"{spec.name} batched decode B={args.batch}, ctx~U[128,2048], 16-token pages"},
+    K, W = args.steps, max(args.warmup, 1)
+    n_max = min(args.batch, 8)
+    port = CpuPort(spec, n_seqs=n_max, ctx_min=args.ctx_min, ctx_max=args.ctx_max)
+    t_tok = min(port.decode(1), port.decode(1))
+    n_s = int(max(1, min(n_max, 150.0 / ((K + W) * t_tok))))
+    for _ in range(W):
+        port.decode(n_s)
+    secs = [port.decode(n_s) for _ in range(K)]
+    step_s = float(np.mean(secs))
+    v = n_s / step_s * port.scale()
+    base = {"value": v, "unit": "tok/s", "cores": port.threads, "kind": "port",
+            "sample": port.describe(f"{K} timed steps of {n_s} of the batch's {args.batch} sequences each, {step_s * 1e3:.0f} ms per step")}
+    line = {"impl": "reference", "metric": "decode tok/s", "value": v, "unit": "tok/s", "n_gpus": args.gpus, "steps": K,
+            "warmup": W, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": {"workload": f"{spec.name} batched decode B={args.batch}, ctx~U[{args.ctx_min},{args.ctx_max}], 16-token pages"},
+            "sequences_per_step": n_s, "same_config": n_s == args.batch and port.full_depth, "extrapolated": not port.full_depth,
+            "note": "value = sampled sequences per step / measured step time; the reference decodes a batch one sequence at a time, so tok/s does not depend on the batch size",
             "cpu_baseline": base, "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     emit(line)
 
@@ -265,10 +306,21 @@ def main():
     if args.layers > 0:
         spec = gs.scaled(spec, args.layers, spec.hidden, spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.ffn, spec.vocab)
     B, K, W = args.batch, args.steps, max(args.warmup, 3)
+    Ka = Kg = min(K, 8)                             # short legs that time the attention and the projection launches
     seeds = replicas.rank_seeds(rank)
-    rng = np.random.default_rng(seeds["workload"])
-    ctx = rng.integers(args.ctx_min, args.ctx_max + 1, B)
-    total_new = W + 2 * K + 16                      # warm-up + device-resident leg + projection leg (the end-to-end leg rolls back)
+    # ONE arrival stream for the whole job: B * world contexts, placed by the dispatcher on the replica with the most free
+    # blocks.  Every rank replays the same stream and keeps its own share (no communication: the placement is a pure function
+    # of the stream).  At one GPU this is the plain draw of B contexts.
+    rng = np.random.default_rng(replicas.GLOBAL_WORKLOAD_SEED)
+    ctx_all = rng.integers(args.ctx_min, args.ctx_max + 1, B * world)
+    tokens_all = rng.integers(0, spec.vocab, B * world).astype(np.int32)
+    total_new = W + 2 * K + Ka + Kg + 16            # warm-up + device-resident leg + the two kernel legs (the end-to-end leg rolls back)
+    seq_cap = B + max(8, B // 8)                    # a replica may take a few more (or fewer) sequences than the mean
+    router = replicas.Dispatcher(world, blocks_per_replica=10 ** 9, max_seqs_per_replica=seq_cap)
+    owner = np.array([router.place(i, int(c) + total_new) for i, c in enumerate(ctx_all)])
+    mine = np.nonzero(owner == rank)[0]
+    ctx = ctx_all[mine]
+    Bl = int(len(mine))                             # this replica's sequences
     blocks_per_seq = int((args.ctx_max + total_new) // 16 + 2)
     max_blocks = int(sum((c + total_new) // 16 + 2 for c in ctx) + 64)
 
@@ -279,44 +331,52 @@ def main():
         be.lib.vx_set_dependent_launch(0)
     if args.no_graphs:
         be.lib.vx_set_graphs(0)
-    model = capi.Model(be, gs.model_config(spec, max_blocks, max_seqs=B, max_batch_tokens=max(B, 8), max_blocks_per_seq=blocks_per_seq))
+    model = capi.Model(be, gs.model_config(spec, max_blocks, max_seqs=seq_cap, max_batch_tokens=max(seq_cap, 8), max_blocks_per_seq=blocks_per_seq))
     gs.synth_weights_on_device(be, model, spec, seed=seeds["weights"])
     model.shuffle_free_list(seeds["free_list"])               # physical blocks shuffled randomly in the pool
-    seqs = np.arange(1, B + 1, dtype=np.int64)
+    seqs = np.arange(1, Bl + 1, dtype=np.int64)
     for i, s in enumerate(seqs):
         model.seq_fill_synthetic(int(s), int(ctx[i]), seed=seeds["kv_fill"] + i)
-    tokens = rng.integers(0, spec.vocab, B).astype(np.int32)
+    tokens = tokens_all[mine].copy()
     pos = ctx.astype(np.int32).copy()
 
-    # ---- warm-up (W >= 3 steps), then K timed steps with the tokens fed back on the device
+    def kv_tokens_over(pos0, n_steps):
+        """Sum over n_steps steps and the sequences of the attended length, as a per-layer mean (windowed layers attend less)."""
+        g = float(sum(int(p) * n_steps + n_steps * (n_steps + 1) // 2 for p in pos0))
+        n_slide = spec.n_layers // 2 if (spec.window_alternating and spec.sliding_window > 0) else 0   # odd layers slide
+        sl = float(sum(min(int(p) + j, spec.sliding_window) for p in pos0 for j in range(1, n_steps + 1))) if n_slide else 0.0
+        return ((spec.n_layers - n_slide) * g + n_slide * sl) / spec.n_layers
+
+    # ---- warm-up (W >= 3 steps; it also captures the step graphs), then K timed steps with the tokens fed back on the device.
+    # No per-kernel events in the timed steps: they replay from CUDA graphs exactly like the end-to-end leg.
     out, _ = model.decode_run(seqs, tokens, pos, W)
     tokens = out[-1].copy(); pos += W
     replicas.barrier(dist)
-    sampler = ClockSampler(local) if rank == 0 else None
+    sampler = ClockSampler(local)
     l0, s0 = model.counters()
-    # CUDA events around every launch of the dominant kernel (paged attention) during the timed steps; the projections are
-    # timed in a short leg of their own afterwards, because five more event pairs per layer cost the step ~6 %
-    model.kernel_time(0, 1); model.kernel_time(1, 0)
-    # sum over the K timed steps and the sequences of the attended length, for global layers and for sliding-window layers
-    kv_tokens_global = float(sum(int(p) * K + K * (K + 1) // 2 for p in pos))
-    n_slide = spec.n_layers // 2 if (spec.window_alternating and spec.sliding_window > 0) else 0   # odd layers slide
-    kv_tokens_slide = float(sum(min(int(p) + j, spec.sliding_window) for p in pos for j in range(1, K + 1))) if n_slide else 0.0
-    kv_tokens_timed = ((spec.n_layers - n_slide) * kv_tokens_global + n_slide * kv_tokens_slide) / spec.n_layers   # per-layer mean
+    g0 = model.graph_stats()[0]
+    kv_tokens_timed = kv_tokens_over(pos, K)
     pos_timed, tokens_timed = pos.copy(), tokens.copy()       # where the timed leg starts: the end-to-end leg starts there again
     out, dev_ms = model.decode_run(seqs, tokens, pos, K)
-    attn_ms, attn_n = model.kernel_time(0, 0)
     l1, s1 = model.counters()
-    clocks = sampler.stop() if sampler else None
+    replayed = model.graph_stats()[0] - g0
+    clocks = sampler.stop()
     tokens = out[-1].copy(); pos += K
-    Kg = min(K, 8)
+    replicas.barrier(dist)
+    value, max_s = replicas.job_throughput(dist, Bl * K, dev_ms / 1e3, local)
+    max_ms = max_s * 1e3
+    # ---- CUDA events around every launch of the dominant kernel (paged attention), in a leg of its own right after the timed
+    # region (events inside the timed steps would keep them out of graph replay); then the same for the projections
+    model.kernel_time(0, 1); model.kernel_time(1, 0)
+    kv_tokens_attn = kv_tokens_over(pos, Ka)
+    out, attn_leg_ms = model.decode_run(seqs, tokens, pos, Ka)
+    attn_ms, attn_n = model.kernel_time(0, 0)
+    tokens = out[-1].copy(); pos += Ka
     model.kernel_time(1, 1)
     out, _ = model.decode_run(seqs, tokens, pos, Kg)
     gemm_ms, gemm_n = model.kernel_time(1, 0)
-    gemm_ms = gemm_ms / Kg * K            # scaled to the K timed steps for the shares below
+    gemm_ms_per_step = gemm_ms / Kg
     tokens = out[-1].copy(); pos += Kg
-    replicas.barrier(dist)
-    value, max_s = replicas.job_throughput(dist, B * K, dev_ms / 1e3, local)
-    max_ms = max_s * 1e3
 
     # ---- end to end through vx_decode_step: host token ids in, host tokens out, every step
     e2e = None
@@ -334,45 +394,55 @@ def main():
             cur = model.decode_step(seqs, cur, pos)
             pos += 1
         be.Sync()
-        e2e_v, e2e_s = replicas.job_throughput(dist, B * K, time.perf_counter() - t0, local)
-        e2e = {"value": e2e_v, "unit": "tok/s", "h2d_bytes_per_step": int(4 * B * 4), "d2h_bytes_per_step": int(4 * B + 4),
+        e2e_v, e2e_s = replicas.job_throughput(dist, Bl * K, time.perf_counter() - t0, local)
+        e2e = {"value": e2e_v, "unit": "tok/s", "h2d_bytes_per_step": int(5 * Bl * 4), "d2h_bytes_per_step": int(4 * Bl + 4),
                "ms_per_step": e2e_s / K * 1e3}
+
+    kv_bytes_per_token_layer = 2 * spec.n_kv_heads * spec.head_dim * 2             # K and V, fp16
+    per_rank = replicas.gather_objects(dist, {
+        "rank": rank, "sequences": Bl, "ms_per_step": dev_ms / K, "kv_GB_per_step": kv_tokens_timed / K * kv_bytes_per_token_layer * spec.n_layers / 1e9,
+        "sm_mhz_median": clocks.get("sm_mhz"), "clock_reasons": clocks.get("reasons"), "graph_replayed_steps": int(replayed),
+        "attn_launch_ms": attn_ms / max(attn_n, 1)})
 
     if rank != 0:
         model.close(); be.close()
         replicas.shutdown(dist)
         return
 
-    # ---- roofline of the dominant kernel (paged attention) and of the whole step
+    # ---- roofline of the dominant kernel (paged attention) and of the whole step (rank 0's replica)
     peak, peak_kind = measured_peak()
-    kv_bytes_per_token_layer = 2 * spec.n_kv_heads * spec.head_dim * 2             # K and V, fp16
-    attn_bytes_per_launch = kv_tokens_timed * kv_bytes_per_token_layer / K         # one launch = one layer of one step
+    attn_bytes_per_launch = kv_tokens_attn * kv_bytes_per_token_layer / Ka         # one launch = one layer of one step
     attn_launch_ms = attn_ms / max(attn_n, 1)
     attn_gbs = attn_bytes_per_launch / (attn_launch_ms * 1e-3) / 1e9 if attn_n else None
     W_bytes = model.weight_bytes()
-    bytes_step = W_bytes + kv_tokens_timed / K * kv_bytes_per_token_layer * spec.n_layers + B * spec.n_layers * kv_bytes_per_token_layer
-    step_gbs = bytes_step / (max_ms / K * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "paged_flash_kernel (+merge), one launch per layer", "achieved": attn_gbs, "peak": peak, "unit": "GB/s",
+    bytes_step = W_bytes + kv_tokens_timed / K * kv_bytes_per_token_layer * spec.n_layers + Bl * spec.n_layers * kv_bytes_per_token_layer
+    step_ms = dev_ms / K                                                           # rank 0's own step time for rank 0's own bytes
+    step_gbs = bytes_step / (step_ms * 1e-3) / 1e9
+    attn_ms_per_step = attn_launch_ms * spec.n_layers
+    roofline = {"bound": "hbm", "kernel": "paged attention (flash kernel + merge/split), one launch pair per layer", "achieved": attn_gbs, "peak": peak, "unit": "GB/s",
                 "frac": (attn_gbs / peak) if attn_gbs else None, "peak_source": f"{peak_kind} copy bandwidth",
                 "traffic": (ATTN_TRAFFIC_RATIO * attn_bytes_per_launch) if ATTN_TRAFFIC_RATIO else None,
+                "traffic_note": "DRAM bytes of one ncu capture of a smaller case, scaled by the algorithmic bytes of this launch",
                 "algorithmic_bytes_per_launch": attn_bytes_per_launch, "launch_ms": attn_launch_ms,
-                "share_of_step": attn_ms / dev_ms if dev_ms else None,
-                "projections": {"timed_in": "a separate leg of %d steps right after the timed region" % Kg, "launch_ms_total_per_step": gemm_ms / K, "share_of_step": gemm_ms / dev_ms if dev_ms else None,
-                                "weight_bytes": W_bytes, "achieved_GBs": W_bytes / (gemm_ms / K * 1e-3) / 1e9 if gemm_ms else None}}
+                "timed_in": "a leg of %d steps right after the timed region, CUDA events around every launch" % Ka,
+                "share_of_step": attn_ms_per_step / step_ms if step_ms else None,
+                "projections": {"timed_in": "a leg of %d steps after the attention leg" % Kg, "launch_ms_total_per_step": gemm_ms_per_step,
+                                "share_of_step": gemm_ms_per_step / step_ms if step_ms else None,
+                                "weight_bytes": W_bytes, "achieved_GBs": W_bytes / (gemm_ms_per_step * 1e-3) / 1e9 if gemm_ms else None}}
     line = {"metric": "decode tok/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": max_ms / K,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations, %s weights, f16 kv" % spec.quant,
             "data": "synthetic",
-            "config": {"workload": f"{spec.name} batched decode, B={B} per GPU, ctx~U[{args.ctx_min},{args.ctx_max}] + generated, 16-token pages, shuffled blocks",
+            "config": {"workload": f"{spec.name} batched decode, B={B} per GPU ({B * world} sequences placed by free blocks), ctx~U[{args.ctx_min},{args.ctx_max}] + generated, 16-token pages, shuffled blocks",
                        "global_batch": world * B, "parallelism": f"replicas x{world} (request sharding, no collective)",
                        "l2": "inputs larger than L2: each step streams %.1f GB of weights+KV" % (bytes_step / 1e9),
-                       "timing": "CUDA events on the launching stream around K steps with on-device token feedback; max over ranks"},
+                       "timing": "CUDA events on the launching stream around K graph-replayed steps with on-device token feedback; max over ranks"},
             "roofline": roofline,
             "step_roofline": {"bytes_per_step": bytes_step, "achieved_GBs": step_gbs, "frac_of_measured": step_gbs / peak,
                               "frac_of_nominal_8TBs": step_gbs / NOMINAL_HBM_GBS,
                               "roofline_tok_s_measured": B / (bytes_step / (peak * 1e9)), "roofline_tok_s_nominal": B / (bytes_step / (NOMINAL_HBM_GBS * 1e9))},
-            "clocks": clocks, "gpu_launches": int(l1 - l0), "e2e": e2e}
+            "clocks": clocks, "gpu_launches": int(l1 - l0), "e2e": e2e, "per_rank": per_rank}
     if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(spec)
+        line["cpu_baseline"] = cpu_baseline(spec, args.ctx_min, args.ctx_max)
     emit(line)
     model.close(); be.close()
     replicas.shutdown(dist)

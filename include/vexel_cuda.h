@@ -329,7 +329,8 @@ int vx_sched_remove_sequence(vx_sched *s, int64_t id);                          
 int vx_sched_step(vx_sched *s, int *n_active_out);                                                         /* step :168-203 */
 /* TokenChan drain (sequence.go:70-80).  *finished: 0 = still running, 1 = ended and drained, 2 = ended because the request
  * was refused: its prompt plus token limit can never fit the block pool or one block table (where the reference stops its
- * whole loop with an allocation error, scheduler.go:134-136).  Once an end has been reported the request is forgotten. */
+ * whole loop with an allocation error, scheduler.go:134-136).  Requests whose end has been reported are forgotten once a few
+ * hundred of them have piled up (VX_E_NO_SEQ from then on), or when their id is added again. */
 int vx_sched_poll(vx_sched *s, int64_t id, int32_t *out, int cap, int *n_out, int *finished);
 int vx_sched_get_metrics(vx_sched *s, vx_sched_metrics *out);                                                /* Metrics :475-481 */
 /* how many times a sequence was preempted to free blocks (its tokens are read again later), and how many requests were

@@ -53,9 +53,14 @@ struct vx_sched {
     }
     vx_sample_params draw() { return vx_sample_params{cfg.temperature, cfg.top_k, cfg.top_p, uniform()}; }
     int limit_of(const Seq &q) const { return q.max_tokens > 0 ? q.max_tokens : cfg.max_tokens; }
-    void purge() {       // entries whose end the caller has seen
-        for (size_t i = 0; i < seqs.size();)
-            if (seqs[i].state == kFinished && seqs[i].reported && seqs[i].chan.empty()) seqs.erase(seqs.begin() + (long)i); else i++;
+    // Entries whose end the caller has seen stay pollable for a while (a client may ask again), but not for ever: beyond
+    // KEEP_REPORTED of them the oldest go, so the scans above stay short however many requests a server has seen.
+    static constexpr size_t KEEP_REPORTED = 256;
+    void purge() {
+        size_t n = 0;
+        for (auto &q : seqs) n += q.state == kFinished && q.reported && q.chan.empty();
+        for (size_t i = 0; i < seqs.size() && n > KEEP_REPORTED;)
+            if (seqs[i].state == kFinished && seqs[i].reported && seqs[i].chan.empty()) { seqs.erase(seqs.begin() + (long)i); n--; } else i++;
     }
 };
 
@@ -243,7 +248,8 @@ int vx_sched_step(vx_sched *s, int *n_active_out) {
 }
 
 // drains the sequence's token channel (Sequence.TokenChan).  *finished: 0 = running, 1 = ended and drained, 2 = ended
-// because it was refused (it could never fit the block pool); an ended sequence is forgotten after this call reported it
+// because it was refused (it could never fit the block pool); ended sequences whose end was reported are forgotten once
+// more than a few hundred of them have piled up
 int vx_sched_poll(vx_sched *s, int64_t id, int32_t *out, int cap, int *n_out, int *finished) {
     if (!s || !n_out) return VX_E_BAD_ARG;
     std::lock_guard<std::mutex> g(s->mu);

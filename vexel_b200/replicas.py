@@ -42,9 +42,75 @@ def shard(request_ids, world, rank):
     return ids[(ids % world) == rank]
 
 
+class Dispatcher:
+    """Places every arriving request on the replica with the most free KV blocks, for the request's whole life.
+
+    The reference admits every request into its one cache (Scheduler.AddSequence, inference/scheduler/scheduler.go:645-676).
+    With one cache per GPU the admission step gains a choice; a request's cost to a replica is the blocks its context will
+    hold, and a decode step lasts as long as the replica with the most resident KV, so the router keeps the free-block counts
+    level: most free blocks first, fewest resident sequences on a tie, lowest rank after that.  The decision is a pure
+    function of the arrival stream, so every rank that replays the same stream reaches the same placement without
+    talking to the others; `refresh` replaces the book-keeping by the replicas' measured free-block counts (one
+    all-gather) where lengths are not known in advance.
+    """
+
+    def __init__(self, world, blocks_per_replica, max_seqs_per_replica=0, block_tokens=16):
+        self.world, self.block_tokens = int(world), int(block_tokens)
+        self.free = [int(blocks_per_replica)] * self.world
+        self.seqs = [0] * self.world
+        self.max_seqs = int(max_seqs_per_replica)
+        self.placed = {}                      # request id -> (rank, blocks)
+
+    def blocks_for(self, tokens):
+        return (int(tokens) + self.block_tokens - 1) // self.block_tokens
+
+    def place(self, request_id, tokens):
+        """Returns the owning rank, or -1 when no replica can hold the request now (the caller queues it)."""
+        need = self.blocks_for(tokens)
+        best = -1
+        for r in range(self.world):
+            if self.free[r] < need or (self.max_seqs and self.seqs[r] >= self.max_seqs):
+                continue
+            if best < 0 or (self.free[r], -self.seqs[r]) > (self.free[best], -self.seqs[best]):
+                best = r
+        if best >= 0:
+            self.free[best] -= need; self.seqs[best] += 1
+            self.placed[request_id] = (best, need)
+        return best
+
+    def release(self, request_id):
+        r, need = self.placed.pop(request_id)
+        self.free[r] += need; self.seqs[r] -= 1
+        return r
+
+    def owner(self, request_id):
+        return self.placed[request_id][0]
+
+    def refresh(self, dist, my_free_blocks, my_seqs):
+        """Replaces the estimates by what every replica measured (rank order); a no-op without a process group."""
+        if dist is None:
+            self.free[0], self.seqs[0] = int(my_free_blocks), int(my_seqs)
+            return
+        got = [None] * self.world
+        dist.all_gather_object(got, (int(my_free_blocks), int(my_seqs)))
+        self.free = [g[0] for g in got]; self.seqs = [g[1] for g in got]
+
+
+def gather_objects(dist, obj):
+    """One picklable object per rank, in rank order, on every rank."""
+    if dist is None:
+        return [obj]
+    out = [None] * dist.get_world_size()
+    dist.all_gather_object(out, obj)
+    return out
+
+
 def rank_seeds(rank, base=0):
     """Distinct synthetic-data seeds per replica: (workload rng, weights, free-list shuffle, KV fill stride)."""
     return {"workload": base + 2 + rank, "weights": base + rank, "free_list": base + 3 + rank, "kv_fill": 1000 * rank}
+
+
+GLOBAL_WORKLOAD_SEED = 2      # the one arrival stream every rank replays through the dispatcher
 
 
 def _device_for(dist, local_rank):
