@@ -296,6 +296,10 @@ int vx_selftest_bounded_wait(vx_ctx *ctx, int limit_us, int *reached_end);
 /* batches with at least this many rows run the projections on the tcgen05 kernel (default 17, and never below 33 for Q4_K;
  * 0 = always the mma.sync kernel) */
 int vx_set_tc_min_rows(int rows);
+/* Q4_0 projections of 17..64 batch rows run on the persistent tcgen05 kernel (one CTA per SM walking weight tiles, its
+ * pipeline kept full across tiles); 0 = one CTA per tile as for the other formats.  Default on.  No counterpart in the
+ * reference. */
+int vx_set_persistent_projections(int enable);
 /* projection kernels are launched as programmatic dependents of the kernel before them (their set-up and first weight
  * tiles overlap its tail); 0 = plain stream order.  Default on.  No counterpart in the reference. */
 int vx_set_dependent_launch(int enable);

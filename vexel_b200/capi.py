@@ -11,7 +11,7 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libvexel_cuda.so")
+LIB_PATH = os.environ.get("VEXEL_CUDA_LIB") or os.path.join(_HERE, "libvexel_cuda.so")     # the override loads another build of the same library
 
 OK, E_BAD_ARG, E_CUDA, E_OOM, E_OOM_BLOCKS, E_NO_SEQ, E_TIMEOUT, E_UNSUPPORTED = range(8)
 T_F32, T_F16, T_Q4_0, T_Q4_K, T_Q6_K = 0, 1, 2, 12, 14
@@ -110,6 +110,7 @@ SIGNATURES = {
     "vx_synth_q4_0": [_vp, _D, _i64, _u64, _f],
     "vx_synth_kquant": [_vp, _D, _i, _i64, _u64, _f],
     "vx_pool_shuffle_free_list": [_vp, C.c_uint32], "vx_model_weight_bytes": [_vp, C.POINTER(_u64)],
+    "vx_set_persistent_projections": [_i],
     "vx_set_gemm_terms": [_i], "vx_set_tc_min_rows": [_i], "vx_set_dependent_launch": [_i], "vx_model_max_blocks": [_vp],
     "vx_sched_create": [_vp, C.POINTER(SchedConfig), C.POINTER(_vp)], "vx_sched_destroy": [_vp],
     "vx_sched_add_sequence": [_vp, _i64, _vp, _i, _i], "vx_sched_remove_sequence": [_vp, _i64],

@@ -191,6 +191,9 @@ int vxq_gemm(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, 
              float *parts, size_t parts_cap_floats);
 int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out, float *parts,
                 size_t parts_cap_floats);
+bool vxq_gemm_tcp_eligible(const VxWeight &w, int m);      // vx_gemm_tcp.cu: the persistent tcgen05 kernel covers this projection
+int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out, float *parts,
+                 size_t parts_cap_floats);
 struct vx_model;
 extern "C" vx_ctx *vx_model_ctx(vx_model *m);     // the context a model lives in (internal)
 int vx_check_device_error(vx_ctx *c);   // after a stream synchronisation: reports and clears the sticky kernel error word

@@ -1,0 +1,444 @@
+// Q4_0 projections for decode batches (17..64 rows) on tcgen05 + TMEM: the persistent form of the kernel in vx_gemm_tc.cu.
+//
+// What the one-CTA-per-tile kernel showed when its parts were switched off one at a time: nothing in it was saturated.  A
+// CTA lived for 16-43 pipeline stages and spent a third of that filling its pipeline and draining its accumulator, a layer's
+// projection needed two or three waves of such CTAs, and inside a stage the loads, the expansion of the weights, the
+// tensor-memory stores and the MMAs ran one after the other (four stages in flight, tied to one ring).  Here:
+//   * one CTA per SM walks (128-row weight tile, split-K slice) units; its rings keep running across unit boundaries, so the
+//     pipeline is filled once per launch and the loads of the next unit are in flight while this one finishes;
+//   * four epilogue warps take a finished unit out of the accumulators and hand them back as soon as it is in their
+//     registers (a few hundred cycles per unit), then scale and store while the next unit's MMAs run;
+//   * the rings are separate: activations eight stages deep, packed nibbles six 128-weight groups (twelve stages), block
+//     scales as their own small tiles -- all fetched by TMA, so no dequantiser waits on a global load; two producer threads
+//     (activations; weights), each a plain loop of one wait and one or two loads per item;
+//   * four dequantiser groups of four warps, group g owning tensor-memory stage g: a thread expands both 32-weight blocks of
+//     its row and stage, the first block before it waits for the stage to come free;
+//   * two issuing warps on alternate stages, each with its own accumulator: the tensor pipe runs only while a thread is
+//     issuing to it, so one warp's barrier probes and commit overlap the other's MMAs.
+// Shape per stage as before ("swap-AB"): D[128 weight rows x 64 batch] += A[128 x 64k] * B^T, A = d (q - 8) as an exact fp16
+// pair (A_hi + A_lo) in tensor memory, B = [x_hi; x_lo] stacked: A_hi x [x_hi; x_lo] (N = 128), then A_lo x x_hi (N = 64).
+// Every TMA load targets this CTA only; every wait is bounded (a timeout raises the context's error word, the CTA drains
+// what it has in flight, frees its tensor memory and returns).
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "vx_tc.cuh"
+
+namespace {
+using namespace vxtc;
+
+constexpr int P_MT = 64;                      // batch rows (MMA N / 2)
+constexpr int P_BK = 64;                      // k per stage
+constexpr int P_AST = 4;                      // weight-operand stages in tensor memory = dequantiser groups
+constexpr int P_XST = 8;                      // activation stages in shared memory
+constexpr int P_RAW = 6;                      // packed-nibble tiles (one 128-weight group = two stages each)
+constexpr int P_SC = 4;                       // scale tiles (two groups = four stages each)
+constexpr int P_X_TILE = P_MT * 128;          // one fp16 activation tile: 64 rows x 128 B
+constexpr int P_STAGE_BYTES = 2 * P_X_TILE;   // x_hi rows, then x_lo rows
+constexpr int P_RAW_BYTES = TC_ROWS * 64;
+constexpr int P_SC_BYTES = TC_ROWS * 16;      // 128 rows x 8 scales
+constexpr int P_DEQ_WARPS = 16, P_EPI_WARP0 = 16, P_ISSUE_WARP = 20, P_ISSUERS = 2, P_XPROD_WARP = 22, P_WPROD_WARP = 23;
+constexpr int P_THREADS = 24 * 32;
+constexpr int P_TMEM_ACC = 128;               // columns per accumulator (one per issuing warp): 0-63 = A_hi x_hi + A_lo x_hi, 64-127 = A_hi x_lo
+constexpr int P_TMEM_A = P_ISSUERS * P_TMEM_ACC;      // weight stages start here, 64 columns each
+constexpr int P_SMEM = P_XST * P_STAGE_BYTES + P_RAW * P_RAW_BYTES + P_SC * P_SC_BYTES + 1024 /*alignment*/ + 512 /*barriers*/ + 256 /*row scales*/;
+static_assert(P_TMEM_A + 64 * P_AST == 512, "tensor memory budget");
+static_assert(P_SMEM <= 232448, "shared memory budget");
+
+#ifndef P_KNOCK
+#define P_KNOCK 0      // timing experiments only (wrong results): 1 no weight expansion, 2 no operand stores, 4 no MMAs, 8 no activation loads, 16 no weight loads
+#endif
+// A CTA's units are blockIdx.x, blockIdx.x + gridDim.x, ...; unit u = (row tile u / split, slice u % split).  Every role walks
+// them with this iterator: one division when it is set up, additions from then on (a role is one thread's instruction stream,
+// and an integer division costs it as much as a pipeline stage has to spare).
+struct Unit { int r0, slice, g_begin, n_g; };
+struct UnitIter {
+    int tile, slice, d_tile, d_slice, split, per, k_groups;
+    __device__ __forceinline__ UnitIter(int first, int stride, int split_, int per_, int k_groups_) : split(split_), per(per_), k_groups(k_groups_) {
+        tile = first / split_; slice = first - tile * split_;
+        d_tile = stride / split_; d_slice = stride - d_tile * split_;
+    }
+    __device__ __forceinline__ Unit get() const {
+        Unit U;
+        U.slice = slice; U.r0 = tile * TC_ROWS; U.g_begin = slice * per; U.n_g = min(per, k_groups - U.g_begin);
+        return U;
+    }
+    __device__ __forceinline__ void next() {
+        tile += d_tile; slice += d_slice;
+        if (slice >= split) { slice -= split; tile++; }
+    }
+};
+
+#define VX_P_LD16(v, taddr) VX_TMEM_LD16(v, taddr)
+
+// grid: one CTA per SM (or per unit when there are fewer); out layout [split][M][ld_out]; per and k_groups are even
+__global__ void __launch_bounds__(P_THREADS, 1)
+gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_x,
+                const float *__restrict__ xscale, float *__restrict__ out, int M, int N, int k_groups,
+                int per, int split, int n_units, int ld_out, size_t part_stride, int *__restrict__ err_flag) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;            // operand tiles need 1024-byte alignment
+    const uint32_t raw_base = base + P_XST * P_STAGE_BYTES;
+    const uint32_t sc_base = raw_base + P_RAW * P_RAW_BYTES;
+    const uint32_t bar_base = sc_base + P_SC * P_SC_BYTES;
+    unsigned char *gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const unsigned char *raw_gen = gen_base + P_XST * P_STAGE_BYTES;
+    const unsigned char *sc_gen = raw_gen + P_RAW * P_RAW_BYTES;
+    float *s_xscale = reinterpret_cast<float *>(gen_base + P_XST * P_STAGE_BYTES + P_RAW * P_RAW_BYTES + P_SC * P_SC_BYTES + 512);
+    auto xfull = [&](int s) { return bar_base + 8u * s; };                                  // activation stage landed
+    auto done = [&](int s) { return bar_base + 8u * (P_XST + s); };                         // the MMAs of the stage in activation slot s have finished: the
+                                                                                            // slot and the stage's weight operand in tensor memory are free
+    auto rawfull = [&](int s) { return bar_base + 8u * (2 * P_XST + s); };                  // nibble tile landed
+    auto rawempty = [&](int s) { return bar_base + 8u * (2 * P_XST + P_RAW + s); };         // ... read by both groups that use it
+    auto scfull = [&](int s) { return bar_base + 8u * (2 * P_XST + 2 * P_RAW + s); };       // scale tile landed
+    auto scempty = [&](int s) { return bar_base + 8u * (2 * P_XST + 2 * P_RAW + P_SC + s); };
+    auto afull = [&](int s) { return bar_base + 8u * (2 * P_XST + 2 * P_RAW + 2 * P_SC + s); };                  // weight operand written
+    const uint32_t accfull = bar_base + 8u * (2 * P_XST + 2 * P_RAW + 2 * P_SC + 2 * P_AST);       // a unit's MMAs are done (one commit per issuer)
+    const uint32_t accempty = accfull + 8u;                                                         // ... and the accumulators are in registers
+
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);      // a broadcast value: the role branches below are warp-uniform
+    const int n_my = (n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;      // this CTA's units: blockIdx.x + i * gridDim.x
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < P_XST; s++) { mbar_init(xfull(s), 1); mbar_init(done(s), 1); }
+        for (int s = 0; s < P_RAW; s++) { mbar_init(rawfull(s), 1); mbar_init(rawempty(s), 8); }     // one arrival per warp of the two groups
+        for (int s = 0; s < P_SC; s++) { mbar_init(scfull(s), 1); mbar_init(scempty(s), P_DEQ_WARPS); }
+        for (int s = 0; s < P_AST; s++) mbar_init(afull(s), 4);
+        mbar_init(accfull, P_ISSUERS); mbar_init(accempty, 4);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == P_ISSUE_WARP) {   // the MMA warp owns the tensor-memory allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    volatile int *abort_flag = &s_abort;
+
+    if (warp < P_DEQ_WARPS) {
+        // ------------------------------------------------------------------ dequantisers
+        // Group fg = warp / 4 owns tensor-memory stage fg and expands the stages kb = fg (mod 4) of every unit (a unit has a
+        // multiple of four stages, so this holds across units); within the group a warp owns the 32 operand rows (tensor-memory
+        // lanes) of quadrant warp % 4.  Weights and scales do not depend on the kernel before this one, so this role never
+        // waits for it.
+        const int fg = warp >> 2;
+        const int row = (warp & 3) * 32 + lane;
+        // nibble tile rows are 64 bytes with SWIZZLE_64B: 16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3); chunk c holds
+        // word c of the four blocks of the 128-weight group; this thread's stage is blocks 2 (fg & 1) and + 1
+        const int rsw = (row >> 1) & 3;
+        int raw_off[4];
+#pragma unroll
+        for (int c = 0; c < 4; c++) raw_off[c] = row * 64 + ((c ^ rsw) << 4) + 8 * (fg & 1);
+        // scale tile: row r holds the eight block scales of two groups; this thread's stage is group (fg >> 1) & 1 of the pair
+        const int sc_off = row * 16 + (((fg >> 1) & 1) * 4 + (fg & 1) * 2) * 2;
+        const uint32_t a_st = tmem + ((uint32_t)((warp & 3) * 32) << 16) + P_TMEM_A + 64 * fg;
+        int it = 0, g_count = 0, t_count = 0;        // this group's iterations; nibble tiles and scale tiles before the current unit
+        bool ok = true;
+        UnitIter uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups);
+        for (int ui = 0; ui < n_my && ok; ui++, uit.next()) {
+            const Unit U = uit.get();
+            const int n_kb = 2 * U.n_g;
+            for (int kb = fg; kb < n_kb; kb += P_AST, it++) {
+                const int gi = g_count + (kb >> 1), ti = t_count + (kb >> 2);
+                const int slot = gi % P_RAW, ss = ti % P_SC;
+                if (!mbar_wait(scfull(ss), (uint32_t)(ti / P_SC) & 1u, abort_flag)) { ok = false; break; }
+                const __half2 d2 = *reinterpret_cast<const __half2 *>(sc_gen + ss * P_SC_BYTES + sc_off);
+                if (!mbar_wait(rawfull(slot), (uint32_t)(gi / P_RAW) & 1u, abort_flag)) { ok = false; break; }
+                const unsigned char *rp = raw_gen + slot * P_RAW_BYTES;
+                uint2 w[4];
+#pragma unroll
+                for (int c = 0; c < 4; c++) w[c] = *reinterpret_cast<const uint2 *>(rp + raw_off[c]);
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(scempty(ss)); mbar_arrive(rawempty(slot)); }
+                uint32_t hi[16], lo[16];
+                // bytes e and e + 2 of word c: weights 16 nib + 4 c + {e, e + 2} of the block (the activation tiles carry the same
+                // order of k within every four), exact product d * (q - 8) as an fp16 pair
+#define VX_P_EXPAND(WORD, DD)                                                              \
+    _Pragma("unroll") for (int nib = 0; nib < 2; nib++)                                    \
+    _Pragma("unroll") for (int c = 0; c < 4; c++)                                          \
+    _Pragma("unroll") for (int e = 0; e < 2; e++) {                                        \
+        if (P_KNOCK & 1) { hi[8 * nib + 2 * c + e] = w[c].WORD; lo[8 * nib + 2 * c + e] = h2u(DD); } else {   \
+        const __half2 q = nib2(w[c].WORD >> (4 * nib + 8 * e));                            \
+        const __half2 ph = __hmul2(q, DD);                                                 \
+        const __half2 pl = __hfma2(q, DD, __hneg2(ph));                                    \
+        hi[8 * nib + 2 * c + e] = h2u(ph); lo[8 * nib + 2 * c + e] = h2u(pl); }            \
+    }
+                const __half2 dd0 = __half2half2(__low2half(d2)), dd1 = __half2half2(__high2half(d2));
+                VX_P_EXPAND(x, dd0)                          // the first block is expanded before the stage is known to be free
+                // this group's previous stage, global index 4 (it - 1) + fg, sat in activation slot (4 (it - 1) + fg) % 8
+                if (it >= 1 && !mbar_wait(done((4 * (it - 1) + fg) & (P_XST - 1)), (uint32_t)((4 * (it - 1) + fg) / P_XST) & 1u, abort_flag)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (P_KNOCK & 2) asm volatile("" :: "r"(hi[0]), "r"(hi[15]), "r"(lo[3]), "r"(lo[12])); else
+                tmem_st32(a_st, hi, lo);                     // columns 0-15 hi, 16-31 lo of K=16 steps 0, 1; in flight while the second block is expanded
+                VX_P_EXPAND(y, dd1)
+                if (P_KNOCK & 2) asm volatile("" :: "r"(hi[0]), "r"(hi[15]), "r"(lo[3]), "r"(lo[12])); else
+                tmem_st32(a_st + 32, hi, lo);                // K=16 steps 2, 3
+#undef VX_P_EXPAND
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(afull(fg));
+            }
+            g_count += U.n_g; t_count += U.n_g >> 1;
+        }
+    } else if (warp == P_XPROD_WARP) {
+        // ------------------------------------------------------------------ activation producer (one thread): per stage one wait, one
+        // expect_tx and ONE load -- x_hi and x_lo are the two planes of a 3-D tensor map, so both tiles arrive with one TMA
+        // instruction.  (A single producer thread polling three streams, with a division per unit, took ~900 cycles per stage
+        // and was what every other role waited for.)
+        if (lane == 0) {
+            vx_pdl_wait();                                   // the activations are the output of the kernel ahead of this one in the stream
+            UnitIter uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups);
+            int xc = 0;
+            bool ok = true;
+            for (int ui = 0; ui < n_my && ok; ui++, uit.next()) {
+                const Unit U = uit.get();
+                const int n_kb = 2 * U.n_g;
+                int kcoord = U.g_begin * 2 * P_BK;
+                for (int kb = 0; kb < n_kb; kb++, xc++, kcoord += P_BK) {
+                    const int slot = xc & (P_XST - 1);
+                    if (xc >= P_XST && !mbar_wait(done(slot), (uint32_t)(xc / P_XST - 1) & 1u, abort_flag)) { ok = false; break; }
+                    if (P_KNOCK & 8) { mbar_arrive(xfull(slot)); continue; }
+                    mbar_arrive_expect_tx(xfull(slot), P_STAGE_BYTES);
+                    tma_load_3d(base + slot * P_STAGE_BYTES, &map_x, kcoord, 0, 0, xfull(slot));
+                }
+            }
+        }
+    } else if (warp == P_WPROD_WARP) {
+        // ------------------------------------------------------------------ weight producer (one thread): nibble tiles (one per 128-weight
+        // group) and scale tiles (one per two groups), in the order the dequantisers need them.  Weights do not depend on the
+        // kernel ahead of this one, so this role never waits for it: the rings fill while that kernel finishes.
+        if (lane == 0) {
+            UnitIter uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups);
+            int rc = 0, scn = 0;
+            bool ok = true;
+            for (int ui = 0; ui < n_my && ok; ui++, uit.next()) {
+                const Unit U = uit.get();
+                int raw_row = ((U.r0 / TC_ROWS) * k_groups + U.g_begin) * TC_ROWS;                      // tile-major arrays: one box = one run of memory
+                int sc_row = ((U.r0 / TC_ROWS) * (k_groups >> 1) + (U.g_begin >> 1)) * TC_ROWS;
+                for (int g = 0; g < U.n_g; g++, rc++, raw_row += TC_ROWS) {
+                    if ((g & 1) == 0) {
+                        const int ss = scn & (P_SC - 1);
+                        if (scn >= P_SC && !mbar_wait(scempty(ss), (uint32_t)(scn / P_SC - 1) & 1u, abort_flag)) { ok = false; break; }
+                        if (P_KNOCK & 16) mbar_arrive(scfull(ss)); else {
+                        mbar_arrive_expect_tx(scfull(ss), P_SC_BYTES);
+                        tma_load_2d(sc_base + ss * P_SC_BYTES, &map_s, 0, sc_row, scfull(ss)); }
+                        scn++; sc_row += TC_ROWS;
+                    }
+                    const int slot = rc % P_RAW;
+                    if (rc >= P_RAW && !mbar_wait(rawempty(slot), (uint32_t)(rc / P_RAW - 1) & 1u, abort_flag)) { ok = false; break; }
+                    if (P_KNOCK & 16) mbar_arrive(rawfull(slot)); else {
+                    mbar_arrive_expect_tx(rawfull(slot), P_RAW_BYTES);
+                    tma_load_2d(raw_base + slot * P_RAW_BYTES, &map_w, 0, raw_row, rawfull(slot)); }
+                }
+            }
+        }
+    } else if (warp >= P_ISSUE_WARP && warp < P_ISSUE_WARP + P_ISSUERS) {
+        // ------------------------------------------------------------------ MMA issue
+        // A thread that issues tcgen05.mma is held until the tensor pipe takes the instruction, and the pipe queues next to
+        // nothing: measured alone, the eight MMAs of a stage take the issuing thread 384 cycles, and every other instruction
+        // it executes between stages (barrier probes ~45 cycles each, a commit ~50, a wait ~90) is added to the stage time
+        // with the pipe idle.  So two warps on different schedulers take alternate stages, each into its own accumulator
+        // (summed in a fixed order by the epilogue): while one runs its probes and its commit, the pipe works for the other.
+        // The warp runs its loop converged and one elected lane issues, so addresses and descriptors stay warp-uniform.
+        const int j = warp - P_ISSUE_WARP;
+        int gs = 0;                                           // stages before the current unit (a multiple of four)
+        bool ok = true;
+        const bool leader = elect_one();
+        const uint32_t acc = tmem + P_TMEM_ACC * j;
+        UnitIter uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups);
+        for (int ui = 0; ui < n_my && ok; ui++, uit.next()) {
+            const Unit U = uit.get();
+            const int n_kb = 2 * U.n_g;
+            if (ui >= 1) {                                    // the epilogue must have read the previous unit out of the accumulators
+                ok = __all_sync(0xffffffffu, mbar_wait(accempty, (uint32_t)(ui - 1) & 1u, abort_flag));
+                if (!ok) break;
+            }
+            uint32_t first = 0u;
+#pragma unroll 2
+            for (int kb = j; kb < n_kb; kb += P_ISSUERS) {
+                const int gsi = gs + kb;
+                const int s = kb & (P_AST - 1), xs = gsi & (P_XST - 1);
+                const uint32_t pa = (uint32_t)(gsi / P_AST) & 1u, px = (uint32_t)(gsi / P_XST) & 1u;
+                const bool ra = mbar_try(afull(s), pa), rx = mbar_try(xfull(xs), px);     // probed back to back; the slow path is out of line
+                if (!(ra && rx)) {
+                    ok = mbar_wait(afull(s), pa, abort_flag) && mbar_wait(xfull(xs), px, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (leader) {
+                    // stage layout in tensor memory: [hi k0 k1 | lo k0 k1 | hi k2 k3 | lo k2 k3], 8 columns per K=16 step
+                    const uint32_t a0 = tmem + P_TMEM_A + 64 * s;
+                    const uint64_t xd = umma_desc(base + xs * P_STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < P_BK / 16; k++) {
+                        const uint32_t a_hi = a0 + 32 * (k >> 1) + 8 * (k & 1), a_lo = a_hi + 16;
+                        if ((P_KNOCK & 4) && !(kb < 2 && k == 0)) continue;
+                        umma_f16_ts(acc, a_hi, xd + (uint64_t)(2 * k), umma_idesc(2 * P_MT), k == 0 ? first : 1u);    // [x_hi; x_lo]: N = 128; +32 bytes of K per step
+                        umma_f16_ts(acc, a_lo, xd + (uint64_t)(2 * k), umma_idesc(P_MT), 1u);                        // x_hi only:   N = 64
+                    }
+                    umma_commit(done(xs));                // one commit releases the activation slot and the weight stage
+                    if (kb + P_ISSUERS >= n_kb) umma_commit(accfull);
+                }
+                first = 1u;
+            }
+            gs += n_kb;
+        }
+    } else if (warp >= P_EPI_WARP0 && warp < P_EPI_WARP0 + 4) {
+        // ------------------------------------------------------------------ epilogue: warp w reads the 32 accumulator lanes of quadrant
+        // w % 4 (one weight row per lane), adds the x_hi and x_lo halves, applies the batch rows' power-of-two scales and stores;
+        // the accumulator is handed back as soon as it is in registers
+        vx_pdl_wait();                                       // the scales are the previous kernel's output, and `out` may still be read by it
+        const int q = warp & 3;
+        for (int i = tid - P_EPI_WARP0 * 32; i < P_MT; i += 128) s_xscale[i] = i < M ? xscale[i] : 0.f;
+        asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps only
+        bool ok = true;
+        UnitIter uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups);
+        for (int ui = 0; ui < n_my && ok; ui++, uit.next()) {
+            const Unit U = uit.get();
+            ok = mbar_wait(accfull, (uint32_t)ui & 1u, abort_flag);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t t0 = tmem + ((uint32_t)(q * 32) << 16);
+            float v[P_MT];
+#pragma unroll
+            for (int cb = 0; cb < P_MT / 16; cb++) {              // issuer 0's x_hi and x_lo halves, then issuer 1's: a fixed order
+                uint32_t a[16], c2[16], a1[16], c3[16];
+                VX_P_LD16(a, t0 + 16 * cb);
+                VX_P_LD16(c2, t0 + P_MT + 16 * cb);
+                VX_P_LD16(a1, t0 + P_TMEM_ACC + 16 * cb);
+                VX_P_LD16(c3, t0 + P_TMEM_ACC + P_MT + 16 * cb);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    v[16 * cb + i] = ((__uint_as_float(a[i]) + __uint_as_float(c2[i])) + __uint_as_float(a1[i])) + __uint_as_float(c3[i]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(accempty);
+            const int n = U.r0 + q * 32 + lane;
+            if (n < N) {
+                float *o = out + (size_t)U.slice * part_stride + n;
+#pragma unroll
+                for (int m = 0; m < P_MT; m++)
+                    if (m < M) o[(size_t)m * ld_out] = v[m] * s_xscale[m];
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == P_ISSUE_WARP) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+    if (tid == 0 && s_abort) atomicExch(err_flag, VX_E_TIMEOUT);
+}
+
+// tile-major copies: [row tile][group][128 rows][64 B] nibbles, [row tile][group pair][128 rows][16 B] scales
+__global__ void tile_major_kernel(const uint4 *__restrict__ qs, const uint4 *__restrict__ sc, uint4 *__restrict__ qt, uint4 *__restrict__ st, int n, int k_groups) {
+    const long idx = blockIdx.x * (long)blockDim.x + threadIdx.x;       // (tile, group, row in tile, 16-byte chunk)
+    const int n_tiles = (n + TC_ROWS - 1) / TC_ROWS;
+    const long total = (long)n_tiles * k_groups * TC_ROWS * 4;
+    if (idx >= total) return;
+    const int c = (int)(idx & 3); long t = idx >> 2;
+    const int r = (int)(t % TC_ROWS); t /= TC_ROWS;
+    const int g = (int)(t % k_groups); const int tile = (int)(t / k_groups);
+    const int row = tile * TC_ROWS + r;
+    qt[idx] = row < n ? qs[((size_t)row * k_groups + g) * 4 + c] : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+    if (c == 0 && (g & 1) == 0)
+        st[((size_t)tile * (k_groups >> 1) + (g >> 1)) * TC_ROWS + r] = row < n ? sc[(size_t)row * (k_groups >> 1) + (g >> 1)] : make_uint4(0, 0, 0, 0);
+}
+
+}  // namespace
+
+static int g_tcp = 1;
+extern "C" int vx_set_persistent_projections(int enable) { g_tcp = enable != 0; return VX_OK; }
+
+// Eligible: Q4_0, at most 64 batch rows, an even number of 128-weight groups per row (the scale tiles cover two groups).
+bool vxq_gemm_tcp_eligible(const VxWeight &w, int m) {
+    return g_tcp && w.type == VX_T_Q4_0 && m <= P_MT && ((w.k_pad / 128) % 2) == 0;
+}
+
+// same contract as vxq_gemm (vx_quant.cu); the context's device error word receives VX_E_TIMEOUT if a bounded wait gave up
+int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out, float *parts,
+                 size_t parts_cap_floats) {
+    int *err_flag = c->d_int_result + 8;
+    if (x.k_pad != w.k_pad) return vx_fail(c, VX_E_BAD_ARG, "projection: activation row stride %d != weight k_pad %d", x.k_pad, w.k_pad);
+    {
+        static VxPerDevice attr;
+        VX_CUDA(c, attr.max_dynamic_smem(c, gemm_tcp_kernel, P_SMEM));
+    }
+    const int k_groups = w.k_pad / 128;
+    const int tiles = ceil_div(w.n, TC_ROWS);
+    const int slots = c->sm_count;
+    // Split-K in whole pairs of groups.  Cost in pipeline stages: the busiest CTA's stages, a little per unit it walks (the
+    // accumulator hand-over), and the partial sums' write and read (mostly L2); the smaller split wins near-ties.
+    int split = 1, per = k_groups;
+    if (parts) {
+        constexpr double UNIT_STAGES = 1.5, PART_STAGES_PER_FLOAT = 2.2e-6;
+        double best = 1e300;
+        for (int s = 1; s <= 8 && 2 * s <= k_groups; s++) {
+            if ((size_t)s * m * w.n > parts_cap_floats) break;
+            int p = ceil_div(k_groups, s);
+            p += p & 1;
+            const int s_eff = ceil_div(k_groups, p);
+            const long units = (long)tiles * s_eff;
+            const long per_cta = ceil_div64(units, std::min<long>(units, slots));
+            const double cost = (double)per_cta * (2.0 * p + UNIT_STAGES) + (s_eff > 1 ? PART_STAGES_PER_FLOAT * s_eff * (double)m * w.n : 0.0);
+            if (cost < best * 0.98) { best = cost; split = s_eff; per = p; }
+        }
+    }
+    float *dst = split > 1 ? parts : out;
+    const int ld = split > 1 ? w.n : ld_out;
+    *n_parts_out = split;
+    const int n_units = tiles * split;
+    // tensor maps, kept per (weight, activation buffer) combination: a decode step launches the same ones every time
+    struct MapKey {
+        const void *qs, *sc, *xh, *xl; int n, kg, kp;
+        bool operator<(const MapKey &o) const { return std::tie(qs, sc, xh, xl, n, kg, kp) < std::tie(o.qs, o.sc, o.xh, o.xl, o.n, o.kg, o.kp); }
+    };
+    struct MapSet { CUtensorMap w, s, x; };
+    static std::map<MapKey, MapSet> cache;
+    static std::mutex cache_mu;
+    const MapKey key{w.qs, w.sc, x.hi, x.lo, w.n, k_groups, x.k_pad};
+    MapSet ms;
+    bool have = false;
+    {
+        std::lock_guard<std::mutex> lk(cache_mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { ms = it->second; have = true; }
+    }
+    if (!have) {
+        // EXPERIMENT: tile-major copies of the nibbles and the scales, so that every TMA box is one contiguous run of memory
+        const size_t qt_bytes = (size_t)tiles * k_groups * P_RAW_BYTES, st_bytes = (size_t)tiles * (k_groups / 2) * P_SC_BYTES;
+        void *qt = nullptr, *st = nullptr;
+        VX_CUDA(c, cudaMalloc(&qt, qt_bytes)); VX_CUDA(c, cudaMalloc(&st, st_bytes));
+        {
+            const long total = (long)tiles * k_groups * TC_ROWS * 4;
+            tile_major_kernel<<<(unsigned)((total + 255) / 256), 256, 0, c->stream>>>((const uint4 *)w.qs, (const uint4 *)w.sc, (uint4 *)qt, (uint4 *)st, w.n, k_groups);
+            VX_LAUNCH_CHECK(c);
+        }
+        VX_TRY(make_map(c, &ms.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, qt, 64, (uint64_t)tiles * k_groups * TC_ROWS, 64, 64, TC_ROWS, CU_TENSOR_MAP_SWIZZLE_64B));
+        VX_TRY(make_map(c, &ms.s, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, st, 16, (uint64_t)tiles * (k_groups / 2) * TC_ROWS, 16, 16, TC_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE));
+        // activations: plane 0 = x_hi, plane 1 = x_lo, each fp16 [64 rows][k_pad]; one box brings a stage's two tiles
+        if ((const char *)x.lo <= (const char *)x.hi) return vx_fail(c, VX_E_BAD_ARG, "projection: the lo half of the activation split must follow the hi half");
+        VX_TRY(make_map_3d(c, &ms.x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x.hi, (uint64_t)x.k_pad, (uint64_t)P_MT, 2, (uint64_t)x.k_pad * 2,
+                           (uint64_t)((const char *)x.lo - (const char *)x.hi), P_BK, P_MT, 2, CU_TENSOR_MAP_SWIZZLE_128B));
+        std::lock_guard<std::mutex> lk(cache_mu);
+        if (cache.size() > 4096) cache.clear();     // buffers of destroyed models: start over rather than grow without bound
+        cache[key] = ms;
+    }
+    const dim3 grid(std::min(n_units, slots));
+    cudaError_t le = vx_launch_dependent(gemm_tcp_kernel, grid, dim3(P_THREADS), (size_t)P_SMEM, c->stream, ms.w, ms.s, ms.x,
+                                         (const float *)x.scale, dst, m, w.n, k_groups, per, split, n_units, ld, (size_t)m * w.n, err_flag);
+    if (le != cudaSuccess) return vx_cuda_fail(c, le, "projection launch");
+    VX_LAUNCH_CHECK(c);
+    return VX_OK;
+}

@@ -569,7 +569,9 @@ void time_collect(vx_model *m) {   // call after the stream has been synchronise
     m->ev_used.clear(); m->ev_next = 0;
 }
 
+static int g_dbg_skip = 0;      // timing experiments only (wrong results): 1 no projections, 2 no row kernels, 4 no attention
 int gemm(vx_model *m, const VxWeight &w, const VxSplit &x, int rows, float *out, int ld_out, int *n_parts) {
+    if (g_dbg_skip & 1) { *n_parts = 1; return VX_OK; }
     time_begin(m, 1);
     int rc = vxq_gemm(m->c, w, x, rows, out, ld_out, n_parts, m->parts, m->parts_cap);
     time_end(m, 1);
@@ -586,6 +588,7 @@ int gemm_full(vx_model *m, const VxWeight &w, const VxSplit &x, int rows, float 
 int add_norm_split_rows(vx_model *m, float *x, int rows, const float *parts, int n_parts, size_t part_stride, int part_ld,
                         const float *post_w, const float *w, const VxSplit &s, float *capture, const int32_t *row_idx = nullptr,
                         float *normed_out = nullptr) {
+    if (g_dbg_skip & 2) return VX_OK;
     const int H = m->cfg.hidden;
     if (H > 8192) return vx_fail(m->c, VX_E_UNSUPPORTED, "hidden size %d > 8192", H);
     if (H > 4096) add_norm_split_kernel<2><<<rows, VX_ROW_THREADS, 0, m->c->stream>>>(x, parts, n_parts, part_stride, part_ld, post_w, w, m->cfg.rms_eps, H, s, capture, row_idx, normed_out);
@@ -598,6 +601,7 @@ int add_norm_split(vx_model *m, int rows, const float *parts, int n_parts, size_
     return add_norm_split_rows(m, m->x, rows, parts, n_parts, part_stride, part_ld, post_w, w, s, capture);
 }
 int act_split(vx_model *m, int rows, int n_parts) {
+    if (g_dbg_skip & 2) return VX_OK;
     const int F = m->cfg.ffn;
     const size_t pstride = (size_t)rows * 2 * F;
     // cluster size: a thin batch spreads each row over up to four SMs; from ~a third of the SMs in rows on, one CTA per row
@@ -666,7 +670,7 @@ int forward(vx_model *m, int rows, const std::vector<RowRange> &special, int pla
             for (const ColW &cw : L.wqkv) VX_TRY(gemm_full(m, cw.w, m->sp_h, rows, m->qkv + cw.col, nqkv));
             qkv_src = m->qkv;
         }
-        {
+        if (!(g_dbg_skip & 2)) {
             dim3 rg(rows, ceil_div(Hq + 2 * Hkv, ROPE_HEADS));
             rope_append_kernel<<<rg, 128, 0, c->stream>>>(qkv_src, np_qkv, (size_t)rows * nqkv, m->qkv, nqkv, m->d_cos, m->d_sin, m->d_slot_map,
                                                           m->pool + (size_t)l * m->layer_stride, Hq, Hkv, D, cf.rope_neox);   // block.go:858-868
@@ -700,7 +704,8 @@ int forward(vx_model *m, int rows, const std::vector<RowRange> &special, int pla
             // at most this many split-K chunks per row: the table width bounds a row's pages
             const int n_max = ceil_div(cf.max_blocks_per_seq, max(chunk_pages[wl], 1)) + 1;
             // rows served above have no work items; the merge reads their finished output rows back
-            if (plain_rows > 0) VX_TRY(vxp_attention_split(c, a, &m->sp_q, n_max, &split_done));  // block.go:872 / 881-890
+            if (plain_rows > 0 && !(g_dbg_skip & 4)) VX_TRY(vxp_attention_split(c, a, &m->sp_q, n_max, &split_done));  // block.go:872 / 881-890
+            if (g_dbg_skip & 4) split_done = true;
         }
         time_end(m, 0);
         if (!split_done) VX_TRY(vxq_split_rows(c, m->attn, rows, qd, qd, m->sp_q));
@@ -1589,6 +1594,7 @@ int vx_model_kernel_time(vx_model *m, int which, int enable, float *ms, uint64_t
 }
 
 int vx_set_graphs(int enable) { g_graphs = enable != 0; return VX_OK; }
+int vx_debug_skip(int mask) { g_dbg_skip = mask; return VX_OK; }
 
 int vx_model_max_blocks(vx_model *m) { return m ? m->cfg.max_blocks : 0; }
 
