@@ -221,22 +221,22 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             bool ok = true;
             for (int ui = 0; ui < n_my && ok; ui++, uit.next()) {
                 const Unit U = uit.get();
-                int raw_row = ((U.r0 / TC_ROWS) * k_groups + U.g_begin) * TC_ROWS;                      // tile-major arrays: one box = one run of memory
-                int sc_row = ((U.r0 / TC_ROWS) * (k_groups >> 1) + (U.g_begin >> 1)) * TC_ROWS;
-                for (int g = 0; g < U.n_g; g++, rc++, raw_row += TC_ROWS) {
+                // row-major arrays: nibbles [n][k_groups * 64 B], scales [n][k_groups * 8 B]; a box is 128 rows x 64 (16) bytes
+                int raw_col = U.g_begin * 64, sc_col = U.g_begin * 8;
+                for (int g = 0; g < U.n_g; g++, rc++, raw_col += 64) {
                     if ((g & 1) == 0) {
                         const int ss = scn & (P_SC - 1);
                         if (scn >= P_SC && !mbar_wait(scempty(ss), (uint32_t)(scn / P_SC - 1) & 1u, abort_flag)) { ok = false; break; }
                         if (P_KNOCK & 16) mbar_arrive(scfull(ss)); else {
                         mbar_arrive_expect_tx(scfull(ss), P_SC_BYTES);
-                        tma_load_2d(sc_base + ss * P_SC_BYTES, &map_s, 0, sc_row, scfull(ss)); }
-                        scn++; sc_row += TC_ROWS;
+                        tma_load_2d(sc_base + ss * P_SC_BYTES, &map_s, sc_col, U.r0, scfull(ss)); }
+                        scn++; sc_col += 16;
                     }
                     const int slot = rc % P_RAW;
                     if (rc >= P_RAW && !mbar_wait(rawempty(slot), (uint32_t)(rc / P_RAW - 1) & 1u, abort_flag)) { ok = false; break; }
                     if (P_KNOCK & 16) mbar_arrive(rawfull(slot)); else {
                     mbar_arrive_expect_tx(rawfull(slot), P_RAW_BYTES);
-                    tma_load_2d(raw_base + slot * P_RAW_BYTES, &map_w, 0, raw_row, rawfull(slot)); }
+                    tma_load_2d(raw_base + slot * P_RAW_BYTES, &map_w, raw_col, U.r0, rawfull(slot)); }
                 }
             }
         }
@@ -316,10 +316,13 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 VX_P_LD16(c2, t0 + P_MT + 16 * cb);
                 VX_P_LD16(a1, t0 + P_TMEM_ACC + 16 * cb);
                 VX_P_LD16(c3, t0 + P_TMEM_ACC + P_MT + 16 * cb);
+                float sx[16];                                     // the batch rows' scales, applied here so that the stores below depend on nothing
+#pragma unroll
+                for (int i = 0; i < 4; i++) *reinterpret_cast<float4 *>(&sx[4 * i]) = *reinterpret_cast<const float4 *>(s_xscale + 16 * cb + 4 * i);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                 for (int i = 0; i < 16; i++)
-                    v[16 * cb + i] = ((__uint_as_float(a[i]) + __uint_as_float(c2[i])) + __uint_as_float(a1[i])) + __uint_as_float(c3[i]);
+                    v[16 * cb + i] = (((__uint_as_float(a[i]) + __uint_as_float(c2[i])) + __uint_as_float(a1[i])) + __uint_as_float(c3[i])) * sx[i];
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -327,9 +330,13 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             const int n = U.r0 + q * 32 + lane;
             if (n < N) {
                 float *o = out + (size_t)U.slice * part_stride + n;
+                if (M == P_MT) {
 #pragma unroll
-                for (int m = 0; m < P_MT; m++)
-                    if (m < M) o[(size_t)m * ld_out] = v[m] * s_xscale[m];
+                    for (int m = 0; m < P_MT; m++) { *o = v[m]; o += ld_out; }
+                } else {
+#pragma unroll
+                    for (int m = 0; m < P_MT; m++) { if (m < M) *o = v[m]; o += ld_out; }
+                }
             }
         }
     }
@@ -339,21 +346,6 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
     }
     if (tid == 0 && s_abort) atomicExch(err_flag, VX_E_TIMEOUT);
-}
-
-// tile-major copies: [row tile][group][128 rows][64 B] nibbles, [row tile][group pair][128 rows][16 B] scales
-__global__ void tile_major_kernel(const uint4 *__restrict__ qs, const uint4 *__restrict__ sc, uint4 *__restrict__ qt, uint4 *__restrict__ st, int n, int k_groups) {
-    const long idx = blockIdx.x * (long)blockDim.x + threadIdx.x;       // (tile, group, row in tile, 16-byte chunk)
-    const int n_tiles = (n + TC_ROWS - 1) / TC_ROWS;
-    const long total = (long)n_tiles * k_groups * TC_ROWS * 4;
-    if (idx >= total) return;
-    const int c = (int)(idx & 3); long t = idx >> 2;
-    const int r = (int)(t % TC_ROWS); t /= TC_ROWS;
-    const int g = (int)(t % k_groups); const int tile = (int)(t / k_groups);
-    const int row = tile * TC_ROWS + r;
-    qt[idx] = row < n ? qs[((size_t)row * k_groups + g) * 4 + c] : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
-    if (c == 0 && (g & 1) == 0)
-        st[((size_t)tile * (k_groups >> 1) + (g >> 1)) * TC_ROWS + r] = row < n ? sc[(size_t)row * (k_groups >> 1) + (g >> 1)] : make_uint4(0, 0, 0, 0);
 }
 
 }  // namespace
@@ -382,7 +374,7 @@ int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *o
     // accumulator hand-over), and the partial sums' write and read (mostly L2); the smaller split wins near-ties.
     int split = 1, per = k_groups;
     if (parts) {
-        constexpr double UNIT_STAGES = 1.5, PART_STAGES_PER_FLOAT = 2.2e-6;
+        constexpr double UNIT_STAGES = 2.5, PART_STAGES_PER_FLOAT = 2.2e-6;
         double best = 1e300;
         for (int s = 1; s <= 8 && 2 * s <= k_groups; s++) {
             if ((size_t)s * m * w.n > parts_cap_floats) break;
@@ -416,17 +408,11 @@ int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *o
         if (it != cache.end()) { ms = it->second; have = true; }
     }
     if (!have) {
-        // EXPERIMENT: tile-major copies of the nibbles and the scales, so that every TMA box is one contiguous run of memory
-        const size_t qt_bytes = (size_t)tiles * k_groups * P_RAW_BYTES, st_bytes = (size_t)tiles * (k_groups / 2) * P_SC_BYTES;
-        void *qt = nullptr, *st = nullptr;
-        VX_CUDA(c, cudaMalloc(&qt, qt_bytes)); VX_CUDA(c, cudaMalloc(&st, st_bytes));
-        {
-            const long total = (long)tiles * k_groups * TC_ROWS * 4;
-            tile_major_kernel<<<(unsigned)((total + 255) / 256), 256, 0, c->stream>>>((const uint4 *)w.qs, (const uint4 *)w.sc, (uint4 *)qt, (uint4 *)st, w.n, k_groups);
-            VX_LAUNCH_CHECK(c);
-        }
-        VX_TRY(make_map(c, &ms.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, qt, 64, (uint64_t)tiles * k_groups * TC_ROWS, 64, 64, TC_ROWS, CU_TENSOR_MAP_SWIZZLE_64B));
-        VX_TRY(make_map(c, &ms.s, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, st, 16, (uint64_t)tiles * (k_groups / 2) * TC_ROWS, 16, 16, TC_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE));
+        // packed nibbles as bytes [n][k_groups * 64]; block scales as bytes [n][k_groups * 8]
+        VX_TRY(make_map(c, &ms.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w.qs, (uint64_t)k_groups * 64, (uint64_t)w.n, (uint64_t)k_groups * 64, 64, TC_ROWS,
+                        CU_TENSOR_MAP_SWIZZLE_64B));
+        VX_TRY(make_map(c, &ms.s, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w.sc, (uint64_t)k_groups * 8, (uint64_t)w.n, (uint64_t)k_groups * 8, 16, TC_ROWS,
+                        CU_TENSOR_MAP_SWIZZLE_NONE));
         // activations: plane 0 = x_hi, plane 1 = x_lo, each fp16 [64 rows][k_pad]; one box brings a stage's two tiles
         if ((const char *)x.lo <= (const char *)x.hi) return vx_fail(c, VX_E_BAD_ARG, "projection: the lo half of the activation split must follow the hi half");
         VX_TRY(make_map_3d(c, &ms.x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x.hi, (uint64_t)x.k_pad, (uint64_t)P_MT, 2, (uint64_t)x.k_pad * 2,
