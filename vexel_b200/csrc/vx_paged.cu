@@ -83,8 +83,12 @@ __device__ __forceinline__ void unpack8(const uint4 &u, float (&f)[8]) {
     for (int i = 0; i < 4; i++) { float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
 }
 
+// Five CTAs per SM (96 registers, a two-word spill) instead of the four that 115 registers allow: 3 % more bandwidth.  Six
+// (80 registers) spills enough to give that back; eight is 25 % slower.  Folding the chunk merge and the output split into
+// this kernel (arrival tickets, the last CTA of a row finishes it) was measured too: the fence and the ticket every CTA then
+// pays cost more (+9 us per launch) than the separate 10 us merge kernel.
 template <int D, int G>
-__global__ void __launch_bounds__(ATT_WARPS * 32)
+__global__ void __launch_bounds__(ATT_WARPS * 32, 5)
 paged_flash_kernel(VxAttnArgs a) {
     constexpr int LPT = D / 8;            // lanes per token
     constexpr int TPW = 32 / LPT;         // tokens per warp-wide load
