@@ -316,7 +316,7 @@ def main():
     ctx_all = rng.integers(args.ctx_min, args.ctx_max + 1, B * world)
     tokens_all = rng.integers(0, spec.vocab, B * world).astype(np.int32)
     total_new = W + 2 * K + Ka + Kg + 16            # warm-up + device-resident leg + the two kernel legs (the end-to-end leg rolls back)
-    seq_cap = B + max(8, B // 8)                    # a replica may take a few more (or fewer) sequences than the mean
+    seq_cap = B                                     # a replica's batch limit: the projections' fast path covers 64 rows, the 65th would cost more than it balances
     router = replicas.Dispatcher(world, blocks_per_replica=10 ** 9, max_seqs_per_replica=seq_cap)
     owner = np.array([router.place(i, int(c) + total_new) for i, c in enumerate(ctx_all)])
     mine = np.nonzero(owner == rank)[0]

@@ -80,21 +80,25 @@ def test_two_ranks_gloo_throughput_and_sharding():
 
 
 def test_dispatcher_levels_the_kv_load():
-    """Each request goes to the replica with the most free blocks; after 8 x 64 requests with contexts ~U[128, 2048] the
-    replicas' resident KV differs by less than one request, where independent draws per replica differ by several per cent."""
+    """Without a sequence limit each request goes to the replica with the most free blocks and the replicas' resident KV
+    differs by less than one request.  With the benchmark's limit of 64 sequences per replica every replica ends up with
+    exactly 64 and the resident KV within 3 % of the mean, where independent draws per replica differ by 6 % (one sigma)."""
     rng = np.random.default_rng(2)
     for world in (1, 2, 4, 8):
         ctx = rng.integers(128, 2049, 64 * world)
-        d = replicas.Dispatcher(world, blocks_per_replica=64 * 140, max_seqs_per_replica=80)
+        d = replicas.Dispatcher(world, blocks_per_replica=64 * 140)
         owner = np.array([d.place(i, int(c)) for i, c in enumerate(ctx)])
         assert owner.min() >= 0 and all(d.owner(i) == owner[i] for i in range(len(ctx)))
         blocks = np.array([sum(d.blocks_for(c) for c in ctx[owner == r]) for r in range(world)])
         assert blocks.max() - blocks.min() <= d.blocks_for(2048)
-        counts = np.bincount(owner, minlength=world)
-        assert counts.max() <= 80 and counts.sum() == 64 * world
         for i in range(0, len(ctx), 2):
             d.release(i)
-        assert sum(d.seqs) == len(ctx) // 2
+        assert sum(d.seqs) == len(ctx) // 2 and sum(d.used) == sum(d.blocks_for(c) for c in ctx[1::2])
+        c = replicas.Dispatcher(world, blocks_per_replica=10 ** 9, max_seqs_per_replica=64)
+        owner = np.array([c.place(i, int(t)) for i, t in enumerate(ctx)])
+        assert np.bincount(owner, minlength=world).tolist() == [64] * world
+        blocks = np.array(c.used, dtype=np.float64)
+        assert (blocks.max() - blocks.min()) <= 0.03 * blocks.mean()
     # a request nobody can hold is not placed (the caller queues it), and a replica at its sequence limit is skipped
     d = replicas.Dispatcher(2, blocks_per_replica=10, max_seqs_per_replica=1)
     assert d.place(1, 16 * 11) == -1

@@ -48,7 +48,8 @@ class Dispatcher:
     The reference admits every request into its one cache (Scheduler.AddSequence, inference/scheduler/scheduler.go:645-676).
     With one cache per GPU the admission step gains a choice; a request's cost to a replica is the blocks its context will
     hold, and a decode step lasts as long as the replica with the most resident KV, so the router keeps the free-block counts
-    level: most free blocks first, fewest resident sequences on a tie, lowest rank after that.  The decision is a pure
+    level: most free blocks first, fewest resident sequences on a tie, lowest rank after that (`place` says what changes when
+    a replica's batch size is capped).  The decision is a pure
     function of the arrival stream, so every rank that replays the same stream reaches the same placement without
     talking to the others; `refresh` replaces the book-keeping by the replicas' measured free-block counts (one
     all-gather) where lengths are not known in advance.
@@ -57,6 +58,7 @@ class Dispatcher:
     def __init__(self, world, blocks_per_replica, max_seqs_per_replica=0, block_tokens=16):
         self.world, self.block_tokens = int(world), int(block_tokens)
         self.free = [int(blocks_per_replica)] * self.world
+        self.used = [0] * self.world          # blocks held by the requests placed on each replica
         self.seqs = [0] * self.world
         self.max_seqs = int(max_seqs_per_replica)
         self.placed = {}                      # request id -> (rank, blocks)
@@ -65,22 +67,32 @@ class Dispatcher:
         return (int(tokens) + self.block_tokens - 1) // self.block_tokens
 
     def place(self, request_id, tokens):
-        """Returns the owning rank, or -1 when no replica can hold the request now (the caller queues it)."""
+        """Returns the owning rank, or -1 when no replica can hold the request now (the caller queues it).
+
+        Without a per-replica sequence limit: the replica with the most free blocks.  With one (a replica's batch is capped,
+        e.g. at the 64 rows the projections' fast path covers), a replica that fills its slots with short requests could not
+        take its share of the long ones later, so the choice is made among the replicas with the fewest sequences (at most one
+        more than the emptiest) and goes to the one whose block load per sequence this request brings closest to the running
+        mean over all replicas."""
         need = self.blocks_for(tokens)
-        best = -1
-        for r in range(self.world):
-            if self.free[r] < need or (self.max_seqs and self.seqs[r] >= self.max_seqs):
-                continue
-            if best < 0 or (self.free[r], -self.seqs[r]) > (self.free[best], -self.seqs[best]):
-                best = r
-        if best >= 0:
-            self.free[best] -= need; self.seqs[best] += 1
-            self.placed[request_id] = (best, need)
+        cand = [r for r in range(self.world) if self.free[r] >= need and not (self.max_seqs and self.seqs[r] >= self.max_seqs)]
+        if not cand:
+            return -1
+        if self.max_seqs:
+            fewest = min(self.seqs[r] for r in cand)
+            cand = [r for r in cand if self.seqs[r] <= fewest + 1]
+            n_placed = sum(self.seqs) + 1
+            mean = (sum(self.used) + need) / n_placed
+            best = min(cand, key=lambda r: (abs(self.used[r] + need - mean * (self.seqs[r] + 1)), -self.free[r], r))
+        else:
+            best = max(cand, key=lambda r: (self.free[r], -self.seqs[r], -r))
+        self.free[best] -= need; self.used[best] += need; self.seqs[best] += 1
+        self.placed[request_id] = (best, need)
         return best
 
     def release(self, request_id):
         r, need = self.placed.pop(request_id)
-        self.free[r] += need; self.seqs[r] -= 1
+        self.free[r] += need; self.used[r] -= need; self.seqs[r] -= 1
         return r
 
     def owner(self, request_id):
