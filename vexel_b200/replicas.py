@@ -72,8 +72,8 @@ class Dispatcher:
         Without a per-replica sequence limit: the replica with the most free blocks.  With one (a replica's batch is capped,
         e.g. at the 64 rows the projections' fast path covers), a replica that fills its slots with short requests could not
         take its share of the long ones later, so the choice is made among the replicas with the fewest sequences (at most one
-        more than the emptiest) and goes to the one whose block load per sequence this request brings closest to the running
-        mean over all replicas."""
+        more than the emptiest) so that the total squared deviation of the replicas' loads from the running mean
+        load per sequence grows least."""
         need = self.blocks_for(tokens)
         cand = [r for r in range(self.world) if self.free[r] >= need and not (self.max_seqs and self.seqs[r] >= self.max_seqs)]
         if not cand:
@@ -83,7 +83,10 @@ class Dispatcher:
             cand = [r for r in cand if self.seqs[r] <= fewest + 1]
             n_placed = sum(self.seqs) + 1
             mean = (sum(self.used) + need) / n_placed
-            best = min(cand, key=lambda r: (abs(self.used[r] + need - mean * (self.seqs[r] + 1)), -self.free[r], r))
+            # deviation of a replica from the mean load for its sequence count: d_r = used_r - mean * seqs_r.  Adding a request
+            # that is (need - mean) above the mean changes sum(d_r^2) by 2 d_r (need - mean) + const: a request heavier than
+            # the mean goes to the most under-loaded candidate, a lighter one to the most over-loaded
+            best = min(cand, key=lambda r: ((self.used[r] - mean * self.seqs[r]) * (need - mean), -self.free[r], r))
         else:
             best = max(cand, key=lambda r: (self.free[r], -self.seqs[r], -r))
         self.free[best] -= need; self.used[best] += need; self.seqs[best] += 1
