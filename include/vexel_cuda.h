@@ -304,6 +304,21 @@ int vx_set_persistent_projections(int enable);
  * tiles overlap its tail); 0 = plain stream order.  Default on.  No counterpart in the reference. */
 int vx_set_dependent_launch(int enable);
 
+/* ------------------------------------------------------------------ tensor parallelism (one process per GPU, NCCL)
+ * No counterpart in the reference, which keeps whole Wq..W2 per block on one device (runtime/block.go:256-266).  A model too
+ * large for (or too slow on) one GPU is split Megatron-style: Wq/Wk/Wv and W1/W3 by output rows, Wo and W2 by input columns
+ * (their outputs are summed over the ranks with ncclAllReduce on the compute stream, once after each), the output head by
+ * vocabulary rows (local first-maximum, one all-gather of (value, index) pairs).  Every rank runs the same step on the same
+ * token ids; the KV pool of a rank holds its own KV heads only.
+ *   rank 0: vx_tp_unique_id(buf, 128) and hand buf to the other ranks; every rank: vx_tp_init(ctx, buf, rank, world);
+ *   vx_model_create with the LOCAL counts (n_heads / world, n_kv_heads / world, ffn / world, vocab / world),
+ *   vx_model_enable_tp(model, vocab_full), then vx_model_set_tensor with the rank's slices (the embedding and the norms whole).
+ * Steps are greedy (vx_decode_step, vx_prefill, vx_decode_run); logits, if requested, are the rank's vocabulary slice. */
+int vx_tp_unique_id(void *out, int cap);
+int vx_tp_init(vx_ctx *ctx, const void *unique_id, int rank, int world);
+int vx_tp_shutdown(vx_ctx *ctx);
+int vx_model_enable_tp(vx_model *m, int vocab_full);
+
 /* ------------------------------------------------------------------ continuous-batching scheduler
  * The host loop of inference/scheduler (Scheduler.step / runDecodeStep, scheduler/scheduler.go:168-483; Sequence state
  * machine, scheduler/sequence.go:15-80) over vx_decode_step_ex, for embedders without the Go scheduler.  Every iteration

@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #include <atomic>
 #include <mutex>
@@ -29,6 +30,7 @@ struct vx_ctx {
     int *h_int_result = nullptr;      // pinned
     int sm_count = 148;
     uint64_t launches = 0;
+    void *tp = nullptr;               // tensor-parallel communicator of this context (vx_tp.cu), null for single-GPU use
 };
 
 struct VxGuard {
@@ -194,6 +196,11 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
 bool vxq_gemm_tcp_eligible(const VxWeight &w, int m);      // vx_gemm_tcp.cu: the persistent tcgen05 kernel covers this projection
 int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out, float *parts,
                  size_t parts_cap_floats);
+// tensor parallelism (vx_tp.cu)
+int vxtp_world(vx_ctx *c);
+int vxtp_rank(vx_ctx *c);
+int vxtp_allreduce_sum(vx_ctx *c, float *buf, size_t n);
+int vxtp_global_argmax(vx_ctx *c, const float *logits, long ld, const int32_t *local_idx, int rows, int local_vocab, void *scratch, int32_t *out_tok);
 struct vx_model;
 extern "C" vx_ctx *vx_model_ctx(vx_model *m);     // the context a model lives in (internal)
 int vx_check_device_error(vx_ctx *c);   // after a stream synchronisation: reports and clears the sticky kernel error word

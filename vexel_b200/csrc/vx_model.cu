@@ -58,6 +58,9 @@ struct vx_model {
             *d_row_kv_start = nullptr, *d_row_route = nullptr, *d_last_row = nullptr;
     float *d_hidden = nullptr;                   // post-final-norm hidden states of the output rows of the last step
     bool fast_attn_shape = false;                // the paged attention kernels that walk work lists cover this head shape
+    // tensor parallelism: this model is one rank's slice (local heads / FFN columns / vocabulary rows in cfg); the embedding
+    // table covers the whole vocabulary
+    bool tp = false; int vocab_full = 0; float *ar_buf = nullptr; void *tp_scratch = nullptr;
     int4 *d_work[2] = {nullptr, nullptr}; int32_t *d_rws[2] = {nullptr, nullptr}; int32_t *d_n_work[2] = {nullptr, nullptr};
     float *d_partials = nullptr;
     float *d_cos = nullptr, *d_sin = nullptr, *d_freq = nullptr;
@@ -647,7 +650,7 @@ int forward(vx_model *m, int rows, const std::vector<RowRange> &special, int pla
     const int qd = Hq * D, kvd = Hkv * D, nqkv = qd + 2 * kvd;
     const float scale = (float)(1.0 / sqrt((double)D));   // block.go:862
     const int32_t *tokens = m->d_step_in + 4 * m->last_seqs;
-    embed_kernel<<<rows, 256, 0, c->stream>>>(tokens, m->embed.dev, m->embed.type, m->x, H, cf.vocab, cf.embed_scale);
+    embed_kernel<<<rows, 256, 0, c->stream>>>(tokens, m->embed.dev, m->embed.type, m->x, H, m->tp ? m->vocab_full : cf.vocab, cf.embed_scale);
     VX_LAUNCH_CHECK(c);
     {
         int n = rows * (D / 2);
@@ -656,11 +659,11 @@ int forward(vx_model *m, int rows, const std::vector<RowRange> &special, int pla
     }
     const size_t cap_stride = (size_t)rows * H;
     int np_prev = 0;                 // partial count of the previous W2 projection, consumed by the next add
-    const float *post_prev = nullptr;
+    const float *post_prev = nullptr, *prev_out = m->parts;
     for (int l = 0; l < cf.n_layers; l++) {
         const LayerW &L = m->layers[l];
         // x += W2 output of the previous layer; normOut = RMSNorm(x) (block.go:836)
-        VX_TRY(add_norm_split(m, rows, m->parts, np_prev, (size_t)rows * H, H, post_prev, L.attn_norm, m->sp_h,
+        VX_TRY(add_norm_split(m, rows, prev_out, np_prev, (size_t)rows * H, H, post_prev, L.attn_norm, m->sp_h,
                               m->capture_on ? m->capture + (size_t)l * cap_stride : nullptr));
         int np_qkv = 1;
         const float *qkv_src = m->parts;
@@ -711,25 +714,38 @@ int forward(vx_model *m, int rows, const std::vector<RowRange> &special, int pla
         if (!split_done) VX_TRY(vxq_split_rows(c, m->attn, rows, qd, qd, m->sp_q));
         int np_o = 1;
         VX_TRY(gemm(m, L.wo, m->sp_q, rows, m->parts, H, &np_o));                       // block.go:983
+        const float *wo_out = m->parts;
+        if (m->tp) {   // this rank holds a column slice of Wo: its output is a partial sum over the ranks
+            VX_TRY(vxq_reduce_parts(c, m->parts, np_o, rows, H, m->ar_buf, H));
+            VX_TRY(vxtp_allreduce_sum(c, m->ar_buf, (size_t)rows * H));
+            wo_out = m->ar_buf; np_o = 1;
+        }
         // x += Wo output (post-attn norm first for Gemma 2); normOut = RMSNorm(x, ffn_norm) (block.go:985-997)
-        VX_TRY(add_norm_split(m, rows, m->parts, np_o, (size_t)rows * H, H, cf.post_norms ? L.post_attn_norm : nullptr, L.ffn_norm,
+        VX_TRY(add_norm_split(m, rows, wo_out, np_o, (size_t)rows * H, H, cf.post_norms ? L.post_attn_norm : nullptr, L.ffn_norm,
                               m->sp_h, nullptr));
         int np_13 = 1;
         VX_TRY(gemm(m, L.w13, m->sp_h, rows, m->parts, 2 * F, &np_13));                 // block.go:1045-1049
         VX_TRY(act_split(m, rows, np_13));                                              // block.go:1051-1057
         VX_TRY(gemm(m, L.w2, m->sp_f, rows, m->parts, H, &np_prev));                    // block.go:1060
+        if (m->tp) {   // W2 is split along its input columns as well
+            VX_TRY(vxq_reduce_parts(c, m->parts, np_prev, rows, H, m->ar_buf, H));
+            VX_TRY(vxtp_allreduce_sum(c, m->ar_buf, (size_t)rows * H));
+            prev_out = m->ar_buf; np_prev = 1;
+        } else prev_out = m->parts;
         post_prev = cf.post_norms ? L.post_ffn_norm : nullptr;
     }
     // last residual add, then the final norm on the rows that need logits (decode.go:442, 1057-1086)
     const bool last_rows = (out_flags & OUT_LAST_ROWS) != 0;
     const int r0 = last_rows ? 0 : rows - logit_rows;
-    VX_TRY(add_norm_split(m, rows, m->parts, np_prev, (size_t)rows * H, H, post_prev, nullptr, m->sp_h,
+    VX_TRY(add_norm_split(m, rows, prev_out, np_prev, (size_t)rows * H, H, post_prev, nullptr, m->sp_h,
                           m->capture_on ? m->capture + (size_t)cf.n_layers * cap_stride : nullptr));
     // norm + split only the logit rows (the trailing ones, or the last row of every entry), written to split rows [0, logit_rows)
     VX_TRY(add_norm_split_rows(m, m->x + (size_t)r0 * H, logit_rows, nullptr, 0, 0, 0, nullptr, m->final_norm, m->sp_h, nullptr,
                                last_rows ? m->d_last_row : nullptr, (out_flags & OUT_HIDDEN) ? m->d_hidden : nullptr));
     VX_TRY(gemm_full(m, m->w_out, m->sp_h, logit_rows, m->logits, cf.vocab));           // model.go:352-422
     VX_TRY(vxe_argmax_rows(c, m->logits, logit_rows, cf.vocab, m->d_out_tok));          // sampler.go:79-90
+    if (m->tp)     // the head is split by vocabulary rows: the local maxima meet in one small all-gather
+        VX_TRY(vxtp_global_argmax(c, m->logits, cf.vocab, m->d_out_tok, logit_rows, cf.vocab, m->tp_scratch, m->d_out_tok));
     return VX_OK;
 }
 
@@ -883,6 +899,8 @@ int enqueue_step(vx_model *m, const StepPlan &p, int out_flags, int logit_rows) 
     if (m->capture_on) m->capture_rows = p.rows;
     int n_work[2] = {p.n_work[0], p.n_work[1]};
     // steps with prefill routes launch one kernel per routed entry, so their launch sequence is not a function of the key
+    // (a tensor-parallel step captures its NCCL collectives with the rest: every rank runs the same shapes in the same order,
+    // so all of them capture, and later replay, the same step)
     const bool can_graph = g_graphs && p.special.empty() && !m->capture_on && !m->time_on[0] && !m->time_on[1];
     if (can_graph) {
         for (int i = 0; i < 2; i++) if (n_work[i] > 0) n_work[i] = std::min(MAX_WORK, (n_work[i] + 31) / 32 * 32);
@@ -969,6 +987,7 @@ int run_step_planned(vx_model *m, const StepPlan &p, int n_seqs, const int *slot
 int run_step(vx_model *m, int n_seqs, const int *slots, const int32_t *tokens, const int32_t *positions, const int32_t *q_lens,
              int flags, int logit_rows_req, int32_t *out_tokens, float *logits, const vx_sample_params *sample = nullptr,
              float *hidden = nullptr) {
+    if (m->tp && sample) return vx_fail(m->c, VX_E_UNSUPPORTED, "sampling from a vocabulary-split output head is not implemented: tensor-parallel steps are greedy");
     StepPlan p;
     VX_TRY(plan_step(m, n_seqs, slots, positions, q_lens, (flags & VX_STEP_PROMPT_ROWS) != 0, &p));
     int out_flags = hidden ? OUT_HIDDEN : 0;
@@ -1124,7 +1143,7 @@ int vx_model_set_tensor(vx_model *m, int layer, int slot, int type, const void *
     int n, k; size_t idx;
     if (layer < 0) {
         VX_REQUIRE(c, slot >= 0 && slot < 3, "bad global slot");
-        n = slot == VX_G_FINAL_NORM ? 1 : m->cfg.vocab; k = m->cfg.hidden;
+        n = slot == VX_G_FINAL_NORM ? 1 : (slot == VX_G_EMBED && m->tp) ? m->vocab_full : m->cfg.vocab; k = m->cfg.hidden;
         idx = (size_t)m->cfg.n_layers * VX_W_PER_LAYER + slot;
     } else {
         VX_REQUIRE(c, layer < m->cfg.n_layers && slot >= 0 && slot < VX_W_PER_LAYER, "bad layer/slot");
@@ -1146,6 +1165,25 @@ int vx_model_set_tensor(vx_model *m, int layer, int slot, int type, const void *
 
 // Repacks the projection matrices for the MMA kernel, concatenating Wq|Wk|Wv and W1|W3 row-wise
 // (rows are independent in the GGUF row-major block layout), and releases the raw copies.
+// Marks the model as one rank's slice of a tensor-parallel model (call before any tensor is set, on a context that has
+// run vx_tp_init).  The model's config holds the LOCAL head / FFN / vocabulary counts; vocab_full is the whole vocabulary,
+// which the (replicated) embedding table covers.
+int vx_model_enable_tp(vx_model *m, int vocab_full) {
+    if (!m) return VX_E_BAD_ARG;
+    vx_ctx *c = m->c;
+    VxGuard g(c);
+    VX_REQUIRE(c, !m->finalized, "model already finalized");
+    VX_REQUIRE(c, c->tp != nullptr, "vx_tp_init has not been called on this context");
+    VX_REQUIRE(c, vocab_full == m->cfg.vocab * vxtp_world(c), "the local vocabulary must be vocab_full / world");
+    for (auto &r : m->raw) VX_REQUIRE(c, r.dev == nullptr, "enable tensor parallelism before setting tensors");
+    m->tp = true; m->vocab_full = vocab_full;
+    VX_TRY(model_alloc_t(m, (size_t)m->cfg.max_batch_tokens * m->cfg.hidden, &m->ar_buf));
+    float2 *sc = nullptr;
+    VX_TRY(model_alloc_t(m, (size_t)m->cfg.max_batch_tokens * (1 + vxtp_world(c)), &sc));
+    m->tp_scratch = sc;
+    return VX_OK;
+}
+
 int vx_model_finalize(vx_model *m) {
     if (!m) return VX_E_BAD_ARG;
     vx_ctx *c = m->c;

@@ -65,6 +65,7 @@ int vx_init(int device, vx_ctx **out) {
 
 int vx_destroy(vx_ctx *c) {
     if (!c) return VX_E_BAD_ARG;
+    if (c->tp) vx_tp_shutdown(c);      // the NCCL communicator goes before the stream it runs on
     {
         VxGuard g(c);
         cudaStreamSynchronize(c->stream);

@@ -205,16 +205,18 @@ def synth_tensors(spec: ModelSpec, seed=0):
     yield -1, capi.G_OUTPUT, out_type, qmat(spec.vocab, spec.hidden, out_type)
 
 
-def synth_weights_on_device(be, model, spec, seed, sink=None):
+def synth_weights_on_device(be, model, spec, seed, sink=None, embed_vocab=None):
     """Random weights of the model's shape and block formats, generated by CUDA kernels straight into GGUF blocks (Q4_0 by the
     benchmark's quantisation rule from N(0, sigma) draws; Q4_K / Q6_K as valid blocks with hashed payload).  The token
     embedding is kept in Q4_0 for every workload: it is read B rows per step and is not part of the timed traffic.
     sink(layer, slot, type, raw) -- optional -- receives every tensor as host data too (uint8 GGUF bytes, or the float32
-    norm vectors), so that a checker can be given the same model."""
+    norm vectors), so that a checker can be given the same model.  embed_vocab -- rows of the embedding table when they
+    differ from spec.vocab (a tensor-parallel rank: local output head, whole embedding)."""
     ones = np.ones(spec.hidden, np.float32)
     proj_types, _, out_type = tensor_types(spec)
     per_elem = {capi.T_Q4_0: 18 / 32, capi.T_Q4_K: 144 / 256, capi.T_Q6_K: 210 / 256}
-    big = max(spec.vocab * spec.hidden, spec.ffn * spec.hidden)
+    embed_vocab = embed_vocab or spec.vocab
+    big = max(embed_vocab * spec.hidden, spec.ffn * spec.hidden)
     d_tmp = be.AllocPermanent(int(big * max(per_elem.values())) + 256)
     n_t = 0
 
@@ -235,7 +237,7 @@ def synth_weights_on_device(be, model, spec, seed, sink=None):
         if sink is not None:
             sink(layer, slot, capi.T_F32, ones)
 
-    q(-1, capi.G_EMBED, spec.vocab, spec.hidden, capi.T_Q4_0)
+    q(-1, capi.G_EMBED, embed_vocab, spec.hidden, capi.T_Q4_0)
     for layer in range(spec.n_layers):
         norm(layer, capi.W_ATTN_NORM); norm(layer, capi.W_FFN_NORM)
         if spec.post_norms:
