@@ -256,6 +256,89 @@ def trace_arm(args):
 _RESULT_FD = None
 
 
+def tp_arm(args):
+    """One model split over all the ranks (tensor parallelism over NCCL) instead of one replica per rank: the configuration for
+    a model that one GPU cannot hold next to its KV cache.  Every rank keeps 1/world of each projection and of the KV heads of
+    ALL --batch sequences, runs the same greedy step and meets the others in two all-reduces per layer.  Total work is fixed as
+    the ranks grow, so the line reports strong scaling; value = batch * K / the slowest rank's device time."""
+    from vexel_b200 import tp
+    world, rank, local, dist = dist_setup(args.gpus)
+    spec = WORKLOADS[args.workload]
+    if args.layers > 0:
+        spec = gs.scaled(spec, args.layers, spec.hidden, spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.ffn, spec.vocab)
+    B, K, W = args.batch, args.steps, max(args.warmup, 3)
+    loc = tp.local_spec(spec, world)
+    rng = np.random.default_rng(replicas.GLOBAL_WORKLOAD_SEED)
+    ctx = rng.integers(args.ctx_min, args.ctx_max + 1, B)
+    tokens = rng.integers(0, spec.vocab, B).astype(np.int32)
+    total_new = W + 2 * K + 16
+    blocks_per_seq = int((args.ctx_max + total_new) // 16 + 2)
+    max_blocks = int(sum((c + total_new) // 16 + 2 for c in ctx) + 64)
+    be = capi.Backend(local)
+    if args.no_graphs:
+        be.lib.vx_set_graphs(0)
+    if world > 1:
+        tp.init_from_torch(be, dist)
+    else:
+        tp.init(be, tp.unique_id(be), 0, 1)
+    model = tp.create_model(be, spec, world, max_blocks=max_blocks, max_seqs=B, max_batch_tokens=max(B, 8), max_blocks_per_seq=blocks_per_seq)
+    gs.synth_weights_on_device(be, model, loc, seed=1000, embed_vocab=spec.vocab)   # (the same draws on every rank: the embedding is replicated)
+    model.shuffle_free_list(7)                                # the same block order on every rank: one set of block tables
+    seqs = np.arange(1, B + 1, dtype=np.int64)
+    for i, s in enumerate(seqs):
+        model.seq_fill_synthetic(int(s), int(ctx[i]), seed=100 + i)
+    pos = ctx.astype(np.int32).copy()
+    out, _ = model.decode_run(seqs, tokens, pos, W)
+    tokens = out[-1].copy(); pos += W
+    replicas.barrier(dist)
+    sampler = ClockSampler(local)
+    l0, _ = model.counters()
+    pos_timed, tokens_timed = pos.copy(), tokens.copy()
+    out, dev_ms = model.decode_run(seqs, tokens, pos, K)
+    l1, _ = model.counters()
+    clocks = sampler.stop()
+    replicas.barrier(dist)
+    slowest = replicas.max_over_ranks(dist, dev_ms / 1e3, local)
+    same = replicas.gather_objects(dist, int(np.asarray(out[-1], np.int64).sum()))
+    e2e = None
+    if not args.no_e2e:
+        for i, sq in enumerate(seqs):
+            model.seq_truncate(int(sq), int(pos_timed[i]))
+        pos = pos_timed.copy(); cur = tokens_timed
+        replicas.barrier(dist)
+        be.Sync()
+        t0 = time.perf_counter()
+        for _ in range(K):
+            cur = model.decode_step(seqs, cur, pos)
+            pos += 1
+        be.Sync()
+        e2e_s = replicas.max_over_ranks(dist, time.perf_counter() - t0, local)
+        e2e = {"value": B * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": int(5 * B * 4), "d2h_bytes_per_step": int(4 * B + 4),
+               "ms_per_step": e2e_s / K * 1e3}
+    per_rank = replicas.gather_objects(dist, {"rank": rank, "ms_per_step": dev_ms / K, "sm_mhz_median": clocks.get("sm_mhz"),
+                                              "clock_reasons": clocks.get("reasons")})
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        kvb = 2 * loc.n_kv_heads * loc.head_dim * 2
+        kv_tokens = float(sum(int(p) * K + K * (K + 1) // 2 for p in pos_timed)) / K
+        bytes_step = model.weight_bytes() + kv_tokens * kvb * spec.n_layers + B * spec.n_layers * kvb      # this rank's share
+        ar_bytes = 2 * spec.n_layers * B * spec.hidden * 4                                                # two f32 all-reduces per layer
+        step_ms = slowest / K * 1e3
+        emit({"metric": "decode tok/s", "value": B * K / slowest, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+              "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+              "dtype": "f32 activations, %s weights, f16 kv" % spec.quant, "data": "synthetic",
+              "config": {"workload": f"{spec.name} batched decode, B={B} over the whole group, ctx~U[{args.ctx_min},{args.ctx_max}] + generated, 16-token pages, shuffled blocks",
+                         "global_batch": B, "parallelism": f"tp{world} (NCCL all-reduce after Wo and W2, vocabulary-split head)",
+                         "l2": "inputs larger than L2: each step streams %.1f GB of weights+KV per rank" % (bytes_step / 1e9),
+                         "timing": "CUDA events on the launching stream around K steps with on-device token feedback; max over ranks"},
+              "step_roofline": {"bytes_per_step_per_rank": bytes_step, "achieved_GBs_per_rank": bytes_step / (step_ms * 1e-3) / 1e9,
+                                "frac_of_measured": bytes_step / (step_ms * 1e-3) / 1e9 / peak, "peak_source": f"{peak_kind} copy bandwidth",
+                                "allreduce_bytes_per_step": ar_bytes},
+              "ranks_agree_on_tokens": len(set(same)) == 1, "clocks": clocks, "gpu_launches": int(l1 - l0), "e2e": e2e, "per_rank": per_rank})
+    model.close(); be.close()
+    replicas.shutdown(dist)
+
+
 def claim_stdout():
     """Keeps the process's stdout for the one result line: everything else that writes to file descriptor 1 (libraries that
     print a banner from native code, child processes) is sent to stderr from here on."""
@@ -290,6 +373,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiling on a small case)")
     ap.add_argument("--trace", type=int, default=0, help="replay a Poisson arrival trace of this many requests through the scheduler instead of the fixed-batch steps")
+    ap.add_argument("--tp", action="store_true", help="one model split over all the ranks (tensor parallelism) instead of one replica per rank")
     ap.add_argument("--trace-rate", type=float, default=40.0, help="trace arrivals per second")
     ap.add_argument("--trace-max-prompt", type=int, default=8192)
     ap.add_argument("--no-dependent-launch", action="store_true", help="experiment: projections in plain stream order instead of as programmatic dependents")
@@ -302,6 +386,8 @@ def main():
 
     if args.trace > 0:
         return trace_arm(args)
+    if args.tp:
+        return tp_arm(args)
     world, rank, local, dist = dist_setup(args.gpus)
     spec = WORKLOADS[args.workload]
     if args.layers > 0:
