@@ -379,6 +379,7 @@ def main():
     ap.add_argument("--no-dependent-launch", action="store_true", help="experiment: projections in plain stream order instead of as programmatic dependents")
     ap.add_argument("--no-graphs", action="store_true", help="experiment: launch every kernel individually instead of replaying CUDA graphs")
     ap.add_argument("--no-persistent", action="store_true", help="experiment: Q4_0 decode projections on the one-CTA-per-tile tcgen05 kernel instead of the persistent one")
+    ap.add_argument("--no-thin", action="store_true", help="experiment: 1-4 row Q4_0 projections on the staged mma.sync kernel instead of the weight-streaming one")
     ap.add_argument("--tc-min-rows", type=int, default=-1, help="experiment: batch size from which projections use the tcgen05 kernel")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -420,6 +421,8 @@ def main():
         be.lib.vx_set_graphs(0)
     if args.no_persistent:
         be.lib.vx_set_persistent_projections(0)
+    if args.no_thin:
+        be.lib.vx_set_thin_batch_projections(0)
     model = capi.Model(be, gs.model_config(spec, max_blocks, max_seqs=seq_cap, max_batch_tokens=max(seq_cap, 8), max_blocks_per_seq=blocks_per_seq))
     gs.synth_weights_on_device(be, model, spec, seed=seeds["weights"])
     model.shuffle_free_list(seeds["free_list"])               # physical blocks shuffled randomly in the pool

@@ -300,6 +300,10 @@ int vx_set_tc_min_rows(int rows);
  * pipeline kept full across tiles); 0 = one CTA per tile as for the other formats.  Default on.  No counterpart in the
  * reference. */
 int vx_set_persistent_projections(int enable);
+/* Q4_0 projections of 1..4 batch rows run on the weight-streaming mma.sync kernel (the single-sequence decode of
+ * runtime/block.go:947-1060: one quantised mat-vec per projection); 0 = the staged mma.sync kernel as for 5..16 rows.
+ * Default on. */
+int vx_set_thin_batch_projections(int enable);
 /* projection kernels are launched as programmatic dependents of the kernel before them (their set-up and first weight
  * tiles overlap its tail); 0 = plain stream order.  Default on.  No counterpart in the reference. */
 int vx_set_dependent_launch(int enable);

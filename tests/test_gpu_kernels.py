@@ -147,7 +147,10 @@ def test_matmul_f32(be):
 
 # ------------------------------------------------------------------ quantised projections
 @pytest.mark.parametrize("m,n,k", [(1, 256, 256), (1, 4096, 4096), (3, 1000, 512), (8, 2560, 2048), (13, 384, 1024),
-                                   (32, 512, 4096), (64, 1024, 11008), (100, 300, 160), (1, 32000, 2048)])
+                                   (32, 512, 4096), (64, 1024, 11008), (100, 300, 160), (1, 32000, 2048),
+                                   # thin batches on the register-streaming kernel: odd row counts, a K that is not a whole
+                                   # number of 128-weight groups, more groups than one staged chunk, both tile modes
+                                   (2, 4096, 11008), (4, 12288, 4096), (5, 1000, 1184), (7, 200, 4096), (8, 22016, 4096), (1, 70, 32)])
 def test_matmul_q4_0(be, m, n, k):
     rng = np.random.default_rng(m * 1000 + n)
     w = rng.standard_normal((n, k)).astype(np.float32) * 0.02

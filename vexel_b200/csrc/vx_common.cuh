@@ -75,6 +75,14 @@ struct VxPerDevice {
         if (e == cudaSuccess && tracked) mask.fetch_or(1ull << c->device, std::memory_order_release);
         return e;
     }
+    // runs set() (any per-device kernel attribute calls) the first time this device comes by
+    template <typename F> cudaError_t once(const vx_ctx *c, F set) {
+        const bool tracked = c->device >= 0 && c->device < 64;
+        if (tracked && ((mask.load(std::memory_order_acquire) >> c->device) & 1ull)) return cudaSuccess;
+        cudaError_t e = set();
+        if (e == cudaSuccess && tracked) mask.fetch_or(1ull << c->device, std::memory_order_release);
+        return e;
+    }
 };
 
 template <typename T> static inline T *dp(vx_dptr p) { return reinterpret_cast<T *>(static_cast<uintptr_t>(p)); }
@@ -196,6 +204,10 @@ int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *ou
 bool vxq_gemm_tcp_eligible(const VxWeight &w, int m);      // vx_gemm_tcp.cu: the persistent tcgen05 kernel covers this projection
 int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out, float *parts,
                  size_t parts_cap_floats);
+// thin batches (1-8 rows) of Q4_0 weights: mma.sync kernel that streams the weights through registers (vx_gemv.cu)
+bool vxq_gemv_eligible(const VxWeight &w, int m);
+int vxq_gemv(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out, float *parts,
+             size_t parts_cap_floats);
 // tensor parallelism (vx_tp.cu)
 int vxtp_world(vx_ctx *c);
 int vxtp_rank(vx_ctx *c);

@@ -621,6 +621,7 @@ int vxq_gemm(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, 
     if (x.k_pad != w.k_pad) return vx_fail(c, VX_E_BAD_ARG, "projection: activation row stride %d != weight k_pad %d", x.k_pad, w.k_pad);
     // measured crossover to the tcgen05 kernel (whose cost per weight does not depend on the batch): 17 rows for Q4_0 and
     // Q6_K, 33 for Q4_K, whose mma.sync variant stays ahead up to its 32-row tile
+    if (g_gemm_terms == 2 && vxq_gemv_eligible(w, m)) return vxq_gemv(c, w, x, m, out, ld_out, n_parts_out, parts, parts_cap_floats);
     const int tc_rows = (w.type == VX_T_Q4_K && g_tc_min_rows > 0) ? max(g_tc_min_rows, 33) : g_tc_min_rows;
     if (tc_rows > 0 && m >= tc_rows && g_gemm_terms == 2)
         return vxq_gemm_tc(c, w, x, m, out, ld_out, n_parts_out, parts, parts_cap_floats);
