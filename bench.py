@@ -242,12 +242,13 @@ def trace_arm(args):
     be = capi.Backend(0)
     kv_block_bytes = spec.kv_bytes_per_token() * 16
     max_blocks = int(min(120e9 // kv_block_bytes, 256 * (max_ctx // 16 + 2)))         # as much pool as ~120 GB allows; admission handles the rest
-    model = capi.Model(be, gs.model_config(spec, max_blocks, max_seqs=256, max_batch_tokens=256, max_blocks_per_seq=max_ctx // 16 + 2))
+    # a step packs the decode rows of up to 256 sequences plus prompt chunks up to this row budget
+    model = capi.Model(be, gs.model_config(spec, max_blocks, max_seqs=256, max_batch_tokens=args.trace_step_tokens, max_blocks_per_seq=max_ctx // 16 + 2))
     gs.synth_weights_on_device(be, model, spec, seed=0)
     res = tr.replay(model, arrivals, prompts, olen, max_batch=256)
     line = {"metric": "trace decode tok/s", "value": res["tok_per_s"], "unit": "tok/s", "n_gpus": 1, "higher_is_better": True, "data": "synthetic",
             "config": {"workload": f"{spec.name}: {args.trace} requests, Poisson {args.trace_rate}/s, prompts lognormal(ln 512, 0.8) clipped to "
-                                   f"[16,{args.trace_max_prompt}], outputs U[32,512], max batch 256, pool {max_blocks} blocks"},
+                                   f"[16,{args.trace_max_prompt}], outputs U[32,512], max batch 256, {args.trace_step_tokens} rows per step (decode rows + prompt chunks), pool {max_blocks} blocks"},
             "trace": res}
     emit(line)
     model.close(); be.close()
@@ -376,6 +377,7 @@ def main():
     ap.add_argument("--tp", action="store_true", help="one model split over all the ranks (tensor parallelism) instead of one replica per rank")
     ap.add_argument("--trace-rate", type=float, default=40.0, help="trace arrivals per second")
     ap.add_argument("--trace-max-prompt", type=int, default=8192)
+    ap.add_argument("--trace-step-tokens", type=int, default=1024, help="rows per scheduler step in the trace replay: decode rows plus prompt chunks")
     ap.add_argument("--no-dependent-launch", action="store_true", help="experiment: projections in plain stream order instead of as programmatic dependents")
     ap.add_argument("--no-graphs", action="store_true", help="experiment: launch every kernel individually instead of replaying CUDA graphs")
     ap.add_argument("--no-persistent", action="store_true", help="experiment: Q4_0 decode projections on the one-CTA-per-tile tcgen05 kernel instead of the persistent one")

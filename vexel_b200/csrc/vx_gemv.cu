@@ -4,9 +4,9 @@
 // inference/runtime/block.go:947-1060, kernels metal_bridge_darwin.m matvec_q4_0*).  With a handful of rows the product is
 // a stream over the weights, and what limits it is the number of instructions spent per weight byte, so this kernel keeps
 // that number low:
-//   * a warp owns 16 weight rows; lane (g, c) loads, straight from global memory into registers, the 16-byte slot c of rows
-//     g and g + 8 of every 128-weight group (the repacked layout of vx_quant.cu) -- exactly the nibbles of its own mma.sync
-//     A fragments, so no ldmatrix and no CTA barrier; the copies go through a per-warp cp.async ring, seven groups ahead;
+//   * a warp owns 16 weight rows; lane (g, c) fetches the 16-byte slot c of rows g and g + 8 of every 128-weight group (the
+//     repacked layout of vx_quant.cu) -- exactly the nibbles of its own mma.sync A fragments, so no ldmatrix and no CTA
+//     barrier; the copies go through a per-warp cp.async ring, seven groups ahead;
 //   * a nibble becomes an fp16 integer with one logic operation and one subtraction (0x6400 | q = 1024 + q); the high
 //     nibbles are taken in place, (1024 + 16 q) / 16 - 72 in one exact FMA, so nothing is shifted into position;
 //   * the rows keep their fp16 hi and lo parts side by side in the eight columns of one m16n8k16 tile, so that the

@@ -48,6 +48,7 @@ def replay(model: capi.Model, arrivals, prompts, out_lens, max_batch=256, max_se
             if fin:
                 done_at[i] = now; live.discard(i)
     met = sched.Metrics()
+    preemptions, refused = sched.pressure()
     sched.close()
     gen = int(got.sum())
     return {"requests": n, "generated_tokens": gen, "prompt_tokens": int(sum(len(p) for p in prompts)), "makespan_s": now, "busy_s": busy,
@@ -55,4 +56,5 @@ def replay(model: capi.Model, arrivals, prompts, out_lens, max_batch=256, max_se
             "ttft_mean_s": float(np.nanmean(first_tok - arrivals[:n])), "ttft_p95_s": float(np.nanpercentile(first_tok - arrivals[:n], 95)),
             "latency_mean_s": float(np.nanmean(done_at - arrivals[:n])),
             "sched_prefill_s": met.prefill_seconds, "sched_decode_s": met.decode_seconds, "sched_decode_tokens": met.decode_tokens,
-            "sched_prefill_tokens": met.prefill_tokens}
+            "sched_prefill_tokens": met.prefill_tokens, "completed": int(np.isfinite(done_at).sum()), "preemptions": int(preemptions),
+            "refused": int(refused)}
