@@ -304,6 +304,10 @@ int vx_set_persistent_projections(int enable);
  * runtime/block.go:947-1060: one quantised mat-vec per projection); 0 = the staged mma.sync kernel as for 5..16 rows.
  * Default on. */
 int vx_set_thin_batch_projections(int enable);
+/* timing experiments only: bit 0 skips every projection launch of a step, bit 1 the row kernels, bit 2 the attention
+ * kernels (the step's results are then meaningless; what remains is timed to attribute a step's time to kernel classes).
+ * 0 restores the real step. */
+int vx_debug_skip(int mask);
 /* projection kernels are launched as programmatic dependents of the kernel before them (their set-up and first weight
  * tiles overlap its tail); 0 = plain stream order.  Default on.  No counterpart in the reference. */
 int vx_set_dependent_launch(int enable);
