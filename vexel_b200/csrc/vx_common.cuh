@@ -234,6 +234,11 @@ struct VxAttnArgs {
     float *out; int out_row_stride;           // [rows][Hq*D]
     int rows, n_q_heads, n_kv_heads, head_dim, block_size;
     float scale, softcap;
+    // optional, zeroed by the caller before the launch: the work-list kernels raise row_bound[row] (float bits, atomicMax) to
+    // the largest |O| / L of any chunk and head of the row -- an upper bound of the row's largest output magnitude, since
+    // the merged output is a convex combination of the chunks' normalised outputs.  With it the merge + split kernel knows
+    // the row scale without a row-wide reduction and can spread a row over several CTAs.
+    unsigned int *row_bound;
 };
 int vxp_attention(vx_ctx *c, const VxAttnArgs &a);
 int vxp_prefill_f32(vx_ctx *c, const float *q, int q_ld, const float *k, const float *v, long kv_ld, float *out, int out_ld, int n_rows,

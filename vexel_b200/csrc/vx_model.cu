@@ -56,6 +56,7 @@ struct vx_model {
     int32_t *d_step_in = nullptr, *h_step_in = nullptr;   // pinned staging + device copy
     int32_t *d_cu = nullptr, *d_row_slot = nullptr, *d_row_pos = nullptr, *d_slot_map = nullptr, *d_row_kv_len = nullptr,
             *d_row_kv_start = nullptr, *d_row_route = nullptr, *d_last_row = nullptr;
+    unsigned int *d_row_bound = nullptr;         // per packed row: upper bound of the attention output's magnitude (float bits)
     float *d_hidden = nullptr;                   // post-final-norm hidden states of the output rows of the last step
     bool fast_attn_shape = false;                // the paged attention kernels that walk work lists cover this head shape
     // tensor parallelism: this model is one rank's slice (local heads / FFN columns / vocabulary rows in cfg); the embedding
@@ -428,8 +429,9 @@ constexpr int ROPE_HEADS = 4;   // heads per CTA
 __global__ void __launch_bounds__(128)
 rope_append_kernel(const float *src, int n_parts, size_t part_stride, float *qkv, int ld,   // src may alias qkv (n_parts == 1)
                    const float *__restrict__ cs, const float *__restrict__ sn, const int32_t *__restrict__ slot_map,
-                   __half *__restrict__ pool_layer, int n_heads, int n_kv_heads, int D, int neox) {
+                   __half *__restrict__ pool_layer, int n_heads, int n_kv_heads, int D, int neox, unsigned int *row_bound) {
     const int t = blockIdx.x, half = D / 2;
+    if (row_bound && blockIdx.y == 0 && threadIdx.x == 0) row_bound[t] = 0u;   // the attention kernels behind this one raise it
     const int h0 = blockIdx.y * ROPE_HEADS, h1 = min(h0 + ROPE_HEADS, n_heads + 2 * n_kv_heads);
     const float *srow = src + (size_t)t * ld;
     float *drow = qkv + (size_t)t * ld;
@@ -676,7 +678,8 @@ int forward(vx_model *m, int rows, const std::vector<RowRange> &special, int pla
         if (!(g_dbg_skip & 2)) {
             dim3 rg(rows, ceil_div(Hq + 2 * Hkv, ROPE_HEADS));
             rope_append_kernel<<<rg, 128, 0, c->stream>>>(qkv_src, np_qkv, (size_t)rows * nqkv, m->qkv, nqkv, m->d_cos, m->d_sin, m->d_slot_map,
-                                                          m->pool + (size_t)l * m->layer_stride, Hq, Hkv, D, cf.rope_neox);   // block.go:858-868
+                                                          m->pool + (size_t)l * m->layer_stride, Hq, Hkv, D, cf.rope_neox,
+                                                          (special.empty() && !(g_dbg_skip & 8)) ? m->d_row_bound : nullptr);   // block.go:858-868
             VX_LAUNCH_CHECK(c);
         }
         time_begin(m, 0);
@@ -691,6 +694,9 @@ int forward(vx_model *m, int rows, const std::vector<RowRange> &special, int pla
             a.partials = m->d_partials; a.out = m->attn; a.out_row_stride = qd;
             a.rows = rows; a.n_q_heads = Hq; a.n_kv_heads = Hkv; a.head_dim = D; a.block_size = BS;
             a.scale = scale; a.softcap = cf.attn_softcap;
+            // every row walks the work list: the kernels report a bound of each row's output and the merge spreads a row over
+            // several CTAs (rows served by the prompt kernels below have no such bound)
+            a.row_bound = (special.empty() && !(g_dbg_skip & (2 | 8))) ? m->d_row_bound : nullptr;
             for (const RowRange &r : special) {
                 if (r.route == 1) {
                     const float *q = m->qkv + (size_t)r.row0 * nqkv;
@@ -1065,7 +1071,7 @@ int vx_model_create(vx_ctx *c, const vx_model_config *cfg, vx_model **out) {
     MA(model_alloc_t(m, (size_t)T, &m->d_row_slot)); MA(model_alloc_t(m, (size_t)T, &m->d_row_pos));
     MA(model_alloc_t(m, (size_t)T, &m->d_slot_map)); MA(model_alloc_t(m, (size_t)T, &m->d_row_kv_len));
     MA(model_alloc_t(m, (size_t)std::max(T, cfg->max_seqs) + 1, &m->d_row_kv_start));
-    MA(model_alloc_t(m, (size_t)T, &m->d_row_route)); MA(model_alloc_t(m, (size_t)cfg->max_seqs, &m->d_last_row));
+    MA(model_alloc_t(m, (size_t)T, &m->d_row_route)); MA(model_alloc_t(m, (size_t)T, &m->d_row_bound)); MA(model_alloc_t(m, (size_t)cfg->max_seqs, &m->d_last_row));
     MA(model_alloc_t(m, (size_t)T * H, &m->d_hidden));
     {
         const int G = cfg->n_heads / cfg->n_kv_heads;

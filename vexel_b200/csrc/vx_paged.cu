@@ -74,6 +74,12 @@ __global__ void paged_generic_kernel(VxAttnArgs a) {
 }
 
 // ------------------------------------------------------------------ split-K FlashDecoding kernel (f16 pool, 16-token pages)
+// one atomic per warp: non-negative floats order like their bit patterns (a NaN or infinity becomes a huge bound, and the
+// row scale falls back to 1 exactly as the row-wide maximum would make it)
+__device__ __forceinline__ void vx_raise_row_bound(unsigned int *slot, float v) {
+    v = warp_max(v);
+    if ((threadIdx.x & 31) == 0 && v > 0.f) atomicMax(slot, __float_as_uint(v));
+}
 constexpr int ATT_WARPS = 4;
 constexpr int ATT_BS = 16;
 
@@ -205,6 +211,7 @@ paged_flash_kernel(VxAttnArgs a) {
     }
     __syncthreads();
     const bool single = (a.row_work_start[row + 1] - a.row_work_start[row]) == 1;
+    float bound = 0.f;
     for (int idx = threadIdx.x; idx < G * D; idx += ATT_WARPS * 32) {
         const int gi = idx / D, d = idx % D;
         float M = -INFINITY;
@@ -217,14 +224,17 @@ paged_flash_kernel(VxAttnArgs a) {
             L = fmaf(sm_l[w][gi], f, L); O = fmaf(sm_acc[w][gi][d], f, O);
         }
         const int h = kvh * G + gi;
+        const float o = L > 0.f ? O / L : 0.f;
+        bound = fmaxf(bound, fabsf(o));
         if (single) {
-            a.out[(size_t)row * a.out_row_stride + (size_t)h * D + d] = L > 0.f ? O / L : 0.f;
+            a.out[(size_t)row * a.out_row_stride + (size_t)h * D + d] = o;
         } else {
             float *part = a.partials + ((size_t)wi * a.n_q_heads + h) * (D + 2);
             part[d] = O;
             if (d == 0) { part[D] = M; part[D + 1] = L; }
         }
     }
+    if (a.row_bound) vx_raise_row_bound(a.row_bound + row, bound);
 }
 
 // ------------------------------------------------------------------ grouped-query variant on the tensor cores
@@ -421,6 +431,7 @@ paged_flash_mma_kernel(VxAttnArgs a) {
     }
     __syncthreads();
     const bool single = (a.row_work_start[row + 1] - a.row_work_start[row]) == 1;
+    float bound = 0.f;
     for (int idx = threadIdx.x; idx < G * D; idx += NW * 32) {
         const int gi = idx / D, d = idx % D;
         float M = -INFINITY;
@@ -433,14 +444,17 @@ paged_flash_mma_kernel(VxAttnArgs a) {
             L = fmaf(sm_l[w * G + gi], f, L); O = fmaf(sm_acc[(w * G + gi) * D + d], f, O);
         }
         const int h = kvh * G + gi;
+        const float o = L > 0.f ? O / L : 0.f;
+        bound = fmaxf(bound, fabsf(o));
         if (single) {
-            a.out[(size_t)row * a.out_row_stride + (size_t)h * D + d] = L > 0.f ? O / L : 0.f;
+            a.out[(size_t)row * a.out_row_stride + (size_t)h * D + d] = o;
         } else {
             float *part = a.partials + ((size_t)wi * a.n_q_heads + h) * (D + 2);
             part[d] = O;
             if (d == 0) { part[D] = M; part[D + 1] = L; }
         }
     }
+    if (a.row_bound) vx_raise_row_bound(a.row_bound + row, bound);
 }
 
 // rows cut into more than one chunk: out = sum_c O_c e^{m_c-M} / sum_c l_c e^{m_c-M}
@@ -856,6 +870,66 @@ __global__ void __launch_bounds__(VX_ROW_THREADS) paged_merge_split_kernel(VxAtt
     }
 }
 
+// The same merge + split with the row scale taken from a.row_bound instead of a row-wide maximum: nothing ties the CTAs of
+// a row together any more, so a row is spread over cols / 1024 CTAs of 256 threads (four consecutive head dimensions per
+// thread, whole heads per CTA), four times as many SMs work on the launch and every CTA's chain of dependent loads is a
+// quarter as wide.  The bound is at least the row's largest magnitude and rarely more than a small factor above it: the
+// fp16 pair keeps 22 - log2(factor) significant bits.
+constexpr int MS_THREADS = 256, MS_COLS = MS_THREADS * 4;
+__global__ void __launch_bounds__(MS_THREADS) paged_merge_split_heads_kernel(VxAttnArgs a, VxSplit s, int n_max) {
+    extern __shared__ float fw[];                  // [heads of this CTA][n_max] normalised chunk weights, then the chunk sums
+    vx_pdl_trigger();          // the projection that follows may become resident and fetch its first weights now
+    const int row = blockIdx.x, D = a.head_dim, Hq = a.n_q_heads;
+    const int col0 = blockIdx.y * MS_COLS, h0 = col0 / D, nh = MS_COLS / D;
+    const int w0 = a.row_work_start[row], n = a.row_work_start[row + 1] - w0;
+    float sc, inv;
+    vx_row_scale(__uint_as_float(a.row_bound[row]), sc, inv);
+    if (blockIdx.y == 0 && threadIdx.x == 0) s.scale[row] = sc;
+    if (n > 1) {
+        float *ms = fw, *ls = fw + nh * n_max;
+        for (int i = threadIdx.x; i < nh * n; i += MS_THREADS) {
+            const int c = i / nh, h = i % nh;
+            const float *p0 = a.partials + ((size_t)(w0 + c) * Hq + h0 + h) * (D + 2) + D;
+            ms[h * n_max + c] = p0[0]; ls[h * n_max + c] = p0[1];
+        }
+        __syncthreads();
+        for (int h = threadIdx.x; h < nh; h += MS_THREADS) {
+            float M = -INFINITY;
+            for (int c = 0; c < n; c++) M = fmaxf(M, ms[h * n_max + c]);
+            float L = 0.f;
+            for (int c = 0; c < n; c++) {
+                const float mc = ms[h * n_max + c];
+                const float f = mc == -INFINITY ? 0.f : __expf(mc - M);
+                ms[h * n_max + c] = f;
+                L = fmaf(ls[h * n_max + c], f, L);
+            }
+            const float il = L > 0.f ? 1.0f / L : 0.f;
+            for (int c = 0; c < n; c++) fw[h * n_max + c] = ms[h * n_max + c] * il;
+        }
+        __syncthreads();
+    }
+    const int k0 = col0 + threadIdx.x * 4;
+    float4 v;
+    if (n > 1) {
+        const int h = k0 / D, d = k0 % D;
+        const float *pp = a.partials + ((size_t)w0 * Hq + h) * (D + 2) + d;
+        const size_t cs = (size_t)Hq * (D + 2);
+        const float *f = fw + (h - h0) * n_max;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int c = 0; c < n; c++) {
+            const float2 x0 = *reinterpret_cast<const float2 *>(pp + c * cs), x1 = *reinterpret_cast<const float2 *>(pp + c * cs + 2);
+            const float fc = f[c];
+            acc.x = fmaf(x0.x, fc, acc.x); acc.y = fmaf(x0.y, fc, acc.y); acc.z = fmaf(x1.x, fc, acc.z); acc.w = fmaf(x1.y, fc, acc.w);
+        }
+        v = acc;
+    } else {
+        v = *reinterpret_cast<const float4 *>(a.out + (size_t)row * a.out_row_stride + k0);
+    }
+    const float t[4] = {v.x * inv, v.y * inv, v.z * inv, v.w * inv};
+    vx_split_store4(t, s.hi + (size_t)row * s.k_pad, s.lo + (size_t)row * s.k_pad, s.bsum + (size_t)row * (s.k_pad / 32), k0);
+}
+
 template <int D, int G>
 static int flash_launch_mma(vx_ctx *c, const VxAttnArgs &a, dim3 grid) {
     // head_dim 256 doubles the staging buffers and the register file per warp: two warps per CTA keep three CTAs on an SM
@@ -909,6 +983,14 @@ int vxp_attention_split(vx_ctx *c, const VxAttnArgs &a, const VxSplit *split, in
             VX_LAUNCH_CHECK(c);
             const int cols = a.n_q_heads * D;
             const size_t fw_bytes = 2 * (size_t)a.n_q_heads * max(n_max_chunks, 1) * sizeof(float);
+            if (split && fused && a.row_bound && n_max_chunks > 0 && cols % MS_COLS == 0 && split->k_pad == cols && MS_COLS % D == 0 &&
+                a.out_row_stride % 4 == 0 && 2 * (size_t)(MS_COLS / D) * n_max_chunks * sizeof(float) <= 40 * 1024) {
+                const size_t bytes = 2 * (size_t)(MS_COLS / D) * n_max_chunks * sizeof(float);
+                paged_merge_split_heads_kernel<<<dim3(a.rows, cols / MS_COLS), MS_THREADS, bytes, c->stream>>>(a, *split, n_max_chunks);
+                VX_LAUNCH_CHECK(c);
+                *fused = true;
+                return VX_OK;
+            }
             if (split && fused && n_max_chunks > 0 && fw_bytes <= 40 * 1024 && split->k_pad <= 8 * VX_ROW_THREADS * 4 && a.out_row_stride % 4 == 0) {
                 const int nc = ceil_div(split->k_pad, VX_ROW_THREADS * 4);
                 switch (nc) {
