@@ -379,6 +379,7 @@ def main():
     ap.add_argument("--trace-max-prompt", type=int, default=8192)
     ap.add_argument("--trace-step-tokens", type=int, default=1024, help="rows per scheduler step in the trace replay: decode rows plus prompt chunks")
     ap.add_argument("--no-dependent-launch", action="store_true", help="experiment: projections in plain stream order instead of as programmatic dependents")
+    ap.add_argument("--chain-launch", action="store_true", help="experiment: every kernel of a layer launched as a programmatic dependent of the one before it, not only the projections")
     ap.add_argument("--no-graphs", action="store_true", help="experiment: launch every kernel individually instead of replaying CUDA graphs")
     ap.add_argument("--no-persistent", action="store_true", help="experiment: Q4_0 decode projections on the one-CTA-per-tile tcgen05 kernel instead of the persistent one")
     ap.add_argument("--no-thin", action="store_true", help="experiment: 1-4 row Q4_0 projections on the staged mma.sync kernel instead of the weight-streaming one")
@@ -419,6 +420,8 @@ def main():
         be.lib.vx_set_tc_min_rows(args.tc_min_rows)
     if args.no_dependent_launch:
         be.lib.vx_set_dependent_launch(0)
+    if args.chain_launch:
+        be.lib.vx_set_dependent_launch(2)
     if args.no_graphs:
         be.lib.vx_set_graphs(0)
     if args.no_persistent:

@@ -140,6 +140,19 @@ static inline cudaError_t vx_launch_dependent(void (*kernel)(KArgs...), dim3 gri
     cfg.attrs = at; cfg.numAttrs = g_vx_pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
+// The other kernels of a layer (norms, RoPE + append, attention, merge, activation) chained the same way when the switch is
+// at 2: each of them starts with vx_pdl_wait() followed by vx_pdl_trigger(), so its successor's launch is processed while it
+// runs, but becomes resident only once its own predecessor has completed.  At 0 or 1 this is a plain launch.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t vx_launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = g_vx_pdl >= 2 ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 // ---- shared between translation units ---------------------------------------------------------
 // Activation rows prepared for the tensor-core projections: x = s * (hi + lo) with hi, lo fp16 and

@@ -100,6 +100,7 @@ gemv_q4_0_kernel(const uint4 *__restrict__ qs, const __half *__restrict__ sc, co
 #pragma unroll
     for (int j = 0; j < GV_STAGES - 1; j++) request(j);
     vx_pdl_wait();
+    vx_pdl_trigger();                                        // (chained launch) the row kernel behind this one may be set up now
 
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int j = 0; j < n_j; j++) {

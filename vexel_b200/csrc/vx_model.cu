@@ -334,6 +334,7 @@ __global__ void __launch_bounds__(VX_ROW_THREADS)
 add_norm_split_kernel(float *x, const float *parts, int n_parts, size_t part_stride, int part_ld, const float *post_w, const float *w,
                       float eps, int hidden, VxSplit s, float *capture, const int32_t *row_idx, float *normed_out) {
     __shared__ float red[32];
+    vx_pdl_wait();             // (chained launch: the kernel before this one has completed)
     vx_pdl_trigger();          // the projection that follows may become resident and fetch its first weights now
     const int r = blockIdx.x;
     float *xr = x + (size_t)(row_idx ? row_idx[r] : r) * hidden;
@@ -430,6 +431,8 @@ __global__ void __launch_bounds__(128)
 rope_append_kernel(const float *src, int n_parts, size_t part_stride, float *qkv, int ld,   // src may alias qkv (n_parts == 1)
                    const float *__restrict__ cs, const float *__restrict__ sn, const int32_t *__restrict__ slot_map,
                    __half *__restrict__ pool_layer, int n_heads, int n_kv_heads, int D, int neox, unsigned int *row_bound) {
+    vx_pdl_wait();
+    vx_pdl_trigger();
     const int t = blockIdx.x, half = D / 2;
     if (row_bound && blockIdx.y == 0 && threadIdx.x == 0) row_bound[t] = 0u;   // the attention kernels behind this one raise it
     const int h0 = blockIdx.y * ROPE_HEADS, h1 = min(h0 + ROPE_HEADS, n_heads + 2 * n_kv_heads);
@@ -496,6 +499,7 @@ act_split_kernel(const float *__restrict__ h13, int n_parts, size_t part_stride,
     const int CL = (int)cluster.num_blocks(), q = (int)cluster.block_rank();
     __shared__ float red[32];
     __shared__ float cl_amax;
+    vx_pdl_wait();             // (chained launch: the kernel before this one has completed)
     vx_pdl_trigger();          // the projection that follows may become resident and fetch its first weights now
     const int r = blockIdx.x / CL;
     const float *gr = h13 + (size_t)r * 2 * ffn, *ur = gr + ffn;
@@ -596,8 +600,10 @@ int add_norm_split_rows(vx_model *m, float *x, int rows, const float *parts, int
     if (g_dbg_skip & 2) return VX_OK;
     const int H = m->cfg.hidden;
     if (H > 8192) return vx_fail(m->c, VX_E_UNSUPPORTED, "hidden size %d > 8192", H);
-    if (H > 4096) add_norm_split_kernel<2><<<rows, VX_ROW_THREADS, 0, m->c->stream>>>(x, parts, n_parts, part_stride, part_ld, post_w, w, m->cfg.rms_eps, H, s, capture, row_idx, normed_out);
-    else add_norm_split_kernel<1><<<rows, VX_ROW_THREADS, 0, m->c->stream>>>(x, parts, n_parts, part_stride, part_ld, post_w, w, m->cfg.rms_eps, H, s, capture, row_idx, normed_out);
+    cudaError_t le;
+    if (H > 4096) le = vx_launch_chain(add_norm_split_kernel<2>, dim3(rows), dim3(VX_ROW_THREADS), 0, m->c->stream, x, parts, n_parts, part_stride, part_ld, post_w, w, m->cfg.rms_eps, H, s, capture, row_idx, normed_out);
+    else le = vx_launch_chain(add_norm_split_kernel<1>, dim3(rows), dim3(VX_ROW_THREADS), 0, m->c->stream, x, parts, n_parts, part_stride, part_ld, post_w, w, m->cfg.rms_eps, H, s, capture, row_idx, normed_out);
+    if (le != cudaSuccess) return vx_cuda_fail(m->c, le, "add + norm launch");
     VX_LAUNCH_CHECK(m->c);
     return VX_OK;
 }
@@ -616,9 +622,10 @@ int act_split(vx_model *m, int rows, int n_parts) {
     int nc = ceil_div(m->sp_f.k_pad, cl * VX_ROW_THREADS * 4);
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(rows * cl); lc.blockDim = dim3(VX_ROW_THREADS); lc.dynamicSmemBytes = 0; lc.stream = m->c->stream;
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = cl; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-    lc.attrs = at; lc.numAttrs = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[1].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at; lc.numAttrs = g_vx_pdl >= 2 ? 2 : 1;
     const float *parts_c = m->parts;
     switch (nc) {
 #define VX_ACT_CASE(N) case N: VX_CUDA(m->c, cudaLaunchKernelEx(&lc, act_split_kernel<N>, parts_c, n_parts, pstride, F, m->cfg.geglu, m->sp_f)); break;
@@ -677,9 +684,11 @@ int forward(vx_model *m, int rows, const std::vector<RowRange> &special, int pla
         }
         if (!(g_dbg_skip & 2)) {
             dim3 rg(rows, ceil_div(Hq + 2 * Hkv, ROPE_HEADS));
-            rope_append_kernel<<<rg, 128, 0, c->stream>>>(qkv_src, np_qkv, (size_t)rows * nqkv, m->qkv, nqkv, m->d_cos, m->d_sin, m->d_slot_map,
-                                                          m->pool + (size_t)l * m->layer_stride, Hq, Hkv, D, cf.rope_neox,
-                                                          (special.empty() && !(g_dbg_skip & 8)) ? m->d_row_bound : nullptr);   // block.go:858-868
+            cudaError_t le = vx_launch_chain(rope_append_kernel, rg, dim3(128), 0, c->stream, qkv_src, np_qkv, (size_t)rows * nqkv, m->qkv, nqkv,
+                                             (const float *)m->d_cos, (const float *)m->d_sin, (const int32_t *)m->d_slot_map,
+                                             m->pool + (size_t)l * m->layer_stride, Hq, Hkv, D, (int)cf.rope_neox,
+                                             (special.empty() && !(g_dbg_skip & 8)) ? m->d_row_bound : nullptr);   // block.go:858-868
+            if (le != cudaSuccess) return vx_cuda_fail(c, le, "RoPE + append launch");
             VX_LAUNCH_CHECK(c);
         }
         time_begin(m, 0);

@@ -96,6 +96,8 @@ __device__ __forceinline__ void unpack8(const uint4 &u, float (&f)[8]) {
 template <int D, int G>
 __global__ void __launch_bounds__(ATT_WARPS * 32, 5)
 paged_flash_kernel(VxAttnArgs a) {
+    vx_pdl_wait();
+    vx_pdl_trigger();
     constexpr int LPT = D / 8;            // lanes per token
     constexpr int TPW = 32 / LPT;         // tokens per warp-wide load
     constexpr int NI = ATT_BS / TPW;      // loads per page
@@ -276,6 +278,8 @@ paged_flash_mma_kernel(VxAttnArgs a) {
     constexpr int STAGE_B = 2 * TILE_B;           // K tile then V tile
     constexpr int CPL = STAGE_B / 16 / 32;        // 16-byte chunks per lane and page
     extern __shared__ __align__(128) unsigned char att_smem[];
+    vx_pdl_wait();
+    vx_pdl_trigger();
 
     const int wi = blockIdx.x;
     if (wi >= *a.n_work_dev) return;
@@ -801,6 +805,7 @@ template <int NC>
 __global__ void __launch_bounds__(VX_ROW_THREADS) paged_merge_split_kernel(VxAttnArgs a, VxSplit s, int cols, int n_max) {
     extern __shared__ float fw[];                  // [n_q_heads][n_max] normalised chunk weights, then [n_q_heads][n_max] chunk sums
     __shared__ float red[32];
+    vx_pdl_wait();             // (chained launch: the attention kernel before this one has completed)
     vx_pdl_trigger();          // the projection that follows may become resident and fetch its first weights now
     const int row = blockIdx.x, D = a.head_dim, Hq = a.n_q_heads;
     const int w0 = a.row_work_start[row], n = a.row_work_start[row + 1] - w0;
@@ -878,6 +883,7 @@ __global__ void __launch_bounds__(VX_ROW_THREADS) paged_merge_split_kernel(VxAtt
 constexpr int MS_THREADS = 256, MS_COLS = MS_THREADS * 4;
 __global__ void __launch_bounds__(MS_THREADS) paged_merge_split_heads_kernel(VxAttnArgs a, VxSplit s, int n_max) {
     extern __shared__ float fw[];                  // [heads of this CTA][n_max] normalised chunk weights, then the chunk sums
+    vx_pdl_wait();             // (chained launch: the attention kernel before this one has completed)
     vx_pdl_trigger();          // the projection that follows may become resident and fetch its first weights now
     const int row = blockIdx.x, D = a.head_dim, Hq = a.n_q_heads;
     const int col0 = blockIdx.y * MS_COLS, h0 = col0 / D, nh = MS_COLS / D;
@@ -938,7 +944,7 @@ static int flash_launch_mma(vx_ctx *c, const VxAttnArgs &a, dim3 grid) {
     static_assert(SMEM >= (int)((NW * G * D + 2 * NW * G) * sizeof(float)), "merge buffers fit in the staging area");
     static VxPerDevice attr;
     if (attr.max_dynamic_smem(c, paged_flash_mma_kernel<D, G, NW>, SMEM) != cudaSuccess) { cudaGetLastError(); return -1; }
-    paged_flash_mma_kernel<D, G, NW><<<grid, NW * 32, SMEM, c->stream>>>(a);
+    if (vx_launch_chain(paged_flash_mma_kernel<D, G, NW>, grid, dim3(NW * 32), (size_t)SMEM, c->stream, a) != cudaSuccess) return VX_E_CUDA;
     return 0;
 }
 
@@ -954,10 +960,10 @@ static int flash_launch_g(vx_ctx *c, const VxAttnArgs &a, int G) {
         }
     }
     switch (G) {
-    case 1: paged_flash_kernel<D, 1><<<grid, ATT_WARPS * 32, 0, c->stream>>>(a); break;
-    case 2: paged_flash_kernel<D, 2><<<grid, ATT_WARPS * 32, 0, c->stream>>>(a); break;
-    case 4: paged_flash_kernel<D, 4><<<grid, ATT_WARPS * 32, 0, c->stream>>>(a); break;
-    case 8: paged_flash_kernel<D, 8><<<grid, ATT_WARPS * 32, 0, c->stream>>>(a); break;
+    case 1: if (vx_launch_chain(paged_flash_kernel<D, 1>, grid, dim3(ATT_WARPS * 32), 0, c->stream, a) != cudaSuccess) return VX_E_CUDA; break;
+    case 2: if (vx_launch_chain(paged_flash_kernel<D, 2>, grid, dim3(ATT_WARPS * 32), 0, c->stream, a) != cudaSuccess) return VX_E_CUDA; break;
+    case 4: if (vx_launch_chain(paged_flash_kernel<D, 4>, grid, dim3(ATT_WARPS * 32), 0, c->stream, a) != cudaSuccess) return VX_E_CUDA; break;
+    case 8: if (vx_launch_chain(paged_flash_kernel<D, 8>, grid, dim3(ATT_WARPS * 32), 0, c->stream, a) != cudaSuccess) return VX_E_CUDA; break;
     default: return -1;
     }
     return 0;
@@ -986,7 +992,7 @@ int vxp_attention_split(vx_ctx *c, const VxAttnArgs &a, const VxSplit *split, in
             if (split && fused && a.row_bound && n_max_chunks > 0 && cols % MS_COLS == 0 && split->k_pad == cols && MS_COLS % D == 0 &&
                 a.out_row_stride % 4 == 0 && 2 * (size_t)(MS_COLS / D) * n_max_chunks * sizeof(float) <= 40 * 1024) {
                 const size_t bytes = 2 * (size_t)(MS_COLS / D) * n_max_chunks * sizeof(float);
-                paged_merge_split_heads_kernel<<<dim3(a.rows, cols / MS_COLS), MS_THREADS, bytes, c->stream>>>(a, *split, n_max_chunks);
+                if (vx_launch_chain(paged_merge_split_heads_kernel, dim3(a.rows, cols / MS_COLS), dim3(MS_THREADS), bytes, c->stream, a, *split, n_max_chunks) != cudaSuccess) return vx_fail(c, VX_E_CUDA, "merge launch");
                 VX_LAUNCH_CHECK(c);
                 *fused = true;
                 return VX_OK;
@@ -994,7 +1000,7 @@ int vxp_attention_split(vx_ctx *c, const VxAttnArgs &a, const VxSplit *split, in
             if (split && fused && n_max_chunks > 0 && fw_bytes <= 40 * 1024 && split->k_pad <= 8 * VX_ROW_THREADS * 4 && a.out_row_stride % 4 == 0) {
                 const int nc = ceil_div(split->k_pad, VX_ROW_THREADS * 4);
                 switch (nc) {
-#define VX_MS_CASE(N) case N: paged_merge_split_kernel<N><<<a.rows, VX_ROW_THREADS, fw_bytes, c->stream>>>(a, *split, cols, n_max_chunks); break;
+#define VX_MS_CASE(N) case N: if (vx_launch_chain(paged_merge_split_kernel<N>, dim3(a.rows), dim3(VX_ROW_THREADS), fw_bytes, c->stream, a, *split, cols, n_max_chunks) != cudaSuccess) return vx_fail(c, VX_E_CUDA, "merge launch"); break;
                     VX_MS_CASE(1) VX_MS_CASE(2) VX_MS_CASE(3) VX_MS_CASE(4) VX_MS_CASE(5) VX_MS_CASE(6) VX_MS_CASE(7) VX_MS_CASE(8)
 #undef VX_MS_CASE
                 }

@@ -248,6 +248,7 @@ size_t vxq_split_bytes(int rows, int k, size_t *hi_off, size_t *lo_off, size_t *
 template <int NC>
 __global__ void __launch_bounds__(VX_ROW_THREADS) split_rows_kernel(const float *__restrict__ x, int cols, int ld, VxSplit s) {
     __shared__ float red[32];
+    vx_pdl_wait();
     vx_pdl_trigger();          // the projection that follows may become resident and fetch its first weights now
     const int row = blockIdx.x;
     const float *xr = x + (size_t)row * ld;
@@ -788,7 +789,7 @@ int vx_matmul_q4_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, i
 int vx_matmul_q6_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k) { return matmul_quant(c, VX_T_Q6_K, a, b, out, m, n, k); }
 
 int vx_set_tc_min_rows(int rows) { g_tc_min_rows = rows; return VX_OK; }
-int vx_set_dependent_launch(int enable) { g_vx_pdl = enable != 0; return VX_OK; }
+int vx_set_dependent_launch(int mode) { g_vx_pdl = mode < 0 ? 0 : mode > 2 ? 2 : mode; return VX_OK; }
 int vx_set_gemm_terms(int terms) { if (terms == 1 || terms == 2) { g_gemm_terms = terms; return VX_OK; } return VX_E_BAD_ARG; }
 
 }  // extern "C"
