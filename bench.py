@@ -382,6 +382,7 @@ def main():
     ap.add_argument("--chain-launch", action="store_true", help="experiment: every kernel of a layer launched as a programmatic dependent of the one before it, not only the projections")
     ap.add_argument("--no-graphs", action="store_true", help="experiment: launch every kernel individually instead of replaying CUDA graphs")
     ap.add_argument("--no-persistent", action="store_true", help="experiment: Q4_0 decode projections on the one-CTA-per-tile tcgen05 kernel instead of the persistent one")
+    ap.add_argument("--aligned-split", action="store_true", help="experiment: persistent projections with tile-aligned split-K only (no stream mode)")
     ap.add_argument("--no-thin", action="store_true", help="experiment: 1-4 row Q4_0 projections on the staged mma.sync kernel instead of the weight-streaming one")
     ap.add_argument("--tc-min-rows", type=int, default=-1, help="experiment: batch size from which projections use the tcgen05 kernel")
     args = ap.parse_args()
@@ -426,6 +427,8 @@ def main():
         be.lib.vx_set_graphs(0)
     if args.no_persistent:
         be.lib.vx_set_persistent_projections(0)
+    if args.aligned_split:
+        be.lib.vx_set_persistent_projections(1)
     if args.no_thin:
         be.lib.vx_set_thin_batch_projections(0)
     model = capi.Model(be, gs.model_config(spec, max_blocks, max_seqs=seq_cap, max_batch_tokens=max(seq_cap, 8), max_blocks_per_seq=blocks_per_seq))

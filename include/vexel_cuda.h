@@ -297,9 +297,10 @@ int vx_selftest_bounded_wait(vx_ctx *ctx, int limit_us, int *reached_end);
  * 0 = always the mma.sync kernel) */
 int vx_set_tc_min_rows(int rows);
 /* Q4_0 projections of 17..64 batch rows run on the persistent tcgen05 kernel (one CTA per SM walking weight tiles, its
- * pipeline kept full across tiles); 0 = one CTA per tile as for the other formats.  Default on.  No counterpart in the
- * reference. */
-int vx_set_persistent_projections(int enable);
+ * pipeline kept full across tiles).  mode 0 = one CTA per tile as for the other formats; 1 = persistent with split-K slices
+ * aligned to tiles; 2 (default) = persistent, and where it is cheaper the stages of all tiles are cut into one equal run per
+ * CTA (a tile's partial sums then come from the CTAs that share it).  No counterpart in the reference. */
+int vx_set_persistent_projections(int mode);
 /* Q4_0 projections of 1..4 batch rows run on the weight-streaming mma.sync kernel (the single-sequence decode of
  * runtime/block.go:947-1060: one quantised mat-vec per projection); 0 = the staged mma.sync kernel as for 5..16 rows.
  * Default on. */

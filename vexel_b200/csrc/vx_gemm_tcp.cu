@@ -49,19 +49,29 @@ static_assert(P_SMEM <= 232448, "shared memory budget");
 #ifndef P_KNOCK
 #define P_KNOCK 0      // timing experiments only (wrong results): 1 no weight expansion, 2 no operand stores, 4 no MMAs, 8 no activation loads, 16 no weight loads
 #endif
-// A CTA's units are blockIdx.x, blockIdx.x + gridDim.x, ...; unit u = (row tile u / split, slice u % split).  Every role walks
-// them with this iterator: one division when it is set up, additions from then on (a role is one thread's instruction stream,
-// and an integer division costs it as much as a pipeline stage has to spare).
-struct Unit { int r0, slice, g_begin, n_g; };
-struct UnitIter {
+// The units a CTA walks, in one of two modes.  Every role uses this iterator: divisions only when it is set up, additions
+// from then on (a role is one thread's instruction stream, and an integer division costs it as much as a pipeline stage has
+// to spare).
+//   aligned: unit u = (row tile u / split, slice u % split) with slices of `per` groups; a CTA takes units blockIdx.x,
+//            blockIdx.x + gridDim.x, ...
+//   stream:  the stages of all tiles form one sequence (tile 0's K range, then tile 1's, ...) cut into gridDim.x equal runs
+//            of whole quanta (a quantum = two 128-weight groups = four stages, the granularity of the scale tiles and of the
+//            dequantiser groups); a CTA's run covers the tail of one tile, whole tiles, and the head of another.  Every CTA
+//            then has the same number of stages (+- one quantum) whatever the tile count.  The CTAs that share a tile write
+//            their partial sums to consecutive slots, in K order; the one that finishes a tile zero-fills the slots the tile
+//            does not use, so that a consumer always sums `split` slots.
+struct Unit { int r0, slice, g_begin, n_g; bool last; };
+template <bool STREAM> struct UnitIter;
+template <> struct UnitIter<false> {
     int tile, slice, d_tile, d_slice, split, per, k_groups;
-    __device__ __forceinline__ UnitIter(int first, int stride, int split_, int per_, int k_groups_) : split(split_), per(per_), k_groups(k_groups_) {
+    __device__ __forceinline__ UnitIter(int first, int stride, int split_, int per_, int k_groups_, int) : split(split_), per(per_), k_groups(k_groups_) {
         tile = first / split_; slice = first - tile * split_;
         d_tile = stride / split_; d_slice = stride - d_tile * split_;
     }
+    __device__ __forceinline__ int count(int first, int stride, int n_units) const { return (n_units - first + stride - 1) / stride; }
     __device__ __forceinline__ Unit get() const {
         Unit U;
-        U.slice = slice; U.r0 = tile * TC_ROWS; U.g_begin = slice * per; U.n_g = min(per, k_groups - U.g_begin);
+        U.slice = slice; U.r0 = tile * TC_ROWS; U.g_begin = slice * per; U.n_g = min(per, k_groups - U.g_begin); U.last = false;
         return U;
     }
     __device__ __forceinline__ void next() {
@@ -69,14 +79,34 @@ struct UnitIter {
         if (slice >= split) { slice -= split; tile++; }
     }
 };
+template <> struct UnitIter<true> {
+    int tile, slice, q, q_end, qt;                              // this CTA's quanta [q, q_end), quanta per tile
+    __device__ __forceinline__ UnitIter(int first, int stride, int, int, int k_groups_, int stream_q) {
+        qt = k_groups_ >> 1;
+        q = (int)(((long long)first * stream_q) / stride); q_end = (int)(((long long)(first + 1) * stream_q) / stride);
+        tile = q / qt;
+        // slot of this CTA's first unit = how many CTAs before it touch the same tile: the first of them holds quantum tile * qt
+        const int first_cta = (int)((((long long)tile * qt + 1) * stride + stream_q - 1) / stream_q) - 1;
+        slice = first - first_cta;
+    }
+    __device__ __forceinline__ int count(int, int, int) const { return q_end > q ? (q_end - 1) / qt - q / qt + 1 : 0; }
+    __device__ __forceinline__ Unit get() const {
+        Unit U;
+        const int off = q - tile * qt, n = min(q_end - q, qt - off);
+        U.slice = slice; U.r0 = tile * TC_ROWS; U.g_begin = 2 * off; U.n_g = 2 * n; U.last = off + n == qt;
+        return U;
+    }
+    __device__ __forceinline__ void next() { q = min(q_end, (tile + 1) * qt); tile++; slice = 0; }   // the next tile starts at its first quantum: this CTA is its first writer
+};
 
 #define VX_P_LD16(v, taddr) VX_TMEM_LD16(v, taddr)
 
 // grid: one CTA per SM (or per unit when there are fewer); out layout [split][M][ld_out]; per and k_groups are even
+template <bool STREAM>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_x,
                 const float *__restrict__ xscale, float *__restrict__ out, int M, int N, int k_groups,
-                int per, int split, int n_units, int ld_out, size_t part_stride, int *__restrict__ err_flag) {
+                int per, int split, int n_units, int stream_q, int ld_out, size_t part_stride, int *__restrict__ err_flag) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
@@ -101,7 +131,7 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 
     const int tid = threadIdx.x, lane = tid & 31;
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);      // a broadcast value: the role branches below are warp-uniform
-    const int n_my = (n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;      // this CTA's units: blockIdx.x + i * gridDim.x
+    const int n_my = UnitIter<STREAM>((int)blockIdx.x, (int)gridDim.x, split, per, k_groups, stream_q).count((int)blockIdx.x, (int)gridDim.x, n_units);   // this CTA's units
 
     if (tid == 0) {
         s_abort = 0;
@@ -141,7 +171,7 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         const uint32_t a_st = tmem + ((uint32_t)((warp & 3) * 32) << 16) + P_TMEM_A + 64 * fg;
         int it = 0, g_count = 0, t_count = 0;        // this group's iterations; nibble tiles and scale tiles before the current unit
         bool ok = true;
-        UnitIter uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups);
+        UnitIter<STREAM> uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups, stream_q);
         for (int ui = 0; ui < n_my && ok; ui++, uit.next()) {
             const Unit U = uit.get();
             const int n_kb = 2 * U.n_g;
@@ -195,7 +225,7 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // and was what every other role waited for.)
         if (lane == 0) {
             vx_pdl_wait();                                   // the activations are the output of the kernel ahead of this one in the stream
-            UnitIter uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups);
+            UnitIter<STREAM> uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups, stream_q);
             int xc = 0;
             bool ok = true;
             for (int ui = 0; ui < n_my && ok; ui++, uit.next()) {
@@ -216,7 +246,7 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // group) and scale tiles (one per two groups), in the order the dequantisers need them.  Weights do not depend on the
         // kernel ahead of this one, so this role never waits for it: the rings fill while that kernel finishes.
         if (lane == 0) {
-            UnitIter uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups);
+            UnitIter<STREAM> uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups, stream_q);
             int rc = 0, scn = 0;
             bool ok = true;
             for (int ui = 0; ui < n_my && ok; ui++, uit.next()) {
@@ -253,7 +283,7 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         bool ok = true;
         const bool leader = elect_one();
         const uint32_t acc = tmem + P_TMEM_ACC * j;
-        UnitIter uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups);
+        UnitIter<STREAM> uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups, stream_q);
         for (int ui = 0; ui < n_my && ok; ui++, uit.next()) {
             const Unit U = uit.get();
             const int n_kb = 2 * U.n_g;
@@ -301,7 +331,7 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         for (int i = tid - P_EPI_WARP0 * 32; i < P_MT; i += 128) s_xscale[i] = i < M ? xscale[i] : 0.f;
         asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps only
         bool ok = true;
-        UnitIter uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups);
+        UnitIter<STREAM> uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups, stream_q);
         for (int ui = 0; ui < n_my && ok; ui++, uit.next()) {
             const Unit U = uit.get();
             ok = mbar_wait(accfull, (uint32_t)ui & 1u, abort_flag);
@@ -337,6 +367,12 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
                     for (int m = 0; m < P_MT; m++) { if (m < M) *o = v[m]; o += ld_out; }
                 }
+                if (STREAM && U.last) {                       // stream mode: the tile is complete; the slots it does not use count as zero
+                    for (int sl = U.slice + 1; sl < split; sl++) {
+                        float *z = out + (size_t)sl * part_stride + n;
+                        for (int m = 0; m < M; m++) { *z = 0.f; z += ld_out; }
+                    }
+                }
             }
         }
     }
@@ -350,8 +386,9 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 
 }  // namespace
 
-static int g_tcp = 1;
-extern "C" int vx_set_persistent_projections(int enable) { g_tcp = enable != 0; return VX_OK; }
+static int g_tcp = 1, g_tcp_stream = 1;
+// 0 = the one-CTA-per-tile kernel; 1 = persistent, aligned split-K only; 2 (default) = persistent, stream mode where it is cheaper
+extern "C" int vx_set_persistent_projections(int mode) { g_tcp = mode != 0; g_tcp_stream = mode != 1; return VX_OK; }
 
 // Eligible: Q4_0, at most 64 batch rows, an even number of 128-weight groups per row (the scale tiles cover two groups).
 bool vxq_gemm_tcp_eligible(const VxWeight &w, int m) {
@@ -365,7 +402,9 @@ int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *o
     if (x.k_pad != w.k_pad) return vx_fail(c, VX_E_BAD_ARG, "projection: activation row stride %d != weight k_pad %d", x.k_pad, w.k_pad);
     {
         static VxPerDevice attr;
-        VX_CUDA(c, attr.max_dynamic_smem(c, gemm_tcp_kernel, P_SMEM));
+        VX_CUDA(c, attr.max_dynamic_smem(c, gemm_tcp_kernel<false>, P_SMEM));
+        static VxPerDevice attr_s;
+        VX_CUDA(c, attr_s.max_dynamic_smem(c, gemm_tcp_kernel<true>, P_SMEM));
     }
     const int k_groups = w.k_pad / 128;
     const int tiles = ceil_div(w.n, TC_ROWS);
@@ -387,10 +426,36 @@ int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *o
             if (cost < best * 0.98) { best = cost; split = s_eff; per = p; }
         }
     }
+    int n_units = tiles * split, stream_q = 0;
+    if (parts && g_tcp_stream) {
+        // Stream mode: all tiles' stages as one sequence cut into equal runs (see UnitIter).  Same cost terms, evaluated on the
+        // busiest CTA; the slots are as many as the CTAs that can share one tile.
+        constexpr double UNIT_STAGES = 2.5, PART_STAGES_PER_FLOAT = 2.2e-6;
+        const int qt = k_groups / 2;
+        const long Q = (long)tiles * qt;
+        const long G = std::min<long>(Q, slots);
+        int n_slots = 1;
+        double worst = 0.0;
+        auto cta_of = [&](long x) { return (int)(((x + 1) * G + Q - 1) / Q - 1); };
+        for (int t = 0; t < tiles; t++) n_slots = std::max(n_slots, cta_of((long)(t + 1) * qt - 1) - cta_of((long)t * qt) + 1);
+        for (long i = 0; i < G; i++) {
+            const long q0 = i * Q / G, q1 = (i + 1) * Q / G;
+            const long units = (q1 - 1) / qt - q0 / qt + 1;
+            worst = std::max(worst, 4.0 * (double)(q1 - q0) + UNIT_STAGES * (double)units);
+        }
+        const double cost = worst + (n_slots > 1 ? PART_STAGES_PER_FLOAT * n_slots * (double)m * w.n : 0.0);
+        // the aligned split's cost, in the same terms
+        const long units_a = (long)tiles * split;
+        const double cost_a = (double)ceil_div64(units_a, std::min<long>(units_a, slots)) * (2.0 * per + UNIT_STAGES) +
+                              (split > 1 ? PART_STAGES_PER_FLOAT * split * (double)m * w.n : 0.0);
+        // (an aligned launch without partial sums also spares its consumer a pass over them: it needs a clearer margin to lose)
+        if (n_slots > 1 && (size_t)n_slots * m * w.n <= parts_cap_floats && cost < cost_a * (split > 1 ? 0.98 : 0.90)) {
+            stream_q = (int)Q; split = n_slots; per = qt; n_units = (int)G;
+        }
+    }
     float *dst = split > 1 ? parts : out;
     const int ld = split > 1 ? w.n : ld_out;
     *n_parts_out = split;
-    const int n_units = tiles * split;
     // tensor maps, kept per (weight, activation buffer) combination: a decode step launches the same ones every time
     struct MapKey {
         const void *qs, *sc, *xh, *xl; int n, kg, kp;
@@ -421,9 +486,12 @@ int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *o
         if (cache.size() > 4096) cache.clear();     // buffers of destroyed models: start over rather than grow without bound
         cache[key] = ms;
     }
-    const dim3 grid(std::min(n_units, slots));
-    cudaError_t le = vx_launch_dependent(gemm_tcp_kernel, grid, dim3(P_THREADS), (size_t)P_SMEM, c->stream, ms.w, ms.s, ms.x,
-                                         (const float *)x.scale, dst, m, w.n, k_groups, per, split, n_units, ld, (size_t)m * w.n, err_flag);
+    const dim3 grid(std::min(n_units, slots));        // (stream mode: n_units is the number of runs = CTAs)
+    cudaError_t le = stream_q > 0
+        ? vx_launch_dependent(gemm_tcp_kernel<true>, grid, dim3(P_THREADS), (size_t)P_SMEM, c->stream, ms.w, ms.s, ms.x,
+                              (const float *)x.scale, dst, m, w.n, k_groups, per, split, n_units, stream_q, ld, (size_t)m * w.n, err_flag)
+        : vx_launch_dependent(gemm_tcp_kernel<false>, grid, dim3(P_THREADS), (size_t)P_SMEM, c->stream, ms.w, ms.s, ms.x,
+                              (const float *)x.scale, dst, m, w.n, k_groups, per, split, n_units, stream_q, ld, (size_t)m * w.n, err_flag);
     if (le != cudaSuccess) return vx_cuda_fail(c, le, "projection launch");
     VX_LAUNCH_CHECK(c);
     return VX_OK;
