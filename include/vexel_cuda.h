@@ -88,6 +88,11 @@ int vx_sdpa_prefill(vx_ctx *, vx_dptr q, vx_dptr k, vx_dptr v, vx_dptr out, int 
 int vx_matmul_q4_0(vx_ctx *, vx_dptr a, vx_dptr b_raw, vx_dptr out, int m, int n, int k); /* QuantizedMatMul.MatMulQ4_0 backend.go:50 */
 int vx_matmul_q4_k(vx_ctx *, vx_dptr a, vx_dptr b_raw, vx_dptr out, int m, int n, int k); /* MatMulQ4_K :55 */
 int vx_matmul_q6_k(vx_ctx *, vx_dptr a, vx_dptr b_raw, vx_dptr out, int m, int n, int k); /* MatMulQ6_K :60 */
+/* The three calls above repack the GGUF blocks into the kernels' layout.  For weights that live in a vx_alloc_permanent
+ * buffer (as runtime/loader.go:507-708 uploads them) the repacked copy is kept and reused by later calls on the same
+ * tensor; vx_h2d / vx_d2d / vx_memset into the raw bytes and vx_free drop it.  A kernel of this library must not be pointed
+ * at such a tensor as its OUTPUT once it has served as a weight (the reference never does).  0 switches the cache off. */
+int vx_set_repack_cache(vx_ctx *ctx, int enable);
 int vx_argmax(vx_ctx *, vx_dptr x, int n, int *out_index);                /* ArgmaxOps.Argmax :202 (synchronous, first max wins) */
 int vx_argmax_rows(vx_ctx *, vx_dptr x, int rows, int cols, vx_dptr out_i32); /* batched form, asynchronous */
 int vx_gelu(vx_ctx *, vx_dptr x, vx_dptr out, int n);                     /* GELUOps.GELU :220 */

@@ -165,6 +165,53 @@ def test_matmul_q4_0(be, m, n, k):
     be.ResetPool()
 
 
+def test_matmul_quant_reuses_and_drops_repacked_weights(be):
+    """Weights in a permanent buffer are repacked once; overwriting them through the API must be seen by the next call."""
+    rng = np.random.default_rng(77)
+    m, n, k = 3, 512, 1024
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    raw1 = gs.quantize_q4_0(rng.standard_normal((n, k)).astype(np.float32) * 0.02)
+    raw2 = gs.quantize_q4_0(rng.standard_normal((n, k)).astype(np.float32) * 0.02)
+    dw = be.AllocPermanent(raw1.nbytes)
+    be.ToDevice(dw, raw1)
+    da, do = be.upload(a), be.Alloc(m * n * 4)
+    want1, want2 = O.matmul_q4_0(a, raw1, m, n, k), O.matmul_q4_0(a, raw2, m, n, k)
+    for _ in range(3):                                  # the second and third call run on the kept copy
+        be.MatMulQ4_0(da, dw, do, m, n, k)
+        assert rel_l2(be.download(do, (m, n)), want1) < 1e-5
+    be.ToDevice(dw, raw2)                               # new bytes at the same address
+    be.MatMulQ4_0(da, dw, do, m, n, k)
+    assert rel_l2(be.download(do, (m, n)), want2) < 1e-5
+    be.lib.vx_set_repack_cache(be.h, 0)                 # and with the cache off
+    be.MatMulQ4_0(da, dw, do, m, n, k)
+    assert rel_l2(be.download(do, (m, n)), want2) < 1e-5
+    be.lib.vx_set_repack_cache(be.h, 1)
+    be.Free(dw)
+    be.ResetPool()
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 12288, 4096), (40, 22016, 4096), (17, 12300, 4096), (64, 4096, 11008)])
+def test_matmul_q4_0_split_modes(be, m, n, k):
+    """The persistent projection kernel with tile-aligned split-K slices (mode 1) and with the stages of all tiles cut into
+    one run per CTA (mode 2, the default where the cost model prefers it): both against the oracle, at the benchmark's
+    matrix shapes and with a row count that is not a multiple of the 128-row tile."""
+    rng = np.random.default_rng(m + n)
+    w = rng.standard_normal((n, k)).astype(np.float32) * 0.02
+    raw = gs.quantize_q4_0(w)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    want = O.matmul_q4_0(a, raw, m, n, k)
+    da, dw, do = be.upload(a), be.upload(raw), be.Alloc(m * n * 4)
+    try:
+        for mode in (1, 2):
+            be.lib.vx_set_persistent_projections(mode)
+            be.MatMulQ4_0(da, dw, do, m, n, k)
+            got = be.download(do, (m, n))
+            assert rel_l2(got, want) < 1e-5, (mode, rel_l2(got, want))
+    finally:
+        be.lib.vx_set_persistent_projections(2)
+    be.ResetPool()
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 256, 256), (3, 200, 1024), (8, 1000, 4096), (20, 130, 512), (70, 384, 2048)])
 @pytest.mark.parametrize("type_id,quant,fn", [(capi.T_Q4_K, gs.quantize_q4_k, "MatMulQ4_K"), (capi.T_Q6_K, gs.quantize_q6_k, "MatMulQ6_K")])
 def test_matmul_kquants(be, type_id, quant, fn, m, n, k):

@@ -110,7 +110,7 @@ SIGNATURES = {
     "vx_synth_q4_0": [_vp, _D, _i64, _u64, _f],
     "vx_synth_kquant": [_vp, _D, _i, _i64, _u64, _f],
     "vx_pool_shuffle_free_list": [_vp, C.c_uint32], "vx_model_weight_bytes": [_vp, C.POINTER(_u64)],
-    "vx_set_persistent_projections": [_i], "vx_set_thin_batch_projections": [_i], "vx_debug_skip": [_i],
+    "vx_set_persistent_projections": [_i], "vx_set_thin_batch_projections": [_i], "vx_debug_skip": [_i], "vx_set_repack_cache": [_vp, _i],
     "vx_tp_unique_id": [_vp, _i], "vx_tp_init": [_vp, _vp, _i, _i], "vx_tp_shutdown": [_vp], "vx_model_enable_tp": [_vp, _i],
     "vx_set_gemm_terms": [_i], "vx_set_tc_min_rows": [_i], "vx_set_dependent_launch": [_i], "vx_model_max_blocks": [_vp],
     "vx_sched_create": [_vp, C.POINTER(SchedConfig), C.POINTER(_vp)], "vx_sched_destroy": [_vp],

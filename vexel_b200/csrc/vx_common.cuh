@@ -31,7 +31,15 @@ struct vx_ctx {
     int sm_count = 148;
     uint64_t launches = 0;
     void *tp = nullptr;               // tensor-parallel communicator of this context (vx_tp.cu), null for single-GPU use
+    // Repacked copies of quantised weights that the interface-level MatMulQ* calls were given, keyed by the raw tensor's
+    // address.  Only tensors inside a permanent allocation are kept (the reference uploads weights once into
+    // AllocPermanent buffers, runtime/loader.go:507-708); an entry is dropped when the API writes into its raw bytes
+    // (ToDevice, CopyBuffer, memset) or frees them.
+    struct Repacked { int type, n, k; size_t raw_bytes; void *buf; };
+    std::unordered_map<const void *, Repacked> repacked;
+    bool repack_cache = true;
 };
+void vx_repack_invalidate(vx_ctx *c, const void *dst, size_t bytes);   // drops cached repacks whose raw bytes overlap [dst, dst + bytes)
 
 struct VxGuard {
     vx_ctx *c;

@@ -769,13 +769,40 @@ static int matmul_quant(vx_ctx *c, int type, vx_dptr a, vx_dptr b_raw, vx_dptr o
     size_t hi, lo, so, bo; int kp;
     size_t sbytes = vxq_split_bytes(m, k, &hi, &lo, &so, &bo, &kp);
     size_t parts_floats = (size_t)8 * m * n;
+    // The repacked weights: kept across calls for tensors that live in a permanent allocation (the reference hands the same
+    // weight buffers to MatMulQ* on every token; repacking them each time would double the traffic of a mat-vec), rebuilt
+    // in the scratch buffer otherwise.  An entry goes when the API overwrites or frees the raw bytes (vx_repack_invalidate).
+    const void *raw = dp<void>(b_raw);
+    const double bpw = type == VX_T_Q4_0 ? 18.0 / 32 : type == VX_T_Q4_K ? 144.0 / 256 : 210.0 / 256;
+    const size_t raw_bytes = (size_t)((double)n * k * bpw);
+    char *wbuf = nullptr;
+    if (c->repack_cache) {
+        auto it = c->repacked.find(raw);
+        if (it != c->repacked.end() && (it->second.type != type || it->second.n != n || it->second.k != k)) {
+            vx_repack_invalidate(c, raw, 1);
+            it = c->repacked.end();
+        }
+        if (it != c->repacked.end()) wbuf = (char *)it->second.buf;
+        else {
+            bool permanent = false;
+            for (const auto &pa : c->permanent)
+                if ((const char *)raw >= (const char *)pa.first && (const char *)raw + raw_bytes <= (const char *)pa.first + pa.second) { permanent = true; break; }
+            void *nb = nullptr;
+            if (permanent && cudaMalloc(&nb, L.total) == cudaSuccess) {
+                int rc = vxq_repack_rows(c, type, raw, n, k, nb, L, 0);
+                if (rc != VX_OK) { cudaFree(nb); return rc; }
+                c->repacked[raw] = vx_ctx::Repacked{type, n, k, raw_bytes, nb};
+                wbuf = (char *)nb;
+            } else cudaGetLastError();
+        }
+    }
     void *base;
-    VX_TRY(vx_scratch(c, L.total + sbytes + parts_floats * 4 + 1024, &base));
+    VX_TRY(vx_scratch(c, (wbuf ? 0 : L.total) + sbytes + parts_floats * 4 + 1024, &base));
     char *p = (char *)base;
-    VX_TRY(vxq_repack_rows(c, type, dp<void>(b_raw), n, k, p, L, 0));
+    if (!wbuf) VX_TRY(vxq_repack_rows(c, type, raw, n, k, p, L, 0));
     VxWeight w;
-    vxq_weight_view(type, n, k, p, L, &w);
-    char *sp = p + L.total;
+    vxq_weight_view(type, n, k, wbuf ? wbuf : p, L, &w);
+    char *sp = p + (wbuf ? 0 : L.total);
     VxSplit s{(__half *)(sp + hi), (__half *)(sp + lo), (float *)(sp + so), (float *)(sp + bo), kp};
     VX_TRY(vxq_split_rows(c, dp<float>(a), m, k, k, s));
     float *parts = (float *)(sp + sbytes);
@@ -789,6 +816,13 @@ int vx_matmul_q4_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, i
 int vx_matmul_q6_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k) { return matmul_quant(c, VX_T_Q6_K, a, b, out, m, n, k); }
 
 int vx_set_tc_min_rows(int rows) { g_tc_min_rows = rows; return VX_OK; }
+int vx_set_repack_cache(vx_ctx *c, int enable) {
+    if (!c) return VX_E_BAD_ARG;
+    VxGuard g(c);
+    c->repack_cache = enable != 0;
+    if (!enable) vx_repack_invalidate(c, nullptr, ~(size_t)0 >> 1);
+    return VX_OK;
+}
 int vx_set_dependent_launch(int mode) { g_vx_pdl = mode < 0 ? 0 : mode > 2 ? 2 : mode; return VX_OK; }
 int vx_set_gemm_terms(int terms) { if (terms == 1 || terms == 2) { g_gemm_terms = terms; return VX_OK; } return VX_E_BAD_ARG; }
 

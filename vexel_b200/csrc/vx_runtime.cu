@@ -42,6 +42,19 @@ int vx_check_device_error(vx_ctx *c) {
     return VX_OK;
 }
 
+void vx_repack_invalidate(vx_ctx *c, const void *dst, size_t bytes) {
+    if (c->repacked.empty()) return;
+    const char *lo = (const char *)dst, *hi = lo + bytes;
+    for (auto it = c->repacked.begin(); it != c->repacked.end();) {
+        const char *r0 = (const char *)it->first, *r1 = r0 + it->second.raw_bytes;
+        if (r0 < hi && lo < r1) {
+            cudaStreamSynchronize(c->stream);
+            cudaFree(it->second.buf);
+            it = c->repacked.erase(it);
+        } else ++it;
+    }
+}
+
 extern "C" {
 
 int vx_init(int device, vx_ctx **out) {
@@ -69,6 +82,7 @@ int vx_destroy(vx_ctx *c) {
     {
         VxGuard g(c);
         cudaStreamSynchronize(c->stream);
+        for (auto &r : c->repacked) cudaFree(r.second.buf);
         for (auto &b : c->pooled) cudaFree(b.p);
         for (auto &kv : c->permanent) cudaFree(kv.first);
         if (c->scratch) cudaFree(c->scratch);
@@ -125,6 +139,7 @@ int vx_free(vx_ctx *c, vx_dptr p) {
     auto it = c->permanent.find(vp);
     if (it != c->permanent.end()) {
         VX_CUDA(c, cudaStreamSynchronize(c->stream));
+        vx_repack_invalidate(c, vp, it->second);
         cudaFree(vp);
         c->permanent.erase(it);
         return VX_OK;
@@ -145,6 +160,7 @@ int vx_h2d(vx_ctx *c, vx_dptr dst, const void *src, size_t bytes) {
     if (!c) return VX_E_BAD_ARG;
     VxGuard g(c);
     if (bytes == 0 || dst == 0 || !src) return VX_OK;   // ToDevice ignores nil/empty (backend/cpu/cpu.go:57-63)
+    vx_repack_invalidate(c, dp<void>(dst), bytes);
     VX_CUDA(c, cudaMemcpyAsync(dp<void>(dst), src, bytes, cudaMemcpyHostToDevice, c->stream));
     VX_CUDA(c, cudaStreamSynchronize(c->stream));   // the Go slice may be reused as soon as the call returns
     return VX_OK;
@@ -164,6 +180,7 @@ int vx_d2d(vx_ctx *c, vx_dptr dst, vx_dptr src, size_t bytes) {
     VxGuard g(c);
     if (bytes == 0) return VX_OK;
     VX_REQUIRE(c, dst != 0 && src != 0, "nil device pointer");
+    vx_repack_invalidate(c, dp<void>(dst), bytes);
     VX_CUDA(c, cudaMemcpyAsync(dp<void>(dst), dp<void>(src), bytes, cudaMemcpyDeviceToDevice, c->stream));
     return VX_OK;
 }
@@ -173,6 +190,7 @@ int vx_memset(vx_ctx *c, vx_dptr dst, int byte, size_t bytes) {
     VxGuard g(c);
     if (bytes == 0) return VX_OK;
     VX_REQUIRE(c, dst != 0, "nil device pointer");
+    vx_repack_invalidate(c, dp<void>(dst), bytes);
     VX_CUDA(c, cudaMemsetAsync(dp<void>(dst), byte, bytes, c->stream));
     return VX_OK;
 }
