@@ -791,8 +791,11 @@ int plan_chunks(vx_model *m, const std::vector<int> &kv_start, const std::vector
     for (size_t i = 0; i < kv_len.size(); i++) pages += (kv_len[i] - 1) / BS - kv_start[i] / BS + 1;
     long target = 6L * m->c->sm_count;
     // grouped-query shapes have few KV heads, hence few CTAs per chunk: longer chunks amortise a CTA's start-up
-    // (block-table and query loads) and merge over more pages
-    const long max_chunk = m->cfg.n_heads > m->cfg.n_kv_heads ? 64 : 16;
+    // (block-table and query loads) and merge over more pages.  Multi-head shapes: 32 pages measured best at 64 sequences
+    // (step 9.87 ms against 9.98 at 16 and at 48, 9.99 at 64, 10.30 at 8: fewer partial sums to write and merge against a
+    // longer tail of the last wave)
+    long max_chunk = m->cfg.n_heads > m->cfg.n_kv_heads ? 64 : 32;
+    if (g_dbg_skip >> 8) max_chunk = g_dbg_skip >> 8;       // timing experiments: another cap
     int chunk = (int)std::min<long>(max_chunk, std::max<long>(4, (pages * m->cfg.n_kv_heads + target - 1) / target));
     for (;;) {
         long n = 0;
