@@ -388,7 +388,7 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 
 static int g_tcp = 1, g_tcp_stream = 1;
 // 0 = the one-CTA-per-tile kernel; 1 = persistent, aligned split-K only; 2 (default) = persistent, stream mode where it is cheaper
-extern "C" int vx_set_persistent_projections(int mode) { g_tcp = mode != 0; g_tcp_stream = mode != 1; return VX_OK; }
+extern "C" int vx_set_persistent_projections(int mode) { g_tcp = mode != 0; g_tcp_stream = mode == 1 ? 0 : mode == 3 ? 2 : 1; return VX_OK; }   // (3: stream mode wherever it applies, for timing comparisons)
 
 // Eligible: Q4_0, at most 64 batch rows, an even number of 128-weight groups per row (the scale tiles cover two groups).
 bool vxq_gemm_tcp_eligible(const VxWeight &w, int m) {
@@ -449,7 +449,7 @@ int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *o
         const double cost_a = (double)ceil_div64(units_a, std::min<long>(units_a, slots)) * (2.0 * per + UNIT_STAGES) +
                               (split > 1 ? PART_STAGES_PER_FLOAT * split * (double)m * w.n : 0.0);
         // (an aligned launch without partial sums also spares its consumer a pass over them: it needs a clearer margin to lose)
-        if (n_slots > 1 && (size_t)n_slots * m * w.n <= parts_cap_floats && cost < cost_a * (split > 1 ? 0.98 : 0.90)) {
+        if (n_slots > 1 && (size_t)n_slots * m * w.n <= parts_cap_floats && (g_tcp_stream == 2 ? split > 1 : cost < cost_a * (split > 1 ? 0.98 : 0.90))) {
             stream_q = (int)Q; split = n_slots; per = qt; n_units = (int)G;
         }
     }
