@@ -38,13 +38,16 @@ constexpr int P_X_TILE = P_MT * 128;          // one fp16 activation tile: 64 ro
 constexpr int P_STAGE_BYTES = 2 * P_X_TILE;   // x_hi rows, then x_lo rows
 constexpr int P_RAW_BYTES = TC_ROWS * 64;
 constexpr int P_SC_BYTES = TC_ROWS * 16;      // 128 rows x 8 scales
+constexpr int P_RAWH_BYTES = TC_ROWS * 32;    // Q6_K only: the top two bits of a 128-weight group
+enum { P_Q4_0 = 0, P_Q6_K = 2 };
 constexpr int P_DEQ_WARPS = 16, P_EPI_WARP0 = 16, P_ISSUE_WARP = 20, P_ISSUERS = 2, P_XPROD_WARP = 22, P_WPROD_WARP = 23;
 constexpr int P_THREADS = 24 * 32;
 constexpr int P_TMEM_ACC = 128;               // columns per accumulator (one per issuing warp): 0-63 = A_hi x_hi + A_lo x_hi, 64-127 = A_hi x_lo
 constexpr int P_TMEM_A = P_ISSUERS * P_TMEM_ACC;      // weight stages start here, 64 columns each
 constexpr int P_SMEM = P_XST * P_STAGE_BYTES + P_RAW * P_RAW_BYTES + P_SC * P_SC_BYTES + 1024 /*alignment*/ + 512 /*barriers*/ + 256 /*row scales*/;
+constexpr int P_SMEM_Q6 = P_SMEM + P_RAW * P_RAWH_BYTES + 256;     // the high-bit tiles follow everything else
 static_assert(P_TMEM_A + 64 * P_AST == 512, "tensor memory budget");
-static_assert(P_SMEM <= 232448, "shared memory budget");
+static_assert(P_SMEM_Q6 <= 232448, "shared memory budget");
 
 #ifndef P_KNOCK
 #define P_KNOCK 0      // timing experiments only (wrong results): 1 no weight expansion, 2 no operand stores, 4 no MMAs, 8 no activation loads, 16 no weight loads
@@ -102,9 +105,10 @@ template <> struct UnitIter<true> {
 #define VX_P_LD16(v, taddr) VX_TMEM_LD16(v, taddr)
 
 // grid: one CTA per SM (or per unit when there are fewer); out layout [split][M][ld_out]; per and k_groups are even
-template <bool STREAM>
+template <bool STREAM, int FMT>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_x,
+                const __grid_constant__ CUtensorMap map_h, const __half *__restrict__ sup,
                 const float *__restrict__ xscale, float *__restrict__ out, int M, int N, int k_groups,
                 int per, int split, int n_units, int stream_q, int ld_out, size_t part_stride, int *__restrict__ err_flag) {
     extern __shared__ unsigned char smem_raw[];
@@ -118,6 +122,8 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     const unsigned char *raw_gen = gen_base + P_XST * P_STAGE_BYTES;
     const unsigned char *sc_gen = raw_gen + P_RAW * P_RAW_BYTES;
     float *s_xscale = reinterpret_cast<float *>(gen_base + P_XST * P_STAGE_BYTES + P_RAW * P_RAW_BYTES + P_SC * P_SC_BYTES + 512);
+    const uint32_t rawh_base = bar_base + 1024;                              // (Q6_K) 16-byte aligned: every region before it is a multiple of 256 bytes
+    const unsigned char *rawh_gen = gen_base + (rawh_base - base);
     auto xfull = [&](int s) { return bar_base + 8u * s; };                                  // activation stage landed
     auto done = [&](int s) { return bar_base + 8u * (P_XST + s); };                         // the MMAs of the stage in activation slot s have finished: the
                                                                                             // slot and the stage's weight operand in tensor memory are free
@@ -170,47 +176,101 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         const int sc_off = row * 16 + (((fg >> 1) & 1) * 4 + (fg & 1) * 2) * 2;
         const uint32_t a_st = tmem + ((uint32_t)((warp & 3) * 32) << 16) + P_TMEM_A + 64 * fg;
         int it = 0, g_count = 0, t_count = 0;        // this group's iterations; nibble tiles and scale tiles before the current unit
+        __half dsup_h = __float2half(0.f);          // (Q6_K) super-block scale of this thread's next stage
+        const __half *sup_row = nullptr;
         bool ok = true;
         UnitIter<STREAM> uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups, stream_q);
         for (int ui = 0; ui < n_my && ok; ui++, uit.next()) {
             const Unit U = uit.get();
             const int n_kb = 2 * U.n_g;
+            if constexpr (FMT == P_Q6_K) {
+                sup_row = sup + (size_t)min(U.r0 + row, N - 1) * (k_groups >> 1);
+                if (fg < n_kb) dsup_h = __ldg(sup_row + ((U.g_begin + (fg >> 1)) >> 1));
+            }
             for (int kb = fg; kb < n_kb; kb += P_AST, it++) {
                 const int gi = g_count + (kb >> 1), ti = t_count + (kb >> 2);
                 const int slot = gi % P_RAW, ss = ti % P_SC;
                 if (!mbar_wait(scfull(ss), (uint32_t)(ti / P_SC) & 1u, abort_flag)) { ok = false; break; }
-                const __half2 d2 = *reinterpret_cast<const __half2 *>(sc_gen + ss * P_SC_BYTES + sc_off);
-                if (!mbar_wait(rawfull(slot), (uint32_t)(gi / P_RAW) & 1u, abort_flag)) { ok = false; break; }
-                const unsigned char *rp = raw_gen + slot * P_RAW_BYTES;
-                uint2 w[4];
+                if constexpr (FMT == P_Q6_K) {
+                    // Q6_K (inference/pkg/gguf/dequant.go:272-331): the stage is 64-weight half `fg & 1` of the 128-weight group; word
+                    // 2 (fg & 1) + b of every chunk holds the 16-weight sub-blocks 4 (fg & 1) + 2 b (low nibbles) and + 1 (high
+                    // nibbles), the top two bits come from the second tile; fl(d * sc) travels as an fp16 pair so that
+                    // A_hi + A_lo = d1 (q - 32) to 2^-22.
+                    const uint32_t sw = *reinterpret_cast<const uint32_t *>(sc_gen + ss * P_SC_BYTES + row * 16 + ((fg >> 1) & 1) * 8 + (fg & 1) * 4);
+                    const float dsup = __half2float(dsup_h);
+                    {   // the super-block scale of this group's next stage (two 128-weight groups further on: one scale per 256 weights)
+                        const int kbn = kb + P_AST < n_kb ? kb + P_AST : kb;
+                        dsup_h = __ldg(sup_row + ((U.g_begin + (kbn >> 1)) >> 1));
+                    }
+                    if (!mbar_wait(rawfull(slot), (uint32_t)(gi / P_RAW) & 1u, abort_flag)) { ok = false; break; }
+                    const unsigned char *rp = raw_gen + slot * P_RAW_BYTES, *hp = rawh_gen + slot * P_RAWH_BYTES + row * 32 + 4 * (fg & 1);
+                    uint2 w[4]; uint32_t hw[4];
 #pragma unroll
-                for (int c = 0; c < 4; c++) w[c] = *reinterpret_cast<const uint2 *>(rp + raw_off[c]);
-                __syncwarp();
-                if (lane == 0) { mbar_arrive(scempty(ss)); mbar_arrive(rawempty(slot)); }
-                uint32_t hi[16], lo[16];
-                // bytes e and e + 2 of word c: weights 16 nib + 4 c + {e, e + 2} of the block (the activation tiles carry the same
-                // order of k within every four), exact product d * (q - 8) as an fp16 pair
+                    for (int c = 0; c < 4; c++) { w[c] = *reinterpret_cast<const uint2 *>(rp + raw_off[c]); hw[c] = *reinterpret_cast<const uint32_t *>(hp + 8 * c); }
+                    __syncwarp();
+                    if (lane == 0) { mbar_arrive(scempty(ss)); mbar_arrive(rawempty(slot)); }
+                    uint32_t hi[16], lo[16];
+#pragma unroll
+                    for (int b = 0; b < 2; b++) {
+                        __half2 dh[2], dl[2];
+                        split_scale(__fmul_rn(dsup, (float)(int)(signed char)((sw >> (16 * b)) & 0xFF)), &dh[0], &dl[0]);        // dequant.go:296-299
+                        split_scale(__fmul_rn(dsup, (float)(int)(signed char)((sw >> (16 * b + 8)) & 0xFF)), &dh[1], &dl[1]);
+#pragma unroll
+                        for (int t = 0; t < 2; t++)
+#pragma unroll
+                            for (int c = 0; c < 4; c++)
+#pragma unroll
+                                for (int e = 0; e < 2; e++) {
+                                    const uint32_t word = b ? w[c].y : w[c].x;
+                                    const uint32_t v = (t ? word >> 4 : word) >> (8 * e);
+                                    const uint32_t h8 = (hw[c] >> (16 * b + 8 * t)) & 0xFF;
+                                    const __half2 q = q6h2(v, e ? (((h8 & 0x0C) << 2) | ((h8 & 0xC0) << 14)) : (((h8 & 0x03) << 4) | ((h8 & 0x30) << 16)));
+                                    const __half2 ph = __hmul2(q, dh[t]);
+                                    __half2 pl = __hfma2(q, dh[t], __hneg2(ph));
+                                    pl = __hfma2(q, dl[t], pl);
+                                    hi[8 * t + 2 * c + e] = h2u(ph); lo[8 * t + 2 * c + e] = h2u(pl);
+                                }
+                        if (b == 0) {       // the first block is expanded before the stage is known to be free
+                            if (it >= 1 && !mbar_wait(done((4 * (it - 1) + fg) & (P_XST - 1)), (uint32_t)((4 * (it - 1) + fg) / P_XST) & 1u, abort_flag)) { ok = false; break; }
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        }
+                        tmem_st32(a_st + 32 * b, hi, lo);
+                    }
+                    if (!ok) break;
+                } else {
+                    const __half2 d2 = *reinterpret_cast<const __half2 *>(sc_gen + ss * P_SC_BYTES + sc_off);
+                    if (!mbar_wait(rawfull(slot), (uint32_t)(gi / P_RAW) & 1u, abort_flag)) { ok = false; break; }
+                    const unsigned char *rp = raw_gen + slot * P_RAW_BYTES;
+                    uint2 w[4];
+#pragma unroll
+                    for (int c = 0; c < 4; c++) w[c] = *reinterpret_cast<const uint2 *>(rp + raw_off[c]);
+                    __syncwarp();
+                    if (lane == 0) { mbar_arrive(scempty(ss)); mbar_arrive(rawempty(slot)); }
+                    uint32_t hi[16], lo[16];
+                    // bytes e and e + 2 of word c: weights 16 nib + 4 c + {e, e + 2} of the block (the activation tiles carry the same
+                    // order of k within every four), exact product d * (q - 8) as an fp16 pair
 #define VX_P_EXPAND(WORD, DD)                                                              \
     _Pragma("unroll") for (int nib = 0; nib < 2; nib++)                                    \
     _Pragma("unroll") for (int c = 0; c < 4; c++)                                          \
     _Pragma("unroll") for (int e = 0; e < 2; e++) {                                        \
-        if (P_KNOCK & 1) { hi[8 * nib + 2 * c + e] = w[c].WORD; lo[8 * nib + 2 * c + e] = h2u(DD); } else {   \
-        const __half2 q = nib2(w[c].WORD >> (4 * nib + 8 * e));                            \
-        const __half2 ph = __hmul2(q, DD);                                                 \
-        const __half2 pl = __hfma2(q, DD, __hneg2(ph));                                    \
-        hi[8 * nib + 2 * c + e] = h2u(ph); lo[8 * nib + 2 * c + e] = h2u(pl); }            \
-    }
-                const __half2 dd0 = __half2half2(__low2half(d2)), dd1 = __half2half2(__high2half(d2));
-                VX_P_EXPAND(x, dd0)                          // the first block is expanded before the stage is known to be free
-                // this group's previous stage, global index 4 (it - 1) + fg, sat in activation slot (4 (it - 1) + fg) % 8
-                if (it >= 1 && !mbar_wait(done((4 * (it - 1) + fg) & (P_XST - 1)), (uint32_t)((4 * (it - 1) + fg) / P_XST) & 1u, abort_flag)) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (P_KNOCK & 2) asm volatile("" :: "r"(hi[0]), "r"(hi[15]), "r"(lo[3]), "r"(lo[12])); else
-                tmem_st32(a_st, hi, lo);                     // columns 0-15 hi, 16-31 lo of K=16 steps 0, 1; in flight while the second block is expanded
-                VX_P_EXPAND(y, dd1)
-                if (P_KNOCK & 2) asm volatile("" :: "r"(hi[0]), "r"(hi[15]), "r"(lo[3]), "r"(lo[12])); else
-                tmem_st32(a_st + 32, hi, lo);                // K=16 steps 2, 3
+            if (P_KNOCK & 1) { hi[8 * nib + 2 * c + e] = w[c].WORD; lo[8 * nib + 2 * c + e] = h2u(DD); } else {   \
+            const __half2 q = nib2(w[c].WORD >> (4 * nib + 8 * e));                            \
+            const __half2 ph = __hmul2(q, DD);                                                 \
+            const __half2 pl = __hfma2(q, DD, __hneg2(ph));                                    \
+            hi[8 * nib + 2 * c + e] = h2u(ph); lo[8 * nib + 2 * c + e] = h2u(pl); }            \
+        }
+                    const __half2 dd0 = __half2half2(__low2half(d2)), dd1 = __half2half2(__high2half(d2));
+                    VX_P_EXPAND(x, dd0)                          // the first block is expanded before the stage is known to be free
+                    // this group's previous stage, global index 4 (it - 1) + fg, sat in activation slot (4 (it - 1) + fg) % 8
+                    if (it >= 1 && !mbar_wait(done((4 * (it - 1) + fg) & (P_XST - 1)), (uint32_t)((4 * (it - 1) + fg) / P_XST) & 1u, abort_flag)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (P_KNOCK & 2) asm volatile("" :: "r"(hi[0]), "r"(hi[15]), "r"(lo[3]), "r"(lo[12])); else
+                    tmem_st32(a_st, hi, lo);                     // columns 0-15 hi, 16-31 lo of K=16 steps 0, 1; in flight while the second block is expanded
+                    VX_P_EXPAND(y, dd1)
+                    if (P_KNOCK & 2) asm volatile("" :: "r"(hi[0]), "r"(hi[15]), "r"(lo[3]), "r"(lo[12])); else
+                    tmem_st32(a_st + 32, hi, lo);                // K=16 steps 2, 3
 #undef VX_P_EXPAND
+                }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
@@ -265,8 +325,9 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     const int slot = rc % P_RAW;
                     if (rc >= P_RAW && !mbar_wait(rawempty(slot), (uint32_t)(rc / P_RAW - 1) & 1u, abort_flag)) { ok = false; break; }
                     if (P_KNOCK & 16) mbar_arrive(rawfull(slot)); else {
-                    mbar_arrive_expect_tx(rawfull(slot), P_RAW_BYTES);
-                    tma_load_2d(raw_base + slot * P_RAW_BYTES, &map_w, raw_col, U.r0, rawfull(slot)); }
+                    mbar_arrive_expect_tx(rawfull(slot), FMT == P_Q6_K ? P_RAW_BYTES + P_RAWH_BYTES : P_RAW_BYTES);
+                    tma_load_2d(raw_base + slot * P_RAW_BYTES, &map_w, raw_col, U.r0, rawfull(slot));
+                    if (FMT == P_Q6_K) tma_load_2d(rawh_base + slot * P_RAWH_BYTES, &map_h, raw_col >> 1, U.r0, rawfull(slot)); }
                 }
             }
         }
@@ -386,13 +447,14 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 
 }  // namespace
 
-static int g_tcp = 1, g_tcp_stream = 1;
+static int g_tcp = 1, g_tcp_stream = 1, g_tcp_q6 = 1;
 // 0 = the one-CTA-per-tile kernel; 1 = persistent, aligned split-K only; 2 (default) = persistent, stream mode where it is cheaper
-extern "C" int vx_set_persistent_projections(int mode) { g_tcp = mode != 0; g_tcp_stream = mode == 1 ? 0 : mode == 3 ? 2 : 1; return VX_OK; }   // (3: stream mode wherever it applies, for timing comparisons)
+extern "C" int vx_set_persistent_projections(int mode) { g_tcp = mode != 0; g_tcp_stream = mode == 1 ? 0 : mode == 3 ? 2 : 1; g_tcp_q6 = mode != 4; return VX_OK; }   // (3: stream mode wherever it applies, for timing comparisons)
 
-// Eligible: Q4_0, at most 64 batch rows, an even number of 128-weight groups per row (the scale tiles cover two groups).
+// Eligible: Q4_0 or Q6_K, at most 64 batch rows, an even number of 128-weight groups per row (the scale tiles cover two
+// groups; a Q6_K row is whole 256-weight super-blocks anyway).
 bool vxq_gemm_tcp_eligible(const VxWeight &w, int m) {
-    return g_tcp && w.type == VX_T_Q4_0 && m <= P_MT && ((w.k_pad / 128) % 2) == 0;
+    return g_tcp && (w.type == VX_T_Q4_0 || (w.type == VX_T_Q6_K && g_tcp_q6)) && m <= P_MT && ((w.k_pad / 128) % 2) == 0;
 }
 
 // same contract as vxq_gemm (vx_quant.cu); the context's device error word receives VX_E_TIMEOUT if a bounded wait gave up
@@ -402,9 +464,11 @@ int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *o
     if (x.k_pad != w.k_pad) return vx_fail(c, VX_E_BAD_ARG, "projection: activation row stride %d != weight k_pad %d", x.k_pad, w.k_pad);
     {
         static VxPerDevice attr;
-        VX_CUDA(c, attr.max_dynamic_smem(c, gemm_tcp_kernel<false>, P_SMEM));
-        static VxPerDevice attr_s;
-        VX_CUDA(c, attr_s.max_dynamic_smem(c, gemm_tcp_kernel<true>, P_SMEM));
+        VX_CUDA(c, attr.max_dynamic_smem(c, gemm_tcp_kernel<false, P_Q4_0>, P_SMEM));
+        static VxPerDevice attr_s, attr6, attr6_s;
+        VX_CUDA(c, attr_s.max_dynamic_smem(c, gemm_tcp_kernel<true, P_Q4_0>, P_SMEM));
+        VX_CUDA(c, attr6.max_dynamic_smem(c, gemm_tcp_kernel<false, P_Q6_K>, P_SMEM_Q6));
+        VX_CUDA(c, attr6_s.max_dynamic_smem(c, gemm_tcp_kernel<true, P_Q6_K>, P_SMEM_Q6));
     }
     const int k_groups = w.k_pad / 128;
     const int tiles = ceil_div(w.n, TC_ROWS);
@@ -458,13 +522,13 @@ int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *o
     *n_parts_out = split;
     // tensor maps, kept per (weight, activation buffer) combination: a decode step launches the same ones every time
     struct MapKey {
-        const void *qs, *sc, *xh, *xl; int n, kg, kp;
-        bool operator<(const MapKey &o) const { return std::tie(qs, sc, xh, xl, n, kg, kp) < std::tie(o.qs, o.sc, o.xh, o.xl, o.n, o.kg, o.kp); }
+        const void *qs, *sc, *xh, *xl, *hi; int n, kg, kp;
+        bool operator<(const MapKey &o) const { return std::tie(qs, sc, xh, xl, hi, n, kg, kp) < std::tie(o.qs, o.sc, o.xh, o.xl, o.hi, o.n, o.kg, o.kp); }
     };
-    struct MapSet { CUtensorMap w, s, x; };
+    struct MapSet { CUtensorMap w, s, x, h; };
     static std::map<MapKey, MapSet> cache;
     static std::mutex cache_mu;
-    const MapKey key{w.qs, w.sc, x.hi, x.lo, w.n, k_groups, x.k_pad};
+    const MapKey key{w.qs, w.sc, x.hi, x.lo, w.type == VX_T_Q6_K ? w.hi : nullptr, w.n, k_groups, x.k_pad};
     MapSet ms;
     bool have = false;
     {
@@ -482,16 +546,24 @@ int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *o
         if ((const char *)x.lo <= (const char *)x.hi) return vx_fail(c, VX_E_BAD_ARG, "projection: the lo half of the activation split must follow the hi half");
         VX_TRY(make_map_3d(c, &ms.x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, x.hi, (uint64_t)x.k_pad, (uint64_t)P_MT, 2, (uint64_t)x.k_pad * 2,
                            (uint64_t)((const char *)x.lo - (const char *)x.hi), P_BK, P_MT, 2, CU_TENSOR_MAP_SWIZZLE_128B));
+        // Q6_K: the top two bits of every weight as bytes [n][k_groups * 32]; Q4_0 passes the nibble map again (unused)
+        if (w.type == VX_T_Q6_K)
+            VX_TRY(make_map(c, &ms.h, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w.hi, (uint64_t)k_groups * 32, (uint64_t)w.n, (uint64_t)k_groups * 32, 32,
+                            TC_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE));
+        else ms.h = ms.w;
         std::lock_guard<std::mutex> lk(cache_mu);
         if (cache.size() > 4096) cache.clear();     // buffers of destroyed models: start over rather than grow without bound
         cache[key] = ms;
     }
     const dim3 grid(std::min(n_units, slots));        // (stream mode: n_units is the number of runs = CTAs)
-    cudaError_t le = stream_q > 0
-        ? vx_launch_dependent(gemm_tcp_kernel<true>, grid, dim3(P_THREADS), (size_t)P_SMEM, c->stream, ms.w, ms.s, ms.x,
-                              (const float *)x.scale, dst, m, w.n, k_groups, per, split, n_units, stream_q, ld, (size_t)m * w.n, err_flag)
-        : vx_launch_dependent(gemm_tcp_kernel<false>, grid, dim3(P_THREADS), (size_t)P_SMEM, c->stream, ms.w, ms.s, ms.x,
-                              (const float *)x.scale, dst, m, w.n, k_groups, per, split, n_units, stream_q, ld, (size_t)m * w.n, err_flag);
+    cudaError_t le;
+#define VX_TCP_LAUNCH(S, F, BYTES)                                                                                              \
+    le = vx_launch_dependent(gemm_tcp_kernel<S, F>, grid, dim3(P_THREADS), (size_t)(BYTES), c->stream, ms.w, ms.s, ms.x, ms.h,  \
+                             (const __half *)w.aux, (const float *)x.scale, dst, m, w.n, k_groups, per, split, n_units, stream_q, ld, \
+                             (size_t)m * w.n, err_flag)
+    if (w.type == VX_T_Q6_K) { if (stream_q > 0) VX_TCP_LAUNCH(true, P_Q6_K, P_SMEM_Q6); else VX_TCP_LAUNCH(false, P_Q6_K, P_SMEM_Q6); }
+    else { if (stream_q > 0) VX_TCP_LAUNCH(true, P_Q4_0, P_SMEM); else VX_TCP_LAUNCH(false, P_Q4_0, P_SMEM); }
+#undef VX_TCP_LAUNCH
     if (le != cudaSuccess) return vx_cuda_fail(c, le, "projection launch");
     VX_LAUNCH_CHECK(c);
     return VX_OK;
