@@ -212,7 +212,10 @@ def test_matmul_q4_0_split_modes(be, m, n, k):
     be.ResetPool()
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 256, 256), (3, 200, 1024), (8, 1000, 4096), (20, 130, 512), (70, 384, 2048)])
+@pytest.mark.parametrize("m,n,k", [(1, 256, 256), (3, 200, 1024), (8, 1000, 4096), (20, 130, 512), (70, 384, 2048),
+                                   # 33-64 rows: both K-quant formats on the persistent tcgen05 kernel (aligned and stream splits,
+                                   # a row count that is not a multiple of the 128-row tile, the benchmark's gate/up shape)
+                                   (40, 384, 2048), (64, 1000, 4096), (33, 12300, 4096), (64, 28672, 4096)])
 @pytest.mark.parametrize("type_id,quant,fn", [(capi.T_Q4_K, gs.quantize_q4_k, "MatMulQ4_K"), (capi.T_Q6_K, gs.quantize_q6_k, "MatMulQ6_K")])
 def test_matmul_kquants(be, type_id, quant, fn, m, n, k):
     rng = np.random.default_rng(7 + m)

@@ -487,7 +487,8 @@ extern "C" int vx_selftest_bounded_wait(vx_ctx *c, int limit_us, int *reached_en
 // same contract as vxq_gemm (vx_quant.cu); the context's device error word receives VX_E_TIMEOUT if a bounded wait gave up
 int vxq_gemm_tc(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out, float *parts,
                 size_t parts_cap_floats) {
-    if (vxq_gemm_tcp_eligible(w, m)) return vxq_gemm_tcp(c, w, x, m, out, ld_out, n_parts_out, parts, parts_cap_floats);   // decode batches of Q4_0: the persistent kernel
+    if (vxq_gemm_tcp_eligible(w, m) && (w.type != VX_T_Q4_K || (parts && (size_t)2 * m * w.n <= parts_cap_floats)))   // (Q4_K needs a slot for its minima)
+        return vxq_gemm_tcp(c, w, x, m, out, ld_out, n_parts_out, parts, parts_cap_floats);   // decode batches of Q4_0: the persistent kernel
     int *err_flag = c->d_int_result + 8;
     if (w.type != VX_T_Q4_0 && w.type != VX_T_Q4_K && w.type != VX_T_Q6_K) return vx_fail(c, VX_E_UNSUPPORTED, "tensor-core projection: weight type %d", w.type);
     if (x.k_pad != w.k_pad) return vx_fail(c, VX_E_BAD_ARG, "projection: activation row stride %d != weight k_pad %d", x.k_pad, w.k_pad);

@@ -39,7 +39,7 @@ constexpr int P_STAGE_BYTES = 2 * P_X_TILE;   // x_hi rows, then x_lo rows
 constexpr int P_RAW_BYTES = TC_ROWS * 64;
 constexpr int P_SC_BYTES = TC_ROWS * 16;      // 128 rows x 8 scales
 constexpr int P_RAWH_BYTES = TC_ROWS * 32;    // Q6_K only: the top two bits of a 128-weight group
-enum { P_Q4_0 = 0, P_Q6_K = 2 };
+enum { P_Q4_0 = 0, P_Q4_K = 1, P_Q6_K = 2 };
 constexpr int P_DEQ_WARPS = 16, P_EPI_WARP0 = 16, P_ISSUE_WARP = 20, P_ISSUERS = 2, P_XPROD_WARP = 22, P_WPROD_WARP = 23;
 constexpr int P_THREADS = 24 * 32;
 constexpr int P_TMEM_ACC = 128;               // columns per accumulator (one per issuing warp): 0-63 = A_hi x_hi + A_lo x_hi, 64-127 = A_hi x_lo
@@ -178,6 +178,8 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         int it = 0, g_count = 0, t_count = 0;        // this group's iterations; nibble tiles and scale tiles before the current unit
         __half dsup_h = __float2half(0.f);          // (Q6_K) super-block scale of this thread's next stage
         const __half *sup_row = nullptr;
+        __half2 dsup2 = __float2half2_rn(0.f);      // (Q4_K) {d, dmin} of this thread's next stage
+        const __half2 *sup2_row = nullptr;
         bool ok = true;
         UnitIter<STREAM> uit((int)blockIdx.x, (int)gridDim.x, split, per, k_groups, stream_q);
         for (int ui = 0; ui < n_my && ok; ui++, uit.next()) {
@@ -187,11 +189,59 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 sup_row = sup + (size_t)min(U.r0 + row, N - 1) * (k_groups >> 1);
                 if (fg < n_kb) dsup_h = __ldg(sup_row + ((U.g_begin + (fg >> 1)) >> 1));
             }
+            if constexpr (FMT == P_Q4_K) {
+                sup2_row = reinterpret_cast<const __half2 *>(sup) + (size_t)min(U.r0 + row, N - 1) * (k_groups >> 1);
+                if (fg < n_kb) dsup2 = __ldg(sup2_row + ((U.g_begin + (fg >> 1)) >> 1));
+            }
             for (int kb = fg; kb < n_kb; kb += P_AST, it++) {
                 const int gi = g_count + (kb >> 1), ti = t_count + (kb >> 2);
                 const int slot = gi % P_RAW, ss = ti % P_SC;
                 if (!mbar_wait(scfull(ss), (uint32_t)(ti / P_SC) & 1u, abort_flag)) { ok = false; break; }
-                if constexpr (FMT == P_Q6_K) {
+                if constexpr (FMT == P_Q4_K) {
+                    // Q4_K (inference/pkg/gguf/dequant.go:342-396): the stage is 64-weight half `fg & 1` of the 128-weight group =
+                    // sub-blocks 2 (fg & 1) + b; the same two words of every chunk hold positions 0-15 / 16-31 of both sub-blocks,
+                    // b selects the nibble.  w = d1 q - dm1 is carried as d1 (q - 8) + (8 d1 - dm1): the centred term goes through
+                    // the tensor cores with fl(d * sc) as an fp16 pair, the constant per sub-block meets the activations' block
+                    // sums in a kernel of its own (q4k_minima_kernel), whose result is one more partial-sum slot.
+                    const uint32_t scw = *reinterpret_cast<const uint32_t *>(sc_gen + ss * P_SC_BYTES + row * 16 + ((fg >> 1) & 1) * 8);
+                    const float dsup = __low2float(dsup2);
+                    {   // {d, dmin} of this group's next stage (one pair per 256 weights)
+                        const int kbn = kb + P_AST < n_kb ? kb + P_AST : kb;
+                        dsup2 = __ldg(sup2_row + ((U.g_begin + (kbn >> 1)) >> 1));
+                    }
+                    if (!mbar_wait(rawfull(slot), (uint32_t)(gi / P_RAW) & 1u, abort_flag)) { ok = false; break; }
+                    const unsigned char *rp = raw_gen + slot * P_RAW_BYTES;
+                    uint2 w[4];
+#pragma unroll
+                    for (int c = 0; c < 4; c++) w[c] = *reinterpret_cast<const uint2 *>(rp + raw_off[c]);
+                    __syncwarp();
+                    if (lane == 0) { mbar_arrive(scempty(ss)); mbar_arrive(rawempty(slot)); }
+                    uint32_t hi[16], lo[16];
+#pragma unroll
+                    for (int b = 0; b < 2; b++) {
+                        __half2 dh, dl;
+                        split_scale(__fmul_rn(dsup, (float)((scw >> (8 * (2 * (fg & 1) + b))) & 0xFF)), &dh, &dl);                 // dequant.go:369-372
+#pragma unroll
+                        for (int t = 0; t < 2; t++)
+#pragma unroll
+                            for (int c = 0; c < 4; c++)
+#pragma unroll
+                                for (int e = 0; e < 2; e++) {
+                                    const uint32_t word = t ? w[c].y : w[c].x;
+                                    const __half2 q = nib2(word >> (4 * b + 8 * e));           // q - 8
+                                    const __half2 ph = __hmul2(q, dh);
+                                    __half2 pl = __hfma2(q, dh, __hneg2(ph));
+                                    pl = __hfma2(q, dl, pl);
+                                    hi[8 * t + 2 * c + e] = h2u(ph); lo[8 * t + 2 * c + e] = h2u(pl);
+                                }
+                        if (b == 0) {       // the first block is expanded before the stage is known to be free
+                            if (it >= 1 && !mbar_wait(done((4 * (it - 1) + fg) & (P_XST - 1)), (uint32_t)((4 * (it - 1) + fg) / P_XST) & 1u, abort_flag)) { ok = false; break; }
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        }
+                        tmem_st32(a_st + 32 * b, hi, lo);
+                    }
+                    if (!ok) break;
+                } else if constexpr (FMT == P_Q6_K) {
                     // Q6_K (inference/pkg/gguf/dequant.go:272-331): the stage is 64-weight half `fg & 1` of the 128-weight group; word
                     // 2 (fg & 1) + b of every chunk holds the 16-weight sub-blocks 4 (fg & 1) + 2 b (low nibbles) and + 1 (high
                     // nibbles), the top two bits come from the second tile; fl(d * sc) travels as an fp16 pair so that
@@ -412,8 +462,10 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 for (int i = 0; i < 4; i++) *reinterpret_cast<float4 *>(&sx[4 * i]) = *reinterpret_cast<const float4 *>(s_xscale + 16 * cb + 4 * i);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int i = 0; i < 16; i++)
-                    v[16 * cb + i] = (((__uint_as_float(a[i]) + __uint_as_float(c2[i])) + __uint_as_float(a1[i])) + __uint_as_float(c3[i])) * sx[i];
+                for (int i = 0; i < 16; i++) {
+                    const float t = ((__uint_as_float(a[i]) + __uint_as_float(c2[i])) + __uint_as_float(a1[i])) + __uint_as_float(c3[i]);
+                    v[16 * cb + i] = t * sx[i];
+                }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -447,14 +499,103 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 
 }  // namespace
 
+// Q4_K minima: out[m][n] = s_m * sum_u (8 fl(d sc_u) - fl(dmin m_u)) * bsum[m][u] over all 32-weight sub-blocks u of row n
+// (dequant.go:369-392: w = d1 q - dm1, and the projection kernel carries d1 (q - 8)).  A small float32 GEMM (K = k / 32):
+// a CTA owns ROWS weight rows x 64 batch rows, a thread a 4 x 4 tile; up to 128 sub-blocks are staged at a time (one round
+// of global loads, one barrier), the constants computed from the scale bytes as they are staged.  Its result is written
+// as one more partial-sum slot, which the consumer adds like the others.  (Measured variants that were no faster: 64
+// sub-blocks per round with two-wide FMAs, and 8 x 8 register tiles: the kernel is bound by its staging round, not by FMAs.)
+constexpr int MN_U = 128;
+template <int ROWS>
+__global__ void __launch_bounds__(4 * ROWS) q4k_minima_kernel(const uint2 *__restrict__ sc, const __half2 *__restrict__ sup, const float *__restrict__ xbsum,
+                                                              int bsum_ld, const float *__restrict__ xscale, float *__restrict__ out, int M, int N,
+                                                              int k_groups, int ld_out) {
+    extern __shared__ __align__(16) float mn_smem[];
+    float (*ce)[ROWS] = reinterpret_cast<float (*)[ROWS]>(mn_smem);                    // [sub-block][weight row]
+    float (*bs)[P_MT] = reinterpret_cast<float (*)[P_MT]>(mn_smem + MN_U * ROWS);      // [sub-block][batch row]
+    vx_pdl_wait();
+    vx_pdl_trigger();
+    constexpr int NT = 4 * ROWS, TX = ROWS / 4;
+    const int tid = threadIdx.x, tx = tid % TX, ty = tid / TX;
+    const int n0 = blockIdx.x * ROWS;
+    float acc[4][4];                                        // [batch row 4 ty + i][weight row 4 tx + j]
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    const int n_u = k_groups * 4;
+    for (int u0 = 0; u0 < n_u; u0 += MN_U) {
+        if (u0) __syncthreads();
+        {   // constants: thread t -> weight row t % ROWS, the eight groups (t / ROWS) * 8 .. + 7 of the chunk's 32
+            const int r = tid % ROWS, gq = tid / ROWS;
+            const int gn = min(n0 + r, N - 1);
+            uint2 sm8[8]; __half2 dd2[4];
+#pragma unroll
+            for (int gg = 0; gg < 8; gg++) {
+                const int g = min((u0 >> 2) + 8 * gq + gg, k_groups - 1);
+                sm8[gg] = __ldg(sc + (size_t)gn * k_groups + g);
+                if ((gg & 1) == 0) dd2[gg >> 1] = __ldg(sup + (size_t)gn * (k_groups >> 1) + (g >> 1));
+            }
+            // block sums: 64 batch rows x 32 groups of four sums
+            for (int i = tid; i < P_MT * (MN_U / 4); i += NT) {
+                const int mrow = i % P_MT, u4 = i / P_MT;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (u0 + 4 * u4 < n_u) v = __ldg(reinterpret_cast<const float4 *>(xbsum + (size_t)min(mrow, M - 1) * bsum_ld + u0 + 4 * u4));
+                bs[4 * u4 + 0][mrow] = v.x; bs[4 * u4 + 1][mrow] = v.y; bs[4 * u4 + 2][mrow] = v.z; bs[4 * u4 + 3][mrow] = v.w;
+            }
+#pragma unroll
+            for (int gg = 0; gg < 8; gg++) {
+                const bool live = (u0 >> 2) + 8 * gq + gg < k_groups;
+                const float2 dd = __half22float2(dd2[gg >> 1]);
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const float d1 = __fmul_rn(dd.x, (float)((sm8[gg].x >> (8 * u)) & 0xFF)), dm = __fmul_rn(dd.y, (float)((sm8[gg].y >> (8 * u)) & 0xFF));
+                    ce[(8 * gq + gg) * 4 + u][r] = live ? fmaf(8.f, d1, -dm) : 0.f;
+                }
+            }
+        }
+        __syncthreads();
+        const int n_c = min(MN_U, n_u - u0);
+#pragma unroll 8
+        for (int u = 0; u < n_c; u++) {
+            const float4 a = *reinterpret_cast<const float4 *>(&ce[u][4 * tx]);
+            const float4 b = *reinterpret_cast<const float4 *>(&bs[u][4 * ty]);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(bv[i], av[j], acc[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int m = 4 * ty + i;
+        if (m < M) {
+            const float sxm = xscale[m];
+            float *o = out + (size_t)m * ld_out + n0 + 4 * tx;
+#pragma unroll
+            for (int j = 0; j < 4; j++) if (n0 + 4 * tx + j < N) o[j] = acc[i][j] * sxm;
+        }
+    }
+}
+template <int ROWS>
+static cudaError_t minima_launch(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *slot, int k_groups) {
+    const int bytes = MN_U * (ROWS + P_MT) * (int)sizeof(float);
+    static VxPerDevice attr;
+    cudaError_t e = attr.max_dynamic_smem(c, q4k_minima_kernel<ROWS>, bytes);
+    if (e != cudaSuccess) return e;
+    return vx_launch_chain(q4k_minima_kernel<ROWS>, dim3(ceil_div(w.n, ROWS)), dim3(4 * ROWS), (size_t)bytes, c->stream, (const uint2 *)w.sc,
+                           (const __half2 *)w.aux, (const float *)x.bsum, x.k_pad / 32, (const float *)x.scale, slot, m, w.n, k_groups, w.n);
+}
+
 static int g_tcp = 1, g_tcp_stream = 1, g_tcp_q6 = 1;
 // 0 = the one-CTA-per-tile kernel; 1 = persistent, aligned split-K only; 2 (default) = persistent, stream mode where it is cheaper
 extern "C" int vx_set_persistent_projections(int mode) { g_tcp = mode != 0; g_tcp_stream = mode == 1 ? 0 : mode == 3 ? 2 : 1; g_tcp_q6 = mode != 4; return VX_OK; }   // (3: stream mode wherever it applies, for timing comparisons)
 
-// Eligible: Q4_0 or Q6_K, at most 64 batch rows, an even number of 128-weight groups per row (the scale tiles cover two
+// Eligible: Q4_0, Q4_K or Q6_K, at most 64 batch rows, an even number of 128-weight groups per row (the scale tiles cover two
 // groups; a Q6_K row is whole 256-weight super-blocks anyway).
 bool vxq_gemm_tcp_eligible(const VxWeight &w, int m) {
-    return g_tcp && (w.type == VX_T_Q4_0 || (w.type == VX_T_Q6_K && g_tcp_q6)) && m <= P_MT && ((w.k_pad / 128) % 2) == 0;
+    return g_tcp && (w.type == VX_T_Q4_0 || ((w.type == VX_T_Q6_K || w.type == VX_T_Q4_K) && g_tcp_q6)) && m <= P_MT && ((w.k_pad / 128) % 2) == 0;
 }
 
 // same contract as vxq_gemm (vx_quant.cu); the context's device error word receives VX_E_TIMEOUT if a bounded wait gave up
@@ -469,6 +610,9 @@ int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *o
         VX_CUDA(c, attr_s.max_dynamic_smem(c, gemm_tcp_kernel<true, P_Q4_0>, P_SMEM));
         VX_CUDA(c, attr6.max_dynamic_smem(c, gemm_tcp_kernel<false, P_Q6_K>, P_SMEM_Q6));
         VX_CUDA(c, attr6_s.max_dynamic_smem(c, gemm_tcp_kernel<true, P_Q6_K>, P_SMEM_Q6));
+        static VxPerDevice attr4, attr4_s;
+        VX_CUDA(c, attr4.max_dynamic_smem(c, gemm_tcp_kernel<false, P_Q4_K>, P_SMEM));
+        VX_CUDA(c, attr4_s.max_dynamic_smem(c, gemm_tcp_kernel<true, P_Q4_K>, P_SMEM));
     }
     const int k_groups = w.k_pad / 128;
     const int tiles = ceil_div(w.n, TC_ROWS);
@@ -476,11 +620,12 @@ int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *o
     // Split-K in whole pairs of groups.  Cost in pipeline stages: the busiest CTA's stages, a little per unit it walks (the
     // accumulator hand-over), and the partial sums' write and read (mostly L2); the smaller split wins near-ties.
     int split = 1, per = k_groups;
+    const int extra = w.type == VX_T_Q4_K ? 1 : 0;          // the minima slot
     if (parts) {
         constexpr double UNIT_STAGES = 2.5, PART_STAGES_PER_FLOAT = 2.2e-6;
         double best = 1e300;
         for (int s = 1; s <= 8 && 2 * s <= k_groups; s++) {
-            if ((size_t)s * m * w.n > parts_cap_floats) break;
+            if ((size_t)(s + extra) * m * w.n > parts_cap_floats) break;
             int p = ceil_div(k_groups, s);
             p += p & 1;
             const int s_eff = ceil_div(k_groups, p);
@@ -513,12 +658,13 @@ int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *o
         const double cost_a = (double)ceil_div64(units_a, std::min<long>(units_a, slots)) * (2.0 * per + UNIT_STAGES) +
                               (split > 1 ? PART_STAGES_PER_FLOAT * split * (double)m * w.n : 0.0);
         // (an aligned launch without partial sums also spares its consumer a pass over them: it needs a clearer margin to lose)
-        if (n_slots > 1 && (size_t)n_slots * m * w.n <= parts_cap_floats && (g_tcp_stream == 2 ? split > 1 : cost < cost_a * (split > 1 ? 0.98 : 0.90))) {
+        if (n_slots > 1 && (size_t)(n_slots + extra) * m * w.n <= parts_cap_floats && (g_tcp_stream == 2 ? split > 1 : cost < cost_a * (split > 1 ? 0.98 : 0.90))) {
             stream_q = (int)Q; split = n_slots; per = qt; n_units = (int)G;
         }
     }
-    float *dst = split > 1 ? parts : out;
-    const int ld = split > 1 ? w.n : ld_out;
+    const bool to_slots = split > 1 || w.type == VX_T_Q4_K;   // Q4_K always writes slots: its minima come as one more
+    float *dst = to_slots ? parts : out;
+    const int ld = to_slots ? w.n : ld_out;
     *n_parts_out = split;
     // tensor maps, kept per (weight, activation buffer) combination: a decode step launches the same ones every time
     struct MapKey {
@@ -562,9 +708,18 @@ int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *o
                              (const __half *)w.aux, (const float *)x.scale, dst, m, w.n, k_groups, per, split, n_units, stream_q, ld, \
                              (size_t)m * w.n, err_flag)
     if (w.type == VX_T_Q6_K) { if (stream_q > 0) VX_TCP_LAUNCH(true, P_Q6_K, P_SMEM_Q6); else VX_TCP_LAUNCH(false, P_Q6_K, P_SMEM_Q6); }
+    else if (w.type == VX_T_Q4_K) { if (stream_q > 0) VX_TCP_LAUNCH(true, P_Q4_K, P_SMEM); else VX_TCP_LAUNCH(false, P_Q4_K, P_SMEM); }
     else { if (stream_q > 0) VX_TCP_LAUNCH(true, P_Q4_0, P_SMEM); else VX_TCP_LAUNCH(false, P_Q4_0, P_SMEM); }
 #undef VX_TCP_LAUNCH
     if (le != cudaSuccess) return vx_cuda_fail(c, le, "projection launch");
     VX_LAUNCH_CHECK(c);
+    if (w.type == VX_T_Q4_K) {     // the minima as one more slot behind the projection's own
+        // 64-row CTAs when they fill the GPU, 32-row CTAs for the narrow matrices
+        float *slot = parts + (size_t)split * m * w.n;
+        le = w.n >= 64 * 2 * c->sm_count ? minima_launch<64>(c, w, x, m, slot, k_groups) : minima_launch<32>(c, w, x, m, slot, k_groups);
+        if (le != cudaSuccess) return vx_cuda_fail(c, le, "minima launch");
+        VX_LAUNCH_CHECK(c);
+        *n_parts_out = split + 1;
+    }
     return VX_OK;
 }
