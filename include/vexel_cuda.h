@@ -298,7 +298,7 @@ int vx_set_graphs(int enable);
  * must return (reached_end = 1) and the next vx_sync must report VX_E_TIMEOUT while the context stays usable.  This is
  * how every device-side wait of the library behaves when its peer never shows up; no counterpart in the reference. */
 int vx_selftest_bounded_wait(vx_ctx *ctx, int limit_us, int *reached_end);
-/* batches with at least this many rows run the projections on the tcgen05 kernel (default 17, and never below 33 for Q4_K;
+/* batches with at least this many rows run the projections on the tcgen05 kernel (default 17;
  * 0 = always the mma.sync kernel) */
 int vx_set_tc_min_rows(int rows);
 /* Q4_0 projections of 17..64 batch rows run on the persistent tcgen05 kernel (one CTA per SM walking weight tiles, its

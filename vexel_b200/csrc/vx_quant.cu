@@ -612,6 +612,8 @@ static int gemm_launch_fmt(vx_ctx *c, int nt, int terms, const VxWeight &w, cons
 
 static int g_gemm_terms = 2;   // 2: x = hi + lo (float32-faithful); 1: fp16 activations only
 int g_vx_pdl = 1;               // projections start under the tail of the kernel before them (programmatic dependent launch)
+static int g_q4k_tc_floor = 17;  // Q4_K: 33 while it ran on the one-CTA-per-tile kernel; on the persistent kernel 17 like the others
+                                 // (70B-shaped step at 32 rows 10.46 -> 8.80 ms, 8B-shaped at 24 rows 3.57 -> 3.29 ms)
 static int g_tc_min_rows = 17;  // batches of at least this many rows use the tcgen05 kernel (0 = never)
 
 // out receives [m][ld_out] when *n_parts_out == 1, otherwise `parts` holds [n_parts][m][w.n]
@@ -620,10 +622,9 @@ int vxq_gemm(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, 
     if (w.type != VX_T_Q4_0 && w.type != VX_T_Q4_K && w.type != VX_T_Q6_K)
         return vx_fail(c, VX_E_UNSUPPORTED, "projection: weight type %d has no MMA kernel", w.type);
     if (x.k_pad != w.k_pad) return vx_fail(c, VX_E_BAD_ARG, "projection: activation row stride %d != weight k_pad %d", x.k_pad, w.k_pad);
-    // measured crossover to the tcgen05 kernel (whose cost per weight does not depend on the batch): 17 rows for Q4_0 and
-    // Q6_K, 33 for Q4_K, whose mma.sync variant stays ahead up to its 32-row tile
+    // measured crossover to the tcgen05 kernels (whose cost per weight does not depend on the batch): 17 rows
     if (g_gemm_terms == 2 && vxq_gemv_eligible(w, m)) return vxq_gemv(c, w, x, m, out, ld_out, n_parts_out, parts, parts_cap_floats);
-    const int tc_rows = (w.type == VX_T_Q4_K && g_tc_min_rows > 0) ? max(g_tc_min_rows, 33) : g_tc_min_rows;
+    const int tc_rows = (w.type == VX_T_Q4_K && g_tc_min_rows > 0) ? max(g_tc_min_rows, g_q4k_tc_floor) : g_tc_min_rows;
     if (tc_rows > 0 && m >= tc_rows && g_gemm_terms == 2)
         return vxq_gemm_tc(c, w, x, m, out, ld_out, n_parts_out, parts, parts_cap_floats);
     int k_groups = w.k_pad / 128;
@@ -815,7 +816,7 @@ int vx_matmul_q4_0(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, i
 int vx_matmul_q4_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k) { return matmul_quant(c, VX_T_Q4_K, a, b, out, m, n, k); }
 int vx_matmul_q6_k(vx_ctx *c, vx_dptr a, vx_dptr b, vx_dptr out, int m, int n, int k) { return matmul_quant(c, VX_T_Q6_K, a, b, out, m, n, k); }
 
-int vx_set_tc_min_rows(int rows) { g_tc_min_rows = rows; return VX_OK; }
+int vx_set_tc_min_rows(int rows) { if (rows >= 1000) { g_q4k_tc_floor = rows - 1000; return VX_OK; } g_tc_min_rows = rows; return VX_OK; }   // (1000 + r: the Q4_K floor, for timing comparisons)
 int vx_set_repack_cache(vx_ctx *c, int enable) {
     if (!c) return VX_E_BAD_ARG;
     VxGuard g(c);
