@@ -500,91 +500,136 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 }  // namespace
 
 // Q4_K minima: out[m][n] = s_m * sum_u (8 fl(d sc_u) - fl(dmin m_u)) * bsum[m][u] over all 32-weight sub-blocks u of row n
-// (dequant.go:369-392: w = d1 q - dm1, and the projection kernel carries d1 (q - 8)).  A small float32 GEMM (K = k / 32):
-// a CTA owns ROWS weight rows x 64 batch rows, a thread a 4 x 4 tile; up to 128 sub-blocks are staged at a time (one round
-// of global loads, one barrier), the constants computed from the scale bytes as they are staged.  Its result is written
-// as one more partial-sum slot, which the consumer adds like the others.  (Measured variants that were no faster: 64
-// sub-blocks per round with two-wide FMAs, and 8 x 8 register tiles: the kernel is bound by its staging round, not by FMAs.)
-constexpr int MN_U = 128;
+// (dequant.go:369-392: w = d1 q - dm1, and the projection kernel carries d1 (q - 8)).  A small GEMM (K = k / 32) on
+// mma.sync.m16n8k16: the constants (times 2^8) and the block sums (times 2^-6, they reach 32 * 2048) are staged in shared
+// memory as exact fp16 hi + lo pairs, weight rows are the M dimension (a warp owns 16 of them), batch rows the N dimension
+// (eight tiles of 8), three MMAs per tile and K step (hi hi, lo hi, hi lo), float32 accumulation.  As float32 FMAs on
+// 4 x 4 register tiles the same product took 30 us for the 28672-row gate/up matrix -- as long as two thirds of the
+// projection it corrects.  Its result is written as one more partial-sum slot, which the consumer adds like the others.
+constexpr int MN_U = 128;                 // sub-blocks staged per round
+constexpr int MN_LD = MN_U + 8;           // row stride in halves: 68 words, so a fragment load touches 32 different banks
+__device__ __forceinline__ void mn_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mn_split4(const float (&v)[4], __half *hi, __half *lo) {     // four values -> fp16 hi and lo parts, 8-byte stores
+    __half h[4], l[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) { h[i] = __float2half_rn(v[i]); l[i] = __float2half_rn(v[i] - __half2float(h[i])); }
+    *reinterpret_cast<uint2 *>(hi) = make_uint2((uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[1]) << 16),
+                                                (uint32_t)__half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[3]) << 16));
+    *reinterpret_cast<uint2 *>(lo) = make_uint2((uint32_t)__half_as_ushort(l[0]) | ((uint32_t)__half_as_ushort(l[1]) << 16),
+                                                (uint32_t)__half_as_ushort(l[2]) | ((uint32_t)__half_as_ushort(l[3]) << 16));
+}
 template <int ROWS>
-__global__ void __launch_bounds__(4 * ROWS) q4k_minima_kernel(const uint2 *__restrict__ sc, const __half2 *__restrict__ sup, const float *__restrict__ xbsum,
+__global__ void __launch_bounds__(2 * ROWS) q4k_minima_kernel(const uint2 *__restrict__ sc, const __half2 *__restrict__ sup, const float *__restrict__ xbsum,
                                                               int bsum_ld, const float *__restrict__ xscale, float *__restrict__ out, int M, int N,
                                                               int k_groups, int ld_out) {
-    extern __shared__ __align__(16) float mn_smem[];
-    float (*ce)[ROWS] = reinterpret_cast<float (*)[ROWS]>(mn_smem);                    // [sub-block][weight row]
-    float (*bs)[P_MT] = reinterpret_cast<float (*)[P_MT]>(mn_smem + MN_U * ROWS);      // [sub-block][batch row]
+    extern __shared__ __align__(16) __half mn_smem[];
+    __half *ceh = mn_smem, *cel = ceh + ROWS * MN_LD;                  // [weight row][sub-block]
+    __half *bsh = cel + ROWS * MN_LD, *bsl = bsh + P_MT * MN_LD;       // [batch row][sub-block]
     vx_pdl_wait();
     vx_pdl_trigger();
-    constexpr int NT = 4 * ROWS, TX = ROWS / 4;
-    const int tid = threadIdx.x, tx = tid % TX, ty = tid / TX;
+    constexpr int NT = 2 * ROWS;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
     const int n0 = blockIdx.x * ROWS;
-    float acc[4][4];                                        // [batch row 4 ty + i][weight row 4 tx + j]
+    float acc[8][4];                                        // tile t: weight rows 16 warp + {g, g + 8}, batch rows 8 t + {2c, 2c + 1}
 #pragma unroll
-    for (int i = 0; i < 4; i++)
-#pragma unroll
-        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    for (int t = 0; t < 8; t++) { acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f; }
     const int n_u = k_groups * 4;
     for (int u0 = 0; u0 < n_u; u0 += MN_U) {
         if (u0) __syncthreads();
-        {   // constants: thread t -> weight row t % ROWS, the eight groups (t / ROWS) * 8 .. + 7 of the chunk's 32
-            const int r = tid % ROWS, gq = tid / ROWS;
-            const int gn = min(n0 + r, N - 1);
-            uint2 sm8[8]; __half2 dd2[4];
+        // Staging, eight items per thread at a time with all eight global loads issued before the first is used (as a plain
+        // loop the rounds of dependent loads, ~1 us each, were most of the kernel's time).
+        // constants: (weight row, group) items, groups fastest: 8-byte loads of a row's scale bytes side by side
+        for (int base = 0; base < ROWS * (MN_U / 4); base += 8 * NT) {
+            uint2 sm8[8]; __half2 dd2[8];
 #pragma unroll
-            for (int gg = 0; gg < 8; gg++) {
-                const int g = min((u0 >> 2) + 8 * gq + gg, k_groups - 1);
-                sm8[gg] = __ldg(sc + (size_t)gn * k_groups + g);
-                if ((gg & 1) == 0) dd2[gg >> 1] = __ldg(sup + (size_t)gn * (k_groups >> 1) + (g >> 1));
-            }
-            // block sums: 64 batch rows x 32 groups of four sums
-            for (int i = tid; i < P_MT * (MN_U / 4); i += NT) {
-                const int mrow = i % P_MT, u4 = i / P_MT;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (u0 + 4 * u4 < n_u) v = __ldg(reinterpret_cast<const float4 *>(xbsum + (size_t)min(mrow, M - 1) * bsum_ld + u0 + 4 * u4));
-                bs[4 * u4 + 0][mrow] = v.x; bs[4 * u4 + 1][mrow] = v.y; bs[4 * u4 + 2][mrow] = v.z; bs[4 * u4 + 3][mrow] = v.w;
+            for (int j = 0; j < 8; j++) {
+                const int i = base + j * NT + tid;
+                const int gl = i % (MN_U / 4), r = i / (MN_U / 4), gq = min((u0 >> 2) + gl, k_groups - 1);
+                const int gn = min(n0 + min(r, ROWS - 1), N - 1);
+                sm8[j] = __ldg(sc + (size_t)gn * k_groups + gq);
+                dd2[j] = __ldg(sup + (size_t)gn * (k_groups >> 1) + (gq >> 1));
             }
 #pragma unroll
-            for (int gg = 0; gg < 8; gg++) {
-                const bool live = (u0 >> 2) + 8 * gq + gg < k_groups;
-                const float2 dd = __half22float2(dd2[gg >> 1]);
+            for (int j = 0; j < 8; j++) {
+                const int i = base + j * NT + tid;
+                if (i < ROWS * (MN_U / 4)) {
+                    const int gl = i % (MN_U / 4), r = i / (MN_U / 4);
+                    const bool live = (u0 >> 2) + gl < k_groups;
+                    const float2 dd = __half22float2(dd2[j]);
+                    float c4[4];
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const float d1 = __fmul_rn(dd.x, (float)((sm8[gg].x >> (8 * u)) & 0xFF)), dm = __fmul_rn(dd.y, (float)((sm8[gg].y >> (8 * u)) & 0xFF));
-                    ce[(8 * gq + gg) * 4 + u][r] = live ? fmaf(8.f, d1, -dm) : 0.f;
+                    for (int u = 0; u < 4; u++) {
+                        const float d1 = __fmul_rn(dd.x, (float)((sm8[j].x >> (8 * u)) & 0xFF)), dm = __fmul_rn(dd.y, (float)((sm8[j].y >> (8 * u)) & 0xFF));
+                        c4[u] = live ? fmaf(8.f, d1, -dm) * 256.f : 0.f;
+                    }
+                    mn_split4(c4, ceh + r * MN_LD + 4 * gl, cel + r * MN_LD + 4 * gl);
+                }
+            }
+        }
+        // block sums: (batch row, group) items, groups fastest
+        for (int base = 0; base < P_MT * (MN_U / 4); base += 8 * NT) {
+            float4 v8[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int i = min(base + j * NT + tid, P_MT * (MN_U / 4) - 1);
+                const int gl = i % (MN_U / 4), mrow = i / (MN_U / 4);
+                v8[j] = __ldg(reinterpret_cast<const float4 *>(xbsum + (size_t)min(mrow, M - 1) * bsum_ld + min(u0 + 4 * gl, n_u - 4)));
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int i = base + j * NT + tid;
+                if (i < P_MT * (MN_U / 4)) {
+                    const int gl = i % (MN_U / 4), mrow = i / (MN_U / 4);
+                    const float f = u0 + 4 * gl < n_u ? 1.f / 64.f : 0.f;
+                    const float b4[4] = {v8[j].x * f, v8[j].y * f, v8[j].z * f, v8[j].w * f};
+                    mn_split4(b4, bsh + mrow * MN_LD + 4 * gl, bsl + mrow * MN_LD + 4 * gl);
                 }
             }
         }
         __syncthreads();
-        const int n_c = min(MN_U, n_u - u0);
-#pragma unroll 8
-        for (int u = 0; u < n_c; u++) {
-            const float4 a = *reinterpret_cast<const float4 *>(&ce[u][4 * tx]);
-            const float4 b = *reinterpret_cast<const float4 *>(&bs[u][4 * ty]);
-            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+        const int n_k = (min(MN_U, n_u - u0) + 15) / 16;         // (sub-blocks past the end were staged as zeros)
+        const __half *ah = ceh + (16 * warp + g) * MN_LD + 2 * c, *al = cel + (16 * warp + g) * MN_LD + 2 * c;
+        for (int k = 0; k < n_k; k++) {
+            uint32_t fh[4], fl[4];
+            fh[0] = *reinterpret_cast<const uint32_t *>(ah + 16 * k);                fl[0] = *reinterpret_cast<const uint32_t *>(al + 16 * k);
+            fh[1] = *reinterpret_cast<const uint32_t *>(ah + 16 * k + 8 * MN_LD);    fl[1] = *reinterpret_cast<const uint32_t *>(al + 16 * k + 8 * MN_LD);
+            fh[2] = *reinterpret_cast<const uint32_t *>(ah + 16 * k + 8);            fl[2] = *reinterpret_cast<const uint32_t *>(al + 16 * k + 8);
+            fh[3] = *reinterpret_cast<const uint32_t *>(ah + 16 * k + 8 * MN_LD + 8); fl[3] = *reinterpret_cast<const uint32_t *>(al + 16 * k + 8 * MN_LD + 8);
 #pragma unroll
-            for (int i = 0; i < 4; i++)
-#pragma unroll
-                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(bv[i], av[j], acc[i][j]);
+            for (int t = 0; t < 8; t++) {
+                const __half *bh = bsh + (8 * t + g) * MN_LD + 16 * k + 2 * c, *bl = bsl + (8 * t + g) * MN_LD + 16 * k + 2 * c;
+                const uint32_t bh0 = *reinterpret_cast<const uint32_t *>(bh), bh1 = *reinterpret_cast<const uint32_t *>(bh + 8);
+                const uint32_t bl0 = *reinterpret_cast<const uint32_t *>(bl), bl1 = *reinterpret_cast<const uint32_t *>(bl + 8);
+                mn_mma(acc[t], fh, bh0, bh1);
+                mn_mma(acc[t], fl, bh0, bh1);
+                mn_mma(acc[t], fh, bl0, bl1);
+            }
         }
     }
+    // undo the two scalings (2^8 * 2^-6) and apply the batch rows' own scales
+    const int na = n0 + 16 * warp + g, nb = na + 8;
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const int m = 4 * ty + i;
-        if (m < M) {
-            const float sxm = xscale[m];
-            float *o = out + (size_t)m * ld_out + n0 + 4 * tx;
+    for (int t = 0; t < 8; t++)
 #pragma unroll
-            for (int j = 0; j < 4; j++) if (n0 + 4 * tx + j < N) o[j] = acc[i][j] * sxm;
+        for (int e = 0; e < 2; e++) {
+            const int m = 8 * t + 2 * c + e;
+            if (m < M) {
+                const float sxm = xscale[m] * 0.25f;
+                if (na < N) out[(size_t)m * ld_out + na] = acc[t][e] * sxm;
+                if (nb < N) out[(size_t)m * ld_out + nb] = acc[t][2 + e] * sxm;
+            }
         }
-    }
 }
 template <int ROWS>
 static cudaError_t minima_launch(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *slot, int k_groups) {
-    const int bytes = MN_U * (ROWS + P_MT) * (int)sizeof(float);
+    const int bytes = 2 * (ROWS + P_MT) * MN_LD * (int)sizeof(__half);
     static VxPerDevice attr;
     cudaError_t e = attr.max_dynamic_smem(c, q4k_minima_kernel<ROWS>, bytes);
     if (e != cudaSuccess) return e;
-    return vx_launch_chain(q4k_minima_kernel<ROWS>, dim3(ceil_div(w.n, ROWS)), dim3(4 * ROWS), (size_t)bytes, c->stream, (const uint2 *)w.sc,
+    return vx_launch_chain(q4k_minima_kernel<ROWS>, dim3(ceil_div(w.n, ROWS)), dim3(2 * ROWS), (size_t)bytes, c->stream, (const uint2 *)w.sc,
                            (const __half2 *)w.aux, (const float *)x.bsum, x.k_pad / 32, (const float *)x.scale, slot, m, w.n, k_groups, w.n);
 }
 
@@ -714,9 +759,9 @@ int vxq_gemm_tcp(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *o
     if (le != cudaSuccess) return vx_cuda_fail(c, le, "projection launch");
     VX_LAUNCH_CHECK(c);
     if (w.type == VX_T_Q4_K) {     // the minima as one more slot behind the projection's own
-        // 64-row CTAs when they fill the GPU, 32-row CTAs for the narrow matrices
+        // 128-row CTAs when they fill the GPU, 64-row CTAs for the narrow matrices
         float *slot = parts + (size_t)split * m * w.n;
-        le = w.n >= 64 * 2 * c->sm_count ? minima_launch<64>(c, w, x, m, slot, k_groups) : minima_launch<32>(c, w, x, m, slot, k_groups);
+        le = w.n >= 128 * c->sm_count ? minima_launch<128>(c, w, x, m, slot, k_groups) : minima_launch<64>(c, w, x, m, slot, k_groups);
         if (le != cudaSuccess) return vx_cuda_fail(c, le, "minima launch");
         VX_LAUNCH_CHECK(c);
         *n_parts_out = split + 1;
