@@ -306,7 +306,7 @@ int vx_set_tc_min_rows(int rows);
  * aligned to tiles; 2 (default) = persistent, and where it is cheaper the stages of all tiles are cut into one equal run per
  * CTA (a tile's partial sums then come from the CTAs that share it).  No counterpart in the reference. */
 int vx_set_persistent_projections(int mode);
-/* Q4_0 projections of 1..4 batch rows run on the weight-streaming mma.sync kernel (the single-sequence decode of
+/* Q4_0 projections of 1..4 batch rows (Q4_K: 1..3) run on the weight-streaming mma.sync kernel (the single-sequence decode of
  * runtime/block.go:947-1060: one quantised mat-vec per projection); 0 = the staged mma.sync kernel as for 5..16 rows.
  * Default on. */
 int vx_set_thin_batch_projections(int enable);

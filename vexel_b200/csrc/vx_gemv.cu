@@ -1,4 +1,4 @@
-// Thin-batch Q4_0 projection (1 to 4 activation rows): y[m][n] = sum_k x[m][k] * d[n][k/32] * (q[n][k] - 8).
+// Thin-batch Q4_0 (and, further down, Q4_K) projection (1 to 4 activation rows): y[m][n] = sum_k x[m][k] * d[n][k/32] * (q[n][k] - 8).
 //
 // The reference runs its decode projections as one quantised mat-vec per sequence (MatMulQ4_0 with M = 1,
 // inference/runtime/block.go:947-1060, kernels metal_bridge_darwin.m matvec_q4_0*).  With a handful of rows the product is
@@ -146,11 +146,121 @@ gemv_q4_0_kernel(const uint4 *__restrict__ qs, const __half *__restrict__ sc, co
     }
 }
 
+// ---- the same design for Q4_K (inference/pkg/gguf/dequant.go:342-396): w = fl(d sc_u) q - fl(dmin m_u) per 32-weight sub-block u.
+// The repacked group of a row holds word c of the halves (64-weight group jj, 16-byte half t) = (0,0), (0,1), (1,0), (1,1);
+// the low nibbles of a 64-weight group are sub-block 2 jj, the high nibbles sub-block 2 jj + 1, and half t is one K = 16 step.
+// q stays unsigned here: the minimum term meets the activations' block sums (one float4 per batch row and group) in the hi
+// columns of the tile.  A ring stage carries the nibbles, the scale / minimum bytes and {d, dmin} of 16 rows.
+constexpr int GVK_STAGE_BYTES = 1024 + 128 + 64;
+// two low nibbles of v -> half2 {q0, q1};  two high nibbles in place -> half2 {q0, q1}: (1024 + 16 q) / 16 - 64
+__device__ __forceinline__ uint32_t lo_nibu(uint32_t v) {
+    uint32_t h = (v & 0x000F000Fu) | 0x64006400u;
+    __half2 r = __hsub2(*reinterpret_cast<__half2 *>(&h), __half2half2(__ushort_as_half((unsigned short)0x6400)));
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+__device__ __forceinline__ uint32_t hi_nibu(uint32_t v) {
+    uint32_t h = (v & 0x00F000F0u) | 0x64006400u;
+    __half2 r = __hfma2(*reinterpret_cast<__half2 *>(&h), __half2half2(__ushort_as_half((unsigned short)0x2C00)),    // 1/16
+                        __half2half2(__ushort_as_half((unsigned short)0xD400)));                                      // -64
+    return *reinterpret_cast<uint32_t *>(&r);
+}
+__device__ __forceinline__ void cp_async4(void *smem, const void *gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+
+__global__ void __launch_bounds__(GV_THREADS, 5)
+gemv_q4_k_kernel(const uint4 *__restrict__ qs, const uint2 *__restrict__ sc, const __half2 *__restrict__ sup, const __half *__restrict__ xh,
+                 const __half *__restrict__ xl, const float *__restrict__ xscale, const float *__restrict__ xbsum, int bsum_ld,
+                 float *__restrict__ out, int M, int N, int k_groups, int groups_per_split, int x_ld, int ld_out, size_t part_stride) {
+    __shared__ __align__(16) unsigned char ring[GV_WARPS][GV_STAGES][GVK_STAGE_BYTES];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+    const int r0 = blockIdx.x * (GV_WARPS * 16) + warp * 16;
+    const int j_begin = blockIdx.y * groups_per_split;
+    const int n_j = min(groups_per_split, k_groups - j_begin);
+    const int row_a = min(r0 + g, N - 1), row_b = min(r0 + g + 8, N - 1);
+    const uint4 *qa = qs + ((size_t)row_a * k_groups + j_begin) * 4 + c;
+    const uint4 *qb = qs + ((size_t)row_b * k_groups + j_begin) * 4 + c;
+    // lanes c = 0 / 1 fetch the scale bytes of rows g / g + 8, lanes c = 2 / 3 their {d, dmin}
+    const int my_row = (c & 1) ? row_b : row_a;
+    const uint2 *sp = sc + (size_t)my_row * k_groups + j_begin;
+    const __half2 *dp2 = sup + (size_t)my_row * (k_groups >> 1);
+    const int xrow = min(g & 3, M - 1);
+    const __half *x0 = (g >= 4 ? xl : xh) + (size_t)xrow * x_ld + (size_t)j_begin * 128 + 4 * c;
+    // block sums of the two batch rows whose hi columns this lane holds (lanes c >= 2 hold lo columns: no minimum term)
+    const float *bs0 = xbsum + (size_t)min(2 * (c & 1), M - 1) * bsum_ld + (size_t)j_begin * 4;
+    const float *bs1 = xbsum + (size_t)min(2 * (c & 1) + 1, M - 1) * bsum_ld + (size_t)j_begin * 4;
+    const float hi_col = c < 2 ? 1.f : 0.f;
+    unsigned char *my = &ring[warp][0][0];
+
+    auto request = [&](int j) {
+        if (j < n_j) {
+            unsigned char *st = my + (j % GV_STAGES) * GVK_STAGE_BYTES;
+            cp_async16(st + lane * 16, qa + (size_t)j * 4);
+            cp_async16(st + 512 + lane * 16, qb + (size_t)j * 4);
+            if (c < 2) cp_async8(st + 1024 + (g + 8 * c) * 8, sp + j);
+            else cp_async4(st + 1152 + (g + 8 * (c - 2)) * 4, dp2 + ((j_begin + j) >> 1));
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int j = 0; j < GV_STAGES - 1; j++) request(j);
+    vx_pdl_wait();
+    vx_pdl_trigger();
+
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < n_j; j++) {
+        cp_async_wait<GV_STAGES - 2>();
+        __syncwarp();
+        request(j + GV_STAGES - 1);
+        const unsigned char *st = my + (j % GV_STAGES) * GVK_STAGE_BYTES;
+        const uint4 wa = *reinterpret_cast<const uint4 *>(st + lane * 16), wb = *reinterpret_cast<const uint4 *>(st + 512 + lane * 16);
+        const uint2 ma = *reinterpret_cast<const uint2 *>(st + 1024 + g * 8), mb = *reinterpret_cast<const uint2 *>(st + 1024 + (g + 8) * 8);
+        const float2 da = __half22float2(*reinterpret_cast<const __half2 *>(st + 1152 + g * 4));
+        const float2 db = __half22float2(*reinterpret_cast<const __half2 *>(st + 1152 + (g + 8) * 4));
+        const float4 b0 = __ldg(reinterpret_cast<const float4 *>(bs0 + 4 * j)), b1 = __ldg(reinterpret_cast<const float4 *>(bs1 + 4 * j));
+        const float bv0[4] = {b0.x, b0.y, b0.z, b0.w}, bv1[4] = {b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+        for (int u = 0; u < 4; u++) {                          // sub-block u = 2 jj + nib
+            const int jj = u >> 1, nib = u & 1;
+            const uint32_t a0w = word_of(wa, 2 * jj), a1w = word_of(wa, 2 * jj + 1), b0w = word_of(wb, 2 * jj), b1w = word_of(wb, 2 * jj + 1);
+            const uint2 xa = __ldg(reinterpret_cast<const uint2 *>(x0 + 32 * u)), xb = __ldg(reinterpret_cast<const uint2 *>(x0 + 32 * u + 16));
+            float s[4];
+            if (nib == 0) {
+                mma16816_first(s, lo_nibu(a0w), lo_nibu(b0w), lo_nibu(a0w >> 8), lo_nibu(b0w >> 8), xa.x, xa.y);
+                mma16816(s, lo_nibu(a1w), lo_nibu(b1w), lo_nibu(a1w >> 8), lo_nibu(b1w >> 8), xb.x, xb.y);
+            } else {
+                mma16816_first(s, hi_nibu(a0w), hi_nibu(b0w), hi_nibu(a0w >> 8), hi_nibu(b0w >> 8), xa.x, xa.y);
+                mma16816(s, hi_nibu(a1w), hi_nibu(b1w), hi_nibu(a1w >> 8), hi_nibu(b1w >> 8), xb.x, xb.y);
+            }
+            const float d1a = __fmul_rn(da.x, (float)((ma.x >> (8 * u)) & 0xFF)), m1a = __fmul_rn(da.y, (float)((ma.y >> (8 * u)) & 0xFF)) * hi_col;
+            const float d1b = __fmul_rn(db.x, (float)((mb.x >> (8 * u)) & 0xFF)), m1b = __fmul_rn(db.y, (float)((mb.y >> (8 * u)) & 0xFF)) * hi_col;
+            acc[0] = fmaf(d1a, s[0], fmaf(-m1a, bv0[u], acc[0])); acc[1] = fmaf(d1a, s[1], fmaf(-m1a, bv1[u], acc[1]));
+            acc[2] = fmaf(d1b, s[2], fmaf(-m1b, bv0[u], acc[2])); acc[3] = fmaf(d1b, s[3], fmaf(-m1b, bv1[u], acc[3]));
+        }
+        x0 += 128;
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int i = 0; i < 4; i++) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 2);
+    if (c >= 2) return;
+    float *o = out + (size_t)blockIdx.y * part_stride;
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+        const int m = 2 * c + e;
+        if (m < M) {
+            const float s = xscale[m];
+            if (r0 + g < N) o[(size_t)m * ld_out + r0 + g] = acc[e] * s;
+            if (r0 + g + 8 < N) o[(size_t)m * ld_out + r0 + g + 8] = acc[2 + e] * s;
+        }
+    }
+}
+
 int g_gemv = 1;
 
 }  // namespace
 
-bool vxq_gemv_eligible(const VxWeight &w, int m) { return g_gemv && w.type == VX_T_Q4_0 && m >= 1 && m <= 4; }
+// Q4_0 up to four rows; Q4_K up to three (Llama-3-8B-shaped step: 4.14 -> 3.80 ms at one row, 4.18 -> 4.07 at three, no gain at four)
+bool vxq_gemv_eligible(const VxWeight &w, int m) { return g_gemv && m >= 1 && ((w.type == VX_T_Q4_0 && m <= 4) || (w.type == VX_T_Q4_K && m <= 3)); }
 
 // out receives [m][ld_out] when *n_parts_out == 1, otherwise `parts` holds [n_parts][m][w.n]
 int vxq_gemv(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, int ld_out, int *n_parts_out, float *parts,
@@ -184,6 +294,16 @@ int vxq_gemv(vx_ctx *c, const VxWeight &w, const VxSplit &x, int m, float *out, 
         return cudaFuncSetAttribute(gemv_q4_0_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     });
     if (le != cudaSuccess) return vx_cuda_fail(c, le, "thin-batch projection attributes");
+    if (w.type == VX_T_Q4_K) {
+        static VxPerDevice carveout_k;
+        le = carveout_k.once(c, [&]() {
+            return cudaFuncSetAttribute(gemv_q4_k_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        });
+        if (le != cudaSuccess) return vx_cuda_fail(c, le, "thin-batch projection attributes");
+        le = vx_launch_dependent(gemv_q4_k_kernel, grid, dim3(GV_THREADS), 0, c->stream, (const uint4 *)w.qs, (const uint2 *)w.sc, (const __half2 *)w.aux,
+                                 (const __half *)x.hi, (const __half *)x.lo, (const float *)x.scale, (const float *)x.bsum, x.k_pad / 32, dst, m, w.n,
+                                 k_groups, gps, x.k_pad, ld, pstride);
+    } else
     le = vx_launch_dependent(gemv_q4_0_kernel, grid, dim3(GV_THREADS), 0, c->stream, (const uint4 *)w.qs, (const __half *)w.sc, (const __half *)x.hi,
                              (const __half *)x.lo, (const float *)x.scale, dst, m, w.n, k_groups, gps, x.k_pad, ld, pstride);
     if (le != cudaSuccess) return vx_cuda_fail(c, le, "thin-batch projection launch");
