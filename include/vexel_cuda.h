@@ -301,10 +301,12 @@ int vx_selftest_bounded_wait(vx_ctx *ctx, int limit_us, int *reached_end);
 /* batches with at least this many rows run the projections on the tcgen05 kernel (default 17;
  * 0 = always the mma.sync kernel) */
 int vx_set_tc_min_rows(int rows);
-/* Q4_0 projections of 17..64 batch rows run on the persistent tcgen05 kernel (one CTA per SM walking weight tiles, its
- * pipeline kept full across tiles).  mode 0 = one CTA per tile as for the other formats; 1 = persistent with split-K slices
- * aligned to tiles; 2 (default) = persistent, and where it is cheaper the stages of all tiles are cut into one equal run per
- * CTA (a tile's partial sums then come from the CTAs that share it).  No counterpart in the reference. */
+/* Q4_0, Q4_K and Q6_K projections of 17..64 batch rows run on the persistent tcgen05 kernel (one CTA per SM walking weight
+ * tiles, its pipeline kept full across tiles; Q4_K adds a small kernel for its minima).  mode 0 = one CTA per tile; 1 =
+ * persistent with split-K slices aligned to tiles; 2 (default) = persistent, and where it is cheaper the stages of all tiles
+ * are cut into one equal run per CTA (a tile's partial sums then come from the CTAs that share it); 3 = that cut wherever it
+ * applies, 4 = as 2 but the K-quant formats on the one-CTA-per-tile kernel (both for timing comparisons).  No counterpart in
+ * the reference. */
 int vx_set_persistent_projections(int mode);
 /* Q4_0 projections of 1..4 batch rows (Q4_K: 1..3) run on the weight-streaming mma.sync kernel (the single-sequence decode of
  * runtime/block.go:947-1060: one quantised mat-vec per projection); 0 = the staged mma.sync kernel as for 5..16 rows.
