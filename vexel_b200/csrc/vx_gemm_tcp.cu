@@ -273,8 +273,12 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                                 for (int e = 0; e < 2; e++) {
                                     const uint32_t word = b ? w[c].y : w[c].x;
                                     const uint32_t v = (t ? word >> 4 : word) >> (8 * e);
-                                    const uint32_t h8 = (hw[c] >> (16 * b + 8 * t)) & 0xFF;
-                                    const __half2 q = q6h2(v, e ? (((h8 & 0x0C) << 2) | ((h8 & 0xC0) << 14)) : (((h8 & 0x03) << 4) | ((h8 & 0x30) << 16)));
+                                    // byte 2 b + t of hw[c]: bits [1:0], [3:2], [5:4], [7:6] are the top bits of positions 0..3.  One
+                                    // multiply copies the two fields of a pair to bits 4-5 and 20-21 (and to places the mask drops):
+                                    // pair (0, 2): x = h & 0x33, (x << 4 | x << 16);  pair (1, 3): y = h & 0xCC, (y << 2 | y << 14)
+                                    const uint32_t h8 = hw[c] >> (16 * b + 8 * t);
+                                    const uint32_t h6 = (e ? (h8 & 0xCCu) * 0x4004u : (h8 & 0x33u) * 0x10010u) & 0x00300030u;
+                                    const __half2 q = q6h2(v, h6);
                                     const __half2 ph = __hmul2(q, dh[t]);
                                     __half2 pl = __hfma2(q, dh[t], __hneg2(ph));
                                     pl = __hfma2(q, dl[t], pl);
