@@ -308,7 +308,12 @@ gemm_tcp_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     _Pragma("unroll") for (int c = 0; c < 4; c++)                                          \
     _Pragma("unroll") for (int e = 0; e < 2; e++) {                                        \
             if (P_KNOCK & 1) { hi[8 * nib + 2 * c + e] = w[c].WORD; lo[8 * nib + 2 * c + e] = h2u(DD); } else {   \
-            const __half2 q = nib2(w[c].WORD >> (4 * nib + 8 * e));                            \
+            /* low nibbles: 0x6400 | q = 1024 + q, minus 1032; high nibbles in place: (1024 + 16 q) / 16 - 72, one exact FMA */ \
+        const uint32_t wv = e ? w[c].WORD >> 8 : w[c].WORD;                                \
+        const uint32_t hb = (wv & (nib ? 0x00F000F0u : 0x000F000Fu)) | 0x64006400u;        \
+        const __half2 q = nib ? __hfma2(*reinterpret_cast<const __half2 *>(&hb), __half2half2(__ushort_as_half((unsigned short)0x2C00)), \
+                                        __half2half2(__ushort_as_half((unsigned short)0xD480)))                                            \
+                              : __hsub2(*reinterpret_cast<const __half2 *>(&hb), __half2half2(__ushort_as_half((unsigned short)0x6408))); \
             const __half2 ph = __hmul2(q, DD);                                                 \
             const __half2 pl = __hfma2(q, DD, __hneg2(ph));                                    \
             hi[8 * nib + 2 * c + e] = h2u(ph); lo[8 * nib + 2 * c + e] = h2u(pl); }            \
