@@ -1,5 +1,6 @@
 // Quantised projections (GGUF Q4_0, Q4_K, Q6_K) on the 5th-generation tensor cores (tcgen05 + TMEM) for batches above the
-// measured crossover (17 rows; 33 for Q4_K).
+// measured crossover (17 rows).  Decode batches of up to 64 rows take the persistent kernel (vx_gemm_tcp.cu) when it is
+// eligible; this kernel serves larger batches, odd group counts and the cases where no partial-sum buffer is passed.
 //
 // Shape ("swap-AB"): D[128 weight rows x batch] += A[128 x 64k] * B[batch x 64k]^T per pipeline stage, accumulator in tensor
 // memory, one CTA per (128-row weight tile, split-K slice, 64-row batch tile).

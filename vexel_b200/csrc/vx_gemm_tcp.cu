@@ -1,4 +1,7 @@
-// Q4_0 projections for decode batches (17..64 rows) on tcgen05 + TMEM: the persistent form of the kernel in vx_gemm_tc.cu.
+// Q4_0, Q4_K and Q6_K projections for decode batches (17..64 rows) on tcgen05 + TMEM: the persistent form of the kernel
+// in vx_gemm_tc.cu.  The text below describes the Q4_0 instance; the K-quant instances differ in the expansion step (the
+// sub-block scale fl(d sc) carried as an fp16 pair, Q6_K with a second ring for its top-bit tiles, Q4_K with its minima
+// term in a small kernel of its own that writes one more partial slot).
 //
 // What the one-CTA-per-tile kernel showed when its parts were switched off one at a time: nothing in it was saturated.  A
 // CTA lived for 16-43 pipeline stages and spent a third of that filling its pipeline and draining its accumulator, a layer's
